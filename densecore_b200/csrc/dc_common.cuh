@@ -1,0 +1,377 @@
+// Device-side building blocks shared by every kernel of the library:
+// block layouts, exact scalar helpers, the per-warp bulk-copy pipeline that
+// streams weight rows HBM -> shared memory, and the K-quant row-dot decoders.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define DC_QK_K 256
+#define DC_Q4K_BYTES 144
+#define DC_Q6K_BYTES 210
+#define DC_Q8K_BYTES 292
+#define DC_KV_BLOCK 16   // core/include/densecore/memory/kv_cache.h:50
+#define DC_MAX_T 16      // tokens per step (kMaxSmallBatchColsHard, core/src/llm/matmul/userdata.h:14)
+#define DC_TYPE_F32 0
+#define DC_TYPE_F16 1
+#define DC_TYPE_Q4_K 12
+#define DC_TYPE_Q6_K 14
+
+// Bounded waits: every wait on an mbarrier gives up after this many polls,
+// records an error code in the context's device error word and carries on, so
+// no kernel can hang the GPU.
+#define DC_WAIT_LIMIT (1u << 22)
+#define DC_ERR_MBAR_TIMEOUT 1
+
+namespace dc {
+
+__device__ __forceinline__ float fp16_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// core/src/kernels/hwy/hwy_fastexp.h:50-84 (fused multiply-add Horner form).
+__device__ __forceinline__ float fast_exp_fma(float x) {
+    x = fmaxf(fminf(x, 50.0f), -50.0f);
+    const float y = __fmul_rn(x, 1.4426950408889634f);
+    const float i_f = floorf(y);
+    const float f = __fsub_rn(y, i_f);
+    float p = __fmaf_rn(0.07944023841053369f, f, 0.224494337302845f);
+    p = __fmaf_rn(p, f, 0.6960656421638072f);
+    p = __fmaf_rn(p, f, 1.0f);
+    return __fmul_rn(p, __int_as_float(((int)i_f + 127) << 23));
+}
+// core/src/backend/cpu_backend_internal.h:99-114 (separate multiply and add).
+__device__ __forceinline__ float fast_exp(float x) {
+    x = fmaxf(fminf(x, 50.0f), -50.0f);
+    const float y = __fmul_rn(x, 1.4426950408889634f);
+    const int i = (int)floorf(y);
+    const float f = __fsub_rn(y, (float)i);
+    float p = __fadd_rn(0.224494337302845f, __fmul_rn(f, 0.07944023841053369f));
+    p = __fadd_rn(0.6960656421638072f, __fmul_rn(f, p));
+    p = __fadd_rn(1.0f, __fmul_rn(f, p));
+    return __fmul_rn(__int_as_float((i + 127) << 23), p);
+}
+// SiLU of the production SwiGLU kernels: g / (1 + fast_exp(-g))
+// (core/src/backend/cpu_backend_moe_quant_projection.inl:710-802).
+__device__ __forceinline__ float silu_fast(float g) { return __fdiv_rn(g, __fadd_rn(1.0f, fast_exp(-g))); }
+
+// ---------------------------------------------------------------- mbarrier
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; returns false (and records the error) if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_word) {
+    for (uint32_t i = 0; i < DC_WAIT_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    if (err_word) atomicExch(err_word, DC_ERR_MBAR_TIMEOUT);
+    return false;
+}
+// Untiled bulk copy global -> this CTA's shared memory (no multicast).
+// dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Programmatic dependent launch: let the next kernel in the stream start its
+// prologue, and wait for the previous kernel's results.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ------------------------------------------------- per-warp row pipeline
+// Each warp owns NSTAGE shared-memory buffers and one mbarrier per buffer.
+// Lane 0 issues one bulk copy per stage covering a byte range of the weight
+// tensor (rounded out to 16-byte boundaries); all lanes wait on the stage's
+// barrier, decode from shared memory, __syncwarp, and lane 0 refills.
+template <int NSTAGE>
+struct WarpPipe {
+    uint32_t buf0;       // shared address of stage 0
+    uint32_t bar0;       // shared address of barrier 0
+    uint32_t stage_bytes;
+    uint32_t issued, consumed;
+    int* err;
+
+    __device__ __forceinline__ void init(uint8_t* smem_bufs, uint64_t* smem_bars, uint32_t stage_bytes_, int* err_word) {
+        buf0 = smem_u32(smem_bufs);
+        bar0 = smem_u32(smem_bars);
+        stage_bytes = stage_bytes_;
+        issued = consumed = 0;
+        err = err_word;
+        if ((threadIdx.x & 31) == 0) {
+            for (int s = 0; s < NSTAGE; ++s) mbar_init(bar0 + 8 * s, 1);
+            mbar_fence_init();
+        }
+        __syncwarp();
+    }
+    // Lane 0 only.  Copies [src, src+bytes) (any alignment) as the enclosing
+    // 16-byte aligned range; returns nothing, the consumer recomputes the skew.
+    __device__ __forceinline__ void issue(const uint8_t* src, uint32_t bytes) {
+        const uint32_t s = issued % NSTAGE;
+        const uintptr_t a = (uintptr_t)src;
+        const uintptr_t a0 = a & ~(uintptr_t)15;
+        const uint32_t len = (uint32_t)(((a + bytes + 15) & ~(uintptr_t)15) - a0);
+        mbar_expect_tx(bar0 + 8 * s, len);
+        bulk_g2s(buf0 + s * stage_bytes, (const void*)a0, len, bar0 + 8 * s);
+        ++issued;
+    }
+    // Two ranges into one stage (gate row + up row).  Second lands at offset off2.
+    __device__ __forceinline__ void issue2(const uint8_t* src1, const uint8_t* src2, uint32_t bytes, uint32_t off2) {
+        const uint32_t s = issued % NSTAGE;
+        const uintptr_t a = (uintptr_t)src1, b = (uintptr_t)src2;
+        const uintptr_t a0 = a & ~(uintptr_t)15, b0 = b & ~(uintptr_t)15;
+        const uint32_t la = (uint32_t)(((a + bytes + 15) & ~(uintptr_t)15) - a0);
+        const uint32_t lb = (uint32_t)(((b + bytes + 15) & ~(uintptr_t)15) - b0);
+        mbar_expect_tx(bar0 + 8 * s, la + lb);
+        bulk_g2s(buf0 + s * stage_bytes, (const void*)a0, la, bar0 + 8 * s);
+        bulk_g2s(buf0 + s * stage_bytes + off2, (const void*)b0, lb, bar0 + 8 * s);
+        ++issued;
+    }
+    // All lanes.  Returns the shared address of the stage's buffer.
+    __device__ __forceinline__ uint32_t wait() {
+        const uint32_t s = consumed % NSTAGE;
+        mbar_wait(bar0 + 8 * s, (consumed / NSTAGE) & 1, err);
+        return buf0 + s * stage_bytes;
+    }
+    __device__ __forceinline__ void release() {
+        ++consumed;
+        __syncwarp();
+    }
+};
+
+// ------------------------------------------------------- shared loads
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ int lds_s8(uint32_t a) {
+    int v;
+    asm volatile("ld.shared.s8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+// 32-bit load from a 2-byte aligned shared address.
+__device__ __forceinline__ uint32_t lds32_a2(uint32_t a) { return lds16(a) | (lds16(a + 2) << 16); }
+
+// ------------------------------------------------------- activations
+// Q8_K activations of the step's tokens, laid out in shared memory for the
+// dot kernels: qs[T][K] int8 (16-byte aligned rows), d[T][nb] f32,
+// bs[T][nb][16] int16.  Filled from the native 292-byte blocks in global memory.
+struct ActSmem {
+    uint32_t qs, d, bs;  // shared addresses
+    int K, nb;
+    __host__ __device__ __forceinline__ static size_t bytes(int T, int K) {
+        const int nb = K / DC_QK_K;
+        return (size_t)T * K + (size_t)T * nb * 4 + (size_t)T * nb * 32;
+    }
+    __device__ __forceinline__ void bind(uint8_t* base, int T, int K_) {
+        K = K_;
+        nb = K_ / DC_QK_K;
+        qs = smem_u32(base);
+        d = qs + T * K;
+        bs = d + T * nb * 4;
+    }
+    // Cooperative fill by the whole CTA from native Q8_K rows (row stride nb*292).
+    __device__ __forceinline__ void fill(const uint8_t* q8, int T) {
+        const int words_per_row = nb * 73;  // 292/4
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(q8);
+        for (int i = threadIdx.x; i < T * words_per_row; i += blockDim.x) {
+            const int t = i / words_per_row, w = i - t * words_per_row;
+            const int b = w / 73, o = w - b * 73;
+            const uint32_t v = src[i];
+            uint32_t dst;
+            if (o == 0) dst = d + (t * nb + b) * 4;
+            else if (o <= 64) dst = qs + t * K + b * 256 + (o - 1) * 4;
+            else dst = bs + (t * nb + b) * 32 + (o - 65) * 4;
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(v));
+        }
+    }
+};
+
+// ------------------------------------------------------- Q4_K row dot
+// One "item" = (super-block b, chunk c): 32 bytes of qs = sub-blocks 2c (low
+// nibbles) and 2c+1 (high nibbles) (core/src/kernels/hwy/hwy_moe_quant.cc:202-211).
+// Returns the lane's exact integer partials: I = sc_lo*dot_lo + sc_hi*dot_hi,
+// M = m_lo*(bsums[4c]+bsums[4c+1]) + m_hi*(bsums[4c+2]+bsums[4c+3]).
+struct Q4Item {
+    uint32_t q[8];
+    int sc_lo, sc_hi, m_lo, m_hi;
+    float d, dmin;
+};
+__device__ __forceinline__ void q4k_load_item(uint32_t row, int b, int c, Q4Item& it) {
+    const uint32_t blk = row + b * DC_Q4K_BYTES;
+    const uint4 a = lds128(blk + 16 + 32 * c), e = lds128(blk + 32 + 32 * c);
+    it.q[0] = a.x; it.q[1] = a.y; it.q[2] = a.z; it.q[3] = a.w;
+    it.q[4] = e.x; it.q[5] = e.y; it.q[6] = e.z; it.q[7] = e.w;
+    const uint32_t dd = lds32(blk);
+    it.d = fp16_bits_to_float((uint16_t)(dd & 0xFFFF));
+    it.dmin = fp16_bits_to_float((uint16_t)(dd >> 16));
+    // 6-bit scale/min unpack, scalar form of hwy_moe_quant.cc:90-101
+    // (per sub-block j: j<4: sc=s[j]&63, m=s[j+4]&63; else sc=(s[j+4]&15)|((s[j-4]>>6)<<4),
+    //  m=(s[j+4]>>4)|((s[j]>>6)<<4)), for j = 2c and 2c+1.
+    const uint32_t s = blk + 4;
+    const int j = 2 * c;
+    if (c < 2) {
+        const uint32_t p = lds16(s + j), m = lds16(s + j + 4);
+        it.sc_lo = p & 63; it.sc_hi = (p >> 8) & 63;
+        it.m_lo = m & 63; it.m_hi = (m >> 8) & 63;
+    } else {
+        const uint32_t hi = lds16(s + j + 4), lo = lds16(s + j - 4), mid = lds16(s + j);
+        it.sc_lo = (hi & 15) | (((lo >> 6) & 3) << 4);
+        it.sc_hi = ((hi >> 8) & 15) | (((lo >> 14) & 3) << 4);
+        it.m_lo = ((hi >> 4) & 15) | (((mid >> 6) & 3) << 4);
+        it.m_hi = ((hi >> 12) & 15) | (((mid >> 14) & 3) << 4);
+    }
+}
+__device__ __forceinline__ void q4k_item_ints(const Q4Item& it, uint32_t yq /*shared addr of 64 int8*/,
+                                              uint32_t ybs /*shared addr of 4 int16*/, int& I, int& M) {
+    int lo = 0, hi = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint4 y0 = lds128(yq + 16 * h), y1 = lds128(yq + 32 + 16 * h);
+        const uint32_t* w = &it.q[4 * h];
+        lo = __dp4a((int)(w[0] & 0x0F0F0F0F), (int)y0.x, lo);
+        lo = __dp4a((int)(w[1] & 0x0F0F0F0F), (int)y0.y, lo);
+        lo = __dp4a((int)(w[2] & 0x0F0F0F0F), (int)y0.z, lo);
+        lo = __dp4a((int)(w[3] & 0x0F0F0F0F), (int)y0.w, lo);
+        hi = __dp4a((int)((w[0] >> 4) & 0x0F0F0F0F), (int)y1.x, hi);
+        hi = __dp4a((int)((w[1] >> 4) & 0x0F0F0F0F), (int)y1.y, hi);
+        hi = __dp4a((int)((w[2] >> 4) & 0x0F0F0F0F), (int)y1.z, hi);
+        hi = __dp4a((int)((w[3] >> 4) & 0x0F0F0F0F), (int)y1.w, hi);
+    }
+    const uint32_t b01 = lds32(ybs), b23 = lds32(ybs + 4);
+    const int s_lo = (int)(short)(b01 & 0xFFFF) + (int)(short)(b01 >> 16);
+    const int s_hi = (int)(short)(b23 & 0xFFFF) + (int)(short)(b23 >> 16);
+    I = it.sc_lo * lo + it.sc_hi * hi;
+    M = it.m_lo * s_lo + it.m_hi * s_hi;
+}
+
+// ------------------------------------------------------- Q6_K row dot
+// One "item" = (super-block b, half j, eighth t): 8 bytes of ql at 64j+8t, 8 at
+// 64j+32+8t, 8 of qh at 32j+8t -> 4 quadrants x 8 elements
+// (core/src/llm/matmul/q6_small_batch.h:52-74).  Block bytes are only 2-byte
+// aligned in shared memory.
+struct Q6Item {
+    uint32_t q[8];  // signed bytes (q-32), quadrant-major: q[2*quad + w]
+    int sc[4];
+    float d;
+};
+__device__ __forceinline__ void q6k_load_item(uint32_t row, int b, int j, int t, Q6Item& it) {
+    const uint32_t blk = row + b * DC_Q6K_BYTES;
+    const uint32_t ql0 = blk + 64 * j + 8 * t, ql1 = ql0 + 32, qh = blk + 128 + 32 * j + 8 * t;
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const uint32_t a = lds32_a2(ql0 + 4 * w), c = lds32_a2(ql1 + 4 * w), h = lds32_a2(qh + 4 * w);
+        it.q[0 + w] = __vsub4((a & 0x0F0F0F0F) | ((h & 0x03030303) << 4), 0x20202020);
+        it.q[2 + w] = __vsub4((c & 0x0F0F0F0F) | (((h >> 2) & 0x03030303) << 4), 0x20202020);
+        it.q[4 + w] = __vsub4(((a >> 4) & 0x0F0F0F0F) | (((h >> 4) & 0x03030303) << 4), 0x20202020);
+        it.q[6 + w] = __vsub4(((c >> 4) & 0x0F0F0F0F) | (((h >> 6) & 0x03030303) << 4), 0x20202020);
+    }
+    const uint32_t s = blk + 192 + 8 * j + (t >> 1);
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) it.sc[qd] = lds_s8(s + 2 * qd);
+    it.d = fp16_bits_to_float((uint16_t)lds16(blk + 208));
+}
+// yq: shared address of the activation int8 at element 256b + 128j + 8t; quadrant stride 32.
+__device__ __forceinline__ int q6k_item_int(const Q6Item& it, uint32_t yq) {
+    int I = 0;
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) {
+        const uint32_t y0 = lds32(yq + 32 * qd), y1 = lds32(yq + 32 * qd + 4);
+        int s = __dp4a((int)it.q[2 * qd], (int)y0, 0);
+        s = __dp4a((int)it.q[2 * qd + 1], (int)y1, s);
+        I += it.sc[qd] * s;
+    }
+    return I;
+}
+
+// Sum over the G lanes of a power-of-two lane group (all 32 lanes call it).
+template <int G>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Row dot for up to NT tokens: weights decoded once per item and reused for
+// each token.  G lanes cooperate on one row.  tok[s] = row of the activation
+// arrays in shared memory used by token slot s (slots >= nt are skipped).
+// acc[] receives each lane's float partial; callers reduce with group_sum.
+template <int NT>
+__device__ __forceinline__ void row_dot_partial(int type, uint32_t row, int lane_in_group, int G, const ActSmem& act,
+                                                int nt, const int (&tok)[NT], float (&acc)[NT]) {
+    const int nb = act.nb;
+    if (type == DC_TYPE_Q4_K) {
+        for (int i = lane_in_group; i < nb * 4; i += G) {
+            const int b = i >> 2, c = i & 3;
+            Q4Item it;
+            q4k_load_item(row, b, c, it);
+#pragma unroll
+            for (int s = 0; s < NT; ++s) {
+                if (s < nt) {
+                    const int t = tok[s];
+                    int I, M;
+                    q4k_item_ints(it, act.qs + t * act.K + b * 256 + 64 * c, act.bs + (t * nb + b) * 32 + 8 * c, I, M);
+                    const float yd = __int_as_float(lds32(act.d + (t * nb + b) * 4));
+                    acc[s] += yd * (it.d * (float)I - it.dmin * (float)M);
+                }
+            }
+        }
+    } else {
+        for (int i = lane_in_group; i < nb * 8; i += G) {
+            const int b = i >> 3, j = (i >> 2) & 1, tq = i & 3;
+            Q6Item it;
+            q6k_load_item(row, b, j, tq, it);
+#pragma unroll
+            for (int s = 0; s < NT; ++s) {
+                if (s < nt) {
+                    const int t = tok[s];
+                    const int I = q6k_item_int(it, act.qs + t * act.K + b * 256 + 128 * j + 8 * tq);
+                    const float yd = __int_as_float(lds32(act.d + (t * nb + b) * 4));
+                    acc[s] += (yd * it.d) * (float)I;
+                }
+            }
+        }
+    }
+}
+// Generic-width lane-group sum (G a power of two <= 32, runtime value).
+__device__ __forceinline__ float group_sum_rt(float v, int G) {
+    for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Lanes that cooperate on one row for a given type and K.
+__host__ __device__ inline int lanes_per_row(int type, int K) {
+    const int items = (K / DC_QK_K) * (type == DC_TYPE_Q4_K ? 4 : 8);
+    int g = 4;
+    while (g < items && g < 32) g <<= 1;
+    return g;
+}
+
+}  // namespace dc

@@ -1,0 +1,392 @@
+// MUL_MAT over Q4_K / Q6_K weights for 1..16 activation rows, and the Q8_K
+// activation quantiser.  Replaces cb_gemv_custom / cb_gemv_batched_custom
+// (core/src/llm/matmul/gemv_exec.cpp:99, core/src/llm/matmul/batched_exec.cpp:55).
+//
+// Weights stay in their GGUF-native 144-byte / 210-byte super-blocks.  Every
+// warp streams a contiguous range of weight rows HBM -> shared memory through
+// its own ring of bulk async copies, decodes the 4/6-bit codes from shared
+// memory and forms exact int32 block sums against the Q8_K activations with
+// dp4a; the fp32 scaling and the cross-block sum are the only float steps.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "dc_common.cuh"
+#include "dc_internal.h"
+
+using namespace dc;
+
+// ------------------------------------------------------------ Q8_K quantise
+// One warp per 256-element block; lane l holds elements 8l..8l+7.
+// Follows core/src/kernels/hwy/hwy_moe_quant.cc:103-144 step by step:
+// first element of largest magnitude keeps its sign; iscale = -127/max;
+// q = min(127, rne(iscale*x)); bsums per 16; d = 1/iscale.
+__device__ __forceinline__ void quantize_block_q8k_warp(const float* __restrict__ x, uint8_t* __restrict__ out,
+                                                        int lane) {
+    float v[8];
+    const float4 a = reinterpret_cast<const float4*>(x)[2 * lane];
+    const float4 b = reinterpret_cast<const float4*>(x)[2 * lane + 1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    float amax = 0.0f, mx = 0.0f;
+    int idx = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float ax = fabsf(v[j]);
+        if (ax > amax) {
+            amax = ax;
+            mx = v[j];
+            idx = 8 * lane + j;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
+        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oa > amax || (oa == amax && oi < idx)) {
+            amax = oa;
+            mx = om;
+            idx = oi;
+        }
+    }
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
+    if (amax == 0.0f) {
+        for (int w = lane; w < 73; w += 32) o32[w] = 0u;
+        return;
+    }
+    const float iscale = __fdiv_rn(-127.0f, mx);
+    int q[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        q[j] = min(127, __float2int_rn(__fmul_rn(iscale, v[j])));
+        sum += q[j];
+    }
+    const uint32_t w0 = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+    const uint32_t w1 = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+    o32[1 + 2 * lane] = w0;
+    o32[2 + 2 * lane] = w1;
+    // bsums: group g = lanes 2g, 2g+1
+    const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
+    const int other = __shfl_xor_sync(0xffffffffu, pair, 2);  // neighbouring group's sum
+    if ((lane & 3) == 0) o32[65 + (lane >> 2)] = (uint32_t)(pair & 0xFFFF) | ((uint32_t)(other & 0xFFFF) << 16);
+    if (lane == 0) o32[0] = __float_as_uint(__fdiv_rn(1.0f, iscale));
+}
+
+__global__ void __launch_bounds__(256) k_quantize_q8k(const float* __restrict__ x, int n_blocks,
+                                                      uint8_t* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int nw = (gridDim.x * blockDim.x) >> 5;
+    for (int b = gw; b < n_blocks; b += nw)
+        quantize_block_q8k_warp(x + (size_t)b * DC_QK_K, out + (size_t)b * DC_Q8K_BYTES, lane);
+}
+
+int dc_launch_quantize_q8k(dc_ctx* ctx, const float* x, int rows, int K, uint8_t* out) {
+    const int n_blocks = rows * (K / DC_QK_K);
+    const int grid = (n_blocks + 7) / 8;
+    k_quantize_q8k<<<grid < 1 ? 1 : grid, 256, 0, ctx->stream>>>(x, n_blocks, out);
+    return dc_check_cuda(ctx, cudaGetLastError(), "k_quantize_q8k");
+}
+
+// ------------------------------------------------------------------- GEMV
+struct GemvParams {
+    dc_gemv_seg seg[3];
+    int n_seg;
+    int rpst[3];      // rows per pipeline stage, per segment
+    int total_rows;   // flattened over segments (pairs count once for SwiGLU)
+    int epi;
+    const uint8_t* act_q8;
+    int T, K;
+    uint32_t stage_bytes;
+    uint32_t up_off;  // SwiGLU: offset of the up rows inside a stage
+    unsigned long long* argmax;
+    int* err;
+};
+
+// Walks a warp's contiguous flattened row range stage by stage.
+struct StageIter {
+    int cur, end;
+    __device__ __forceinline__ bool next(const GemvParams& p, int& seg, int& local, int& n) {
+        if (cur >= end) return false;
+        int s = 0, base = 0;
+        const int nseg = p.epi == DC_EPI_SWIGLU ? 1 : p.n_seg;
+        while (s + 1 < nseg && cur >= base + p.seg[s].n_rows) {
+            base += p.seg[s].n_rows;
+            ++s;
+        }
+        seg = s;
+        local = cur - base;
+        int lim = min(end, base + p.seg[s].n_rows);
+        n = min(p.rpst[s], lim - cur);
+        cur += n;
+        return true;
+    }
+};
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, int row) {
+    uint32_t u = __float_as_uint(v);
+    if (v != v) u = 0;  // NaN never wins
+    else u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)row);
+}
+
+template <int NT>
+__global__ void __launch_bounds__(DC_WARPS * 32) k_gemv(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * DC_NSTAGE;
+    uint8_t* act_base = smem + DC_WARPS * DC_NSTAGE * 8;
+    const size_t act_bytes = (ActSmem::bytes(p.T, p.K) + 127) & ~(size_t)127;
+    uint8_t* bufs = act_base + act_bytes + (size_t)warp * DC_NSTAGE * p.stage_bytes;
+
+    WarpPipe<DC_NSTAGE> pipe;
+    pipe.init(bufs, bars, p.stage_bytes, p.err);
+
+    const int gw = blockIdx.x * DC_WARPS + warp, nw = gridDim.x * DC_WARPS;
+    const int r0 = (int)((long long)gw * p.total_rows / nw), r1 = (int)((long long)(gw + 1) * p.total_rows / nw);
+    StageIter prod{r0, r1}, cons{r0, r1};
+
+    auto issue_next = [&]() {
+        int sg, lr, n;
+        if (!prod.next(p, sg, lr, n)) return;
+        const dc_gemv_seg& s = p.seg[sg];
+        const uint32_t bytes = (uint32_t)n * s.row_bytes;
+        if (p.epi == DC_EPI_SWIGLU)
+            pipe.issue2(s.w + (size_t)lr * s.row_bytes, p.seg[1].w + (size_t)lr * s.row_bytes, bytes, p.up_off);
+        else
+            pipe.issue(s.w + (size_t)lr * s.row_bytes, bytes);
+    };
+    // Weights do not depend on the previous kernel: start streaming before waiting for it.
+    if (lane == 0)
+        for (int s = 0; s < DC_NSTAGE; ++s) issue_next();
+    pdl_launch_dependents();
+    pdl_wait();
+
+    ActSmem act;
+    act.bind(act_base, p.T, p.K);
+    act.fill(p.act_q8, p.T);
+    __syncthreads();
+
+    int tok[NT];
+#pragma unroll
+    for (int s = 0; s < NT; ++s) tok[s] = s;
+    unsigned long long best[NT];
+#pragma unroll
+    for (int s = 0; s < NT; ++s) best[s] = 0ull;
+
+    int sg, lr, n;
+    while (cons.next(p, sg, lr, n)) {
+        const dc_gemv_seg& s = p.seg[sg];
+        const uint32_t buf = pipe.wait();
+        const int G = lanes_per_row(s.type, p.K);
+        const int rows_per_pass = 32 / G;
+        const int grp = lane / G, lig = lane % G;
+        const uint32_t skew = (uint32_t)(((uintptr_t)s.w + (size_t)lr * s.row_bytes) & 15);
+        const uint32_t skew_up =
+            p.epi == DC_EPI_SWIGLU ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
+        for (int r = 0; r < n; r += rows_per_pass) {
+            const int rr = r + grp;
+            const bool active = rr < n;
+            float acc[NT], acc2[NT];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) acc[t] = acc2[t] = 0.0f;
+            if (active) {
+                row_dot_partial<NT>(s.type, buf + skew + rr * s.row_bytes, lig, G, act, p.T, tok, acc);
+                if (p.epi == DC_EPI_SWIGLU)
+                    row_dot_partial<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, lig, G, act, p.T, tok,
+                                        acc2);
+            }
+            // every lane runs the reductions; lane (t mod G) of the row's group stores token t
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                if (t < p.T) {
+                    float v = group_sum_rt(acc[t], G);
+                    if (p.epi == DC_EPI_SWIGLU) {
+                        const float u = group_sum_rt(acc2[t], G);
+                        v = __fmul_rn(silu_fast(v), u);
+                    }
+                    if (active && lig == (t & (G - 1))) {
+                        const int row = lr + rr;
+                        float* o = s.out + (size_t)t * s.ldo + row;
+                        if (p.epi == DC_EPI_ACC) *o += v;
+                        else *o = v;
+                        if (p.argmax) {
+                            const unsigned long long k = argmax_key(v, row);
+                            best[t] = k > best[t] ? k : best[t];
+                        }
+                    }
+                }
+            }
+        }
+        pipe.release();
+        if (lane == 0) issue_next();
+    }
+    if (p.argmax) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            if (t < p.T) {
+                unsigned long long k = best[t];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const unsigned long long ok = __shfl_xor_sync(0xffffffffu, k, o);
+                    k = ok > k ? ok : k;
+                }
+                if (lane == 0 && k) atomicMax(p.argmax + t, k);
+            }
+        }
+    }
+}
+
+static int rows_per_stage(int type, int K, int row_bytes) {
+    const int G = dc::lanes_per_row(type, K);
+    const int per_pass = 32 / G;
+    int r = DC_STAGE_TARGET / row_bytes;
+    r = r / per_pass * per_pass;
+    return r < per_pass ? per_pass : r;
+}
+
+template <int NT>
+static int launch_gemv_nt(dc_ctx* ctx, const GemvParams& p, int grid, size_t smem) {
+    static bool configured = false;
+    cudaError_t e = cudaSuccess;
+    if (!configured) {
+        e = cudaFuncSetAttribute(k_gemv<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_gemv)");
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(DC_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, k_gemv<NT>, p);
+    return dc_check_cuda(ctx, e, "k_gemv");
+}
+
+int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, const uint8_t* act_q8, int T, int K,
+                   unsigned long long* argmax) {
+    if (n_seg < 1 || n_seg > 3 || T < 1 || T > DC_MAX_T || K % DC_QK_K)
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemv: bad shape (n_seg=%d T=%d K=%d)", n_seg, T, K);
+    GemvParams p = {};
+    p.n_seg = n_seg;
+    p.epi = epi;
+    p.act_q8 = act_q8;
+    p.T = T;
+    p.K = K;
+    p.argmax = argmax;
+    p.err = ctx->d_err;
+    uint32_t stage = 0;
+    int total = 0;
+    for (int i = 0; i < n_seg; ++i) {
+        p.seg[i] = segs[i];
+        if (segs[i].type != DC_TYPE_Q4_K && segs[i].type != DC_TYPE_Q6_K)
+            return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemv: weight type %d is not Q4_K/Q6_K", segs[i].type);
+        p.rpst[i] = rows_per_stage(segs[i].type, K, segs[i].row_bytes);
+        const uint32_t need = (uint32_t)p.rpst[i] * segs[i].row_bytes + 32;
+        stage = need > stage ? need : stage;
+        total += segs[i].n_rows;
+    }
+    stage = (stage + 127) & ~127u;
+    if (epi == DC_EPI_SWIGLU) {
+        if (n_seg != 2 || segs[0].n_rows != segs[1].n_rows || segs[0].type != segs[1].type)
+            return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemv: SwiGLU needs matching gate/up segments");
+        total = segs[0].n_rows;
+        p.up_off = stage;
+        stage *= 2;
+    }
+    p.total_rows = total;
+    p.stage_bytes = stage;
+    const size_t act_bytes = (ActSmem::bytes(T, K) + 127) & ~(size_t)127;
+    const size_t smem = DC_WARPS * DC_NSTAGE * 8 + act_bytes + (size_t)DC_WARPS * DC_NSTAGE * stage;
+    if (smem > 200 * 1024) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemv: shared memory need %zu too large", smem);
+    // persistent-style grid: a multiple of the SM count, no more warps than row groups
+    int ctas_per_sm = smem <= 100 * 1024 ? 2 : 1;
+    int grid = ctx->num_sms * ctas_per_sm;
+    const int max_useful = (total + DC_WARPS - 1) / DC_WARPS;
+    if (grid > max_useful) grid = max_useful < 1 ? 1 : max_useful;
+    if (T == 1) return launch_gemv_nt<1>(ctx, p, grid, smem);
+    if (T <= 4) return launch_gemv_nt<4>(ctx, p, grid, smem);
+    if (T <= 8) return launch_gemv_nt<8>(ctx, p, grid, smem);
+    return launch_gemv_nt<16>(ctx, p, grid, smem);
+}
+
+// ------------------------------------------------ per-block integer sums
+// Parity/debug path: writes the exact int32 block sums the GEMV forms
+// (I and M of core/src/kernels/hwy/hwy_moe_quant.cc:218-246; I of
+// core/src/llm/matmul/q6_small_batch.h:62-83).  Same decoders as k_gemv, plain
+// (non-pipelined) staging since speed does not matter here.
+__global__ void __launch_bounds__(256) k_block_sums(const uint8_t* __restrict__ w, int type, int N, int K,
+                                                    int row_bytes, const uint8_t* __restrict__ act_q8, int T,
+                                                    int32_t* __restrict__ I_out, int32_t* __restrict__ M_out) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = K / DC_QK_K;
+    ActSmem act;
+    act.bind(smem, T, K);
+    act.fill(act_q8, T);
+    const size_t act_bytes = (ActSmem::bytes(T, K) + 127) & ~(size_t)127;
+    const int row_pad = (row_bytes + 15) & ~15;
+    uint8_t* rowbuf = smem + act_bytes + (size_t)warp * row_pad;
+    __syncthreads();
+    const int gw = blockIdx.x * 8 + warp, nw = gridDim.x * 8;
+    const int ipb = type == DC_TYPE_Q4_K ? 4 : 8;
+    for (int n = gw; n < N; n += nw) {
+        const uint8_t* src = w + (size_t)n * row_bytes;
+        for (int i = lane; i < row_bytes / 2; i += 32)
+            reinterpret_cast<uint16_t*>(rowbuf)[i] = reinterpret_cast<const uint16_t*>(src)[i];
+        __syncwarp();
+        const uint32_t row = smem_u32(rowbuf);
+        for (int t = 0; t < T; ++t) {
+            for (int i0 = 0; i0 < nb * ipb; i0 += 32) {
+                const int i = i0 + lane;
+                int I = 0, M = 0;
+                if (i < nb * ipb) {
+                    if (type == DC_TYPE_Q4_K) {
+                        const int b = i >> 2, c = i & 3;
+                        Q4Item it;
+                        q4k_load_item(row, b, c, it);
+                        q4k_item_ints(it, act.qs + t * K + b * 256 + 64 * c, act.bs + (t * nb + b) * 32 + 8 * c, I, M);
+                    } else {
+                        const int b = i >> 3, j = (i >> 2) & 1, tq = i & 3;
+                        Q6Item it;
+                        q6k_load_item(row, b, j, tq, it);
+                        I = q6k_item_int(it, act.qs + t * K + b * 256 + 128 * j + 8 * tq);
+                    }
+                }
+                for (int o = 1; o < ipb; o <<= 1) {
+                    I += __shfl_xor_sync(0xffffffffu, I, o);
+                    M += __shfl_xor_sync(0xffffffffu, M, o);
+                }
+                if (i < nb * ipb && (lane % ipb) == 0) {
+                    const size_t idx = ((size_t)t * N + n) * nb + i / ipb;
+                    I_out[idx] = I;
+                    if (M_out) M_out[idx] = M;
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+int dc_launch_block_sums(dc_ctx* ctx, const dc_weight* w, const uint8_t* act_q8, int T, int32_t* I, int32_t* M) {
+    const int K = (int)w->K, N = (int)(w->N * w->E);
+    const size_t act_bytes = (ActSmem::bytes(T, K) + 127) & ~(size_t)127;
+    const size_t smem = act_bytes + 8 * (((size_t)w->row_bytes + 15) & ~(size_t)15);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k_block_sums, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_block_sums)");
+        configured = true;
+    }
+    if (smem > 200 * 1024) return dc_fail(ctx, DC_B200_UNSUPPORTED, "block_sums: shape too large");
+    int grid = (N + 7) / 8;
+    if (grid > ctx->num_sms * 2) grid = ctx->num_sms * 2;
+    k_block_sums<<<grid, 256, smem, ctx->stream>>>(w->dev, w->type, N, K, (int)w->row_bytes, act_q8, T, I,
+                                                   w->type == DC_TYPE_Q4_K ? M : nullptr);
+    return dc_check_cuda(ctx, cudaGetLastError(), "k_block_sums");
+}
