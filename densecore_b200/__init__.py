@@ -6,7 +6,8 @@ reference's op interface, used by the tests and the benchmark.
 """
 from .blocks import (GGML_TYPE_F16, GGML_TYPE_F32, GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, QK_K, row_bytes)
 from ._lib import DcError
-from .ops import Context, Weight
+from .ops import Context, KVCache, Weight
+from .model import Config, Model, dense_0p8b, moe_35b_a3b, tensor_seed
 
-__all__ = ["Context", "Weight", "DcError", "GGML_TYPE_F32", "GGML_TYPE_F16", "GGML_TYPE_Q4_K", "GGML_TYPE_Q6_K",
+__all__ = ["Context", "Weight", "KVCache", "Model", "Config", "dense_0p8b", "moe_35b_a3b", "tensor_seed", "DcError", "GGML_TYPE_F32", "GGML_TYPE_F16", "GGML_TYPE_Q4_K", "GGML_TYPE_Q6_K",
            "QK_K", "row_bytes"]

@@ -66,3 +66,59 @@ int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, con
 int dc_launch_quantize_q8k(dc_ctx* ctx, const float* x, int rows, int K, uint8_t* out);
 // per-block integer sums of W x (debug/parity): I[T][N][nb], M[T][N][nb] (M only for Q4_K)
 int dc_launch_block_sums(dc_ctx* ctx, const dc_weight* w, const uint8_t* act_q8, int T, int32_t* I, int32_t* M);
+
+// ---- misc.cu ----
+int dc_launch_embed(dc_ctx* ctx, const dc_weight* w, const int32_t* tokens, int T, float* x);
+// x (+= add) -> RMSNorm * w -> optional f32 copy and Q8_K blocks
+int dc_launch_rmsnorm_q8k(dc_ctx* ctx, float* x, const float* add, const float* w, int T, int H, float eps,
+                          float* xn_out, uint8_t* q8_out);
+int dc_launch_qknorm_rope_kv(dc_ctx* ctx, const float* qkv, const float* qn_w, const float* kn_w,
+                             const float* cos_sin, int max_pos, const int32_t* positions, const int32_t* seq_ids,
+                             const int32_t* block_tables, int max_blocks, void* k_arena, void* v_arena, int n_head,
+                             int n_kv, float eps, int T, float* q_out);
+int dc_launch_argmax_finish(dc_ctx* ctx, unsigned long long* keys, int T, int32_t* out_tokens, int32_t* next_tokens,
+                            int32_t* positions, int32_t* history, int* history_len, int history_cap);
+int dc_launch_argmax_rows(dc_ctx* ctx, const float* logits, int rows, int n, int32_t* out);
+
+// ---- attn.cu ----
+struct dc_attn_scratch {
+    float* scores;    // [T][n_head][max_blocks*16]
+    float* bmax;      // [T][n_head][max_blocks]
+    float* part_acc;  // [T][n_head][nsplit][128]
+    float* part_d;    // [T][n_head][nsplit]
+    int* tickets;     // [T][n_kv], zeroed once
+};
+size_t dc_attention_scratch_bytes(int T, int n_head, int n_kv, int max_blocks, int nsplit);
+void dc_attn_scratch_bind(dc_attn_scratch* sc, uint8_t* base, int T, int n_head, int n_kv, int max_blocks, int nsplit);
+int dc_launch_attention(dc_ctx* ctx, const float* q, const void* k_arena, const void* v_arena,
+                        const int32_t* block_tables, int max_blocks, const int32_t* seq_ids, const int32_t* positions,
+                        int T, int n_head, int n_kv, float scale, int nsplit, const dc_attn_scratch* sc, float* out,
+                        uint8_t* q8_out);
+
+// ---- moe.cu ----
+struct dc_moe_route {
+    float* logits;     // [T][E]
+    int32_t* ids;      // [T][top_k]
+    float* weights;    // [T][top_k]
+    int* ticket;       // zeroed once; the router resets it itself
+    int* n_active;     // number of distinct local experts hit
+    int32_t* uexp;     // [E]
+    int32_t* uoff;     // [E+1]
+    int32_t* uassign;  // [T*top_k]
+};
+int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_expert, int T, int top_k, float scale,
+                     int ep_lo, int ep_hi, const dc_moe_route* rt);
+// carves a dc_moe_route for (T, E, top_k) out of a byte buffer; returns bytes used
+size_t dc_moe_route_bind(dc_moe_route* rt, uint8_t* base, int T, int E, int top_k);
+int dc_launch_moe_mm(dc_ctx* ctx, bool pair, const dc_weight* w0, const dc_weight* w1, const uint8_t* act_q8,
+                     int act_rows, int T, int top_k, const dc_moe_route* rt, float* out);
+int dc_launch_moe_combine(dc_ctx* ctx, const float* dn, const int32_t* ids, const float* weights, int T, int top_k,
+                          int H, int ep_lo, int ep_hi, float* out);
+
+// ---- sample.cu ----
+// mode 0 greedy / 1 stochastic; result[0] = accepted draft tokens, result[1] = next token
+int dc_launch_verify(dc_ctx* ctx, int mode, int gamma, int vocab, const float* target_logits,
+                     const int32_t* draft_tokens, const float* draft_probs, const float* u, float temperature,
+                     int32_t* argmax_scratch, float* probs_scratch, int32_t* result);
+int dc_launch_verify_uniforms(dc_ctx* ctx, unsigned long long seed, uint32_t step, int n, float* u);
+int dc_launch_det_softmax(dc_ctx* ctx, const float* logits, int rows, int n, float temperature, float* probs);

@@ -1,0 +1,65 @@
+// Decoder state shared by model.cu, ep.cu and spec.cu.
+#pragma once
+#include <map>
+#include <string>
+#include <vector>
+
+#include "dc_internal.h"
+#include "dc_kv.h"
+
+#define DC_HISTORY_CAP 4096
+
+struct dc_layer {
+    dc_weight *attn_norm = nullptr, *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr;
+    dc_weight *q_norm = nullptr, *k_norm = nullptr, *ffn_norm = nullptr;
+    dc_weight *router = nullptr, *gate_exps = nullptr, *up_exps = nullptr, *down_exps = nullptr;
+    dc_weight *ffn_gate = nullptr, *ffn_up = nullptr, *ffn_down = nullptr;
+};
+
+struct dc_step_buffers {
+    int32_t *tokens = nullptr, *seq_ids = nullptr, *positions = nullptr, *out_tokens = nullptr;
+    unsigned long long* argmax_keys = nullptr;
+    float *x = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *h = nullptr, *dn = nullptr, *moe_out = nullptr;
+    float *logits = nullptr, *cos_sin = nullptr;
+    uint8_t *q8_x = nullptr, *q8_attn = nullptr, *q8_h = nullptr, *route_mem = nullptr, *verify_mem = nullptr;
+    uint8_t* attn_mem = nullptr;
+    dc_attn_scratch attn = {};
+    int32_t* history = nullptr;
+    int* history_len = nullptr;
+    dc_moe_route route = {};
+};
+
+struct dc_graph {
+    cudaGraphExec_t exec = nullptr;
+    int launches = 0;
+};
+
+struct dc_model {
+    dc_ctx* ctx = nullptr;
+    dc_model_config cfg = {};
+    std::vector<dc_layer> layers;
+    dc_weight *tok_embd = nullptr, *out_norm = nullptr, *output = nullptr;
+    std::vector<dc_weight*> owned;
+    std::map<std::string, dc_weight*> names;
+    dc_kv_cache kv;
+    dc_step_buffers buf;
+    int nsplit = 16;
+    bool finalized = false;
+    bool use_graphs = true;
+    std::map<int, dc_graph> graphs;
+    std::map<int, bool> warmed;
+    int last_launches = 0;
+    int32_t* h_stage = nullptr;  // pinned, 1024 ints
+    int stage_slot = 0;
+    // expert parallel
+    bool ep_ready = false;
+    void* ep_comm = nullptr;     // ncclComm_t
+    void* ep_lib = nullptr;      // dlopen handle of libnccl
+};
+
+// ---- synth.cu ----
+int dc_launch_synth_quantized(dc_ctx* ctx, int type, uint64_t seed, int64_t rows, int64_t K, float sigma, uint8_t* out);
+int dc_launch_synth_f32(dc_ctx* ctx, uint64_t seed, int64_t n, float sigma, float offset, float* out);
+// ---- ep.cu ----
+int dc_ep_allreduce(dc_model* m, float* buf, size_t n);
+void dc_ep_destroy(dc_model* m);

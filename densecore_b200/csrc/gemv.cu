@@ -15,62 +15,6 @@
 
 using namespace dc;
 
-// ------------------------------------------------------------ Q8_K quantise
-// One warp per 256-element block; lane l holds elements 8l..8l+7.
-// Follows core/src/kernels/hwy/hwy_moe_quant.cc:103-144 step by step:
-// first element of largest magnitude keeps its sign; iscale = -127/max;
-// q = min(127, rne(iscale*x)); bsums per 16; d = 1/iscale.
-__device__ __forceinline__ void quantize_block_q8k_warp(const float* __restrict__ x, uint8_t* __restrict__ out,
-                                                        int lane) {
-    float v[8];
-    const float4 a = reinterpret_cast<const float4*>(x)[2 * lane];
-    const float4 b = reinterpret_cast<const float4*>(x)[2 * lane + 1];
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    float amax = 0.0f, mx = 0.0f;
-    int idx = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float ax = fabsf(v[j]);
-        if (ax > amax) {
-            amax = ax;
-            mx = v[j];
-            idx = 8 * lane + j;
-        }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
-        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (oa > amax || (oa == amax && oi < idx)) {
-            amax = oa;
-            mx = om;
-            idx = oi;
-        }
-    }
-    uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
-    if (amax == 0.0f) {
-        for (int w = lane; w < 73; w += 32) o32[w] = 0u;
-        return;
-    }
-    const float iscale = __fdiv_rn(-127.0f, mx);
-    int q[8], sum = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        q[j] = min(127, __float2int_rn(__fmul_rn(iscale, v[j])));
-        sum += q[j];
-    }
-    const uint32_t w0 = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
-    const uint32_t w1 = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
-    o32[1 + 2 * lane] = w0;
-    o32[2 + 2 * lane] = w1;
-    // bsums: group g = lanes 2g, 2g+1
-    const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
-    const int other = __shfl_xor_sync(0xffffffffu, pair, 2);  // neighbouring group's sum
-    if ((lane & 3) == 0) o32[65 + (lane >> 2)] = (uint32_t)(pair & 0xFFFF) | ((uint32_t)(other & 0xFFFF) << 16);
-    if (lane == 0) o32[0] = __float_as_uint(__fdiv_rn(1.0f, iscale));
-}
-
 __global__ void __launch_bounds__(256) k_quantize_q8k(const float* __restrict__ x, int n_blocks,
                                                       uint8_t* __restrict__ out) {
     pdl_launch_dependents();

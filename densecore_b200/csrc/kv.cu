@@ -1,0 +1,159 @@
+// Paged KV cache: fp16 arenas [layer][block][16 slots][kv_head][head_dim] for K
+// and V (core/src/runtime/memory/kv_cache_storage.cpp:146-200), a free-list block
+// manager and per-sequence block tables (core/include/densecore/memory/kv_cache.h:67-220)
+// mirrored in device memory for the kernels.  Host-side bookkeeping only; the
+// slot writes and reads are in misc.cu / attn.cu.
+#include <string.h>
+
+#include "dc_common.cuh"
+#include "dc_internal.h"
+#include "dc_kv.h"
+
+int dc_kv_init(dc_ctx* ctx, dc_kv_cache* kv, int n_layer, int n_kv_head, int head_dim, int max_blocks, int max_seqs,
+               int max_blocks_per_seq) {
+    if (n_layer <= 0 || n_kv_head <= 0 || head_dim != 128 || max_blocks <= 0 || max_seqs <= 0 || max_blocks_per_seq <= 0)
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "kv_create: bad shape (head_dim must be 128)");
+    kv->ctx = ctx;
+    kv->n_layer = n_layer;
+    kv->n_kv = n_kv_head;
+    kv->head_dim = head_dim;
+    kv->max_blocks = max_blocks;
+    kv->max_seqs = max_seqs;
+    kv->max_blocks_per_seq = max_blocks_per_seq;
+    kv->layer_elems = (size_t)max_blocks * DC_KV_BLOCK * n_kv_head * head_dim;
+    const size_t bytes = kv->layer_elems * n_layer * sizeof(__half);
+    cudaError_t e = cudaMalloc(&kv->k_arena, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&kv->v_arena, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&kv->d_tables, (size_t)max_seqs * max_blocks_per_seq * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemsetAsync(kv->k_arena, 0, bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(kv->v_arena, 0, bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(kv->d_tables, 0, (size_t)max_seqs * max_blocks_per_seq * sizeof(int32_t), ctx->stream);
+    if (e != cudaSuccess) return dc_check_cuda(ctx, e, "kv_create");
+    kv->free_list.clear();
+    for (int b = max_blocks - 1; b >= 0; --b) kv->free_list.push_back(b);
+    kv->seqs.assign(max_seqs, dc_kv_seq());
+    return DC_B200_OK;
+}
+
+void dc_kv_release(dc_kv_cache* kv) {
+    if (kv->k_arena) cudaFree(kv->k_arena);
+    if (kv->v_arena) cudaFree(kv->v_arena);
+    if (kv->d_tables) cudaFree(kv->d_tables);
+    kv->k_arena = kv->v_arena = nullptr;
+    kv->d_tables = nullptr;
+}
+
+int dc_kv_seq_alloc(dc_kv_cache* kv, int* out_seq) {
+    for (int s = 0; s < kv->max_seqs; ++s) {
+        if (!kv->seqs[s].used) {
+            kv->seqs[s].used = true;
+            kv->seqs[s].len = 0;
+            kv->seqs[s].blocks.clear();
+            *out_seq = s;
+            return DC_B200_OK;
+        }
+    }
+    return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: all %d sequence slots are in use", kv->max_seqs);
+}
+
+int dc_kv_seq_free(dc_kv_cache* kv, int seq) {
+    if (seq < 0 || seq >= kv->max_seqs || !kv->seqs[seq].used)
+        return dc_fail(kv->ctx, DC_B200_INVALID_ARGUMENT, "kv: sequence %d is not allocated", seq);
+    for (int b : kv->seqs[seq].blocks) kv->free_list.push_back(b);
+    kv->seqs[seq] = dc_kv_seq();
+    return DC_B200_OK;
+}
+
+// Makes sure blocks exist for positions [0, n_tokens) and mirrors new table
+// entries to the device (ordered on the context's stream).
+int dc_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens) {
+    if (seq < 0 || seq >= kv->max_seqs || !kv->seqs[seq].used)
+        return dc_fail(kv->ctx, DC_B200_INVALID_ARGUMENT, "kv: sequence %d is not allocated", seq);
+    dc_kv_seq& s = kv->seqs[seq];
+    const int need = (n_tokens + DC_KV_BLOCK - 1) / DC_KV_BLOCK;
+    if (need > kv->max_blocks_per_seq)
+        return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: sequence %d needs %d blocks, table holds %d", seq, need,
+                       kv->max_blocks_per_seq);
+    const int have = (int)s.blocks.size();
+    if (need <= have) return DC_B200_OK;
+    if ((int)kv->free_list.size() < need - have)
+        return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: out of blocks (%d free, %d needed)",
+                       (int)kv->free_list.size(), need - have);
+    for (int i = have; i < need; ++i) {
+        s.blocks.push_back(kv->free_list.back());
+        kv->free_list.pop_back();
+    }
+    // staged through a small pinned ring so the async copy source stays valid
+    int32_t* stage = (int32_t*)dc_pinned(kv->ctx, 64 * 1024);
+    if (!stage) return DC_B200_OUT_OF_MEMORY;
+    const int n_new = need - have;
+    if (kv->stage_off + n_new > 16 * 1024) {
+        cudaStreamSynchronize(kv->ctx->stream);
+        kv->stage_off = 0;
+    }
+    if (n_new > 16 * 1024) return dc_fail(kv->ctx, DC_B200_UNSUPPORTED, "kv: too many new blocks at once");
+    memcpy(stage + kv->stage_off, s.blocks.data() + have, (size_t)n_new * sizeof(int32_t));
+    cudaError_t e = cudaMemcpyAsync(kv->d_tables + (size_t)seq * kv->max_blocks_per_seq + have, stage + kv->stage_off,
+                                    (size_t)n_new * sizeof(int32_t), cudaMemcpyHostToDevice, kv->ctx->stream);
+    kv->stage_off += n_new;
+    return dc_check_cuda(kv->ctx, e, "kv: block table upload");
+}
+
+extern "C" {
+
+int dc_b200_kv_create(dc_ctx* ctx, int n_layer, int n_kv_head, int head_dim, int max_blocks, int max_seqs,
+                      int max_blocks_per_seq, dc_kv_cache** out) {
+    if (!ctx || !out) return DC_B200_INVALID_ARGUMENT;
+    *out = nullptr;
+    cudaSetDevice(ctx->device);
+    dc_kv_cache* kv = new dc_kv_cache();
+    int st = dc_kv_init(ctx, kv, n_layer, n_kv_head, head_dim, max_blocks, max_seqs, max_blocks_per_seq);
+    if (st != DC_B200_OK) {
+        dc_kv_release(kv);
+        delete kv;
+        return st;
+    }
+    *out = kv;
+    return DC_B200_OK;
+}
+
+void dc_b200_kv_destroy(dc_kv_cache* kv) {
+    if (!kv) return;
+    cudaSetDevice(kv->ctx->device);
+    cudaStreamSynchronize(kv->ctx->stream);
+    dc_kv_release(kv);
+    delete kv;
+}
+
+int dc_b200_kv_seq_alloc(dc_kv_cache* kv, int* out_seq) {
+    if (!kv || !out_seq) return DC_B200_INVALID_ARGUMENT;
+    return dc_kv_seq_alloc(kv, out_seq);
+}
+int dc_b200_kv_seq_free(dc_kv_cache* kv, int seq) { return kv ? dc_kv_seq_free(kv, seq) : DC_B200_INVALID_ARGUMENT; }
+int dc_b200_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens) {
+    if (!kv) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(kv->ctx->device);
+    return dc_kv_seq_reserve(kv, seq, n_tokens);
+}
+int dc_b200_kv_block_table(dc_kv_cache* kv, int seq, int32_t* out_blocks, int capacity, int* out_n) {
+    if (!kv || seq < 0 || seq >= kv->max_seqs || !kv->seqs[seq].used || !out_n) return DC_B200_INVALID_ARGUMENT;
+    const int n = (int)kv->seqs[seq].blocks.size();
+    *out_n = n;
+    if (out_blocks)
+        for (int i = 0; i < n && i < capacity; ++i) out_blocks[i] = kv->seqs[seq].blocks[i];
+    return DC_B200_OK;
+}
+int dc_b200_kv_free_blocks(dc_kv_cache* kv) { return kv ? (int)kv->free_list.size() : DC_B200_INVALID_ARGUMENT; }
+
+int dc_b200_kv_read_block(dc_kv_cache* kv, int layer, int block, void* k_host, void* v_host) {
+    if (!kv || layer < 0 || layer >= kv->n_layer || block < 0 || block >= kv->max_blocks) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(kv->ctx->device);
+    const size_t be = (size_t)DC_KV_BLOCK * kv->n_kv * kv->head_dim;
+    const size_t off = kv->layer_elems * layer + be * block;
+    cudaError_t e = cudaStreamSynchronize(kv->ctx->stream);
+    if (e == cudaSuccess && k_host) e = cudaMemcpy(k_host, kv->k_arena + off, be * sizeof(__half), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && v_host) e = cudaMemcpy(v_host, kv->v_arena + off, be * sizeof(__half), cudaMemcpyDeviceToHost);
+    return dc_check_cuda(kv->ctx, e, "kv_read_block");
+}
+
+}  // extern "C"

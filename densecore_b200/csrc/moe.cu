@@ -1,0 +1,432 @@
+// Fused MoE layer (MUL_MAT_ID).  Replaces cb_moe_forward
+// (core/src/llm/moe/exec.cpp:813) -> RouteMoESoftmaxTopK (:734) ->
+// CpuBackend::ForwardMoE (core/src/backend/cpu_backend_moe_ops.cpp:1195):
+//   k_router      router logits (F32 matmul, core/src/llm/graph/decoder.cpp:2265),
+//                 stable top-k + weights (core/src/llm/moe/native.cpp:610-676),
+//                 token->expert bucketing (core/src/moe/moe_routing.cpp:534-603)
+//   k_moe_mm<PAIR> gate/up + SwiGLU for every (distinct expert, row), each expert's
+//                 weights read once for all its tokens (native.cpp:3929-4345)
+//   k_moe_mm      down projection per assignment (native.cpp:3051-3295)
+//   k_moe_combine weighted sum in the reference's order
+//                 (cpu_backend_moe_ops.cpp:1578-1597, moe_routing.cpp:647-676)
+#include "dc_common.cuh"
+#include "dc_internal.h"
+#include "dc_launch.cuh"
+
+using namespace dc;
+
+#define MOE_MAX_E 256
+#define MOE_MAX_K 16
+
+// ------------------------------------------------------------------ router
+struct RouterParams {
+    const float* wr;      // [E][H] f32
+    const float* xn;      // [T][H] f32 (normed hidden state)
+    int E, H, T, top_k;
+    float scale;          // moe_routed_scaling_factor
+    int ep_lo, ep_hi;     // experts owned by this GPU
+    float* logits;        // [T][E]
+    int32_t* ids;         // [T][top_k]
+    float* weights;       // [T][top_k]
+    int* ticket;          // zero-initialised, self-resetting
+    int* n_active;        // U
+    int32_t* uexp;        // [E]   distinct local experts, ascending
+    int32_t* uoff;        // [E+1] offsets into uassign
+    int32_t* uassign;     // [T*top_k] assignment indices t*top_k+k, grouped by expert, routing order inside
+};
+
+__device__ __forceinline__ unsigned long long route_key(float v, int id) {
+    uint32_t u;
+    if (v != v) u = 0u;
+    else {
+        if (v == 0.0f) v = 0.0f;  // -0 == +0 for the comparator
+        u = __float_as_uint(v);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    }
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)id);
+}
+
+__global__ void __launch_bounds__(256) k_router(const RouterParams p) {
+    __shared__ int s_last;
+    __shared__ int32_t s_ids[DC_MAX_T * MOE_MAX_K];
+    __shared__ int s_cnt[MOE_MAX_E], s_wsum_a[8], s_wsum_c[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    if (p.wr && e < p.E) {
+        float acc[DC_MAX_T];
+#pragma unroll
+        for (int t = 0; t < DC_MAX_T; ++t) acc[t] = 0.0f;
+        const float* w = p.wr + (size_t)e * p.H;
+        for (int i = lane; i < p.H; i += 32) {
+            const float wv = w[i];
+#pragma unroll
+            for (int t = 0; t < DC_MAX_T; ++t)
+                if (t < p.T) acc[t] = fmaf(wv, p.xn[(size_t)t * p.H + i], acc[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < DC_MAX_T; ++t) {
+            if (t < p.T) {
+                float v = acc[t];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) p.logits[(size_t)t * p.E + e] = v;
+            }
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(p.ticket, 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) *p.ticket = 0;
+
+    // ---- stable top-k per token, one warp per token
+    for (int t = warp; t < p.T; t += 8) {
+        float lv[MOE_MAX_E / 32];
+        bool taken[MOE_MAX_E / 32];
+#pragma unroll
+        for (int j = 0; j < MOE_MAX_E / 32; ++j) {
+            const int id = j * 32 + lane;
+            lv[j] = id < p.E ? __ldcg(p.logits + (size_t)t * p.E + id) : 0.0f;
+            taken[j] = id >= p.E;
+        }
+        float sel_l[MOE_MAX_K];
+        for (int k = 0; k < p.top_k; ++k) {
+            unsigned long long best = 0ull;
+#pragma unroll
+            for (int j = 0; j < MOE_MAX_E / 32; ++j) {
+                if (!taken[j]) {
+                    const unsigned long long key = route_key(lv[j], j * 32 + lane);
+                    best = key > best ? key : best;
+                }
+            }
+            // a real candidate's key is never 0 (its low word is 0xFFFFFFFF - id), so 0 means "none"
+            unsigned long long win = best;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long ok = __shfl_xor_sync(0xffffffffu, win, o);
+                win = ok > win ? ok : win;
+            }
+            const int wid = (int)(0xFFFFFFFFu - (uint32_t)(win & 0xFFFFFFFFull));
+#pragma unroll
+            for (int j = 0; j < MOE_MAX_E / 32; ++j)
+                if (j * 32 + lane == wid) taken[j] = true;
+            const float wl = __ldcg(p.logits + (size_t)t * p.E + wid);
+            if (k < MOE_MAX_K) sel_l[k] = wl;
+            if (lane == 0) {
+                p.ids[t * p.top_k + k] = wid;
+                s_ids[t * p.top_k + k] = wid;
+            }
+        }
+        if (lane == 0) {
+            // weights over the selected experts only (native.cpp:649-674)
+            float mx = -INFINITY;
+            bool finite = true;
+            for (int k = 0; k < p.top_k; ++k) {
+                finite = finite && isfinite(sel_l[k]);
+                if (isfinite(sel_l[k]) && sel_l[k] > mx) mx = sel_l[k];
+            }
+            float den = 0.0f, wv[MOE_MAX_K];
+            if (finite && isfinite(mx)) {
+                for (int k = 0; k < p.top_k; ++k) {
+                    wv[k] = expf(sel_l[k] - mx);
+                    den += wv[k];
+                }
+            }
+            const bool ok = den > 0.0f && isfinite(den);
+            for (int k = 0; k < p.top_k; ++k) {
+                const float w = ok ? __fdiv_rn(wv[k], den) : __fdiv_rn(1.0f, (float)p.top_k);
+                p.weights[t * p.top_k + k] = __fmul_rn(w, p.scale);
+            }
+        }
+    }
+    __syncthreads();
+    // ---- bucketing: thread e owns expert e
+    const int A = p.T * p.top_k;
+    const int me = threadIdx.x;
+    int cnt = 0;
+    if (me < p.E && me >= p.ep_lo && me < p.ep_hi)
+        for (int i = 0; i < A; ++i) cnt += (s_ids[i] == me);
+    int act = cnt > 0 ? 1 : 0;
+    // inclusive scans of (act, cnt) over the 256 threads
+    int sa = act, scn = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int a2 = __shfl_up_sync(0xffffffffu, sa, o), c2 = __shfl_up_sync(0xffffffffu, scn, o);
+        if (lane >= o) {
+            sa += a2;
+            scn += c2;
+        }
+    }
+    if (lane == 31) {
+        s_wsum_a[warp] = sa;
+        s_wsum_c[warp] = scn;
+    }
+    __syncthreads();
+    int base_a = 0, base_c = 0, tot_a = 0, tot_c = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        if (w < warp) {
+            base_a += s_wsum_a[w];
+            base_c += s_wsum_c[w];
+        }
+        tot_a += s_wsum_a[w];
+        tot_c += s_wsum_c[w];
+    }
+    if (act) {
+        const int u = base_a + sa - 1, off = base_c + scn - cnt;
+        p.uexp[u] = me;
+        p.uoff[u] = off;
+        int o = off;
+        for (int i = 0; i < A; ++i)
+            if (s_ids[i] == me) p.uassign[o++] = i;
+    }
+    if (threadIdx.x == 0) {
+        *p.n_active = tot_a;
+        p.uoff[tot_a] = tot_c;
+    }
+}
+
+// --------------------------------------------------- expert matmul kernel
+struct MoeMMParams {
+    const uint8_t* w0;    // gate (PAIR) or down
+    const uint8_t* w1;    // up (PAIR)
+    int type, row_bytes, N /*rows per expert*/, K;
+    const uint8_t* act_q8;  // Q8_K rows: tokens (PAIR) or assignments (down)
+    int act_rows, top_k;
+    const int* n_active;
+    const int32_t* uexp;
+    const int32_t* uoff;
+    const int32_t* uassign;
+    float* out;           // [assignment][N]
+    int rpst;
+    uint32_t stage_bytes, up_off;
+    int* err;
+};
+
+struct MoeIter {
+    int cur, end, N, rpst;
+    __device__ __forceinline__ bool next(int& u, int& r, int& n) {
+        if (cur >= end) return false;
+        u = cur / N;
+        r = cur - u * N;
+        n = min(rpst, min(N - r, end - cur));
+        cur += n;
+        return true;
+    }
+};
+
+template <int NT, bool PAIR>
+__global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * DC_NSTAGE;
+    uint8_t* act_base = smem + DC_WARPS * DC_NSTAGE * 8;
+    const size_t act_bytes = (ActSmem::bytes(p.act_rows, p.K) + 127) & ~(size_t)127;
+    uint8_t* bufs = act_base + act_bytes + (size_t)warp * DC_NSTAGE * p.stage_bytes;
+    WarpPipe<DC_NSTAGE> pipe;
+    pipe.init(bufs, bars, p.stage_bytes, p.err);
+    pdl_launch_dependents();
+    pdl_wait();  // expert ids come from the router kernel: nothing can be fetched before this
+
+    const int U = *p.n_active;
+    const int total = U * p.N;
+    const int gw = blockIdx.x * DC_WARPS + warp, nw = gridDim.x * DC_WARPS;
+    const int r0 = (int)((long long)gw * total / nw), r1 = (int)((long long)(gw + 1) * total / nw);
+    MoeIter prod{r0, r1, p.N, p.rpst}, cons{r0, r1, p.N, p.rpst};
+    const size_t estride = (size_t)p.N * p.row_bytes;
+
+    auto issue_next = [&]() {
+        int u, r, n;
+        if (!prod.next(u, r, n)) return;
+        const size_t off = (size_t)p.uexp[u] * estride + (size_t)r * p.row_bytes;
+        if (PAIR) pipe.issue2(p.w0 + off, p.w1 + off, (uint32_t)n * p.row_bytes, p.up_off);
+        else pipe.issue(p.w0 + off, (uint32_t)n * p.row_bytes);
+    };
+    if (lane == 0)
+        for (int s = 0; s < DC_NSTAGE; ++s) issue_next();
+
+    ActSmem act;
+    act.bind(act_base, p.act_rows, p.K);
+    act.fill(p.act_q8, p.act_rows);
+    __syncthreads();
+
+    const int G = lanes_per_row(p.type, p.K);
+    const int rows_per_pass = 32 / G, grp = lane / G, lig = lane % G;
+    int u, r, n;
+    while (cons.next(u, r, n)) {
+        const uint32_t buf = pipe.wait();
+        const size_t off = (size_t)p.uexp[u] * estride + (size_t)r * p.row_bytes;
+        const uint32_t skew0 = (uint32_t)(((uintptr_t)p.w0 + off) & 15);
+        const uint32_t skew1 = PAIR ? (uint32_t)(((uintptr_t)p.w1 + off) & 15) : 0u;
+        const int a0 = p.uoff[u], nt = min(NT, p.uoff[u + 1] - a0);
+        int tok[NT], asg[NT];
+#pragma unroll
+        for (int s = 0; s < NT; ++s) {
+            asg[s] = s < nt ? p.uassign[a0 + s] : 0;
+            tok[s] = PAIR ? asg[s] / p.top_k : asg[s];
+        }
+        for (int rr0 = 0; rr0 < n; rr0 += rows_per_pass) {
+            const int rr = rr0 + grp;
+            const bool active = rr < n;
+            float acc[NT], acc2[NT];
+#pragma unroll
+            for (int s = 0; s < NT; ++s) acc[s] = acc2[s] = 0.0f;
+            if (active) {
+                row_dot_partial<NT>(p.type, buf + skew0 + rr * p.row_bytes, lig, G, act, nt, tok, acc);
+                if (PAIR)
+                    row_dot_partial<NT>(p.type, buf + p.up_off + skew1 + rr * p.row_bytes, lig, G, act, nt, tok, acc2);
+            }
+#pragma unroll
+            for (int s = 0; s < NT; ++s) {
+                if (s < nt) {
+                    float v = group_sum_rt(acc[s], G);
+                    if (PAIR) v = __fmul_rn(silu_fast(v), group_sum_rt(acc2[s], G));
+                    if (active && lig == (s & (G - 1))) p.out[(size_t)asg[s] * p.N + r + rr] = v;
+                }
+            }
+        }
+        pipe.release();
+        if (lane == 0) issue_next();
+    }
+}
+
+template <int NT, bool PAIR>
+static int launch_moe_mm(dc_ctx* ctx, const MoeMMParams& p, int grid, size_t smem) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k_moe_mm<NT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_moe_mm)");
+        configured = true;
+    }
+    return dc_launch(ctx, "k_moe_mm", k_moe_mm<NT, PAIR>, dim3(grid), dim3(DC_WARPS * 32), smem, p);
+}
+
+static int rows_per_stage_moe(int type, int K, int row_bytes) {
+    const int G = dc::lanes_per_row(type, K);
+    const int per_pass = 32 / G;
+    int r = DC_STAGE_TARGET / row_bytes;
+    r = r / per_pass * per_pass;
+    return r < per_pass ? per_pass : r;
+}
+
+// w0/w1: expert tensors [K, N, E].  pair: gate/up + SwiGLU, activations are the T
+// token rows; else down, activations are the T*top_k assignment rows.
+int dc_launch_moe_mm(dc_ctx* ctx, bool pair, const dc_weight* w0, const dc_weight* w1, const uint8_t* act_q8,
+                     int act_rows, int T, int top_k, const dc_moe_route* rt, float* out) {
+    MoeMMParams p = {};
+    p.w0 = w0->dev;
+    p.w1 = pair ? w1->dev : nullptr;
+    p.type = w0->type;
+    p.row_bytes = (int)w0->row_bytes;
+    p.N = (int)w0->N;
+    p.K = (int)w0->K;
+    if (p.type != DC_TYPE_Q4_K && p.type != DC_TYPE_Q6_K)
+        return dc_fail(ctx, DC_B200_UNSUPPORTED, "moe: expert weight type %d is not Q4_K/Q6_K", p.type);
+    if (pair && (w1->type != w0->type || w1->N != w0->N || w1->K != w0->K))
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "moe: gate and up tensors differ in type or shape");
+    p.act_q8 = act_q8;
+    p.act_rows = act_rows;
+    p.top_k = top_k;
+    p.n_active = rt->n_active;
+    p.uexp = rt->uexp;
+    p.uoff = rt->uoff;
+    p.uassign = rt->uassign;
+    p.out = out;
+    p.rpst = rows_per_stage_moe(p.type, p.K, p.row_bytes);
+    uint32_t stage = ((uint32_t)p.rpst * p.row_bytes + 32 + 127) & ~127u;
+    if (pair) {
+        p.up_off = stage;
+        stage *= 2;
+    }
+    p.stage_bytes = stage;
+    p.err = ctx->d_err;
+    const size_t act_bytes = (ActSmem::bytes(act_rows, p.K) + 127) & ~(size_t)127;
+    const size_t smem = DC_WARPS * DC_NSTAGE * 8 + act_bytes + (size_t)DC_WARPS * DC_NSTAGE * stage;
+    if (smem > 200 * 1024) return dc_fail(ctx, DC_B200_UNSUPPORTED, "moe: shared memory need %zu too large", smem);
+    const int grid = ctx->num_sms * (smem <= 100 * 1024 ? 2 : 1);
+    if (pair) {
+        if (T == 1) return launch_moe_mm<1, true>(ctx, p, grid, smem);
+        if (T <= 4) return launch_moe_mm<4, true>(ctx, p, grid, smem);
+        if (T <= 8) return launch_moe_mm<8, true>(ctx, p, grid, smem);
+        return launch_moe_mm<16, true>(ctx, p, grid, smem);
+    }
+    if (T == 1) return launch_moe_mm<1, false>(ctx, p, grid, smem);
+    if (T <= 4) return launch_moe_mm<4, false>(ctx, p, grid, smem);
+    if (T <= 8) return launch_moe_mm<8, false>(ctx, p, grid, smem);
+    return launch_moe_mm<16, false>(ctx, p, grid, smem);
+}
+
+int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_expert, int T, int top_k, float scale,
+                     int ep_lo, int ep_hi, const dc_moe_route* rt) {
+    // wr == nullptr: rt->logits already holds the router logits (routing only)
+    if (wr && wr->type != DC_TYPE_F32) return dc_fail(ctx, DC_B200_UNSUPPORTED, "router weight must be F32");
+    const int E = wr ? (int)wr->N : n_expert;
+    if (E < 1 || E > MOE_MAX_E || top_k < 1 || top_k > MOE_MAX_K || top_k > E || T < 1 || T > DC_MAX_T)
+        return dc_fail(ctx, DC_B200_UNSUPPORTED, "router: E=%d top_k=%d T=%d out of range", E, top_k, T);
+    RouterParams p = {};
+    p.wr = wr ? (const float*)wr->dev : nullptr;
+    p.xn = xn;
+    p.E = E;
+    p.H = wr ? (int)wr->K : 0;
+    p.T = T;
+    p.top_k = top_k;
+    p.scale = scale;
+    p.ep_lo = ep_lo;
+    p.ep_hi = ep_hi;
+    p.logits = rt->logits;
+    p.ids = rt->ids;
+    p.weights = rt->weights;
+    p.ticket = rt->ticket;
+    p.n_active = rt->n_active;
+    p.uexp = rt->uexp;
+    p.uoff = rt->uoff;
+    p.uassign = rt->uassign;
+    return dc_launch(ctx, "k_router", k_router, dim3(wr ? (p.E + 7) / 8 : 1), dim3(256), 0, p);
+}
+
+// ------------------------------------------------------------ combine
+// out[t][d] = sum over the token's assignments of w * down[assignment][d],
+// added one at a time into a zeroed accumulator.  Order: routing order when
+// T <= 4 and T*top_k <= 32 (cpu_backend_moe_ops.cpp:66,1247-1248,1578-1597),
+// otherwise ascending expert id (moe_routing.cpp:647-676).  Assignments whose
+// expert lives on another GPU are skipped (their share arrives by all-reduce).
+__global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ dn, const int32_t* __restrict__ ids,
+                                                     const float* __restrict__ weights, int T, int top_k, int H,
+                                                     int ep_lo, int ep_hi, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= H) return;
+    int order[MOE_MAX_K];
+    for (int k = 0; k < top_k; ++k) order[k] = k;
+    if (!(T <= 4 && T * top_k <= 32)) {
+        for (int i = 1; i < top_k; ++i) {
+            const int o = order[i], e = ids[t * top_k + o];
+            int j = i - 1;
+            while (j >= 0 && ids[t * top_k + order[j]] > e) {
+                order[j + 1] = order[j];
+                --j;
+            }
+            order[j + 1] = o;
+        }
+    }
+    float sum = 0.0f;
+    for (int k = 0; k < top_k; ++k) {
+        const int a = t * top_k + order[k], e = ids[a];
+        const float w = weights[a];
+        if (e < ep_lo || e >= ep_hi || w == 0.0f) continue;
+        sum = __fadd_rn(sum, __fmul_rn(w, dn[(size_t)a * H + d]));
+    }
+    out[(size_t)t * H + d] = sum;
+}
+
+int dc_launch_moe_combine(dc_ctx* ctx, const float* dn, const int32_t* ids, const float* weights, int T, int top_k,
+                          int H, int ep_lo, int ep_hi, float* out) {
+    return dc_launch(ctx, "k_moe_combine", k_moe_combine, dim3((H + 255) / 256, T), dim3(256), 0, dn, ids, weights, T,
+                     top_k, H, ep_lo, ep_hi, out);
+}

@@ -1,0 +1,279 @@
+// C-ABI entry points for single ops with host buffers: MUL_MAT_ID, paged
+// flash-decode attention, sampling and the speculative verify step.  Each call
+// stages its inputs in the context's scratch area, runs the same kernels the
+// decoder uses, and copies the result back.
+#include <string.h>
+
+#include <vector>
+
+#include "dc_common.cuh"
+#include "dc_internal.h"
+#include "dc_kv.h"
+
+#define DC_TRY(expr)                       \
+    do {                                   \
+        int _st = (expr);                  \
+        if (_st != DC_B200_OK) return _st; \
+    } while (0)
+
+namespace {
+struct Bump {
+    uint8_t* base;
+    size_t off = 0;
+    template <typename T>
+    T* take(size_t n) {
+        T* p = reinterpret_cast<T*>(base + off);
+        off += (n * sizeof(T) + 255) & ~(size_t)255;
+        return p;
+    }
+};
+int h2d(dc_ctx* ctx, void* d, const void* h, size_t n) {
+    return dc_check_cuda(ctx, cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, ctx->stream), "H2D");
+}
+int d2h(dc_ctx* ctx, void* h, const void* d, size_t n) {
+    return dc_check_cuda(ctx, cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, ctx->stream), "D2H");
+}
+}  // namespace
+
+size_t dc_moe_route_bind(dc_moe_route* rt, uint8_t* base, int T, int E, int top_k) {
+    Bump b{base};
+    rt->logits = b.take<float>((size_t)T * E);
+    rt->ids = b.take<int32_t>((size_t)T * top_k);
+    rt->weights = b.take<float>((size_t)T * top_k);
+    rt->ticket = b.take<int>(1);
+    rt->n_active = b.take<int>(1);
+    rt->uexp = b.take<int32_t>(E);
+    rt->uoff = b.take<int32_t>(E + 1);
+    rt->uassign = b.take<int32_t>((size_t)T * top_k);
+    return b.off;
+}
+
+extern "C" {
+
+int dc_b200_alloc_device(dc_ctx* ctx, size_t bytes, void** out_dev) {
+    if (!ctx || !out_dev) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(ctx->device);
+    return dc_check_cuda(ctx, cudaMalloc(out_dev, bytes), "alloc_device");
+}
+int dc_b200_free_device(dc_ctx* ctx, void* dev) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    return dc_check_cuda(ctx, cudaFree(dev), "free_device");
+}
+int dc_b200_copy_to_device(dc_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
+    if (!ctx || !dst_dev || !src_host) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(ctx->device);
+    DC_TRY(h2d(ctx, dst_dev, src_host, bytes));
+    return dc_check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "copy_to_device");
+}
+int dc_b200_copy_from_device(dc_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes) {
+    if (!ctx || !dst_host || !src_dev) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(ctx->device);
+    DC_TRY(d2h(ctx, dst_host, src_dev, bytes));
+    return dc_check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "copy_from_device");
+}
+
+int dc_b200_moe_route(dc_ctx* ctx, const float* logits_host, int T, int n_expert, int top_k, float routed_scale,
+                      int32_t* ids_out, float* weights_out) {
+    if (!ctx || !logits_host || !ids_out || !weights_out || T < 1 || T > DC_MAX_T)
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "moe_route: bad argument");
+    cudaSetDevice(ctx->device);
+    uint8_t* s = dc_scratch(ctx, 1 << 20);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
+    dc_moe_route rt;
+    dc_moe_route_bind(&rt, s, T, n_expert, top_k);
+    DC_TRY(dc_check_cuda(ctx, cudaMemsetAsync(rt.ticket, 0, sizeof(int), ctx->stream), "memset"));
+    DC_TRY(h2d(ctx, rt.logits, logits_host, (size_t)T * n_expert * 4));
+    DC_TRY(dc_launch_router(ctx, nullptr, nullptr, n_expert, T, top_k, routed_scale, 0, n_expert, &rt));
+    DC_TRY(d2h(ctx, ids_out, rt.ids, (size_t)T * top_k * 4));
+    DC_TRY(d2h(ctx, weights_out, rt.weights, (size_t)T * top_k * 4));
+    return dc_b200_synchronize(ctx);
+}
+
+int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
+                       const dc_weight* down, const float* x_host, int T, int top_k, float routed_scale,
+                       float* y_host, int32_t* ids_out, float* weights_out) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!router || !gate || !up || !down || !x_host || !y_host || T < 1 || T > DC_MAX_T)
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: bad argument (T=%d)", T);
+    const int H = (int)gate->K, F = (int)gate->N, E = (int)gate->E;
+    auto fail_closed = [&](int st) {
+        memset(y_host, 0, (size_t)T * H * sizeof(float));  // zero-fill on failure (moe/exec.cpp:397-414)
+        return st;
+    };
+    if (router->K != H || router->N != E || up->K != H || up->N != F || up->E != E || down->K != F || down->N != H ||
+        down->E != E)
+        return fail_closed(dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: tensor shapes do not agree"));
+    cudaSetDevice(ctx->device);
+    const int A = T * top_k;
+    const size_t need = (size_t)T * H * 4 * 3 + (size_t)T * (H / 256) * 292 + (size_t)A * F * 4 +
+                        (size_t)A * (F / 256) * 292 + (size_t)A * H * 4 + (1 << 20);
+    uint8_t* s = dc_scratch(ctx, need);
+    if (!s) return fail_closed(DC_B200_OUT_OF_MEMORY);
+    Bump b{s};
+    float* x = b.take<float>((size_t)T * H);
+    float* y = b.take<float>((size_t)T * H);
+    uint8_t* xq = b.take<uint8_t>((size_t)T * (H / 256) * 292);
+    float* h = b.take<float>((size_t)A * F);
+    uint8_t* hq = b.take<uint8_t>((size_t)A * (F / 256) * 292);
+    float* dn = b.take<float>((size_t)A * H);
+    dc_moe_route rt;
+    dc_moe_route_bind(&rt, s + b.off, T, E, top_k);
+    int st = dc_check_cuda(ctx, cudaMemsetAsync(rt.ticket, 0, sizeof(int), ctx->stream), "memset");
+    if (st == DC_B200_OK) st = h2d(ctx, x, x_host, (size_t)T * H * 4);
+    if (st == DC_B200_OK) st = dc_launch_router(ctx, router, x, E, T, top_k, routed_scale, 0, E, &rt);
+    if (st == DC_B200_OK) st = dc_launch_quantize_q8k(ctx, x, T, H, xq);
+    if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, true, gate, up, xq, T, T, top_k, &rt, h);
+    if (st == DC_B200_OK) st = dc_launch_quantize_q8k(ctx, h, A, F, hq);
+    if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, false, down, nullptr, hq, A, T, top_k, &rt, dn);
+    if (st == DC_B200_OK) st = dc_launch_moe_combine(ctx, dn, rt.ids, rt.weights, T, top_k, H, 0, E, y);
+    if (st == DC_B200_OK) st = d2h(ctx, y_host, y, (size_t)T * H * 4);
+    if (st == DC_B200_OK && ids_out) st = d2h(ctx, ids_out, rt.ids, (size_t)A * 4);
+    if (st == DC_B200_OK && weights_out) st = d2h(ctx, weights_out, rt.weights, (size_t)A * 4);
+    if (st == DC_B200_OK) st = dc_b200_synchronize(ctx);
+    return st == DC_B200_OK ? st : fail_closed(st);
+}
+
+int dc_b200_flash_attn_decode(dc_ctx* ctx, dc_kv_cache* kv, int layer, const float* q_host, const float* k_host,
+                              const float* v_host, const int32_t* seq_ids, const int32_t* positions, int T, int n_head,
+                              float scale, float* out_host) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!out_host || T < 1 || n_head < 1) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "flash_attn_decode: bad argument");
+    const size_t out_n = (size_t)T * n_head * 128;
+    auto fail_closed = [&](int st) {
+        memset(out_host, 0, out_n * sizeof(float));  // zero-fill on failure (paged_exec.cpp:358-412)
+        return st;
+    };
+    if (!kv || !q_host || !k_host || !v_host || !seq_ids || !positions || T > DC_MAX_T || layer < 0 ||
+        layer >= kv->n_layer)
+        return fail_closed(dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "flash_attn_decode: bad argument (T=%d layer=%d)", T, layer));
+    for (int t = 0; t < T; ++t) {
+        const int s = seq_ids[t];
+        if (s < 0 || s >= kv->max_seqs || !kv->seqs[s].used || positions[t] < 0)
+            return fail_closed(dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "flash_attn_decode: token %d has a bad sequence or position", t));
+    }
+    cudaSetDevice(ctx->device);
+    for (int t = 0; t < T; ++t) {
+        int st = dc_kv_seq_reserve(kv, seq_ids[t], positions[t] + 1);
+        if (st != DC_B200_OK) return fail_closed(st);
+        if (kv->seqs[seq_ids[t]].len < positions[t] + 1) kv->seqs[seq_ids[t]].len = positions[t] + 1;
+    }
+    const int n_kv = kv->n_kv, heads = n_head + 2 * n_kv, nsplit = 16;
+    const size_t att_bytes = dc_attention_scratch_bytes(T, n_head, n_kv, kv->max_blocks_per_seq, nsplit);
+    uint8_t* s = dc_scratch(ctx, (size_t)T * heads * 128 * 4 * 3 + att_bytes + (1 << 16));
+    if (!s) return fail_closed(DC_B200_OUT_OF_MEMORY);
+    Bump b{s};
+    float* qkv = b.take<float>((size_t)T * heads * 128);
+    float* q = b.take<float>((size_t)T * n_head * 128);
+    float* out = b.take<float>(out_n);
+    uint8_t* att_mem = b.take<uint8_t>(att_bytes);
+    dc_attn_scratch asc;
+    dc_attn_scratch_bind(&asc, att_mem, T, n_head, n_kv, kv->max_blocks_per_seq, nsplit);
+    int32_t* d_seq = b.take<int32_t>(T);
+    int32_t* d_pos = b.take<int32_t>(T);
+    std::vector<float> packed((size_t)T * heads * 128);
+    for (int t = 0; t < T; ++t) {
+        float* row = packed.data() + (size_t)t * heads * 128;
+        memcpy(row, q_host + (size_t)t * n_head * 128, (size_t)n_head * 128 * 4);
+        memcpy(row + (size_t)n_head * 128, k_host + (size_t)t * n_kv * 128, (size_t)n_kv * 128 * 4);
+        memcpy(row + (size_t)(n_head + n_kv) * 128, v_host + (size_t)t * n_kv * 128, (size_t)n_kv * 128 * 4);
+    }
+    int st = dc_check_cuda(ctx, cudaMemsetAsync(asc.tickets, 0, (size_t)T * n_kv * 4, ctx->stream), "memset");
+    if (st == DC_B200_OK) st = dc_check_cuda(ctx, cudaMemcpyAsync(qkv, packed.data(), packed.size() * 4, cudaMemcpyHostToDevice, ctx->stream), "H2D qkv");
+    if (st == DC_B200_OK) st = h2d(ctx, d_seq, seq_ids, (size_t)T * 4);
+    if (st == DC_B200_OK) st = h2d(ctx, d_pos, positions, (size_t)T * 4);
+    // pageable sources: make sure the copies are done before `packed` goes away
+    if (st == DC_B200_OK) st = dc_check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "sync");
+    __half* ka = kv->k_arena + kv->layer_elems * layer;
+    __half* va = kv->v_arena + kv->layer_elems * layer;
+    if (st == DC_B200_OK)
+        st = dc_launch_qknorm_rope_kv(ctx, qkv, nullptr, nullptr, nullptr, 0, d_pos, d_seq, kv->d_tables,
+                                      kv->max_blocks_per_seq, ka, va, n_head, n_kv, 0.0f, T, q);
+    if (st == DC_B200_OK)
+        st = dc_launch_attention(ctx, q, ka, va, kv->d_tables, kv->max_blocks_per_seq, d_seq, d_pos, T, n_head, n_kv,
+                                 scale, nsplit, &asc, out, nullptr);
+    if (st == DC_B200_OK) st = d2h(ctx, out_host, out, out_n * 4);
+    if (st == DC_B200_OK) st = dc_b200_synchronize(ctx);
+    return st == DC_B200_OK ? st : fail_closed(st);
+}
+
+int dc_b200_argmax(dc_ctx* ctx, const float* logits_host, int rows, int n, int32_t* out_ids) {
+    if (!ctx || !logits_host || !out_ids || rows < 1 || n < 1) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "argmax: bad argument");
+    cudaSetDevice(ctx->device);
+    uint8_t* s = dc_scratch(ctx, (size_t)rows * n * 4 + rows * 4 + 512);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
+    Bump b{s};
+    float* l = b.take<float>((size_t)rows * n);
+    int32_t* o = b.take<int32_t>(rows);
+    DC_TRY(h2d(ctx, l, logits_host, (size_t)rows * n * 4));
+    DC_TRY(dc_launch_argmax_rows(ctx, l, rows, n, o));
+    DC_TRY(d2h(ctx, out_ids, o, (size_t)rows * 4));
+    return dc_b200_synchronize(ctx);
+}
+
+int dc_b200_verify_uniforms(dc_ctx* ctx, uint64_t seed, uint32_t step, int n, float* out_host) {
+    if (!ctx || !out_host || n < 1 || n > 32) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "verify_uniforms: bad argument");
+    cudaSetDevice(ctx->device);
+    uint8_t* s = dc_scratch(ctx, 1024);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
+    DC_TRY(dc_launch_verify_uniforms(ctx, seed, step, n, (float*)s));
+    DC_TRY(d2h(ctx, out_host, s, (size_t)n * 4));
+    return dc_b200_synchronize(ctx);
+}
+
+int dc_b200_softmax(dc_ctx* ctx, const float* logits_host, int rows, int n, float temperature, float* probs_host) {
+    if (!ctx || !logits_host || !probs_host || rows < 1 || n < 1 || !(temperature > 0.0f))
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "softmax: bad argument");
+    cudaSetDevice(ctx->device);
+    uint8_t* s = dc_scratch(ctx, (size_t)rows * n * 8 + 512);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
+    Bump b{s};
+    float* l = b.take<float>((size_t)rows * n);
+    float* p = b.take<float>((size_t)rows * n);
+    DC_TRY(h2d(ctx, l, logits_host, (size_t)rows * n * 4));
+    DC_TRY(dc_launch_det_softmax(ctx, l, rows, n, temperature, p));
+    DC_TRY(d2h(ctx, probs_host, p, (size_t)rows * n * 4));
+    return dc_b200_synchronize(ctx);
+}
+
+int dc_b200_verify_accept(dc_ctx* ctx, const float* target_logits_host, const int32_t* draft_tokens,
+                          const float* draft_probs_host, const float* uniforms, uint64_t seed, uint32_t step,
+                          int gamma, int vocab, int mode, float temperature, int32_t* n_accepted,
+                          int32_t* next_token) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!target_logits_host || !draft_tokens || !n_accepted || !next_token || gamma < 1 || gamma > 16 || vocab < 2 ||
+        (mode != 0 && mode != 1) || (mode == 1 && !draft_probs_host))
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "verify_accept: bad argument");
+    for (int i = 0; i < gamma; ++i)
+        if (draft_tokens[i] < 0 || draft_tokens[i] >= vocab)
+            return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "verify_accept: draft token %d out of range", i);
+    cudaSetDevice(ctx->device);
+    const size_t row = (size_t)vocab * 4;
+    uint8_t* s = dc_scratch(ctx, row * (gamma + 1) * 2 + row * gamma + 4096);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
+    Bump b{s};
+    float* tl = b.take<float>((size_t)(gamma + 1) * vocab);
+    float* probs = b.take<float>((size_t)(gamma + 1) * vocab);
+    float* dp = b.take<float>((size_t)gamma * vocab);
+    int32_t* dt = b.take<int32_t>(gamma);
+    float* u = b.take<float>(gamma + 1);
+    int32_t* am = b.take<int32_t>(gamma + 1);
+    int32_t* res = b.take<int32_t>(2);
+    DC_TRY(h2d(ctx, tl, target_logits_host, row * (gamma + 1)));
+    DC_TRY(h2d(ctx, dt, draft_tokens, (size_t)gamma * 4));
+    if (mode == 1) {
+        DC_TRY(h2d(ctx, dp, draft_probs_host, row * gamma));
+        if (uniforms) DC_TRY(h2d(ctx, u, uniforms, (size_t)(gamma + 1) * 4));
+        else DC_TRY(dc_launch_verify_uniforms(ctx, seed, step, gamma + 1, u));
+    }
+    DC_TRY(dc_launch_verify(ctx, mode, gamma, vocab, tl, dt, dp, u, temperature, am, probs, res));
+    int32_t out[2] = {0, 0};
+    DC_TRY(d2h(ctx, out, res, 8));
+    DC_TRY(dc_b200_synchronize(ctx));
+    *n_accepted = out[0];
+    *next_token = out[1];
+    return DC_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,175 @@
+"""Decoder-level host mirror: model configs of the benchmark and the Model class
+over dc_b200_model_* (the chained ops of one Qwen3-style decoder step)."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, asdict
+
+import numpy as np
+
+from . import _lib
+from .blocks import GGML_TYPE_F32, GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, row_bytes
+from .ops import Context, _vp
+
+
+@dataclass
+class Config:
+    n_layer: int
+    hidden: int
+    n_head: int
+    n_kv_head: int
+    vocab: int
+    head_dim: int = 128
+    ffn: int = 0
+    n_expert: int = 0
+    n_expert_used: int = 0
+    expert_ffn: int = 0
+    rms_eps: float = 1e-6
+    rope_theta: float = 1e6
+    routed_scale: float = 1.0
+    tie_embeddings: bool = False
+    qk_norm: bool = True
+    max_seqs: int = 4
+    max_ctx: int = 2560
+    ep_rank: int = 0
+    ep_size: int = 1
+
+    def to_c(self) -> _lib.ModelConfig:
+        d = asdict(self)
+        c = _lib.ModelConfig()
+        for k, v in d.items():
+            setattr(c, k, int(v) if isinstance(v, bool) else v)
+        return c
+
+
+def dense_0p8b(**kw) -> Config:
+    """Dense 0.8B-class Qwen3-style decoder: 28 layers, hidden 1024, FFN 3072, 16 Q / 8 KV heads, tied embeddings."""
+    return Config(n_layer=28, hidden=1024, n_head=16, n_kv_head=8, vocab=151936, ffn=3072, tie_embeddings=True, **kw)
+
+
+def moe_35b_a3b(**kw) -> Config:
+    """35B-A3B-class MoE decoder: 48 layers, hidden 2048, 32 Q / 4 KV heads, 128 experts top-8 x 768, untied lm_head."""
+    return Config(n_layer=48, hidden=2048, n_head=32, n_kv_head=4, vocab=151936, n_expert=128, n_expert_used=8,
+                  expert_ffn=768, tie_embeddings=False, **kw)
+
+
+def fnv1a64(name: str) -> int:
+    h = 1469598103934665603
+    for b in name.encode():
+        h ^= b
+        h = (h * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return h
+
+
+def tensor_seed(seed: int, name: str) -> int:
+    """Seed init_synthetic uses for one tensor: model seed + FNV-1a(name), mod 2^64."""
+    return (seed + fnv1a64(name)) & 0xFFFFFFFFFFFFFFFF
+
+
+class Model:
+    def __init__(self, ctx: Context, cfg: Config):
+        self.ctx, self.cfg = ctx, cfg
+        self.handle = None
+        h = C.c_void_p()
+        cc = cfg.to_c()
+        ctx._check(_lib.lib().dc_b200_model_create(ctx.handle, C.byref(cc), C.byref(h)))
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            _lib.lib().dc_b200_model_destroy(self.handle)
+            self.handle = None
+
+    def _check(self, st):
+        self.ctx._check(st)
+
+    def set_option(self, name: str, value: int):
+        self._check(_lib.lib().dc_b200_model_set_option(self.handle, name.encode(), int(value)))
+
+    def set_tensor(self, name: str, ggml_type: int, data: np.ndarray, K: int, N: int = 1, E: int = 1):
+        data = np.ascontiguousarray(data)
+        ne = (C.c_int64 * 4)(K, N, E, 1)
+        self._check(_lib.lib().dc_b200_model_set_tensor(self.handle, name.encode(), ggml_type, ne, _vp(data)))
+
+    def init_synthetic(self, seed: int, sigma: float = 0.02):
+        self._check(_lib.lib().dc_b200_model_init_synthetic(self.handle, seed, sigma))
+
+    def get_tensor_info(self, name: str):
+        t = C.c_int(0)
+        ne = (C.c_int64 * 4)()
+        dev = C.c_void_p()
+        nb = C.c_size_t(0)
+        self._check(_lib.lib().dc_b200_model_get_tensor(self.handle, name.encode(), C.byref(t), ne, C.byref(dev),
+                                                        C.byref(nb)))
+        return t.value, tuple(ne), dev.value, nb.value
+
+    def get_tensor(self, name: str):
+        """Downloads a tensor's bytes: (ggml_type, (K, N, E), uint8 array or f32 array)."""
+        t, ne, dev, nb = self.get_tensor_info(name)
+        out = np.zeros(nb, dtype=np.uint8)
+        self.ctx.from_device(dev, out)
+        if t == GGML_TYPE_F32:
+            out = out.view(np.float32)
+        return t, ne[:3], out
+
+    def ep_init(self, unique_id: bytes, nccl_path: str | None = None):
+        buf = (C.c_char * 128).from_buffer_copy(unique_id)
+        self._check(_lib.lib().dc_b200_model_ep_init(self.handle, nccl_path.encode() if nccl_path else None, buf))
+
+    def finalize(self):
+        self._check(_lib.lib().dc_b200_model_finalize(self.handle))
+
+    def weight_bytes(self) -> int:
+        return int(_lib.lib().dc_b200_model_weight_bytes(self.handle))
+
+    def seq_alloc(self) -> int:
+        s = C.c_int(-1)
+        self._check(_lib.lib().dc_b200_seq_alloc(self.handle, C.byref(s)))
+        return s.value
+
+    def seq_free(self, seq: int):
+        self._check(_lib.lib().dc_b200_seq_free(self.handle, seq))
+
+    def seq_len(self, seq: int) -> int:
+        return _lib.lib().dc_b200_seq_len(self.handle, seq)
+
+    def seq_truncate(self, seq: int, new_len: int):
+        self._check(_lib.lib().dc_b200_seq_truncate(self.handle, seq, new_len))
+
+    def prefill(self, seq: int, tokens, want_logits: bool = False):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        logits = np.empty(self.cfg.vocab, dtype=np.float32) if want_logits else None
+        nxt = C.c_int(0)
+        self._check(_lib.lib().dc_b200_prefill(self.handle, seq, _vp(tokens), tokens.size, _vp(logits), C.byref(nxt)))
+        return (nxt.value, logits) if want_logits else nxt.value
+
+    def decode_step(self, seqs, tokens, want_logits: bool = False):
+        seqs = np.ascontiguousarray(seqs, dtype=np.int32)
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.zeros(seqs.size, dtype=np.int32)
+        logits = np.empty((seqs.size, self.cfg.vocab), dtype=np.float32) if want_logits else None
+        self._check(_lib.lib().dc_b200_decode_step(self.handle, _vp(seqs), seqs.size, _vp(tokens), _vp(out), _vp(logits)))
+        return (out, logits) if want_logits else out
+
+    def decode_run(self, seqs, first_tokens, n_steps: int):
+        """Device-resident greedy loop.  Returns (tokens [n_steps, n_seq], device milliseconds)."""
+        seqs = np.ascontiguousarray(seqs, dtype=np.int32)
+        first = np.ascontiguousarray(first_tokens, dtype=np.int32)
+        out = np.zeros((n_steps, seqs.size), dtype=np.int32)
+        ms = C.c_float(0.0)
+        self._check(_lib.lib().dc_b200_decode_run(self.handle, _vp(seqs), seqs.size, _vp(first), n_steps, _vp(out),
+                                                  C.byref(ms)))
+        return out, ms.value
+
+    def forward_chunk(self, seq: int, tokens, want_logits: bool = True):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        logits = np.empty((tokens.size, self.cfg.vocab), dtype=np.float32) if want_logits else None
+        self._check(_lib.lib().dc_b200_forward_chunk(self.handle, seq, _vp(tokens), tokens.size, _vp(logits)))
+        return logits
+
+    def step_stats(self):
+        k = C.c_int(0)
+        wb = C.c_double(0.0)
+        kv = C.c_double(0.0)
+        self._check(_lib.lib().dc_b200_model_step_stats(self.handle, C.byref(k), C.byref(wb), C.byref(kv)))
+        return k.value, wb.value, kv.value

@@ -101,6 +101,154 @@ DC_B200_API int dc_b200_mul_mat_dev(dc_ctx* ctx, const dc_weight* w, const float
 DC_B200_API int dc_b200_mul_mat_block_sums(dc_ctx* ctx, const dc_weight* w, const float* x_host, int M,
                                            int32_t* I_host, int32_t* Mn_host);
 
+/* ---- device buffers ------------------------------------------------------ */
+/* AllocateDevice / FreeDevice / CopyToDevice / CopyFromDevice of the HAL
+ * ComputeBackend contract (core/include/densecore/hal/compute_backend.h:308-692). */
+DC_B200_API int dc_b200_alloc_device(dc_ctx* ctx, size_t bytes, void** out_dev);
+DC_B200_API int dc_b200_free_device(dc_ctx* ctx, void* dev);
+DC_B200_API int dc_b200_copy_to_device(dc_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+DC_B200_API int dc_b200_copy_from_device(dc_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+
+/* ---- MUL_MAT_ID: one MoE FFN layer ---------------------------------------- */
+/* cb_moe_forward (core/src/llm/moe/exec.cpp:813): router logits = x * Wr^T,
+ * top-k routing, per-expert SwiGLU FFN, weighted combine.  router: F32
+ * [hidden, n_expert]; gate/up: [hidden, ffn, n_expert]; down: [ffn, hidden,
+ * n_expert].  x: [T, hidden] f32, T <= 16.  y: [T, hidden].  ids_out [T, top_k]
+ * and weights_out [T, top_k] may be NULL.  routed_scale multiplies the routing
+ * weights (moe_routed_scaling_factor, core/src/llm/moe/exec.cpp:764-768). */
+DC_B200_API int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
+                                   const dc_weight* down, const float* x_host, int T, int top_k, float routed_scale,
+                                   float* y_host, int32_t* ids_out, float* weights_out);
+/* Routing alone from given logits [T, n_expert] (RouteMoESoftmaxTopK,
+ * core/src/llm/moe/exec.cpp:734; stable comparator of core/src/llm/moe/native.cpp:610-676). */
+DC_B200_API int dc_b200_moe_route(dc_ctx* ctx, const float* logits_host, int T, int n_expert, int top_k,
+                                  float routed_scale, int32_t* ids_out, float* weights_out);
+
+/* ---- paged KV cache + FLASH_ATTN (decode) ---------------------------------- */
+typedef struct dc_kv_cache dc_kv_cache;
+/* PagedKVCache: 16-token blocks, F16, arena [layer][block][slot][kv_head][head_dim]
+ * (core/include/densecore/memory/kv_cache.h:50,245-395,
+ * core/src/runtime/memory/kv_cache_storage.cpp:146-200). */
+DC_B200_API int dc_b200_kv_create(dc_ctx* ctx, int n_layer, int n_kv_head, int head_dim, int max_blocks, int max_seqs,
+                                  int max_blocks_per_seq, dc_kv_cache** out);
+DC_B200_API void dc_b200_kv_destroy(dc_kv_cache* kv);
+/* Sequence slots and their block tables (SequenceBlockTable / BlockManager,
+ * kv_cache.h:67-87,92-220).  kv_seq_reserve makes sure blocks exist for
+ * positions [0, n_tokens). */
+DC_B200_API int dc_b200_kv_seq_alloc(dc_kv_cache* kv, int* out_seq);
+DC_B200_API int dc_b200_kv_seq_free(dc_kv_cache* kv, int seq);
+DC_B200_API int dc_b200_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens);
+DC_B200_API int dc_b200_kv_block_table(dc_kv_cache* kv, int seq, int32_t* out_blocks, int capacity, int* out_n);
+DC_B200_API int dc_b200_kv_free_blocks(dc_kv_cache* kv);
+/* cb_paged_attention_decode (core/src/llm/attention/paged_exec.cpp:343): writes
+ * the T current tokens' K/V (f32 [T, n_kv, hd]) into the cache at positions[t]
+ * of sequence seq_ids[t], then attends q [T, n_head, hd] over keys
+ * 0..positions[t].  out: [T, n_head, hd] f32.  scale multiplies q.k. */
+DC_B200_API int dc_b200_flash_attn_decode(dc_ctx* ctx, dc_kv_cache* kv, int layer, const float* q_host,
+                                          const float* k_host, const float* v_host, const int32_t* seq_ids,
+                                          const int32_t* positions, int T, int n_head, float scale, float* out_host);
+/* Raw fp16 contents of one block of one layer (K then V planes), for tests. */
+DC_B200_API int dc_b200_kv_read_block(dc_kv_cache* kv, int layer, int block, void* k_host, void* v_host);
+
+/* ---- sampling / speculative verify ----------------------------------------- */
+/* Greedy pick, first maximum wins (ArgmaxScalar, core/src/sampler/sampler.cpp:42-57). */
+DC_B200_API int dc_b200_argmax(dc_ctx* ctx, const float* logits_host, int rows, int n, int32_t* out_ids);
+/* Verify a draft chain of gamma tokens against target logits [gamma+1, vocab].
+ * mode 0: greedy prefix match.  mode 1: accept t_i iff u_i*q_i[t_i] < p_i[t_i]
+ * with p = softmax(target/temperature); on the first rejection resample from
+ * max(0, p-q), else sample the bonus token from p_gamma.  draft_probs
+ * [gamma, vocab] (mode 1).  uniforms [gamma+1] or NULL to draw them from
+ * Philox4x32-10 keyed by (seed, step).  DenseCore has no such step (its draft
+ * model is loaded and unused, core/src/runtime/engine.cpp:593-645). */
+DC_B200_API int dc_b200_verify_accept(dc_ctx* ctx, const float* target_logits_host, const int32_t* draft_tokens,
+                                      const float* draft_probs_host, const float* uniforms, uint64_t seed,
+                                      uint32_t step, int gamma, int vocab, int mode, float temperature,
+                                      int32_t* n_accepted, int32_t* next_token);
+DC_B200_API int dc_b200_verify_uniforms(dc_ctx* ctx, uint64_t seed, uint32_t step, int n, float* out_host);
+DC_B200_API int dc_b200_softmax(dc_ctx* ctx, const float* logits_host, int rows, int n, float temperature,
+                                float* probs_host);
+
+/* ---- decoder: the ops above chained into one model step --------------------- */
+/* The graph BuildTransformerGraph lays out for a Qwen3-style decoder
+ * (core/src/llm/graph/decoder.cpp:1085-1100 QKV, :1265-1343 Q/K norm, :1422-1450
+ * RoPE, :1846-1872 attention, :2217-2410 MoE, :2662-2730 FFN, :2997 lm_head),
+ * captured as a CUDA graph per batch shape. */
+typedef struct dc_model dc_model;
+typedef struct dc_model_config {
+    int n_layer, hidden, n_head, n_kv_head, head_dim, vocab;
+    int ffn;             /* dense FFN width (0 for MoE layers) */
+    int n_expert;        /* 0 = dense model */
+    int n_expert_used;   /* top-k */
+    int expert_ffn;
+    float rms_eps, rope_theta;
+    float routed_scale;  /* 1.0 unless the model says otherwise */
+    int tie_embeddings;  /* lm_head = token_embd */
+    int qk_norm;         /* per-head RMSNorm on Q and K */
+    int max_seqs, max_ctx;
+    int ep_rank, ep_size; /* expert-parallel shard of this process (0,1 = all experts) */
+} dc_model_config;
+
+DC_B200_API int dc_b200_model_create(dc_ctx* ctx, const dc_model_config* cfg, dc_model** out);
+DC_B200_API void dc_b200_model_destroy(dc_model* m);
+/* GGUF tensor by name ("token_embd.weight", "blk.3.attn_q.weight",
+ * "blk.3.ffn_gate_exps.weight", ...), bytes copied verbatim
+ * (LoadGGUFModel, core/src/models/model_loader.cpp:2037). */
+DC_B200_API int dc_b200_model_set_tensor(dc_model* m, const char* name, int ggml_type, const int64_t ne[4],
+                                         const void* data_host);
+/* Fills every tensor on the device from a seeded counter-based generator and
+ * this library's own Q4_K / Q6_K quantiser (Q4_K_M-style type mix: attn_v,
+ * even-layer ffn_down and the output matrix Q6_K, the rest Q4_K, norms and
+ * router F32).  sigma is the weight standard deviation. */
+DC_B200_API int dc_b200_model_init_synthetic(dc_model* m, uint64_t seed, float sigma);
+/* Looks a tensor up: type, shape, device address, bytes. */
+DC_B200_API int dc_b200_model_get_tensor(dc_model* m, const char* name, int* ggml_type, int64_t ne[4], void** dev,
+                                         size_t* bytes);
+DC_B200_API int dc_b200_model_finalize(dc_model* m);
+DC_B200_API size_t dc_b200_model_weight_bytes(dc_model* m);
+/* Sequences (KV slots). */
+DC_B200_API int dc_b200_seq_alloc(dc_model* m, int* out_seq);
+DC_B200_API int dc_b200_seq_free(dc_model* m, int seq);
+DC_B200_API int dc_b200_seq_len(dc_model* m, int seq);
+DC_B200_API int dc_b200_seq_truncate(dc_model* m, int seq, int new_len);
+/* Runs n tokens of one sequence through the model in chunks of <= 16 and
+ * appends them to its KV cache.  logits_host (NULL or [vocab]) receives the
+ * logits of the last token; next_token its greedy pick. */
+DC_B200_API int dc_b200_prefill(dc_model* m, int seq, const int32_t* tokens_host, int n, float* logits_host,
+                                int32_t* next_token);
+/* One decode step for n_seq sequences: token i is appended to sequence seqs[i].
+ * Inputs come from host memory and the picks go back to host memory inside the
+ * call.  logits_host: NULL or [n_seq, vocab]. */
+DC_B200_API int dc_b200_decode_step(dc_model* m, const int32_t* seqs, int n_seq, const int32_t* tokens_host,
+                                    int32_t* next_tokens_host, float* logits_host);
+/* n_steps greedy decode steps with the tokens fed back on the device; picks
+ * [n_steps, n_seq] are copied to the host once at the end.  ms_out (optional)
+ * receives the device time of the steps, measured with events on the stream. */
+DC_B200_API int dc_b200_decode_run(dc_model* m, const int32_t* seqs, int n_seq, const int32_t* first_tokens_host,
+                                   int n_steps, int32_t* out_tokens_host, float* ms_out);
+/* Forward over a chunk of n <= 16 tokens of one sequence with logits for every
+ * token ([n, vocab], device-resident; copied to logits_host if not NULL): the
+ * batched target forward of a speculative verify step. */
+DC_B200_API int dc_b200_forward_chunk(dc_model* m, int seq, const int32_t* tokens_host, int n, float* logits_host);
+DC_B200_API void* dc_b200_model_logits_dev(dc_model* m);
+/* Per-step counters of the last decode_run / decode_step: kernels launched per
+ * step, bytes of weights and KV a step must read (algorithmic). */
+DC_B200_API int dc_b200_model_step_stats(dc_model* m, int* kernels_per_step, double* weight_bytes_per_step,
+                                         double* kv_bytes_per_token_ctx);
+
+/* "graphs" 0/1: replay each step shape as a CUDA graph (default 1). */
+DC_B200_API int dc_b200_model_set_option(dc_model* m, const char* name, int value);
+
+/* ---- expert parallelism over the GPUs of one node ---------------------------- */
+/* One process per GPU.  Experts are split into contiguous ranges (rank r owns
+ * experts [r*E/G, (r+1)*E/G)); everything else is replicated; the partial MoE
+ * outputs are summed with one NCCL all-reduce per layer.  DenseCore's nearest
+ * analogue is NUMA-sticky expert placement (core/src/llm/moe/native.cpp:1196,
+ * :1506-1567).  Rank 0 makes the 128-byte id, the launcher hands it to every
+ * rank, each rank calls model_ep_init before model_finalize.  nccl_path: path
+ * of libnccl.so.2, or NULL to use the loader's search path. */
+DC_B200_API int dc_b200_ep_unique_id(dc_ctx* ctx, const char* nccl_path, void* id_out_128);
+DC_B200_API int dc_b200_model_ep_init(dc_model* m, const char* nccl_path, const void* id_128);
+
 #ifdef __cplusplus
 }
 #endif
