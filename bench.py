@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the 35B-A3B-class Q4_K_M MoE decoder (48 layers, hidden 2048,
+32 Q / 4 KV heads x 128, 128 experts top-8 x 768, vocab 151936, untied lm_head),
+seeded synthetic weights generated and quantised on the device, a 2048-token
+random-id prompt per stream prefilled into the paged fp16 KV cache (untimed
+set-up), then greedy decode.  A "step" is one decode step (one new token per
+stream).  `value` = output tokens per second at 1 stream with inputs resident in
+HBM (device-side token feedback, CUDA-graph replays, device time from CUDA
+events on the launching stream).  `e2e` = the same metric through
+dc_b200_decode_step with host buffers: every step copies the token ids host ->
+device and the picked ids device -> host.  4-stream numbers ride along in
+`streams4`.
+
+N > 1: expert parallel (experts sharded in contiguous ranges, everything else
+replicated, one NCCL all-reduce per MoE layer); every rank decodes the same
+streams, so the whole job's tokens/s is streams x steps / max-over-ranks time
+and scaling is "strong".
+
+--impl reference: the CPU restatement of DenseCore's ggml path (oracle/) timed on
+the host cores with all threads, on a bounded sample of the same step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s (1 & 4 streams), 35B-A3B-class Q4_K_M; % HBM roofline"
+UNIT = "tok/s"
+PROMPT = 2048
+SAMPLE_LAYERS = 2          # layers of the model the CPU baseline times per sample
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------ CPU baseline
+def cpu_sample_setup(layers: int, ctx_len: int, seed: int = 1):
+    """Random-byte weights with the model's shapes for `layers` layers plus the lm_head, and a
+    random fp16 KV cache of ctx_len tokens: values do not matter for timing."""
+    from densecore_b200 import blocks as B
+    rng = np.random.default_rng(seed)
+    H, QD, KD, E, F, V = 2048, 4096, 512, 128, 768, 151936
+
+    def rnd(t, n, k):
+        out = rng.integers(0, 256, size=n * B.row_bytes(t, k), dtype=np.uint8)
+        bb = B.BLOCK_BYTES[t]
+        blk = out.reshape(-1, bb)
+        if t == B.GGML_TYPE_Q4_K:
+            blk[:, 0:4] = np.array([0x00, 0x1E, 0x00, 0x1E], np.uint8)   # d, dmin = fp16 ~0.006
+        else:
+            blk[:, 208:210] = np.array([0x00, 0x1E], np.uint8)
+        return out
+    L = []
+    for il in range(layers):
+        L.append(dict(q=rnd(12, QD, H), k=rnd(12, KD, H), v=rnd(14, KD, H), o=rnd(12, H, QD),
+                      router=(rng.normal(size=(E, H)) * 0.02).astype(np.float32),
+                      gate=rnd(12, E * F, H), up=rnd(12, E * F, H), down=rnd(14 if il % 2 == 0 else 12, E * H, F),
+                      down_t=14 if il % 2 == 0 else 12))
+    blocks = (ctx_len + 15) // 16
+    kv = (rng.integers(0, 0x3C00, size=(blocks * 16, 4, 128), dtype=np.uint16),
+          rng.integers(0, 0x3C00, size=(blocks * 16, 4, 128), dtype=np.uint16))
+    return dict(layers=L, lm_head=rnd(14, V, H), kv=kv, table=np.arange(blocks, dtype=np.int32), ctx=ctx_len)
+
+
+def cpu_sample_run(o, S, n_streams: int, rng) -> float:
+    """One decode step of `len(S['layers'])` layers + lm_head through the CPU path's matmul, attention, router
+    and MoE calls (norms, RoPE and residual adds are left out: they are negligible).  Returns seconds."""
+    H, QD, KD, E, F, V = 2048, 4096, 512, 128, 768, 151936
+    x = rng.normal(size=(n_streams, H)).astype(np.float32)
+    scale = float(1 / np.sqrt(128.0))
+    t0 = time.perf_counter()
+    for Ly in S["layers"]:
+        q = o.mul_mat(12, Ly["q"], QD, H, x)
+        o.mul_mat(12, Ly["k"], KD, H, x)
+        o.mul_mat(14, Ly["v"], KD, H, x)
+        att = np.stack([o.paged_attention(q[s].reshape(32, 128), S["kv"][0], S["kv"][1], S["table"], S["ctx"] - 1, 32, 4,
+                                          128, scale, "blockwise").reshape(-1) for s in range(n_streams)])
+        o.mul_mat(12, Ly["o"], H, QD, att)
+        lg = o.mul_mat(0, Ly["router"], E, H, x)
+        ids, w = o.route(lg, 8, mode="stable")
+        x = o.moe_forward((12, 12, Ly["down_t"]), Ly["gate"], Ly["up"], Ly["down"], E, H, F, x, ids, w, fast_exp=True)
+    t_layers = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    o.mul_mat(14, S["lm_head"], V, H, x)
+    t_head = time.perf_counter() - t0
+    return t_layers, t_head
+
+
+def cpu_tok_s(o, S, n_streams, reps, rng):
+    tl, th = [], []
+    for _ in range(reps):
+        a, b = cpu_sample_run(o, S, n_streams, rng)
+        tl.append(a)
+        th.append(b)
+    per_token_step = float(np.median(tl)) / len(S["layers"]) * 48 + float(np.median(th))
+    return n_streams / per_token_step, per_token_step
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from oracle import oracle as o
+    o.build()
+    threads = o.max_threads()
+    o.set_threads(threads)
+    rng = np.random.default_rng(0)
+    S = cpu_sample_setup(SAMPLE_LAYERS, PROMPT + 128)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_sample_run(o, S, 1, rng)
+    per = []
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        tl, th = cpu_sample_run(o, S, 1, rng)
+        per.append(tl / SAMPLE_LAYERS * 48 + th)
+    step_s = float(np.median(per))
+    value = 1.0 / step_s
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 x int4/int6 block dots, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "moe35b_a3b_q4km decode, batch 1, ctx 2176", "streams": 1, "prompt_tokens": PROMPT},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{SAMPLE_LAYERS} of 48 layers (QKV/O matmuls, paged attention at ctx 2176, router, "
+                                   f"MoE FFN) + lm_head per step, scaled to 48 layers; CPU restatement of DenseCore's "
+                                   f"ggml path"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t_all,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# -------------------------------------------------------------- our arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=48, help="debug: fewer layers (the result is then not the benchmark)")
+    ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-classes", action="store_true", help="print the per-kernel-class table to stderr")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    import torch
+    import densecore_b200 as dc
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo", rank=rank, world_size=world)   # control plane only; data plane is NCCL in the library
+    torch.cuda.set_device(local_rank)
+    ctx = dc.Context(local_rank)
+    cfg = dc.moe_35b_a3b(max_seqs=4, max_ctx=args.prompt + 512, ep_rank=rank, ep_size=world)
+    cfg.n_layer = args.layers
+    model = dc.Model(ctx, cfg)
+    model.init_synthetic(1234, 0.02)
+    if world > 1:
+        import ctypes as C
+        import nvidia.nccl
+        nccl_path = os.path.join(list(nvidia.nccl.__path__)[0], "lib", "libnccl.so.2")
+        buf = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            raw = (C.c_char * 128)()
+            ctx._check(dc._lib.lib().dc_b200_ep_unique_id(ctx.handle, nccl_path.encode(), raw))
+            buf = torch.frombuffer(bytearray(raw.raw), dtype=torch.uint8).clone()
+        dist.broadcast(buf, 0)
+        model.ep_init(bytes(buf.numpy().tobytes()), nccl_path)
+    model.finalize()
+
+    rng = np.random.default_rng(0)
+    seqs = [model.seq_alloc() for _ in range(4)]
+    first = [model.prefill(s, rng.integers(0, cfg.vocab, size=args.prompt)) for s in seqs]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    results = {}
+    clocks = None
+    for n_streams in (1, 4):
+        sq = seqs[:n_streams]
+        toks, _ = model.decode_run(sq, first[:n_streams], args.warmup)        # warm-up: eager pass, capture, replays
+        sampler = ClockSampler(local_rank) if (n_streams == 1 and rank == 0) else None
+        if sampler:
+            sampler.start()
+        barrier()
+        t0 = time.perf_counter()
+        toks, ms = model.decode_run(sq, toks[-1], args.steps)                 # K steps, device time from CUDA events
+        barrier()
+        wall = time.perf_counter() - t0
+        if sampler:
+            clocks = sampler.stop()
+        ms = max_over_ranks(ms)
+        # end to end: host buffers every step
+        last = toks[-1]
+        for _ in range(args.warmup):
+            last = model.decode_step(sq, last)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            last = model.decode_step(sq, last)
+        barrier()
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        results[n_streams] = dict(ms=ms, wall=wall, e2e_s=e2e_s, ctx=model.seq_len(sq[0]), last=last)
+
+    launches_per_step, weight_bytes, kv_bytes_per_tok = model.step_stats()
+    peak_gbs, peak_kind = measured_peaks()
+    # per-kernel-class device time of one eager step (CUDA events around every launch on the launching stream)
+    prof = model.profile_step(seqs[:1], results[1]["last"][:1])
+    prof = model.profile_step(seqs[:1], results[1]["last"][:1])
+    dom = max(prof.items(), key=lambda kv: kv[1][0])
+    dom_name, (dom_ms, dom_n, dom_bytes) = dom
+    if args.profile_classes and rank == 0:
+        tot = sum(v[0] for v in prof.values())
+        for k, (ms_, n_, b_) in sorted(prof.items(), key=lambda kv: -kv[1][0]):
+            print(f"{k:22s} launches {n_:4d}  {ms_ * 1e3:9.1f} us  {ms_ / tot * 100:5.1f} %  "
+                  f"{b_ / n_ / 1e6:8.2f} MB/launch  {b_ / (ms_ * 1e-3) / 1e9 if ms_ else 0:8.1f} GB/s", file=sys.stderr)
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
+
+    r1, r4 = results[1], results[4]
+    ms_per_step = r1["ms"] / args.steps
+    value = 1 * args.steps / (r1["ms"] * 1e-3)
+    step_bytes = weight_bytes + kv_bytes_per_tok * (r1["ctx"] - args.steps // 2)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 x int4/int6 block dots (dp4a), f32 accumulate", "data": "synthetic",
+        "config": {"workload": "moe35b_a3b_q4km decode: 48 layers, hidden 2048, 128 experts top-8, vocab 151936; "
+                               "2048-token random prompt per stream, greedy, paged fp16 KV",
+                   "streams": 1, "layers": args.layers, "prompt_tokens": args.prompt, "ctx_at_timing": r1["ctx"],
+                   "parallelism": f"ep{world}",
+                   "l2": "each step reads ~1.9 GB of weights, far more than the 126 MB L2, so no flush is needed"},
+        "hbm_fraction_of_step": step_bytes / (ms_per_step * 1e-3) / 1e9 / (peak_gbs * world),
+        "streams4": {"value": 4 * args.steps / (r4["ms"] * 1e-3), "ms_per_step": r4["ms"] / args.steps,
+                     "e2e": 4 * args.steps / r4["e2e_s"], "ctx_at_timing": r4["ctx"]},
+        "e2e": {"value": args.steps / r1["e2e_s"], "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4,
+                "api": "dc_b200_decode_step"},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                     "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "launches_per_step": dom_n, "bytes_per_launch": dom_bytes / dom_n,
+                     "us_per_launch": dom_ms * 1e3 / dom_n},
+    }
+    if rank == 0 and not args.no_cpu_baseline:
+        from oracle import oracle as o
+        o.build()
+        threads = o.max_threads()
+        o.set_threads(threads)
+        S = cpu_sample_setup(SAMPLE_LAYERS, r1["ctx"])
+        cpu_sample_run(o, S, 1, rng)
+        v, step_s = cpu_tok_s(o, S, 1, 3, rng)
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"{SAMPLE_LAYERS} of 48 layers + lm_head of one batch-1 decode step at ctx "
+                                          f"{r1['ctx']}, 3 repeats, scaled to 48 layers; CPU restatement of DenseCore's "
+                                          f"ggml path"}
+    if rank == 0:
+        print(json.dumps(line))
+    model.close()
+    ctx.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

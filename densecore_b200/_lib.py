@@ -63,6 +63,7 @@ def _signatures() -> dict:
         "dc_b200_stream": (vp, [vp]),
         "dc_b200_synchronize": (i32, [vp]),
         "dc_b200_set_option": (i32, [vp, cstr, i32]),
+        "dc_b200_profiler_range": (i32, [i32]),
         "dc_b200_upload_weight": (i32, [vp, i32, C.POINTER(i64), vp, pp]),
         "dc_b200_free_weight": (i32, [vp, vp]),
         "dc_b200_weight_data": (vp, [vp, C.POINTER(sz)]),
@@ -108,6 +109,8 @@ def _signatures() -> dict:
         "dc_b200_model_logits_dev": (vp, [vp]),
         "dc_b200_model_step_stats": (i32, [vp, pi, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
         "dc_b200_model_set_option": (i32, [vp, cstr, i32]),
+        "dc_b200_model_profile_step": (i32, [vp, vp, i32, vp, i32, vp, vp, vp]),
+        "dc_b200_kernel_class_name": (cstr, [i32]),
         "dc_b200_ep_unique_id": (i32, [vp, cstr, vp]),
         "dc_b200_model_ep_init": (i32, [vp, cstr, vp]),
     }

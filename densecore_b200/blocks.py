@@ -27,6 +27,8 @@ def row_bytes(ggml_type: int, K: int) -> int:
         return 4 * K
     if ggml_type == GGML_TYPE_F16:
         return 2 * K
+    if ggml_type not in BLOCK_BYTES:
+        raise ValueError(f"ggml type {ggml_type} is not supported (F32, F16, Q4_K, Q6_K)")
     if K % QK_K:
         raise ValueError(f"K={K} is not a multiple of {QK_K}")
     return K // QK_K * BLOCK_BYTES[ggml_type]

@@ -3,6 +3,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
+#include <cuda_profiler_api.h>
 
 #include "dc_common.cuh"
 #include "dc_internal.h"
@@ -123,6 +124,10 @@ int dc_b200_synchronize(dc_ctx* ctx) {
     cudaSetDevice(ctx->device);
     DC_TRY(dc_check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize"));
     return dc_check_device_error(ctx);
+}
+
+int dc_b200_profiler_range(int start) {
+    return (start ? cudaProfilerStart() : cudaProfilerStop()) == cudaSuccess ? DC_B200_OK : DC_B200_BACKEND_ERROR;
 }
 
 int dc_b200_set_option(dc_ctx* ctx, const char* name, int value) {

@@ -111,7 +111,7 @@ int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_ex
 // carves a dc_moe_route for (T, E, top_k) out of a byte buffer; returns bytes used
 size_t dc_moe_route_bind(dc_moe_route* rt, uint8_t* base, int T, int E, int top_k);
 int dc_launch_moe_mm(dc_ctx* ctx, bool pair, const dc_weight* w0, const dc_weight* w1, const uint8_t* act_q8,
-                     int act_rows, int T, int top_k, const dc_moe_route* rt, float* out);
+                     int act_rows, int T, int top_k, int e_base, const dc_moe_route* rt, float* out);
 int dc_launch_moe_combine(dc_ctx* ctx, const float* dn, const int32_t* ids, const float* weights, int T, int top_k,
                           int H, int ep_lo, int ep_hi, float* out);
 

@@ -9,6 +9,12 @@
 
 #define DC_HISTORY_CAP 4096
 
+enum {
+    DC_K_EMBED = 0, DC_K_RMSNORM, DC_K_GEMV_QKV, DC_K_QKROPE, DC_K_ATTENTION, DC_K_GEMV_O, DC_K_ROUTER, DC_K_MOE_GATEUP,
+    DC_K_QUANT_H, DC_K_MOE_DOWN, DC_K_COMBINE, DC_K_ALLREDUCE, DC_K_FFN_GATEUP, DC_K_FFN_DOWN, DC_K_LM_HEAD, DC_K_ARGMAX,
+    DC_K_COUNT
+};
+
 struct dc_layer {
     dc_weight *attn_norm = nullptr, *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr;
     dc_weight *q_norm = nullptr, *k_norm = nullptr, *ffn_norm = nullptr;
@@ -49,6 +55,11 @@ struct dc_model {
     std::map<int, dc_graph> graphs;
     std::map<int, bool> warmed;
     int last_launches = 0;
+    // per-kernel-class device timing of one eager step (dc_b200_model_profile_step)
+    bool prof = false;
+    struct ProfRec { int cls; cudaEvent_t e0, e1; double bytes; };
+    std::vector<ProfRec> prof_recs;
+    int ep_lo = 0, ep_hi = 0;    // experts stored on this GPU
     int32_t* h_stage = nullptr;  // pinned, 1024 ints
     int stage_slot = 0;
     // expert parallel
@@ -58,7 +69,8 @@ struct dc_model {
 };
 
 // ---- synth.cu ----
-int dc_launch_synth_quantized(dc_ctx* ctx, int type, uint64_t seed, int64_t rows, int64_t K, float sigma, uint8_t* out);
+int dc_launch_synth_quantized(dc_ctx* ctx, int type, uint64_t seed, int64_t first_row, int64_t rows, int64_t K, float sigma,
+                              uint8_t* out);
 int dc_launch_synth_f32(dc_ctx* ctx, uint64_t seed, int64_t n, float sigma, float offset, float* out);
 // ---- ep.cu ----
 int dc_ep_allreduce(dc_model* m, float* buf, size_t n);

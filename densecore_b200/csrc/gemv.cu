@@ -247,7 +247,19 @@ int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, con
     p.stage_bytes = stage;
     const size_t act_bytes = (ActSmem::bytes(T, K) + 127) & ~(size_t)127;
     const size_t smem = DC_WARPS * DC_NSTAGE * 8 + act_bytes + (size_t)DC_WARPS * DC_NSTAGE * stage;
-    if (smem > 200 * 1024) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemv: shared memory need %zu too large", smem);
+    if (smem > 200 * 1024) {
+        // activations of all T tokens do not fit beside the weight pipeline: run the tokens in two halves
+        if (T == 1 || argmax) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemv: shared memory need %zu too large", smem);
+        const int T0 = T / 2;
+        dc_gemv_seg second[3];
+        for (int i = 0; i < n_seg; ++i) {
+            second[i] = segs[i];
+            second[i].out = segs[i].out + (size_t)T0 * segs[i].ldo;
+        }
+        int st = dc_launch_gemv(ctx, segs, n_seg, epi, act_q8, T0, K, nullptr);
+        if (st != DC_B200_OK) return st;
+        return dc_launch_gemv(ctx, second, n_seg, epi, act_q8 + (size_t)T0 * (K / DC_QK_K) * DC_Q8K_BYTES, T - T0, K, nullptr);
+    }
     // persistent-style grid: a multiple of the SM count, no more warps than row groups
     int ctas_per_sm = smem <= 100 * 1024 ? 2 : 1;
     int grid = ctx->num_sms * ctas_per_sm;

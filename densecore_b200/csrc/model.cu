@@ -170,7 +170,7 @@ static int alloc_step_buffers(dc_model* m) {
     }
     DC_TRY(dc_check_cuda(ctx, cudaMemsetAsync(b.argmax_keys, 0, T * sizeof(unsigned long long), ctx->stream), "memset"));
     DC_TRY(dc_check_cuda(ctx, cudaMemsetAsync(b.history_len, 0, sizeof(int), ctx->stream), "memset"));
-    // RoPE table in double, as the oracle builds it: [pos][2i]=cos, [2i+1]=sin of pos*theta^(-2i/d)
+    // RoPE table computed in double: [pos][2i]=cos, [2i+1]=sin of pos*theta^(-2i/d)
     std::vector<float> cs((size_t)c.max_ctx * 128);
     for (int p = 0; p < c.max_ctx; ++p)
         for (int i = 0; i < 64; ++i) {
@@ -193,74 +193,100 @@ static int enqueue_forward(dc_model* m, int T, int lm_mode, bool feedback) {
     const int H = c.hidden, QD = c.n_head * 128, KD = c.n_kv_head * 128, QKV = QD + 2 * KD;
     const float scale = 1.0f / sqrtf((float)c.head_dim);
     const int E = c.n_expert, top_k = c.n_expert_used;
-    int ep_lo = 0, ep_hi = E;
-    if (E > 0 && c.ep_size > 1) {
-        const int per = E / c.ep_size;
-        ep_lo = c.ep_rank * per;
-        ep_hi = ep_lo + per;
-    }
+    const int ep_lo = m->ep_lo, ep_hi = m->ep_hi;
     int launches = 0;
-#define L(expr)       \
-    do {              \
-        DC_TRY(expr); \
-        ++launches;   \
+    // cls: kernel class for the per-class timing; bytes: algorithmic bytes of the launch
+#define L(cls, bytes, n, expr)                                          \
+    do {                                                                \
+        dc_model::ProfRec _r = {cls, nullptr, nullptr, (double)(bytes)}; \
+        if (m->prof) {                                                  \
+            cudaEventCreate(&_r.e0);                                    \
+            cudaEventCreate(&_r.e1);                                    \
+            cudaEventRecord(_r.e0, ctx->stream);                        \
+        }                                                               \
+        DC_TRY(expr);                                                   \
+        if (m->prof) {                                                  \
+            cudaEventRecord(_r.e1, ctx->stream);                        \
+            m->prof_recs.push_back(_r);                                 \
+        }                                                               \
+        launches += (n);                                                \
     } while (0)
-    L(dc_launch_embed(ctx, m->tok_embd, b.tokens, T, b.x));
+    const double q8x = (double)T * (H / 256) * 292, xb = (double)T * H * 4;
+    L(DC_K_EMBED, m->tok_embd->row_bytes * T + xb, 1, dc_launch_embed(ctx, m->tok_embd, b.tokens, T, b.x));
     const float* pending = nullptr;  // MoE output of the previous layer, added in the next norm
     for (int il = 0; il < c.n_layer; ++il) {
         dc_layer& Ly = m->layers[il];
-        L(dc_launch_rmsnorm_q8k(ctx, b.x, pending, (const float*)Ly.attn_norm->dev, T, H, c.rms_eps, nullptr, b.q8_x));
+        L(DC_K_RMSNORM, xb + q8x + H * 4, 1,
+          dc_launch_rmsnorm_q8k(ctx, b.x, pending, (const float*)Ly.attn_norm->dev, T, H, c.rms_eps, nullptr, b.q8_x));
         pending = nullptr;
         dc_gemv_seg qkv[3] = {
             {Ly.wq->dev, Ly.wq->type, QD, (int)Ly.wq->row_bytes, b.qkv, QKV},
             {Ly.wk->dev, Ly.wk->type, KD, (int)Ly.wk->row_bytes, b.qkv + QD, QKV},
             {Ly.wv->dev, Ly.wv->type, KD, (int)Ly.wv->row_bytes, b.qkv + QD + KD, QKV},
         };
-        L(dc_launch_gemv(ctx, qkv, 3, DC_EPI_STORE, b.q8_x, T, H, nullptr));
+        L(DC_K_GEMV_QKV, (double)Ly.wq->bytes + Ly.wk->bytes + Ly.wv->bytes + q8x + (double)T * QKV * 4, 1,
+          dc_launch_gemv(ctx, qkv, 3, DC_EPI_STORE, b.q8_x, T, H, nullptr));
         __half* ka = m->kv.k_arena + m->kv.layer_elems * il;
         __half* va = m->kv.v_arena + m->kv.layer_elems * il;
-        L(dc_launch_qknorm_rope_kv(ctx, b.qkv, Ly.q_norm ? (const float*)Ly.q_norm->dev : nullptr,
+        L(DC_K_QKROPE, (double)T * QKV * 4 * 2, 1,
+          dc_launch_qknorm_rope_kv(ctx, b.qkv, Ly.q_norm ? (const float*)Ly.q_norm->dev : nullptr,
                                    Ly.k_norm ? (const float*)Ly.k_norm->dev : nullptr, b.cos_sin, c.max_ctx, b.positions,
                                    b.seq_ids, m->kv.d_tables, m->kv.max_blocks_per_seq, ka, va, c.n_head, c.n_kv_head,
                                    c.rms_eps, T, b.q));
-        DC_TRY(dc_launch_attention(ctx, b.q, ka, va, m->kv.d_tables, m->kv.max_blocks_per_seq, b.seq_ids, b.positions, T,
-                                   c.n_head, c.n_kv_head, scale, m->nsplit, &b.attn, nullptr, b.q8_attn));
-        launches += 2;
+        // KV bytes depend on the context length; filled in by the caller of the profile
+        L(DC_K_ATTENTION, 0.0, 2,
+          dc_launch_attention(ctx, b.q, ka, va, m->kv.d_tables, m->kv.max_blocks_per_seq, b.seq_ids, b.positions, T,
+                              c.n_head, c.n_kv_head, scale, m->nsplit, &b.attn, nullptr, b.q8_attn));
         dc_gemv_seg wo = {Ly.wo->dev, Ly.wo->type, H, (int)Ly.wo->row_bytes, b.x, H};
-        L(dc_launch_gemv(ctx, &wo, 1, DC_EPI_ACC, b.q8_attn, T, QD, nullptr));
-        L(dc_launch_rmsnorm_q8k(ctx, b.x, nullptr, (const float*)Ly.ffn_norm->dev, T, H, c.rms_eps,
+        L(DC_K_GEMV_O, (double)Ly.wo->bytes + (double)T * (QD / 256) * 292 + 2 * xb, 1,
+          dc_launch_gemv(ctx, &wo, 1, DC_EPI_ACC, b.q8_attn, T, QD, nullptr));
+        L(DC_K_RMSNORM, xb * (E > 0 ? 2 : 1) + q8x + H * 4, 1,
+          dc_launch_rmsnorm_q8k(ctx, b.x, nullptr, (const float*)Ly.ffn_norm->dev, T, H, c.rms_eps,
                                 E > 0 ? b.xn : nullptr, b.q8_x));
         if (E > 0) {
-            L(dc_launch_router(ctx, Ly.router, b.xn, E, T, top_k, c.routed_scale, ep_lo, ep_hi, &b.route));
-            L(dc_launch_moe_mm(ctx, true, Ly.gate_exps, Ly.up_exps, b.q8_x, T, T, top_k, &b.route, b.h));
-            L(dc_launch_quantize_q8k(ctx, b.h, T * top_k, c.expert_ffn, b.q8_h));
-            L(dc_launch_moe_mm(ctx, false, Ly.down_exps, nullptr, b.q8_h, T * top_k, T, top_k, &b.route, b.dn));
-            L(dc_launch_moe_combine(ctx, b.dn, b.route.ids, b.route.weights, T, top_k, H, ep_lo, ep_hi, b.moe_out));
-            if (c.ep_size > 1) DC_TRY(dc_ep_allreduce(m, b.moe_out, (size_t)T * H));
+            const int A = T * top_k, F = c.expert_ffn;
+            // distinct experts hit: top_k for one token; for T > 1 the host only knows the bound
+            const double U = T == 1 ? top_k : (A < E ? A : E);
+            const double local = (double)(ep_hi - ep_lo) / E;
+            L(DC_K_ROUTER, (double)Ly.router->bytes + xb, 1,
+              dc_launch_router(ctx, Ly.router, b.xn, E, T, top_k, c.routed_scale, ep_lo, ep_hi, &b.route));
+            L(DC_K_MOE_GATEUP, U * local * 2.0 * F * Ly.gate_exps->row_bytes + q8x + (double)A * F * 4, 1,
+              dc_launch_moe_mm(ctx, true, Ly.gate_exps, Ly.up_exps, b.q8_x, T, T, top_k, ep_lo, &b.route, b.h));
+            L(DC_K_QUANT_H, (double)A * F * 4 + (double)A * (F / 256) * 292, 1,
+              dc_launch_quantize_q8k(ctx, b.h, A, F, b.q8_h));
+            L(DC_K_MOE_DOWN, U * local * H * Ly.down_exps->row_bytes + (double)A * (F / 256) * 292 + (double)A * H * 4, 1,
+              dc_launch_moe_mm(ctx, false, Ly.down_exps, nullptr, b.q8_h, A, T, top_k, ep_lo, &b.route, b.dn));
+            L(DC_K_COMBINE, (double)A * H * 4 + xb, 1,
+              dc_launch_moe_combine(ctx, b.dn, b.route.ids, b.route.weights, T, top_k, H, ep_lo, ep_hi, b.moe_out));
+            if (c.ep_size > 1) L(DC_K_ALLREDUCE, xb, 1, dc_ep_allreduce(m, b.moe_out, (size_t)T * H));
             pending = b.moe_out;
         } else {
             dc_gemv_seg gu[2] = {
                 {Ly.ffn_gate->dev, Ly.ffn_gate->type, c.ffn, (int)Ly.ffn_gate->row_bytes, b.h, c.ffn},
                 {Ly.ffn_up->dev, Ly.ffn_up->type, c.ffn, (int)Ly.ffn_up->row_bytes, b.h, c.ffn},
             };
-            L(dc_launch_gemv(ctx, gu, 2, DC_EPI_SWIGLU, b.q8_x, T, H, nullptr));
-            L(dc_launch_quantize_q8k(ctx, b.h, T, c.ffn, b.q8_h));
+            L(DC_K_FFN_GATEUP, (double)Ly.ffn_gate->bytes + Ly.ffn_up->bytes + q8x + (double)T * c.ffn * 4, 1,
+              dc_launch_gemv(ctx, gu, 2, DC_EPI_SWIGLU, b.q8_x, T, H, nullptr));
+            L(DC_K_QUANT_H, (double)T * c.ffn * 4 + (double)T * (c.ffn / 256) * 292, 1,
+              dc_launch_quantize_q8k(ctx, b.h, T, c.ffn, b.q8_h));
             dc_gemv_seg dw = {Ly.ffn_down->dev, Ly.ffn_down->type, H, (int)Ly.ffn_down->row_bytes, b.x, H};
-            L(dc_launch_gemv(ctx, &dw, 1, DC_EPI_ACC, b.q8_h, T, c.ffn, nullptr));
+            L(DC_K_FFN_DOWN, (double)Ly.ffn_down->bytes + (double)T * (c.ffn / 256) * 292 + 2 * xb, 1,
+              dc_launch_gemv(ctx, &dw, 1, DC_EPI_ACC, b.q8_h, T, c.ffn, nullptr));
         }
     }
     if (lm_mode != 0) {
         const int rows = lm_mode == 1 ? 1 : T, first = lm_mode == 1 ? T - 1 : 0;
-        L(dc_launch_rmsnorm_q8k(ctx, b.x + (size_t)first * H, pending ? pending + (size_t)first * H : nullptr,
+        L(DC_K_RMSNORM, (double)rows * H * 4 * 2 + (double)rows * (H / 256) * 292, 1,
+          dc_launch_rmsnorm_q8k(ctx, b.x + (size_t)first * H, pending ? pending + (size_t)first * H : nullptr,
                                 (const float*)m->out_norm->dev, rows, H, c.rms_eps, nullptr, b.q8_x));
         const dc_weight* out_w = c.tie_embeddings ? m->tok_embd : m->output;
         dc_gemv_seg lm = {out_w->dev, out_w->type, c.vocab, (int)out_w->row_bytes, b.logits, c.vocab};
-        L(dc_launch_gemv(ctx, &lm, 1, DC_EPI_STORE, b.q8_x, rows, H, b.argmax_keys));
-        L(dc_launch_argmax_finish(ctx, b.argmax_keys, rows, b.out_tokens, feedback ? b.tokens : nullptr,
+        L(DC_K_LM_HEAD, (double)out_w->bytes + (double)rows * (H / 256) * 292 + (double)rows * c.vocab * 4, 1,
+          dc_launch_gemv(ctx, &lm, 1, DC_EPI_STORE, b.q8_x, rows, H, b.argmax_keys));
+        L(DC_K_ARGMAX, 64.0, 1,
+          dc_launch_argmax_finish(ctx, b.argmax_keys, rows, b.out_tokens, feedback ? b.tokens : nullptr,
                                   feedback ? b.positions : nullptr, feedback ? b.history : nullptr,
                                   feedback ? b.history_len : nullptr, DC_HISTORY_CAP));
-    } else if (pending) {
-        // nothing reads x after this chunk, but keep the residual stream consistent
     }
 #undef L
     m->last_launches = launches;
@@ -371,6 +397,13 @@ int dc_b200_model_create(dc_ctx* ctx, const dc_model_config* cfg, dc_model** out
     if (m->cfg.ep_size < 1) m->cfg.ep_size = 1;
     if (m->cfg.routed_scale == 0.0f) m->cfg.routed_scale = 1.0f;
     m->layers.resize(c.n_layer);
+    m->ep_lo = 0;
+    m->ep_hi = c.n_expert;
+    if (c.n_expert > 0 && m->cfg.ep_size > 1) {
+        const int per = c.n_expert / m->cfg.ep_size;
+        m->ep_lo = m->cfg.ep_rank * per;
+        m->ep_hi = m->ep_lo + per;
+    }
     const int blocks_per_seq = (c.max_ctx + DC_KV_BLOCK - 1) / DC_KV_BLOCK;
     int st = dc_kv_init(ctx, &m->kv, c.n_layer, c.n_kv_head, c.head_dim, blocks_per_seq * c.max_seqs, c.max_seqs, blocks_per_seq);
     // split count: about two CTAs per SM for a single-token step, at least 4 KV blocks per split at full context
@@ -428,9 +461,12 @@ int dc_b200_model_set_tensor(dc_model* m, const char* name, int ggml_type, const
     if (!is_vec && ggml_type != DC_TYPE_Q4_K && ggml_type != DC_TYPE_Q6_K)
         return dc_fail(m->ctx, DC_B200_UNSUPPORTED, "set_tensor: '%s' has ggml type %d; only Q4_K and Q6_K matrices are supported", name, ggml_type);
     if (*s.slot) return dc_fail(m->ctx, DC_B200_MODEL_LOAD_FAILED, "set_tensor: '%s' was already set", name);
-    dc_weight* w = new_weight(m, ggml_type, s.K, s.N, s.E);
+    // expert tensors keep only this GPU's contiguous range of experts
+    const int64_t e_first = s.E > 1 ? m->ep_lo : 0, e_count = s.E > 1 ? m->ep_hi - m->ep_lo : 1;
+    dc_weight* w = new_weight(m, ggml_type, s.K, s.N, e_count);
     if (!w) return dc_fail(m->ctx, DC_B200_OUT_OF_MEMORY, "set_tensor: out of device memory for '%s'", name);
-    cudaError_t e = cudaMemcpyAsync(w->dev, data_host, w->bytes, cudaMemcpyHostToDevice, m->ctx->stream);
+    const uint8_t* src = (const uint8_t*)data_host + (size_t)e_first * s.N * w->row_bytes;
+    cudaError_t e = cudaMemcpyAsync(w->dev, src, w->bytes, cudaMemcpyHostToDevice, m->ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->ctx->stream);
     if (e != cudaSuccess) {
         cudaFree(w->dev);
@@ -450,11 +486,12 @@ int dc_b200_model_init_synthetic(dc_model* m, uint64_t seed, float sigma) {
         TensorSlot s;
         if (!find_slot(m, n, &s)) return dc_fail(m->ctx, DC_B200_INTERNAL_ERROR, "init_synthetic: no slot for %s", n.c_str());
         if (*s.slot) continue;
-        dc_weight* w = new_weight(m, s.synth_type, s.K, s.N, s.E);
+        const int64_t e_first = s.E > 1 ? m->ep_lo : 0, e_count = s.E > 1 ? m->ep_hi - m->ep_lo : 1;
+        dc_weight* w = new_weight(m, s.synth_type, s.K, s.N, e_count);
         if (!w) return dc_fail(m->ctx, DC_B200_OUT_OF_MEMORY, "init_synthetic: out of device memory for '%s'", n.c_str());
         const uint64_t ts = seed + fnv1a64(n.c_str());
         int st;
-        if (s.kind == 0) st = dc_launch_synth_quantized(m->ctx, s.synth_type, ts, s.N * s.E, s.K, sigma, w->dev);
+        if (s.kind == 0) st = dc_launch_synth_quantized(m->ctx, s.synth_type, ts, e_first * s.N, s.N * e_count, s.K, sigma, w->dev);
         else st = dc_launch_synth_f32(m->ctx, ts, s.K * s.N * s.E, sigma, s.kind == 1 ? 1.0f : 0.0f, (float*)w->dev);
         if (st != DC_B200_OK) {
             cudaFree(w->dev);
@@ -619,6 +656,50 @@ int dc_b200_decode_run(dc_model* m, const int32_t* seqs, int n_seq, const int32_
     return DC_B200_OK;
 }
 
+static const char* kClassNames[DC_K_COUNT] = {"embed", "rmsnorm_q8k", "gemv_qkv", "qknorm_rope_kv", "attention",
+                                               "gemv_attn_out", "router_topk", "moe_gate_up_swiglu", "quantize_h",
+                                               "moe_down", "moe_combine", "ep_allreduce", "ffn_gate_up_swiglu",
+                                               "ffn_down", "lm_head_argmax", "argmax_finish"};
+
+const char* dc_b200_kernel_class_name(int cls) { return (cls >= 0 && cls < DC_K_COUNT) ? kClassNames[cls] : nullptr; }
+
+int dc_b200_model_profile_step(dc_model* m, const int32_t* seqs, int n_seq, const int32_t* tokens_host, int n_classes,
+                               float* ms_out, int* launches_out, double* bytes_out) {
+    if (!m || !seqs || !tokens_host || !ms_out || !launches_out || !bytes_out || n_classes < DC_K_COUNT)
+        return m ? dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "profile_step: need room for %d classes", DC_K_COUNT) : DC_B200_INVALID_ARGUMENT;
+    const bool graphs = m->use_graphs;
+    const int pdl = m->ctx->use_pdl;
+    m->use_graphs = false;   // events between launches need eager, serialised launches
+    m->ctx->use_pdl = 0;
+    m->prof = true;
+    m->prof_recs.clear();
+    int32_t next[DC_MAX_T];
+    int st = dc_b200_decode_step(m, seqs, n_seq, tokens_host, next, nullptr);
+    m->prof = false;
+    m->use_graphs = graphs;
+    m->ctx->use_pdl = pdl;
+    for (int i = 0; i < n_classes; ++i) {
+        ms_out[i] = 0.0f;
+        launches_out[i] = 0;
+        bytes_out[i] = 0.0;
+    }
+    const double kv_bytes = 2.0 * m->cfg.n_kv_head * m->cfg.head_dim * 2.0;  // K and V, fp16, per token of context
+    for (auto& r : m->prof_recs) {
+        float ms = 0.0f;
+        if (st == DC_B200_OK) cudaEventElapsedTime(&ms, r.e0, r.e1);
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+        ms_out[r.cls] += ms;
+        launches_out[r.cls] += 1;
+        double bytes = r.bytes;
+        if (r.cls == DC_K_ATTENTION)
+            for (int i = 0; i < n_seq; ++i) bytes += kv_bytes * m->kv.seqs[seqs[i]].len;
+        bytes_out[r.cls] += bytes;
+    }
+    m->prof_recs.clear();
+    return st;
+}
+
 int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
     if (!m || !name) return DC_B200_INVALID_ARGUMENT;
     if (!strcmp(name, "graphs")) {
@@ -639,7 +720,7 @@ int dc_b200_model_step_stats(dc_model* m, int* kernels_per_step, double* weight_
         for (const dc_weight* w : {L.attn_norm, L.wq, L.wk, L.wv, L.wo, L.q_norm, L.k_norm, L.ffn_norm, L.router, L.ffn_gate, L.ffn_up, L.ffn_down})
             if (w) wb += (double)w->bytes;
         for (const dc_weight* w : {L.gate_exps, L.up_exps, L.down_exps})
-            if (w) wb += (double)w->bytes / (double)w->E * c.n_expert_used;
+            if (w) wb += (double)w->bytes / (double)w->E * c.n_expert_used;  // whole job: all ranks together read top-k experts
     }
     const dc_weight* out_w = c.tie_embeddings ? m->tok_embd : m->output;
     if (out_w) wb += (double)out_w->bytes;

@@ -197,6 +197,7 @@ struct MoeMMParams {
     int type, row_bytes, N /*rows per expert*/, K;
     const uint8_t* act_q8;  // Q8_K rows: tokens (PAIR) or assignments (down)
     int act_rows, top_k;
+    int e_base;           // first expert stored in w0/w1 (expert-parallel shard)
     const int* n_active;
     const int32_t* uexp;
     const int32_t* uoff;
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
     auto issue_next = [&]() {
         int u, r, n;
         if (!prod.next(u, r, n)) return;
-        const size_t off = (size_t)p.uexp[u] * estride + (size_t)r * p.row_bytes;
+        const size_t off = (size_t)(p.uexp[u] - p.e_base) * estride + (size_t)r * p.row_bytes;
         if (PAIR) pipe.issue2(p.w0 + off, p.w1 + off, (uint32_t)n * p.row_bytes, p.up_off);
         else pipe.issue(p.w0 + off, (uint32_t)n * p.row_bytes);
     };
@@ -259,7 +260,7 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
     int u, r, n;
     while (cons.next(u, r, n)) {
         const uint32_t buf = pipe.wait();
-        const size_t off = (size_t)p.uexp[u] * estride + (size_t)r * p.row_bytes;
+        const size_t off = (size_t)(p.uexp[u] - p.e_base) * estride + (size_t)r * p.row_bytes;
         const uint32_t skew0 = (uint32_t)(((uintptr_t)p.w0 + off) & 15);
         const uint32_t skew1 = PAIR ? (uint32_t)(((uintptr_t)p.w1 + off) & 15) : 0u;
         const int a0 = p.uoff[u], nt = min(NT, p.uoff[u + 1] - a0);
@@ -316,8 +317,9 @@ static int rows_per_stage_moe(int type, int K, int row_bytes) {
 // w0/w1: expert tensors [K, N, E].  pair: gate/up + SwiGLU, activations are the T
 // token rows; else down, activations are the T*top_k assignment rows.
 int dc_launch_moe_mm(dc_ctx* ctx, bool pair, const dc_weight* w0, const dc_weight* w1, const uint8_t* act_q8,
-                     int act_rows, int T, int top_k, const dc_moe_route* rt, float* out) {
+                     int act_rows, int T, int top_k, int e_base, const dc_moe_route* rt, float* out) {
     MoeMMParams p = {};
+    p.e_base = e_base;
     p.w0 = w0->dev;
     p.w1 = pair ? w1->dev : nullptr;
     p.type = w0->type;

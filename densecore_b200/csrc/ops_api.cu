@@ -124,9 +124,9 @@ int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* ga
     if (st == DC_B200_OK) st = h2d(ctx, x, x_host, (size_t)T * H * 4);
     if (st == DC_B200_OK) st = dc_launch_router(ctx, router, x, E, T, top_k, routed_scale, 0, E, &rt);
     if (st == DC_B200_OK) st = dc_launch_quantize_q8k(ctx, x, T, H, xq);
-    if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, true, gate, up, xq, T, T, top_k, &rt, h);
+    if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, true, gate, up, xq, T, T, top_k, 0, &rt, h);
     if (st == DC_B200_OK) st = dc_launch_quantize_q8k(ctx, h, A, F, hq);
-    if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, false, down, nullptr, hq, A, T, top_k, &rt, dn);
+    if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, false, down, nullptr, hq, A, T, top_k, 0, &rt, dn);
     if (st == DC_B200_OK) st = dc_launch_moe_combine(ctx, dn, rt.ids, rt.weights, T, top_k, H, 0, E, y);
     if (st == DC_B200_OK) st = d2h(ctx, y_host, y, (size_t)T * H * 4);
     if (st == DC_B200_OK && ids_out) st = d2h(ctx, ids_out, rt.ids, (size_t)A * 4);

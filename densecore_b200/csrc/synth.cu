@@ -40,12 +40,13 @@ __device__ __forceinline__ float synth_normal(uint64_t seed, uint64_t index, flo
 __device__ __forceinline__ int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
 
 // One thread per super-block.
-__global__ void __launch_bounds__(128) k_synth_quantized(int type, uint64_t seed, int64_t n_blocks, float sigma,
-                                                         uint8_t* __restrict__ out) {
+__global__ void __launch_bounds__(128) k_synth_quantized(int type, uint64_t seed, int64_t first_block, int64_t n_blocks,
+                                                         float sigma, uint8_t* __restrict__ out) {
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
     float x[256];
-    for (int i = 0; i < 256; ++i) x[i] = synth_normal(seed, (uint64_t)(b * 256 + i), sigma);
+    // element index within the whole tensor, so a shard holds the same values as the full tensor's slice
+    for (int i = 0; i < 256; ++i) x[i] = synth_normal(seed, (uint64_t)((first_block + b) * 256 + i), sigma);
     if (type == DC_TYPE_Q4_K) {
         uint8_t* blk = out + b * DC_Q4K_BYTES;
         float sc[8], mn[8], max_sc = 0.0f, max_mn = 0.0f;
@@ -124,10 +125,11 @@ __global__ void k_synth_f32(uint64_t seed, int64_t n, float sigma, float offset,
     if (i < n) out[i] = __fadd_rn(offset, synth_normal(seed, (uint64_t)i, sigma));
 }
 
-int dc_launch_synth_quantized(dc_ctx* ctx, int type, uint64_t seed, int64_t rows, int64_t K, float sigma, uint8_t* out) {
-    const int64_t nb = rows * (K / DC_QK_K);
+int dc_launch_synth_quantized(dc_ctx* ctx, int type, uint64_t seed, int64_t first_row, int64_t rows, int64_t K, float sigma,
+                              uint8_t* out) {
+    const int64_t nb = rows * (K / DC_QK_K), first_block = first_row * (K / DC_QK_K);
     const int64_t grid = (nb + 127) / 128;
-    k_synth_quantized<<<(unsigned)grid, 128, 0, ctx->stream>>>(type, seed, nb, sigma, out);
+    k_synth_quantized<<<(unsigned)grid, 128, 0, ctx->stream>>>(type, seed, first_block, nb, sigma, out);
     return dc_check_cuda(ctx, cudaGetLastError(), "k_synth_quantized");
 }
 

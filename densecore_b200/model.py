@@ -173,3 +173,20 @@ class Model:
         kv = C.c_double(0.0)
         self._check(_lib.lib().dc_b200_model_step_stats(self.handle, C.byref(k), C.byref(wb), C.byref(kv)))
         return k.value, wb.value, kv.value
+
+    def profile_step(self, seqs, tokens):
+        """One eager decode step timed per kernel class.  Returns {class: (ms, launches, algorithmic bytes)}."""
+        seqs = np.ascontiguousarray(seqs, dtype=np.int32)
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        n = 16
+        ms = np.zeros(n, np.float32)
+        launches = np.zeros(n, np.int32)
+        nbytes = np.zeros(n, np.float64)
+        self._check(_lib.lib().dc_b200_model_profile_step(self.handle, _vp(seqs), seqs.size, _vp(tokens), n, _vp(ms),
+                                                          _vp(launches), _vp(nbytes)))
+        out = {}
+        for i in range(n):
+            name = _lib.lib().dc_b200_kernel_class_name(i)
+            if name and launches[i]:
+                out[name.decode()] = (float(ms[i]), int(launches[i]), float(nbytes[i]))
+        return out

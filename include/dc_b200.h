@@ -68,6 +68,10 @@ DC_B200_API int dc_b200_synchronize(dc_ctx* ctx);
 /* 0/1: programmatic dependent launch between consecutive kernels (default 1). */
 DC_B200_API int dc_b200_set_option(dc_ctx* ctx, const char* name, int value);
 
+/* cudaProfilerStart (1) / cudaProfilerStop (0): brackets the region a profiler
+ * run with --profile-from-start off captures. */
+DC_B200_API int dc_b200_profiler_range(int start);
+
 /* ---- weights ---------------------------------------------------------- */
 /* Copies a GGUF tensor to HBM verbatim.  ne[0]=K_in (multiple of 256 for
  * K-quants), ne[1]=N_out, ne[2]=experts (1 for a dense tensor), ne[3]=1.  The
@@ -235,6 +239,15 @@ DC_B200_API void* dc_b200_model_logits_dev(dc_model* m);
 DC_B200_API int dc_b200_model_step_stats(dc_model* m, int* kernels_per_step, double* weight_bytes_per_step,
                                          double* kv_bytes_per_token_ctx);
 
+/* One eager decode step with CUDA events around every launch: device time,
+ * launches and algorithmic bytes per kernel class (dc_b200_kernel_class_name
+ * names class i; pass arrays of at least 16 entries).  The mirror of the
+ * reference's per-op profile buckets (moe_route_ns, moe_w1w3_ns, moe_w2_ns,
+ * paged_attention_ns ..., core/src/llm/moe/exec.cpp:948-960,
+ * core/src/llm/attention/paged_exec.cpp:842-861). */
+DC_B200_API int dc_b200_model_profile_step(dc_model* m, const int32_t* seqs, int n_seq, const int32_t* tokens_host,
+                                           int n_classes, float* ms_out, int* launches_out, double* bytes_out);
+DC_B200_API const char* dc_b200_kernel_class_name(int cls);
 /* "graphs" 0/1: replay each step shape as a CUDA graph (default 1). */
 DC_B200_API int dc_b200_model_set_option(dc_model* m, const char* name, int value);
 

@@ -27,6 +27,9 @@
 #include <stdlib.h>
 #include <string.h>
 #include <pthread.h>
+#if defined(__F16C__)
+#include <immintrin.h>
+#endif
 #include <stdatomic.h>
 #include <unistd.h>
 
@@ -156,6 +159,9 @@ DCO_API int dco_max_threads(void) {
 /* ------------------------------------------------------------------ fp16 */
 /* core/src/kernels/hwy/hwy_moe_quant.cc:55-81 (exact half -> single). */
 DCO_API float dco_fp16_to_fp32(uint16_t h) {
+#if defined(__F16C__)
+    return _cvtsh_ss(h); /* the hardware conversion is exact, identical to the bit manipulation below */
+#endif
     const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
     const uint32_t exp = (h >> 10) & 0x1Fu;
     const uint32_t mant = h & 0x03FFu;
@@ -775,12 +781,25 @@ DCO_API void dco_kv_write(uint16_t* k_arena, uint16_t* v_arena, const int32_t* b
 /* Scalar two-pass reference: std::exp, divide by the plain denominator
  * (core/src/llm/attention/paged_exec.cpp:37-223; no window, no soft-cap).
  * One query token at position query_pos attends keys 0..query_pos. */
-DCO_API void dco_paged_attention_scalar(const float* q, const uint16_t* k_arena, const uint16_t* v_arena,
-                                        const int32_t* block_table, int query_pos, int n_head, int n_kv,
-                                        int head_dim, float scale, float* out) {
-    const int group = n_head / n_kv, ctx = query_pos + 1;
+typedef struct {
+    const float* q;
+    const uint16_t *k_arena, *v_arena;
+    const int32_t* block_table;
+    int query_pos, n_head, n_kv, head_dim;
+    float scale;
+    float* out;
+} attn_ctx;
+static void attn_scalar_heads(int64_t h_lo, int64_t h_hi, void* p) {
+    const attn_ctx* a = (const attn_ctx*)p;
+    const float* q = a->q;
+    const uint16_t *k_arena = a->k_arena, *v_arena = a->v_arena;
+    const int32_t* block_table = a->block_table;
+    const int n_head = a->n_head, n_kv = a->n_kv, head_dim = a->head_dim;
+    const float scale = a->scale;
+    float* out = a->out;
+    const int group = n_head / n_kv, ctx = a->query_pos + 1;
     float* scores = (float*)malloc(sizeof(float) * (size_t)ctx);
-    for (int h = 0; h < n_head; ++h) {
+    for (int h = (int)h_lo; h < (int)h_hi; ++h) {
         const float* qh = q + (size_t)h * head_dim;
         float* oh = out + (size_t)h * head_dim;
         const int kvh = h / group;
@@ -812,15 +831,28 @@ DCO_API void dco_paged_attention_scalar(const float* q, const uint16_t* k_arena,
     }
     free(scores);
 }
+/* Heads are split across threads as the reference splits head tiles
+ * (core/src/llm/attention/paged_exec.cpp:552-573). */
+DCO_API void dco_paged_attention_scalar(const float* q, const uint16_t* k_arena, const uint16_t* v_arena,
+                                        const int32_t* block_table, int query_pos, int n_head, int n_kv,
+                                        int head_dim, float scale, float* out) {
+    attn_ctx a = {q, k_arena, v_arena, block_table, query_pos, n_head, n_kv, head_dim, scale, out};
+    parallel_for(n_head, attn_scalar_heads, &a);
+}
 
 /* Production kernel: per 16-token block online softmax with the fast-exp
  * polynomial, final acc * 1/(d + 1e-6)
  * (core/src/kernels/hwy/hwy_paged_attention.cc:428-629). */
-DCO_API void dco_paged_attention_blockwise(const float* q, const uint16_t* k_arena, const uint16_t* v_arena,
-                                           const int32_t* block_table, int query_pos, int n_head, int n_kv,
-                                           int head_dim, float scale, float* out) {
-    const int group = n_head / n_kv, ctx = query_pos + 1;
-    for (int h = 0; h < n_head; ++h) {
+static void attn_blockwise_heads(int64_t h_lo, int64_t h_hi, void* p) {
+    const attn_ctx* a = (const attn_ctx*)p;
+    const float* q = a->q;
+    const uint16_t *k_arena = a->k_arena, *v_arena = a->v_arena;
+    const int32_t* block_table = a->block_table;
+    const int n_head = a->n_head, n_kv = a->n_kv, head_dim = a->head_dim;
+    const float scale = a->scale;
+    float* out = a->out;
+    const int group = n_head / n_kv, ctx = a->query_pos + 1;
+    for (int h = (int)h_lo; h < (int)h_hi; ++h) {
         const float* qh = q + (size_t)h * head_dim;
         float* oh = out + (size_t)h * head_dim;
         const int kvh = h / group;
@@ -860,6 +892,12 @@ DCO_API void dco_paged_attention_blockwise(const float* q, const uint16_t* k_are
         const float inv = 1.0f / (d_prev + 1e-6f);
         for (int d = 0; d < head_dim; ++d) oh[d] *= inv;
     }
+}
+DCO_API void dco_paged_attention_blockwise(const float* q, const uint16_t* k_arena, const uint16_t* v_arena,
+                                           const int32_t* block_table, int query_pos, int n_head, int n_kv,
+                                           int head_dim, float scale, float* out) {
+    attn_ctx a = {q, k_arena, v_arena, block_table, query_pos, n_head, n_kv, head_dim, scale, out};
+    parallel_for(n_head, attn_blockwise_heads, &a);
 }
 
 /* ------------------------------------------------- norm, RoPE, sampling */
