@@ -184,7 +184,11 @@ __device__ __forceinline__ uint32_t lds32_a2(uint32_t a) { return lds16(a) | (ld
 // Follows core/src/kernels/hwy/hwy_moe_quant.cc:103-144 step by step:
 // first element of largest magnitude keeps its sign; iscale = -127/max;
 // q = min(127, rne(iscale*x)); bsums per 16; d = 1/iscale.
-__device__ __forceinline__ void quantize_block_q8k_regs(const float (&v)[8], uint8_t* __restrict__ out, int lane) {
+// Core of the block quantiser: every lane gets its two packed words of codes,
+// the bsums word it may own (lanes with lane%4==0: groups lane/2 and lane/2+1)
+// and the block scale d (0 for an all-zero block).
+__device__ __forceinline__ void q8k_block_core(const float (&v)[8], int lane, uint32_t& w0, uint32_t& w1,
+                                               uint32_t& bsum_word, float& d) {
     float amax = 0.0f, mx = 0.0f;
     int idx = 0;
 #pragma unroll
@@ -207,9 +211,9 @@ __device__ __forceinline__ void quantize_block_q8k_regs(const float (&v)[8], uin
             idx = oi;
         }
     }
-    uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
     if (amax == 0.0f) {
-        for (int w = lane; w < 73; w += 32) o32[w] = 0u;
+        w0 = w1 = bsum_word = 0u;
+        d = 0.0f;
         return;
     }
     const float iscale = __fdiv_rn(-127.0f, mx);
@@ -219,15 +223,24 @@ __device__ __forceinline__ void quantize_block_q8k_regs(const float (&v)[8], uin
         q[j] = min(127, __float2int_rn(__fmul_rn(iscale, v[j])));
         sum += q[j];
     }
-    const uint32_t w0 = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
-    const uint32_t w1 = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
-    o32[1 + 2 * lane] = w0;
-    o32[2 + 2 * lane] = w1;
+    w0 = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+    w1 = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
     // bsums: group g = lanes 2g, 2g+1
     const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
     const int other = __shfl_xor_sync(0xffffffffu, pair, 2);  // neighbouring group's sum
-    if ((lane & 3) == 0) o32[65 + (lane >> 2)] = (uint32_t)(pair & 0xFFFF) | ((uint32_t)(other & 0xFFFF) << 16);
-    if (lane == 0) o32[0] = __float_as_uint(__fdiv_rn(1.0f, iscale));
+    bsum_word = (uint32_t)(pair & 0xFFFF) | ((uint32_t)(other & 0xFFFF) << 16);
+    d = __fdiv_rn(1.0f, iscale);
+}
+// Writes the native 292-byte block.
+__device__ __forceinline__ void quantize_block_q8k_regs(const float (&v)[8], uint8_t* __restrict__ out, int lane) {
+    uint32_t w0, w1, bw;
+    float d;
+    q8k_block_core(v, lane, w0, w1, bw, d);
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
+    o32[1 + 2 * lane] = w0;
+    o32[2 + 2 * lane] = w1;
+    if ((lane & 3) == 0) o32[65 + (lane >> 2)] = bw;
+    if (lane == 0) o32[0] = __float_as_uint(d);
 }
 __device__ __forceinline__ void quantize_block_q8k_warp(const float* __restrict__ x, uint8_t* __restrict__ out,
                                                         int lane) {
@@ -272,6 +285,18 @@ struct ActSmem {
         }
     }
 };
+
+// Quantises one 256-element block held in registers (lane l: elements 8l..8l+7)
+// straight into the shared-memory activation layout: row t, block b.
+__device__ __forceinline__ void quantize_block_q8k_to_act(const float (&v)[8], const ActSmem& act, int t, int b, int lane) {
+    uint32_t w0, w1, bw;
+    float d;
+    q8k_block_core(v, lane, w0, w1, bw, d);
+    const uint32_t qa = act.qs + t * act.K + b * 256 + 8 * lane;
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(qa), "r"(w0), "r"(w1));
+    if ((lane & 3) == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(act.bs + (t * act.nb + b) * 32 + (lane >> 2) * 4), "r"(bw));
+    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(act.d + (t * act.nb + b) * 4), "f"(d));
+}
 
 // ------------------------------------------------------- Q4_K row dot
 // One "item" = (super-block b, chunk c): 32 bytes of qs = sub-blocks 2c (low

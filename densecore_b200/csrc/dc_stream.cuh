@@ -1,0 +1,243 @@
+// Row-streaming matmul bodies shared by the stand-alone kernels (k_gemv,
+// k_moe_mm) and the persistent decode kernel: each warp walks a contiguous
+// range of weight rows through its bulk-copy pipeline, decodes them against the
+// Q8_K activations in shared memory and writes one float per (row, token).
+#pragma once
+#include "dc_common.cuh"
+#include "dc_internal.h"
+
+namespace dc {
+
+struct GemvParams {
+    dc_gemv_seg seg[3];
+    int n_seg;
+    int rpst[3];      // rows per pipeline stage, per segment
+    int total_rows;   // flattened over segments (pairs count once for SwiGLU)
+    int epi;
+    const uint8_t* act_q8;
+    int T, K;
+    uint32_t stage_bytes;
+    uint32_t up_off;  // SwiGLU: offset of the up rows inside a stage
+    unsigned long long* argmax;
+    int* err;
+};
+
+// Walks a warp's contiguous flattened row range stage by stage.
+struct StageIter {
+    int cur, end;
+    __device__ __forceinline__ bool next(const GemvParams& p, int& seg, int& local, int& n) {
+        if (cur >= end) return false;
+        int s = 0, base = 0;
+        const int nseg = p.epi == DC_EPI_SWIGLU ? 1 : p.n_seg;
+        while (s + 1 < nseg && cur >= base + p.seg[s].n_rows) {
+            base += p.seg[s].n_rows;
+            ++s;
+        }
+        seg = s;
+        local = cur - base;
+        int lim = min(end, base + p.seg[s].n_rows);
+        n = min(p.rpst[s], lim - cur);
+        cur += n;
+        return true;
+    }
+};
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, int row) {
+    uint32_t u = __float_as_uint(v);
+    if (v != v) u = 0;  // NaN never wins
+    else u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)row);
+}
+
+template <int NSTAGE>
+struct GemvStream {
+    StageIter prod, cons;
+    __device__ __forceinline__ void begin(const GemvParams& p, int gw, int nw) {
+        const int r0 = (int)((long long)gw * p.total_rows / nw), r1 = (int)((long long)(gw + 1) * p.total_rows / nw);
+        prod = StageIter{r0, r1};
+        cons = StageIter{r0, r1};
+    }
+    // lane 0 only
+    __device__ __forceinline__ void issue_next(const GemvParams& p, WarpPipe<NSTAGE>& pipe) {
+        int sg, lr, n;
+        if (!prod.next(p, sg, lr, n)) return;
+        const dc_gemv_seg& s = p.seg[sg];
+        const uint32_t bytes = (uint32_t)n * s.row_bytes;
+        if (p.epi == DC_EPI_SWIGLU)
+            pipe.issue2(s.w + (size_t)lr * s.row_bytes, p.seg[1].w + (size_t)lr * s.row_bytes, bytes, p.up_off);
+        else
+            pipe.issue(s.w + (size_t)lr * s.row_bytes, bytes);
+    }
+    __device__ __forceinline__ void prefill(const GemvParams& p, WarpPipe<NSTAGE>& pipe, int lane) {
+        if (lane == 0)
+            for (int s = 0; s < NSTAGE; ++s) issue_next(p, pipe);
+    }
+    template <int NT>
+    __device__ __forceinline__ void consume(const GemvParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
+        int tok[NT];
+#pragma unroll
+        for (int s = 0; s < NT; ++s) tok[s] = s;
+        unsigned long long best[NT];
+#pragma unroll
+        for (int s = 0; s < NT; ++s) best[s] = 0ull;
+        int sg, lr, n;
+        while (cons.next(p, sg, lr, n)) {
+            const dc_gemv_seg& s = p.seg[sg];
+            const uint32_t buf = pipe.wait();
+            const int G = lanes_per_row(s.type, p.K);
+            const int rows_per_pass = 32 / G;
+            const int grp = lane / G, lig = lane % G;
+            const uint32_t skew = (uint32_t)(((uintptr_t)s.w + (size_t)lr * s.row_bytes) & 15);
+            const uint32_t skew_up =
+                p.epi == DC_EPI_SWIGLU ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
+            for (int r = 0; r < n; r += rows_per_pass) {
+                const int rr = r + grp;
+                const bool active = rr < n;
+                float acc[NT], acc2[NT];
+#pragma unroll
+                for (int t = 0; t < NT; ++t) acc[t] = acc2[t] = 0.0f;
+                if (active) {
+                    row_dot_partial<NT>(s.type, buf + skew + rr * s.row_bytes, lig, G, act, p.T, tok, acc);
+                    if (p.epi == DC_EPI_SWIGLU)
+                        row_dot_partial<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, lig, G, act, p.T, tok,
+                                            acc2);
+                }
+                // every lane runs the reductions; lane (t mod G) of the row's group stores token t
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    if (t < p.T) {
+                        float v = group_sum_rt(acc[t], G);
+                        if (p.epi == DC_EPI_SWIGLU) {
+                            const float u = group_sum_rt(acc2[t], G);
+                            v = __fmul_rn(silu_fast(v), u);
+                        }
+                        if (active && lig == (t & (G - 1))) {
+                            const int row = lr + rr;
+                            float* o = s.out + (size_t)t * s.ldo + row;
+                            if (p.epi == DC_EPI_ACC) *o += v;
+                            else *o = v;
+                            if (p.argmax) {
+                                const unsigned long long k = argmax_key(v, row);
+                                best[t] = k > best[t] ? k : best[t];
+                            }
+                        }
+                    }
+                }
+            }
+            pipe.release();
+            if (lane == 0) issue_next(p, pipe);
+        }
+        if (p.argmax) {
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                if (t < p.T) {
+                    unsigned long long k = best[t];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const unsigned long long ok = __shfl_xor_sync(0xffffffffu, k, o);
+                        k = ok > k ? ok : k;
+                    }
+                    if (lane == 0 && k) atomicMax(p.argmax + t, k);
+                }
+            }
+        }
+    }
+};
+
+// ------------------------------------------------------------ expert rows
+struct MoeMMParams {
+    const uint8_t* w0;    // gate (PAIR) or down
+    const uint8_t* w1;    // up (PAIR)
+    int type, row_bytes, N /*rows per expert*/, K;
+    const uint8_t* act_q8;  // Q8_K rows: tokens (PAIR) or assignments (down)
+    int act_rows, top_k;
+    int e_base;           // first expert stored in w0/w1 (expert-parallel shard)
+    const int* n_active;
+    const int32_t* uexp;
+    const int32_t* uoff;
+    const int32_t* uassign;
+    float* out;           // [assignment][N]
+    int rpst;
+    uint32_t stage_bytes, up_off;
+    int* err;
+};
+
+struct MoeIter {
+    int cur, end, N, rpst;
+    __device__ __forceinline__ bool next(int& u, int& r, int& n) {
+        if (cur >= end) return false;
+        u = cur / N;
+        r = cur - u * N;
+        n = min(rpst, min(N - r, end - cur));
+        cur += n;
+        return true;
+    }
+};
+
+template <int NSTAGE, bool PAIR>
+struct MoeStream {
+    MoeIter prod, cons;
+    size_t estride;
+    __device__ __forceinline__ void begin(const MoeMMParams& p, int U, int gw, int nw) {
+        const int total = U * p.N;
+        const int r0 = (int)((long long)gw * total / nw), r1 = (int)((long long)(gw + 1) * total / nw);
+        prod = MoeIter{r0, r1, p.N, p.rpst};
+        cons = MoeIter{r0, r1, p.N, p.rpst};
+        estride = (size_t)p.N * p.row_bytes;
+    }
+    __device__ __forceinline__ void issue_next(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe) {
+        int u, r, n;
+        if (!prod.next(u, r, n)) return;
+        const size_t off = (size_t)(p.uexp[u] - p.e_base) * estride + (size_t)r * p.row_bytes;
+        if (PAIR) pipe.issue2(p.w0 + off, p.w1 + off, (uint32_t)n * p.row_bytes, p.up_off);
+        else pipe.issue(p.w0 + off, (uint32_t)n * p.row_bytes);
+    }
+    __device__ __forceinline__ void prefill(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe, int lane) {
+        if (lane == 0)
+            for (int s = 0; s < NSTAGE; ++s) issue_next(p, pipe);
+    }
+    template <int NT>
+    __device__ __forceinline__ void consume(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
+        const int G = lanes_per_row(p.type, p.K);
+        const int rows_per_pass = 32 / G, grp = lane / G, lig = lane % G;
+        int u, r, n;
+        while (cons.next(u, r, n)) {
+            const uint32_t buf = pipe.wait();
+            const size_t off = (size_t)(p.uexp[u] - p.e_base) * estride + (size_t)r * p.row_bytes;
+            const uint32_t skew0 = (uint32_t)(((uintptr_t)p.w0 + off) & 15);
+            const uint32_t skew1 = PAIR ? (uint32_t)(((uintptr_t)p.w1 + off) & 15) : 0u;
+            const int a0 = p.uoff[u], nt = min(NT, p.uoff[u + 1] - a0);
+            int tok[NT], asg[NT];
+#pragma unroll
+            for (int s = 0; s < NT; ++s) {
+                asg[s] = s < nt ? p.uassign[a0 + s] : 0;
+                tok[s] = PAIR ? asg[s] / p.top_k : asg[s];
+            }
+            for (int rr0 = 0; rr0 < n; rr0 += rows_per_pass) {
+                const int rr = rr0 + grp;
+                const bool active = rr < n;
+                float acc[NT], acc2[NT];
+#pragma unroll
+                for (int s = 0; s < NT; ++s) acc[s] = acc2[s] = 0.0f;
+                if (active) {
+                    row_dot_partial<NT>(p.type, buf + skew0 + rr * p.row_bytes, lig, G, act, nt, tok, acc);
+                    if (PAIR)
+                        row_dot_partial<NT>(p.type, buf + p.up_off + skew1 + rr * p.row_bytes, lig, G, act, nt, tok,
+                                            acc2);
+                }
+#pragma unroll
+                for (int s = 0; s < NT; ++s) {
+                    if (s < nt) {
+                        float v = group_sum_rt(acc[s], G);
+                        if (PAIR) v = __fmul_rn(silu_fast(v), group_sum_rt(acc2[s], G));
+                        if (active && lig == (s & (G - 1))) p.out[(size_t)asg[s] * p.N + r + rr] = v;
+                    }
+                }
+            }
+            pipe.release();
+            if (lane == 0) issue_next(p, pipe);
+        }
+    }
+};
+
+}  // namespace dc

@@ -12,6 +12,7 @@
 
 #include "dc_common.cuh"
 #include "dc_internal.h"
+#include "dc_stream.cuh"
 
 using namespace dc;
 
@@ -33,47 +34,6 @@ int dc_launch_quantize_q8k(dc_ctx* ctx, const float* x, int rows, int K, uint8_t
 }
 
 // ------------------------------------------------------------------- GEMV
-struct GemvParams {
-    dc_gemv_seg seg[3];
-    int n_seg;
-    int rpst[3];      // rows per pipeline stage, per segment
-    int total_rows;   // flattened over segments (pairs count once for SwiGLU)
-    int epi;
-    const uint8_t* act_q8;
-    int T, K;
-    uint32_t stage_bytes;
-    uint32_t up_off;  // SwiGLU: offset of the up rows inside a stage
-    unsigned long long* argmax;
-    int* err;
-};
-
-// Walks a warp's contiguous flattened row range stage by stage.
-struct StageIter {
-    int cur, end;
-    __device__ __forceinline__ bool next(const GemvParams& p, int& seg, int& local, int& n) {
-        if (cur >= end) return false;
-        int s = 0, base = 0;
-        const int nseg = p.epi == DC_EPI_SWIGLU ? 1 : p.n_seg;
-        while (s + 1 < nseg && cur >= base + p.seg[s].n_rows) {
-            base += p.seg[s].n_rows;
-            ++s;
-        }
-        seg = s;
-        local = cur - base;
-        int lim = min(end, base + p.seg[s].n_rows);
-        n = min(p.rpst[s], lim - cur);
-        cur += n;
-        return true;
-    }
-};
-
-__device__ __forceinline__ unsigned long long argmax_key(float v, int row) {
-    uint32_t u = __float_as_uint(v);
-    if (v != v) u = 0;  // NaN never wins
-    else u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)row);
-}
-
 template <int NT>
 __global__ void __launch_bounds__(DC_WARPS * 32) k_gemv(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -85,24 +45,10 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_gemv(const GemvParams p) {
 
     WarpPipe<DC_NSTAGE> pipe;
     pipe.init(bufs, bars, p.stage_bytes, p.err);
-
-    const int gw = blockIdx.x * DC_WARPS + warp, nw = gridDim.x * DC_WARPS;
-    const int r0 = (int)((long long)gw * p.total_rows / nw), r1 = (int)((long long)(gw + 1) * p.total_rows / nw);
-    StageIter prod{r0, r1}, cons{r0, r1};
-
-    auto issue_next = [&]() {
-        int sg, lr, n;
-        if (!prod.next(p, sg, lr, n)) return;
-        const dc_gemv_seg& s = p.seg[sg];
-        const uint32_t bytes = (uint32_t)n * s.row_bytes;
-        if (p.epi == DC_EPI_SWIGLU)
-            pipe.issue2(s.w + (size_t)lr * s.row_bytes, p.seg[1].w + (size_t)lr * s.row_bytes, bytes, p.up_off);
-        else
-            pipe.issue(s.w + (size_t)lr * s.row_bytes, bytes);
-    };
+    GemvStream<DC_NSTAGE> st;
+    st.begin(p, blockIdx.x * DC_WARPS + warp, gridDim.x * DC_WARPS);
     // Weights do not depend on the previous kernel: start streaming before waiting for it.
-    if (lane == 0)
-        for (int s = 0; s < DC_NSTAGE; ++s) issue_next();
+    st.prefill(p, pipe, lane);
     pdl_launch_dependents();
     pdl_wait();
 
@@ -110,75 +56,7 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_gemv(const GemvParams p) {
     act.bind(act_base, p.T, p.K);
     act.fill(p.act_q8, p.T);
     __syncthreads();
-
-    int tok[NT];
-#pragma unroll
-    for (int s = 0; s < NT; ++s) tok[s] = s;
-    unsigned long long best[NT];
-#pragma unroll
-    for (int s = 0; s < NT; ++s) best[s] = 0ull;
-
-    int sg, lr, n;
-    while (cons.next(p, sg, lr, n)) {
-        const dc_gemv_seg& s = p.seg[sg];
-        const uint32_t buf = pipe.wait();
-        const int G = lanes_per_row(s.type, p.K);
-        const int rows_per_pass = 32 / G;
-        const int grp = lane / G, lig = lane % G;
-        const uint32_t skew = (uint32_t)(((uintptr_t)s.w + (size_t)lr * s.row_bytes) & 15);
-        const uint32_t skew_up =
-            p.epi == DC_EPI_SWIGLU ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
-        for (int r = 0; r < n; r += rows_per_pass) {
-            const int rr = r + grp;
-            const bool active = rr < n;
-            float acc[NT], acc2[NT];
-#pragma unroll
-            for (int t = 0; t < NT; ++t) acc[t] = acc2[t] = 0.0f;
-            if (active) {
-                row_dot_partial<NT>(s.type, buf + skew + rr * s.row_bytes, lig, G, act, p.T, tok, acc);
-                if (p.epi == DC_EPI_SWIGLU)
-                    row_dot_partial<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, lig, G, act, p.T, tok,
-                                        acc2);
-            }
-            // every lane runs the reductions; lane (t mod G) of the row's group stores token t
-#pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                if (t < p.T) {
-                    float v = group_sum_rt(acc[t], G);
-                    if (p.epi == DC_EPI_SWIGLU) {
-                        const float u = group_sum_rt(acc2[t], G);
-                        v = __fmul_rn(silu_fast(v), u);
-                    }
-                    if (active && lig == (t & (G - 1))) {
-                        const int row = lr + rr;
-                        float* o = s.out + (size_t)t * s.ldo + row;
-                        if (p.epi == DC_EPI_ACC) *o += v;
-                        else *o = v;
-                        if (p.argmax) {
-                            const unsigned long long k = argmax_key(v, row);
-                            best[t] = k > best[t] ? k : best[t];
-                        }
-                    }
-                }
-            }
-        }
-        pipe.release();
-        if (lane == 0) issue_next();
-    }
-    if (p.argmax) {
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            if (t < p.T) {
-                unsigned long long k = best[t];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    const unsigned long long ok = __shfl_xor_sync(0xffffffffu, k, o);
-                    k = ok > k ? ok : k;
-                }
-                if (lane == 0 && k) atomicMax(p.argmax + t, k);
-            }
-        }
-    }
+    st.template consume<NT>(p, pipe, act, lane);
 }
 
 static int rows_per_stage(int type, int K, int row_bytes) {

@@ -12,6 +12,7 @@
 #include "dc_common.cuh"
 #include "dc_internal.h"
 #include "dc_launch.cuh"
+#include "dc_stream.cuh"
 
 using namespace dc;
 
@@ -53,17 +54,42 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.x * 8 + warp;
-    if (p.wr && e < p.E) {
+    // logits: two experts per CTA, four warps per expert, each warp a quarter of the row
+    // with all of its loads issued before the first use
+    if (p.wr) {
+        __shared__ float s_part[8][DC_MAX_T];
+        const int e = blockIdx.x * 2 + (warp >> 2), quarter = warp & 3;
+        const int seg = p.H / 4;  // H is a multiple of 256
         float acc[DC_MAX_T];
 #pragma unroll
         for (int t = 0; t < DC_MAX_T; ++t) acc[t] = 0.0f;
-        const float* w = p.wr + (size_t)e * p.H;
-        for (int i = lane; i < p.H; i += 32) {
-            const float wv = w[i];
+        if (e < p.E) {
+            const float4* w4 = reinterpret_cast<const float4*>(p.wr + (size_t)e * p.H + quarter * seg);
+            for (int i0 = 0; i0 < seg / 4; i0 += 128) {
+                float4 wv[4];
 #pragma unroll
-            for (int t = 0; t < DC_MAX_T; ++t)
-                if (t < p.T) acc[t] = fmaf(wv, p.xn[(size_t)t * p.H + i], acc[t]);
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * 32 + lane;
+                    wv[j] = i < seg / 4 ? w4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int t = 0; t < DC_MAX_T; ++t) {
+                    if (t < p.T) {
+                        const float4* x4 = reinterpret_cast<const float4*>(p.xn + (size_t)t * p.H + quarter * seg);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int i = i0 + j * 32 + lane;
+                            if (i < seg / 4) {
+                                const float4 xv = x4[i];
+                                acc[t] = fmaf(wv[j].x, xv.x, acc[t]);
+                                acc[t] = fmaf(wv[j].y, xv.y, acc[t]);
+                                acc[t] = fmaf(wv[j].z, xv.z, acc[t]);
+                                acc[t] = fmaf(wv[j].w, xv.w, acc[t]);
+                            }
+                        }
+                    }
+                }
+            }
         }
 #pragma unroll
         for (int t = 0; t < DC_MAX_T; ++t) {
@@ -71,8 +97,15 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
                 float v = acc[t];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) p.logits[(size_t)t * p.E + e] = v;
+                if (lane == 0) s_part[warp][t] = v;
             }
+        }
+        __syncthreads();
+        if (threadIdx.x < 2 * p.T) {
+            const int which = threadIdx.x / p.T, t = threadIdx.x % p.T, ee = blockIdx.x * 2 + which;
+            if (ee < p.E)
+                p.logits[(size_t)t * p.E + ee] = (s_part[which * 4][t] + s_part[which * 4 + 1][t]) +
+                                                 (s_part[which * 4 + 2][t] + s_part[which * 4 + 3][t]);
         }
     }
     __threadfence();
@@ -191,35 +224,6 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
 }
 
 // --------------------------------------------------- expert matmul kernel
-struct MoeMMParams {
-    const uint8_t* w0;    // gate (PAIR) or down
-    const uint8_t* w1;    // up (PAIR)
-    int type, row_bytes, N /*rows per expert*/, K;
-    const uint8_t* act_q8;  // Q8_K rows: tokens (PAIR) or assignments (down)
-    int act_rows, top_k;
-    int e_base;           // first expert stored in w0/w1 (expert-parallel shard)
-    const int* n_active;
-    const int32_t* uexp;
-    const int32_t* uoff;
-    const int32_t* uassign;
-    float* out;           // [assignment][N]
-    int rpst;
-    uint32_t stage_bytes, up_off;
-    int* err;
-};
-
-struct MoeIter {
-    int cur, end, N, rpst;
-    __device__ __forceinline__ bool next(int& u, int& r, int& n) {
-        if (cur >= end) return false;
-        u = cur / N;
-        r = cur - u * N;
-        n = min(rpst, min(N - r, end - cur));
-        cur += n;
-        return true;
-    }
-};
-
 template <int NT, bool PAIR>
 __global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -233,66 +237,14 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
     pdl_launch_dependents();
     pdl_wait();  // expert ids come from the router kernel: nothing can be fetched before this
 
-    const int U = *p.n_active;
-    const int total = U * p.N;
-    const int gw = blockIdx.x * DC_WARPS + warp, nw = gridDim.x * DC_WARPS;
-    const int r0 = (int)((long long)gw * total / nw), r1 = (int)((long long)(gw + 1) * total / nw);
-    MoeIter prod{r0, r1, p.N, p.rpst}, cons{r0, r1, p.N, p.rpst};
-    const size_t estride = (size_t)p.N * p.row_bytes;
-
-    auto issue_next = [&]() {
-        int u, r, n;
-        if (!prod.next(u, r, n)) return;
-        const size_t off = (size_t)(p.uexp[u] - p.e_base) * estride + (size_t)r * p.row_bytes;
-        if (PAIR) pipe.issue2(p.w0 + off, p.w1 + off, (uint32_t)n * p.row_bytes, p.up_off);
-        else pipe.issue(p.w0 + off, (uint32_t)n * p.row_bytes);
-    };
-    if (lane == 0)
-        for (int s = 0; s < DC_NSTAGE; ++s) issue_next();
-
+    MoeStream<DC_NSTAGE, PAIR> st;
+    st.begin(p, *p.n_active, blockIdx.x * DC_WARPS + warp, gridDim.x * DC_WARPS);
+    st.prefill(p, pipe, lane);
     ActSmem act;
     act.bind(act_base, p.act_rows, p.K);
     act.fill(p.act_q8, p.act_rows);
     __syncthreads();
-
-    const int G = lanes_per_row(p.type, p.K);
-    const int rows_per_pass = 32 / G, grp = lane / G, lig = lane % G;
-    int u, r, n;
-    while (cons.next(u, r, n)) {
-        const uint32_t buf = pipe.wait();
-        const size_t off = (size_t)(p.uexp[u] - p.e_base) * estride + (size_t)r * p.row_bytes;
-        const uint32_t skew0 = (uint32_t)(((uintptr_t)p.w0 + off) & 15);
-        const uint32_t skew1 = PAIR ? (uint32_t)(((uintptr_t)p.w1 + off) & 15) : 0u;
-        const int a0 = p.uoff[u], nt = min(NT, p.uoff[u + 1] - a0);
-        int tok[NT], asg[NT];
-#pragma unroll
-        for (int s = 0; s < NT; ++s) {
-            asg[s] = s < nt ? p.uassign[a0 + s] : 0;
-            tok[s] = PAIR ? asg[s] / p.top_k : asg[s];
-        }
-        for (int rr0 = 0; rr0 < n; rr0 += rows_per_pass) {
-            const int rr = rr0 + grp;
-            const bool active = rr < n;
-            float acc[NT], acc2[NT];
-#pragma unroll
-            for (int s = 0; s < NT; ++s) acc[s] = acc2[s] = 0.0f;
-            if (active) {
-                row_dot_partial<NT>(p.type, buf + skew0 + rr * p.row_bytes, lig, G, act, nt, tok, acc);
-                if (PAIR)
-                    row_dot_partial<NT>(p.type, buf + p.up_off + skew1 + rr * p.row_bytes, lig, G, act, nt, tok, acc2);
-            }
-#pragma unroll
-            for (int s = 0; s < NT; ++s) {
-                if (s < nt) {
-                    float v = group_sum_rt(acc[s], G);
-                    if (PAIR) v = __fmul_rn(silu_fast(v), group_sum_rt(acc2[s], G));
-                    if (active && lig == (s & (G - 1))) p.out[(size_t)asg[s] * p.N + r + rr] = v;
-                }
-            }
-        }
-        pipe.release();
-        if (lane == 0) issue_next();
-    }
+    st.template consume<NT>(p, pipe, act, lane);
 }
 
 template <int NT, bool PAIR>
@@ -387,7 +339,7 @@ int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_ex
     p.uexp = rt->uexp;
     p.uoff = rt->uoff;
     p.uassign = rt->uassign;
-    return dc_launch(ctx, "k_router", k_router, dim3(wr ? (p.E + 7) / 8 : 1), dim3(256), 0, p);
+    return dc_launch(ctx, "k_router", k_router, dim3(wr ? (p.E + 1) / 2 : 1), dim3(256), 0, p);
 }
 
 // ------------------------------------------------------------ combine

@@ -380,25 +380,27 @@ def _decoder_parity(ctx, oracle, cfg, sigma, n_prompt, n_decode, n_run, prompt_s
 
 @pytest.mark.parametrize("moe", [False, True])
 def test_decoder_against_cpu_reference(ctx, oracle, moe):
-    """Small decoder end to end: prefill (chunk of 16 + ragged tail), host-loop decode, device-resident
-    decode, against the CPU decoder built from the oracle's ops.
+    """Small decoder end to end against the CPU decoder built from the oracle's ops: prefill (chunk of
+    16 + ragged tail), host-loop decode, device-resident decode.
 
-    Gate: logits max-abs-rel 1e-2, greedy tokens identical wherever the top-2 margin exceeds the
-    tolerance.  CPU and GPU add floats in different orders (~1e-7), and a value on a Q8_K rounding
-    boundary can then quantise differently; one such flip moves one activation by 1/127 of its
-    block maximum, which in a 512-wide two-layer model is ~1e-2 of the logit range by itself and
-    stays in the KV cache for the rest of the sequence.  Three prompts are run: at least two must
-    meet 1e-2 on every step, every step of every prompt must stay within 5e-2, and the token rule is
-    applied to every step."""
-    good = 0
-    for prompt_seed in (7, 8, 9):
-        m, prompt, nxt, errs, agree, decided = _decoder_parity(ctx, oracle, tiny_cfg(moe), 0.05, 21, 6, 5, prompt_seed)
-        assert max(errs) < 5e-2, errs
+    Gate: logits max-abs-rel 1e-2; greedy tokens identical wherever the top-2 margin exceeds it.
+    CPU and GPU add floats in different orders (~1e-7 apart), and a value that sits on a Q8_K
+    rounding boundary can then quantise differently on the two sides.  One such flip moves one
+    activation by 1/127 of its block maximum; in a 512-wide two-layer model that alone is ~1e-2 of
+    the logit range, and when it lands in a K or V row it stays in the cache for the rest of the
+    sequence (measured: steps agree to ~2e-7 until a flip, then sit at ~1.5e-2).  So several
+    independent sequences are run: the median sequence must agree to 1e-5, at least three quarters
+    must meet 1e-2 on every step, none may exceed 5e-2, and the token rule holds on every step."""
+    worst = []
+    for prompt_seed in range(8):
+        m, prompt, nxt, errs, agree, decided = _decoder_parity(ctx, oracle, tiny_cfg(moe), 0.05, 19, 2, 2, prompt_seed)
         assert agree == decided
-        good += int(max(errs) < 1e-2)
-        if prompt_seed != 9:
+        worst.append(max(errs))
+        if prompt_seed != 7:
             m.close()
-    assert good >= 2
+    assert max(worst) < 5e-2, worst
+    assert sum(w < 1e-2 for w in worst) >= 6, worst
+    assert np.median(worst) < 1e-5, worst
     # graphs and eager launches give identical tokens
     m.set_option("graphs", 0)
     seq2 = m.seq_alloc()
@@ -415,6 +417,7 @@ def test_decoder_slice_at_full_width(ctx, oracle):
     m, prompt, nxt, errs, agree, decided = _decoder_parity(ctx, oracle, cfg, 0.02, 37, 3, 3)
     oracle.set_threads(1)
     assert max(errs) < 1e-2, errs
+    assert np.median(errs) < 1e-3, errs
     assert agree == decided
     m.close()
 
