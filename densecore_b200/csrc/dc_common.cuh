@@ -270,13 +270,15 @@ struct ActSmem {
         bs = d + T * nb * 4;
     }
     // Cooperative fill by the whole CTA from native Q8_K rows (row stride nb*292).
+    // CG: read through L2 (the rows were written by other SMs during this kernel).
+    template <bool CG = false>
     __device__ __forceinline__ void fill(const uint8_t* q8, int T) {
         const int words_per_row = nb * 73;  // 292/4
         const uint32_t* src = reinterpret_cast<const uint32_t*>(q8);
         for (int i = threadIdx.x; i < T * words_per_row; i += blockDim.x) {
             const int t = i / words_per_row, w = i - t * words_per_row;
             const int b = w / 73, o = w - b * 73;
-            const uint32_t v = src[i];
+            const uint32_t v = CG ? __ldcg(src + i) : src[i];
             uint32_t dst;
             if (o == 0) dst = d + (t * nb + b) * 4;
             else if (o <= 64) dst = qs + t * K + b * 256 + (o - 1) * 4;

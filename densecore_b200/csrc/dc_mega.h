@@ -1,0 +1,57 @@
+// Parameters of the persistent decode kernel (mega.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#define MG_THREADS 512
+#define MG_WARPS 16
+#define MG_NSTAGE 3
+#define MG_STAGE 2560   // bytes per pipeline stage of one warp
+#define MG_MAX_T 4
+#define MG_MAX_E 256
+#define MG_MAX_K 16
+
+struct MegaLayer {
+    const float *attn_norm, *q_norm, *k_norm, *ffn_norm, *router;
+    const uint8_t *wq, *wk, *wv, *wo, *gate, *up, *down;
+    int wq_type, wk_type, wv_type, wo_type, gate_type, down_type;
+    int wq_rb, wk_rb, wv_rb, wo_rb, gate_rb, down_rb;   // row bytes
+    __half *k_arena, *v_arena;                           // this layer's planes
+};
+
+struct MegaParams {
+    int n_layer, H, n_head, n_kv, vocab, E, top_k, F, T;
+    float eps, scale, routed_scale;
+    const MegaLayer* layers;       // device array [n_layer]
+    const uint8_t* tok_embd;
+    int embd_type, embd_row_bytes;
+    const float* out_norm;
+    const uint8_t* out_w;
+    int out_type, out_rb;
+    // step inputs / outputs
+    int32_t *tokens, *seq_ids, *positions, *out_tokens;
+    unsigned long long* argmax_keys;
+    int32_t* history;
+    int* history_len;
+    int history_cap, feedback, n_steps;
+    const int32_t* block_tables;
+    int max_blocks;
+    const float* cos_sin;
+    int max_pos;
+    // global scratch shared by the CTAs
+    float *xa, *xb, *qkv, *h, *dn, *router_logits, *logits;
+    float *bmax, *part_acc, *part_d;
+    int* tickets;
+    uint8_t* q8_attn;
+    int32_t* route_ids;            // copies of the last layer's routing, for callers
+    float* route_w;
+    int nsplit, s_keys;            // attention runs per (token, kv head); keys a run can hold
+    // sync
+    unsigned* bar_counter;
+    int* err;
+    // dynamic shared memory offsets
+    uint32_t off_pipe, off_act, off_xs, off_sc, smem_bytes;
+    // rows per pipeline stage
+    int rpst_q, rpst_k, rpst_v, rpst_o, rpst_gate, rpst_down, rpst_out;
+    uint32_t up_off;
+};

@@ -62,6 +62,10 @@ struct dc_model {
     int ep_lo = 0, ep_hi = 0;    // experts stored on this GPU
     int32_t* h_stage = nullptr;  // pinned, 1024 ints
     int stage_slot = 0;
+    // persistent decode kernel (mega.cu)
+    void* mega_layers = nullptr;     // device array of MegaLayer
+    unsigned* mega_counter = nullptr;
+    bool use_mega = true;
     // expert parallel
     bool ep_ready = false;
     void* ep_comm = nullptr;     // ncclComm_t
@@ -72,6 +76,11 @@ struct dc_model {
 int dc_launch_synth_quantized(dc_ctx* ctx, int type, uint64_t seed, int64_t first_row, int64_t rows, int64_t K, float sigma,
                               uint8_t* out);
 int dc_launch_synth_f32(dc_ctx* ctx, uint64_t seed, int64_t n, float sigma, float offset, float* out);
+// ---- mega.cu ----
+struct MegaParams;
+bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why);
+int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback);
+int dc_mega_prepare(dc_model* m);
 // ---- ep.cu ----
 int dc_ep_allreduce(dc_model* m, float* buf, size_t n);
 void dc_ep_destroy(dc_model* m);

@@ -114,7 +114,7 @@ struct GemvStream {
                         if (active && lig == (t & (G - 1))) {
                             const int row = lr + rr;
                             float* o = s.out + (size_t)t * s.ldo + row;
-                            if (p.epi == DC_EPI_ACC) *o += v;
+                            if (p.epi == DC_EPI_ACC) *o = __ldcg(o) + v;  // L2 read: another SM may have written it
                             else *o = v;
                             if (p.argmax) {
                                 const unsigned long long k = argmax_key(v, row);

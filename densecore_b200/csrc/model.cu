@@ -16,6 +16,7 @@
 #include "dc_common.cuh"
 #include "dc_internal.h"
 #include "dc_kv.h"
+#include "dc_mega.h"
 #include "dc_model.h"
 
 #define DC_TRY(expr)                       \
@@ -342,6 +343,14 @@ static int upload_step_inputs(dc_model* m, const int32_t* tokens, const int32_t*
     return DC_B200_OK;
 }
 
+// The persistent kernel serves 1..4 decode streams of a single-GPU MoE model.
+static bool mega_ok(dc_model* m, int T) {
+    if (!m->use_mega) return false;
+    MegaParams p;
+    const char* why = "";
+    return dc_mega_plan(m, T, &p, &why);
+}
+
 static bool model_complete(dc_model* m, std::string* missing) {
     for (const std::string& n : tensor_names(m)) {
         TensorSlot s;
@@ -442,6 +451,8 @@ void dc_b200_model_destroy(dc_model* m) {
                     b.route_mem, b.cos_sin, b.verify_mem};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+    if (m->mega_layers) cudaFree(m->mega_layers);
+    if (m->mega_counter) cudaFree(m->mega_counter);
     if (m->h_stage) cudaFreeHost(m->h_stage);
     dc_kv_release(&m->kv);
     delete m;
@@ -527,6 +538,7 @@ int dc_b200_model_finalize(dc_model* m) {
     std::string missing;
     if (!model_complete(m, &missing)) return dc_fail(m->ctx, DC_B200_MODEL_LOAD_FAILED, "finalize: tensor '%s' is missing", missing.c_str());
     if (m->cfg.ep_size > 1 && !m->ep_ready) return dc_fail(m->ctx, DC_B200_MODEL_LOAD_FAILED, "finalize: expert-parallel communicator not initialised");
+    if (!m->mega_layers) DC_TRY(dc_mega_prepare(m));
     m->finalized = true;
     return DC_B200_OK;
 }
@@ -604,7 +616,8 @@ int dc_b200_decode_step(dc_model* m, const int32_t* seqs, int n_seq, const int32
         pos[i] = s.len;
     }
     DC_TRY(upload_step_inputs(m, tokens_host, seqs, pos, n_seq));
-    DC_TRY(run_forward(m, n_seq, 2, false));
+    if (!m->prof && mega_ok(m, n_seq)) DC_TRY(dc_mega_run(m, n_seq, 1, false));
+    else DC_TRY(run_forward(m, n_seq, 2, false));
     int32_t* pin = m->h_stage + 1000;
     DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(pin, m->buf.out_tokens, (size_t)n_seq * 4, cudaMemcpyDeviceToHost, ctx->stream), "D2H tokens"));
     if (logits_host) DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(logits_host, m->buf.logits, (size_t)n_seq * m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream), "D2H logits"));
@@ -640,7 +653,9 @@ int dc_b200_decode_run(dc_model* m, const int32_t* seqs, int n_seq, const int32_
         cudaEventRecord(e0, ctx->stream);
     }
     int st = DC_B200_OK;
-    for (int i = 0; i < n_steps && st == DC_B200_OK; ++i) st = run_forward(m, n_seq, 2, true);
+    if (mega_ok(m, n_seq)) st = dc_mega_run(m, n_seq, n_steps, true);   // all steps in one cooperative launch
+    else
+        for (int i = 0; i < n_steps && st == DC_B200_OK; ++i) st = run_forward(m, n_seq, 2, true);
     if (ms_out) {
         cudaEventRecord(e1, ctx->stream);
         cudaEventSynchronize(e1);
@@ -704,6 +719,10 @@ int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
     if (!m || !name) return DC_B200_INVALID_ARGUMENT;
     if (!strcmp(name, "graphs")) {
         m->use_graphs = value != 0;
+        return DC_B200_OK;
+    }
+    if (!strcmp(name, "persistent")) {
+        m->use_mega = value != 0;
         return DC_B200_OK;
     }
     return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "unknown model option '%s'", name);
