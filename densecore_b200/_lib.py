@@ -107,6 +107,7 @@ def _signatures() -> dict:
         "dc_b200_decode_run": (i32, [vp, vp, i32, vp, i32, vp, C.POINTER(f32)]),
         "dc_b200_forward_chunk": (i32, [vp, i32, vp, i32, vp]),
         "dc_b200_model_logits_dev": (vp, [vp]),
+        "dc_b200_model_phase_timing": (i32, [vp, vp, i32]),
         "dc_b200_model_step_stats": (i32, [vp, pi, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
         "dc_b200_model_set_option": (i32, [vp, cstr, i32]),
         "dc_b200_model_profile_step": (i32, [vp, vp, i32, vp, i32, vp, vp, vp]),

@@ -49,6 +49,7 @@ struct MegaParams {
     // sync
     unsigned* bar_counter;
     int* err;
+    unsigned long long* phase_ns;  // optional [32] phase timing accumulators (CTA 0's view)
     // dynamic shared memory offsets
     uint32_t off_pipe, off_act, off_xs, off_sc, smem_bytes;
     // rows per pipeline stage

@@ -66,6 +66,7 @@ struct dc_model {
     void* mega_layers = nullptr;     // device array of MegaLayer
     unsigned* mega_counter = nullptr;
     bool use_mega = true;
+    bool mega_timing = false;
     // expert parallel
     bool ep_ready = false;
     void* ep_comm = nullptr;     // ncclComm_t

@@ -630,6 +630,22 @@ __device__ __forceinline__ void route_phase(const MegaParams& p, MegaShared& sh)
 }
 
 // ------------------------------------------------------------ the kernel
+__device__ __forceinline__ unsigned long long mg_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Optional phase timing as seen by CTA 0: slot i accumulates the nanoseconds between
+// mark i-1 and mark i over all layers and steps.
+#define MG_MARK(i)                                              \
+    do {                                                        \
+        if (p.phase_ns && blockIdx.x == 0 && tid == 0) {        \
+            const unsigned long long _n = mg_now();             \
+            p.phase_ns[i] += _n - t_last;                       \
+            t_last = _n;                                        \
+        }                                                       \
+    } while (0)
+
 __device__ __forceinline__ GemvParams mg_qkv(const MegaParams& p, const MegaLayer& L) {
     GemvParams g = {};
     const int QD = p.n_head * 128, KD = p.n_kv * 128, QKV = QD + 2 * KD;
@@ -701,6 +717,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
     uint8_t* act_base = smem + p.off_act;
     const int QD = p.n_head * 128, A = p.T * p.top_k;
     unsigned epoch = 0;
+    unsigned long long t_last = mg_now();
     if (tid == 0) sh.have_moe = 0;
     __syncthreads();
 
@@ -716,47 +733,65 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
             const float* xin = (l & 1) ? p.xb : p.xa;
             float* xout = (l & 1) ? p.xa : p.xb;
             // ---- P0: hidden state, attn_norm, Q8_K, QKV rows
+            MG_MARK(0);
             assemble_x(p, sh, xs, xin, xout, l == 0);
             if (tid == 0) sh.have_moe = 0;
+            MG_MARK(1);
             ActSmem act;
             act.bind(act_base, p.T, p.H);
             norm_quant(p, sh, xs, L.attn_norm, act);
+            MG_MARK(2);
             sq.template consume<NT>(gq, pipe, act, lane);
+            MG_MARK(3);
             GemvParams go = mg_single(p, L.wo, L.wo_type, L.wo_rb, p.H, p.rpst_o, QD, DC_EPI_ACC, xout, p.H, nullptr);
             GemvStream<MG_NSTAGE> so;
             so.begin(go, gw, nw);
             so.prefill(go, pipe, lane);   // output-projection rows stream in during attention
             grid_barrier(p, epoch);
+            MG_MARK(4);
             // ---- P1 / P2: attention
             attn_scores_phase(p, L, sh, s_sc);
+            MG_MARK(5);
             grid_barrier(p, epoch);
+            MG_MARK(6);
             attn_pv_phase(p, L, sh, s_sc);
+            MG_MARK(7);
             grid_barrier(p, epoch);
+            MG_MARK(8);
             // ---- P3: output projection, x += Wo . attn
             act.bind(act_base, p.T, QD);
             act.template fill<true>(p.q8_attn, p.T);
             __syncthreads();
+            MG_MARK(9);
             so.template consume<NT>(go, pipe, act, lane);
+            MG_MARK(10);
             grid_barrier(p, epoch);
+            MG_MARK(11);
             // ---- P4: ffn_norm, Q8_K, router logits
             for (int e = tid; e < p.T * p.H; e += MG_THREADS) xs[e] = __ldcg(xout + e);
             __syncthreads();
             act.bind(act_base, p.T, p.H);
             norm_quant(p, sh, xs, L.ffn_norm, act);
+            MG_MARK(12);
             router_logits_phase(p, L, sh, xs);
+            MG_MARK(13);
             grid_barrier(p, epoch);
+            MG_MARK(14);
             // ---- P5: routing, gate/up + SwiGLU
             route_phase(p, sh);
+            MG_MARK(15);
             MoeMMParams mgu = mg_experts(p, sh, L.gate, L.up, L.gate_type, L.gate_rb, p.F, p.H, p.rpst_gate, p.h);
             MoeStream<MG_NSTAGE, true> sg;
             sg.begin(mgu, sh.n_active, gw, nw);
             sg.prefill(mgu, pipe, lane);
             sg.template consume<NT>(mgu, pipe, act, lane);
+            MG_MARK(16);
             MoeMMParams mdn = mg_experts(p, sh, L.down, nullptr, L.down_type, L.down_rb, p.H, p.F, p.rpst_down, p.dn);
             MoeStream<MG_NSTAGE, false> sd;
             sd.begin(mdn, sh.n_active, gw, nw);
             sd.prefill(mdn, pipe, lane);  // down rows stream in across the barrier
             grid_barrier(p, epoch);
+            MG_MARK(17);
             // ---- P6: h -> Q8_K, down rows
             ActSmem acth;
             acth.bind(act_base, A, p.F);
@@ -771,7 +806,9 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
                 }
             }
             __syncthreads();
+            MG_MARK(18);
             sd.template consume<NT>(mdn, pipe, acth, lane);
+            MG_MARK(19);
             if (l + 1 < p.n_layer) {
                 gq = mg_qkv(p, p.layers[l + 1]);
                 sq.begin(gq, gw, nw);
@@ -783,6 +820,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
                 slm.prefill(glm, pipe, lane);
             }
             grid_barrier(p, epoch);
+            MG_MARK(20);
         }
         // ---- final: last MoE output + residual, output norm, lm_head with arg-max keys
         assemble_x(p, sh, xs, (p.n_layer & 1) ? p.xb : p.xa, nullptr, false);
@@ -792,6 +830,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
         norm_quant(p, sh, xs, p.out_norm, act);
         slm.template consume<NT>(glm, pipe, act, lane);
         grid_barrier(p, epoch);
+        MG_MARK(21);
         // greedy pick: first maximum wins (core/src/sampler/sampler.cpp:42-57)
         if (blockIdx.x == 0 && tid < p.T) {
             const unsigned long long k = __ldcg(p.argmax_keys + tid);
@@ -966,6 +1005,7 @@ int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback) {
     p.route_w = b.route.weights;
     p.bar_counter = m->mega_counter;
     p.err = m->ctx->d_err;
+    p.phase_ns = m->mega_timing ? (unsigned long long*)((uint8_t*)m->mega_counter + 64) : nullptr;
     int st = dc_check_cuda(m->ctx, cudaMemsetAsync(m->mega_counter, 0, sizeof(unsigned), m->ctx->stream), "memset");
     if (st != DC_B200_OK) return st;
     m->last_launches = 1;
@@ -994,8 +1034,8 @@ int dc_mega_prepare(dc_model* m) {
         d.v_arena = m->kv.v_arena + m->kv.layer_elems * il;
     }
     cudaError_t e = cudaMalloc(&m->mega_layers, v.size() * sizeof(MegaLayer));
-    if (e == cudaSuccess) e = cudaMalloc((void**)&m->mega_counter, 256);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&m->mega_counter, 512);
     if (e == cudaSuccess) e = cudaMemcpy(m->mega_layers, v.data(), v.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemset(m->mega_counter, 0, 256);
+    if (e == cudaSuccess) e = cudaMemset(m->mega_counter, 0, 512);
     return dc_check_cuda(m->ctx, e, "persistent decode set-up");
 }

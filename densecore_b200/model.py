@@ -190,3 +190,13 @@ class Model:
             if name and launches[i]:
                 out[name.decode()] = (float(ms[i]), int(launches[i]), float(nbytes[i]))
         return out
+
+    PHASES = ["(outside)", "x assemble", "attn_norm+q8", "qkv rows", "barrier", "scores", "barrier", "pv+merge", "barrier",
+              "attn q8 fill", "o-proj rows", "barrier", "ffn_norm+q8", "router logits", "barrier", "top-k+buckets",
+              "gate/up rows", "barrier", "h q8", "down rows", "barrier", "lm_head+barrier"]
+
+    def phase_timing(self):
+        """Nanoseconds per phase boundary accumulated by the persistent kernel (option phase_timing=1)."""
+        out = np.zeros(len(self.PHASES), dtype=np.uint64)
+        self._check(_lib.lib().dc_b200_model_phase_timing(self.handle, _vp(out), out.size))
+        return dict(zip(range(len(self.PHASES)), zip(self.PHASES, out.tolist())))

@@ -234,6 +234,10 @@ DC_B200_API int dc_b200_decode_run(dc_model* m, const int32_t* seqs, int n_seq, 
  * batched target forward of a speculative verify step. */
 DC_B200_API int dc_b200_forward_chunk(dc_model* m, int seq, const int32_t* tokens_host, int n, float* logits_host);
 DC_B200_API void* dc_b200_model_logits_dev(dc_model* m);
+/* With model option "phase_timing" = 1 the persistent decode kernel accumulates, per phase
+ * boundary, the nanoseconds CTA 0 spent since the previous boundary (work and barrier waits
+ * separately); this reads the first n (<= 32) accumulators. */
+DC_B200_API int dc_b200_model_phase_timing(dc_model* m, uint64_t* ns_out, int n);
 /* Per-step counters of the last decode_run / decode_step: kernels launched per
  * step, bytes of weights and KV a step must read (algorithmic). */
 DC_B200_API int dc_b200_model_step_stats(dc_model* m, int* kernels_per_step, double* weight_bytes_per_step,
