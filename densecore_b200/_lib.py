@@ -71,6 +71,7 @@ def _signatures() -> dict:
         "dc_b200_quantize_q8k_dev": (i32, [vp, vp, i32, i32, vp]),
         "dc_b200_mul_mat": (i32, [vp, vp, vp, i32, vp]),
         "dc_b200_mul_mat_dev": (i32, [vp, vp, vp, i32, vp]),
+        "dc_b200_mul_mat_dev_noalloc": (i32, [vp, vp, vp, i32, vp]),
         "dc_b200_mul_mat_block_sums": (i32, [vp, vp, vp, i32, vp, vp]),
         "dc_b200_alloc_device": (i32, [vp, sz, pp]),
         "dc_b200_free_device": (i32, [vp, vp]),

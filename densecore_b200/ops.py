@@ -106,6 +106,13 @@ class Context:
         self._check(_lib.lib().dc_b200_mul_mat(self.handle, w.handle, _vp(x), M, _vp(y)))
         return y
 
+    def mul_mat_dev(self, w: Weight, x_dev: int, M: int, y_dev: int, noalloc: bool = False):
+        """Device-pointer form: x_dev [M, K] f32 and y_dev [M, N] f32 are addresses from alloc().
+        noalloc=True takes the entry point whose Q8_K scratch is built into the library
+        (M <= 16, K <= 16384; performs no allocation)."""
+        fn = _lib.lib().dc_b200_mul_mat_dev_noalloc if noalloc else _lib.lib().dc_b200_mul_mat_dev
+        self._check(fn(self.handle, w.handle, C.c_void_p(x_dev), int(M), C.c_void_p(y_dev)))
+
     def mul_mat_block_sums(self, w: Weight, x: np.ndarray):
         x = np.ascontiguousarray(np.atleast_2d(x), dtype=np.float32)
         M, K = x.shape

@@ -98,6 +98,21 @@ DC_B200_API int dc_b200_quantize_q8k_dev(dc_ctx* ctx, const float* x_dev, int ro
  * core/src/llm/matmul/userdata.h:14). */
 DC_B200_API int dc_b200_mul_mat(dc_ctx* ctx, const dc_weight* w, const float* x_host, int M, float* y_host);
 DC_B200_API int dc_b200_mul_mat_dev(dc_ctx* ctx, const dc_weight* w, const float* x_dev, int M, float* y_dev);
+/* The same product for callers that may not allocate (no counterpart in
+ * DenseCore; added for hosts that forbid allocator calls on the compute path:
+ * op callbacks running under a fixed-buffer graph executor, serving loops that
+ * must not take the CUDA allocator lock after warm-up, code inside a stream
+ * capture).  x_dev [M, K] and y_dev [M, N] are device buffers of the caller;
+ * the Q8_K form of x lives in a 299,008-byte array built into the library
+ * (each GPU that loads the library keeps it until exit).  Limits: M <= 16 and
+ * K <= 16384, larger shapes are refused with DC_B200_UNSUPPORTED.  No
+ * cudaMalloc/cudaFree or allocating routine is called.  The first call on a
+ * GPU looks up the array's device address (cudaGetSymbolAddress); make that
+ * call before any stream capture begins.  All calls on a GPU share the array
+ * and it keeps the previous call's contents (each call overwrites what it
+ * reads), so two calls whose kernels can overlap on the GPU, e.g. from two
+ * contexts or streams, race: serialise them.  Enqueues on the context's stream. */
+DC_B200_API int dc_b200_mul_mat_dev_noalloc(dc_ctx* ctx, const dc_weight* w, const float* x_dev, int M, float* y_dev);
 /* Parity aid: the exact int32 block sums the kernel forms, I[M][N][K/256] and
  * (Q4_K only, else may be NULL) Mn[M][N][K/256]; these are the quantities the
  * reference's vec_dot kernels agree on bit for bit
