@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libdc_b200.so")
+# DC_B200_LIB points at another build of the same library (A/B timing of two builds)
+LIB_PATH = os.environ.get("DC_B200_LIB") or os.path.join(PKG, "libdc_b200.so")
 
 OK = 0
 STATUS_NAMES = {

@@ -45,7 +45,10 @@ def nvcc() -> str:
     return "nvcc"
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, out: str | None = None, extra: list[str] | None = None) -> str:
+    """out / extra: build a variant (extra nvcc flags) to another path, e.g. for A/B timing."""
+    if out or extra:
+        return _build_variant(out or LIB, extra or [])
     if not force and not _stale():
         return LIB
     objs = []
@@ -70,6 +73,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
     link = [nvcc(), "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lcuda", "-ldl"]
     subprocess.check_call(link)
     return LIB
+
+
+def _build_variant(out: str, extra: list[str]) -> str:
+    import tempfile
+    tmp = tempfile.mkdtemp(prefix="dcb200_")
+    objs, procs = [], []
+    for src in sources():
+        obj = os.path.join(tmp, os.path.basename(src)[:-3] + ".o")
+        cmd = [nvcc(), *NVCC_FLAGS, *extra, "-I", os.path.join(ROOT, "include"), "-c", src, "-o", obj]
+        procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        objs.append(obj)
+    for p in procs:
+        o, _ = p.communicate()
+        if p.returncode != 0:
+            raise RuntimeError(o)
+    subprocess.check_call([nvcc(), "-shared", "-o", out, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lcuda", "-ldl"])
+    return out
 
 
 if __name__ == "__main__":

@@ -20,6 +20,13 @@
 // Bounded waits: every wait on an mbarrier gives up after this many polls,
 // records an error code in the context's device error word and carries on, so
 // no kernel can hang the GPU.
+// Hot bodies shared by several call sites (row dots, stream loops, phases of the persistent
+// kernel) are inlined by default; -DDC_HOT_OUTLINE compiles one out-of-line copy of each.
+#ifdef DC_HOT_OUTLINE
+#define DC_HOT __noinline__
+#else
+#define DC_HOT __forceinline__
+#endif
 #define DC_WAIT_LIMIT (1u << 22)
 #define DC_ERR_MBAR_TIMEOUT 1
 
@@ -258,30 +265,41 @@ __device__ __forceinline__ void quantize_block_q8k_warp(const float* __restrict_
 struct ActSmem {
     uint32_t qs, d, bs;  // shared addresses
     int K, nb;
+    uint32_t rs;         // bytes between the int8 rows of two tokens
+    // The int8 codes are stored in 64-byte chunks 80 bytes apart: the lanes of a warp read
+    // chunks that are multiples of 64 values apart, and a stride of 80 bytes (20 banks) spreads
+    // those reads over all 32 banks instead of piling them onto two.
+    __host__ __device__ __forceinline__ static size_t row_stride(int K) { return (size_t)(K / 64) * 80; }
     __host__ __device__ __forceinline__ static size_t bytes(int T, int K) {
         const int nb = K / DC_QK_K;
-        return (size_t)T * K + (size_t)T * nb * 4 + (size_t)T * nb * 32;
+        return (size_t)T * row_stride(K) + (size_t)T * nb * 4 + (size_t)T * nb * 32;
     }
     __device__ __forceinline__ void bind(uint8_t* base, int T, int K_) {
         K = K_;
         nb = K_ / DC_QK_K;
+        rs = (uint32_t)row_stride(K_);
         qs = smem_u32(base);
-        d = qs + T * K;
+        d = qs + T * rs;
         bs = d + T * nb * 4;
     }
+    // shared address of code e (0 <= e < K) of token row t
+    __device__ __forceinline__ uint32_t q(int t, int e) const { return qs + t * rs + (e >> 6) * 80 + (e & 63); }
     // Cooperative fill by the whole CTA from native Q8_K rows (row stride nb*292).
     // CG: read through L2 (the rows were written by other SMs during this kernel).
     template <bool CG = false>
     __device__ __forceinline__ void fill(const uint8_t* q8, int T) {
         const int words_per_row = nb * 73;  // 292/4
         const uint32_t* src = reinterpret_cast<const uint32_t*>(q8);
-        for (int i = threadIdx.x; i < T * words_per_row; i += blockDim.x) {
+        // CG readers are many CTAs reading the same rows at once: each starts somewhere else
+        const int total = T * words_per_row, rot = CG ? (int)((blockIdx.x * 97u) % (unsigned)total) : 0;
+        for (int il = threadIdx.x; il < total; il += blockDim.x) {
+            const int i = CG ? (il + rot) % total : il;
             const int t = i / words_per_row, w = i - t * words_per_row;
             const int b = w / 73, o = w - b * 73;
             const uint32_t v = CG ? __ldcg(src + i) : src[i];
             uint32_t dst;
             if (o == 0) dst = d + (t * nb + b) * 4;
-            else if (o <= 64) dst = qs + t * K + b * 256 + (o - 1) * 4;
+            else if (o <= 64) dst = q(t, b * 256 + (o - 1) * 4);
             else dst = bs + (t * nb + b) * 32 + (o - 65) * 4;
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(v));
         }
@@ -294,7 +312,7 @@ __device__ __forceinline__ void quantize_block_q8k_to_act(const float (&v)[8], c
     uint32_t w0, w1, bw;
     float d;
     q8k_block_core(v, lane, w0, w1, bw, d);
-    const uint32_t qa = act.qs + t * act.K + b * 256 + 8 * lane;
+    const uint32_t qa = act.q(t, b * 256 + 8 * lane);
     asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(qa), "r"(w0), "r"(w1));
     if ((lane & 3) == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(act.bs + (t * act.nb + b) * 32 + (lane >> 2) * 4), "r"(bw));
     if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(act.d + (t * act.nb + b) * 4), "f"(d));
@@ -384,12 +402,14 @@ __device__ __forceinline__ void q6k_load_item(uint32_t row, int b, int j, int t,
     for (int qd = 0; qd < 4; ++qd) it.sc[qd] = lds_s8(s + 2 * qd);
     it.d = fp16_bits_to_float((uint16_t)lds16(blk + 208));
 }
-// yq: shared address of the activation int8 at element 256b + 128j + 8t; quadrant stride 32.
+// yq: shared address of the activation code at element 256b + 128j + 8t.  Quadrant qd
+// is 32*qd elements further on: same 64-value chunk for odd qd, next chunk (80 bytes on) for qd >= 2.
 __device__ __forceinline__ int q6k_item_int(const Q6Item& it, uint32_t yq) {
     int I = 0;
 #pragma unroll
     for (int qd = 0; qd < 4; ++qd) {
-        const uint32_t y0 = lds32(yq + 32 * qd), y1 = lds32(yq + 32 * qd + 4);
+        const uint32_t a = yq + (qd >> 1) * 80 + (qd & 1) * 32;
+        const uint32_t y0 = lds32(a), y1 = lds32(a + 4);
         int s = __dp4a((int)it.q[2 * qd], (int)y0, 0);
         s = __dp4a((int)it.q[2 * qd + 1], (int)y1, s);
         I += it.sc[qd] * s;
@@ -410,7 +430,7 @@ __device__ __forceinline__ float group_sum(float v) {
 // arrays in shared memory used by token slot s (slots >= nt are skipped).
 // acc[] receives each lane's float partial; callers reduce with group_sum.
 template <int NT>
-__device__ __forceinline__ void row_dot_partial(int type, uint32_t row, int lane_in_group, int G, const ActSmem& act,
+__device__ DC_HOT void row_dot_partial(int type, uint32_t row, int lane_in_group, int G, const ActSmem& act,
                                                 int nt, const int (&tok)[NT], float (&acc)[NT]) {
     const int nb = act.nb;
     if (type == DC_TYPE_Q4_K) {
@@ -423,7 +443,7 @@ __device__ __forceinline__ void row_dot_partial(int type, uint32_t row, int lane
                 if (s < nt) {
                     const int t = tok[s];
                     int I, M;
-                    q4k_item_ints(it, act.qs + t * act.K + b * 256 + 64 * c, act.bs + (t * nb + b) * 32 + 8 * c, I, M);
+                    q4k_item_ints(it, act.q(t, b * 256 + 64 * c), act.bs + (t * nb + b) * 32 + 8 * c, I, M);
                     const float yd = __int_as_float(lds32(act.d + (t * nb + b) * 4));
                     acc[s] += yd * (it.d * (float)I - it.dmin * (float)M);
                 }
@@ -438,7 +458,7 @@ __device__ __forceinline__ void row_dot_partial(int type, uint32_t row, int lane
             for (int s = 0; s < NT; ++s) {
                 if (s < nt) {
                     const int t = tok[s];
-                    const int I = q6k_item_int(it, act.qs + t * act.K + b * 256 + 128 * j + 8 * tq);
+                    const int I = q6k_item_int(it, act.q(t, b * 256 + 128 * j + 8 * tq));
                     const float yd = __int_as_float(lds32(act.d + (t * nb + b) * 4));
                     acc[s] += (yd * it.d) * (float)I;
                 }
@@ -452,11 +472,16 @@ __device__ __forceinline__ float group_sum_rt(float v, int G) {
     return v;
 }
 
-// Lanes that cooperate on one row for a given type and K.
+// Lanes that cooperate on one row for a given type and K: one item per lane where the row
+// has that many items (measured: two items per lane and half-warp rows were ~30 % slower).
 __host__ __device__ inline int lanes_per_row(int type, int K) {
     const int items = (K / DC_QK_K) * (type == DC_TYPE_Q4_K ? 4 : 8);
     int g = 4;
+#ifdef DC_TWO_ITEMS_PER_LANE
+    while (2 * g < items && g < 32) g <<= 1;
+#else
     while (g < items && g < 32) g <<= 1;
+#endif
     return g;
 }
 

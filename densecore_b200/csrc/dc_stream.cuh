@@ -57,6 +57,13 @@ struct GemvStream {
         prod = StageIter{r0, r1};
         cons = StageIter{r0, r1};
     }
+    // Rebuilds the iterators of a stream whose first `inflight` stages were already issued
+    // (by prefill in an earlier phase), so that no iterator has to stay live in between.
+    __device__ __forceinline__ void resume(const GemvParams& p, int gw, int nw, int inflight) {
+        begin(p, gw, nw);
+        int sg, lr, n;
+        for (int i = 0; i < inflight; ++i) prod.next(p, sg, lr, n);
+    }
     // lane 0 only
     __device__ __forceinline__ void issue_next(const GemvParams& p, WarpPipe<NSTAGE>& pipe) {
         int sg, lr, n;
@@ -69,11 +76,15 @@ struct GemvStream {
             pipe.issue(s.w + (size_t)lr * s.row_bytes, bytes);
     }
     __device__ __forceinline__ void prefill(const GemvParams& p, WarpPipe<NSTAGE>& pipe, int lane) {
-        if (lane == 0)
+        if (lane == 0) {
+#pragma unroll 1
             for (int s = 0; s < NSTAGE; ++s) issue_next(p, pipe);
+        }
     }
-    template <int NT>
-    __device__ __forceinline__ void consume(const GemvParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
+    // SWIGLU = false leaves the paired gate/up path out of the generated code (callers that
+    // never stream pairs).
+    template <int NT, bool SWIGLU = true>
+    __device__ DC_HOT void consume(const GemvParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
         int tok[NT];
 #pragma unroll
         for (int s = 0; s < NT; ++s) tok[s] = s;
@@ -89,7 +100,7 @@ struct GemvStream {
             const int grp = lane / G, lig = lane % G;
             const uint32_t skew = (uint32_t)(((uintptr_t)s.w + (size_t)lr * s.row_bytes) & 15);
             const uint32_t skew_up =
-                p.epi == DC_EPI_SWIGLU ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
+                (SWIGLU && p.epi == DC_EPI_SWIGLU) ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
             for (int r = 0; r < n; r += rows_per_pass) {
                 const int rr = r + grp;
                 const bool active = rr < n;
@@ -98,7 +109,7 @@ struct GemvStream {
                 for (int t = 0; t < NT; ++t) acc[t] = acc2[t] = 0.0f;
                 if (active) {
                     row_dot_partial<NT>(s.type, buf + skew + rr * s.row_bytes, lig, G, act, p.T, tok, acc);
-                    if (p.epi == DC_EPI_SWIGLU)
+                    if ((SWIGLU && p.epi == DC_EPI_SWIGLU))
                         row_dot_partial<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, lig, G, act, p.T, tok,
                                             acc2);
                 }
@@ -107,7 +118,7 @@ struct GemvStream {
                 for (int t = 0; t < NT; ++t) {
                     if (t < p.T) {
                         float v = group_sum_rt(acc[t], G);
-                        if (p.epi == DC_EPI_SWIGLU) {
+                        if ((SWIGLU && p.epi == DC_EPI_SWIGLU)) {
                             const float u = group_sum_rt(acc2[t], G);
                             v = __fmul_rn(silu_fast(v), u);
                         }
@@ -174,8 +185,13 @@ struct MoeIter {
     }
 };
 
-template <int NSTAGE, bool PAIR>
+// PAIRMODE: 0 = single rows (down), 1 = gate/up pairs with SwiGLU, 2 = decided at run time
+// by p.w1 (one body serves both uses).
+template <int NSTAGE, int PAIRMODE>
 struct MoeStream {
+    __device__ __forceinline__ static bool is_pair(const MoeMMParams& p) {
+        return PAIRMODE == 2 ? p.w1 != nullptr : PAIRMODE == 1;
+    }
     MoeIter prod, cons;
     size_t estride;
     __device__ __forceinline__ void begin(const MoeMMParams& p, int U, int gw, int nw) {
@@ -185,54 +201,68 @@ struct MoeStream {
         cons = MoeIter{r0, r1, p.N, p.rpst};
         estride = (size_t)p.N * p.row_bytes;
     }
+    __device__ __forceinline__ void resume(const MoeMMParams& p, int U, int gw, int nw, int inflight) {
+        begin(p, U, gw, nw);
+        int u, r, n;
+        for (int i = 0; i < inflight; ++i) prod.next(u, r, n);
+    }
     __device__ __forceinline__ void issue_next(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe) {
         int u, r, n;
         if (!prod.next(u, r, n)) return;
         const size_t off = (size_t)(p.uexp[u] - p.e_base) * estride + (size_t)r * p.row_bytes;
-        if (PAIR) pipe.issue2(p.w0 + off, p.w1 + off, (uint32_t)n * p.row_bytes, p.up_off);
+        if (is_pair(p)) pipe.issue2(p.w0 + off, p.w1 + off, (uint32_t)n * p.row_bytes, p.up_off);
         else pipe.issue(p.w0 + off, (uint32_t)n * p.row_bytes);
     }
     __device__ __forceinline__ void prefill(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe, int lane) {
-        if (lane == 0)
+        if (lane == 0) {
+#pragma unroll 1
             for (int s = 0; s < NSTAGE; ++s) issue_next(p, pipe);
+        }
     }
     template <int NT>
-    __device__ __forceinline__ void consume(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
+    __device__ DC_HOT void consume(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
+        const bool pair = is_pair(p);
         const int G = lanes_per_row(p.type, p.K);
         const int rows_per_pass = 32 / G, grp = lane / G, lig = lane % G;
+        const int nhalf = pair ? 2 : 1;
         int u, r, n;
         while (cons.next(u, r, n)) {
             const uint32_t buf = pipe.wait();
             const size_t off = (size_t)(p.uexp[u] - p.e_base) * estride + (size_t)r * p.row_bytes;
             const uint32_t skew0 = (uint32_t)(((uintptr_t)p.w0 + off) & 15);
-            const uint32_t skew1 = PAIR ? (uint32_t)(((uintptr_t)p.w1 + off) & 15) : 0u;
+            const uint32_t skew1 = pair ? p.up_off + (uint32_t)(((uintptr_t)p.w1 + off) & 15) : 0u;
             const int a0 = p.uoff[u], nt = min(NT, p.uoff[u + 1] - a0);
             int tok[NT], asg[NT];
 #pragma unroll
             for (int s = 0; s < NT; ++s) {
                 asg[s] = s < nt ? p.uassign[a0 + s] : 0;
-                tok[s] = PAIR ? asg[s] / p.top_k : asg[s];
+                tok[s] = pair ? asg[s] / p.top_k : asg[s];
             }
             for (int rr0 = 0; rr0 < n; rr0 += rows_per_pass) {
                 const int rr = rr0 + grp;
                 const bool active = rr < n;
-                float acc[NT], acc2[NT];
+                float v[NT];
 #pragma unroll
-                for (int s = 0; s < NT; ++s) acc[s] = acc2[s] = 0.0f;
-                if (active) {
-                    row_dot_partial<NT>(p.type, buf + skew0 + rr * p.row_bytes, lig, G, act, nt, tok, acc);
-                    if (PAIR)
-                        row_dot_partial<NT>(p.type, buf + p.up_off + skew1 + rr * p.row_bytes, lig, G, act, nt, tok,
-                                            acc2);
-                }
+                for (int s = 0; s < NT; ++s) v[s] = 0.0f;
+                // gate row first, then (pairs) the up row of the same output through the same code
+#pragma unroll 1
+                for (int half = 0; half < nhalf; ++half) {
+                    float acc[NT];
 #pragma unroll
-                for (int s = 0; s < NT; ++s) {
-                    if (s < nt) {
-                        float v = group_sum_rt(acc[s], G);
-                        if (PAIR) v = __fmul_rn(silu_fast(v), group_sum_rt(acc2[s], G));
-                        if (active && lig == (s & (G - 1))) p.out[(size_t)asg[s] * p.N + r + rr] = v;
+                    for (int s = 0; s < NT; ++s) acc[s] = 0.0f;
+                    if (active)
+                        row_dot_partial<NT>(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, lig, G, act, nt, tok, acc);
+#pragma unroll
+                    for (int s = 0; s < NT; ++s) {
+                        if (s < nt) {
+                            const float sum = group_sum_rt(acc[s], G);
+                            v[s] = half ? __fmul_rn(silu_fast(v[s]), sum) : sum;
+                        }
                     }
                 }
+#pragma unroll
+                for (int s = 0; s < NT; ++s)
+                    if (s < nt && active && lig == (s & (G - 1))) p.out[(size_t)asg[s] * p.N + r + rr] = v[s];
             }
             pipe.release();
             if (lane == 0) issue_next(p, pipe);

@@ -184,12 +184,12 @@ __global__ void __launch_bounds__(256) k_block_sums(const uint8_t* __restrict__ 
                         const int b = i >> 2, c = i & 3;
                         Q4Item it;
                         q4k_load_item(row, b, c, it);
-                        q4k_item_ints(it, act.qs + t * K + b * 256 + 64 * c, act.bs + (t * nb + b) * 32 + 8 * c, I, M);
+                        q4k_item_ints(it, act.q(t, b * 256 + 64 * c), act.bs + (t * nb + b) * 32 + 8 * c, I, M);
                     } else {
                         const int b = i >> 3, j = (i >> 2) & 1, tq = i & 3;
                         Q6Item it;
                         q6k_load_item(row, b, j, tq, it);
-                        I = q6k_item_int(it, act.qs + t * K + b * 256 + 128 * j + 8 * tq);
+                        I = q6k_item_int(it, act.q(t, b * 256 + 128 * j + 8 * tq));
                     }
                 }
                 for (int o = 1; o < ipb; o <<= 1) {

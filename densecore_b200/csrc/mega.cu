@@ -24,6 +24,7 @@
 using namespace dc;
 
 #define MG_BAR_LIMIT (1u << 21)
+#define MG_MAX_RUN_BLOCKS 64
 #define DC_ERR_GRID_BARRIER 2
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
@@ -34,7 +35,7 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 
 // All CTAs of the (co-resident) grid meet here.  counter only grows during a
 // launch; the host zeroes it before the launch.
-__device__ __forceinline__ void grid_barrier(const MegaParams& p, unsigned& epoch) {
+__device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch) {
     __syncthreads();
     ++epoch;
     if (threadIdx.x == 0) {
@@ -52,6 +53,14 @@ __device__ __forceinline__ void grid_barrier(const MegaParams& p, unsigned& epoc
         __threadfence();
     }
     __syncthreads();
+}
+
+// Every CTA reads the same small arrays (hidden state, expert outputs, attention
+// output) at the same moment; walking them from a CTA-dependent starting point keeps
+// the 148 SMs off the same L2 lines.  Returns a multiple of 32 in [0, n).
+__device__ __forceinline__ int cta_rotation(int n) {
+    const int step = max(32, (n / (int)gridDim.x) & ~31);
+    return (int)(((long long)blockIdx.x * step) % n) & ~31;
 }
 
 // ---- token embedding element (same decode as k_embed) ----
@@ -89,6 +98,27 @@ __device__ __forceinline__ float embed_elem(const uint8_t* row, int type, int e)
     return reinterpret_cast<const float*>(row)[e];
 }
 
+// Eight consecutive elements of a token-embedding row; out of line and rolled, since it runs
+// once per step and its decode is long.
+struct Float8 {
+    float v[8];
+};
+__device__ __noinline__ Float8 embed_row8(const uint8_t* row, int type, int e0) {
+    Float8 r;
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+        const float x = embed_elem(row, type, e0 + i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j == i) r.v[j] = x;
+    }
+    return r;
+}
+
+// A q head sits in shared memory as four 32-dim quarters 36 floats apart: the four lanes of a
+// key read the same offset of different quarters, which then fall into different banks.
+#define MG_SQ_QUARTER 36
+
 // Shared state of one CTA that outlives a phase.
 struct MegaShared {
     int32_t ids[MG_MAX_T * MG_MAX_K];      // routing of the current layer (kept for the combine in the next P0)
@@ -97,100 +127,155 @@ struct MegaShared {
     int32_t uoff[MG_MAX_E + 1];
     int32_t uassign[MG_MAX_T * MG_MAX_K];
     int n_active;
-    int have_moe;                          // a MoE output is pending (added when x is next assembled)
-    double red[MG_WARPS][MG_MAX_T];
-    float scale[MG_MAX_T];
+    alignas(8) double red[MG_WARPS][MG_MAX_T];
+    alignas(8) double red2[32];            // sum of squares per (token, block)
     int wsum_a[MG_WARPS], wsum_c[MG_WARPS];
     // attention
-    float sq[8][128];
+    alignas(16) float sq[8][4 * MG_SQ_QUARTER];   // q heads; each 32-dim quarter padded (bank spread)
     float p[8][DC_KV_BLOCK];
     float m[8], d[8], alpha[8], suffix[8];
     int last;
+    MegaLayer layer[2];                    // descriptor of the current layer and the next one
+    // parameter blocks of the streaming phases (shared, so that no thread keeps a private copy)
+    GemvParams g_qkv, g_o, g_lm;
+    MoeMMParams m_gu, m_dn;
+    // per-step constants of this CTA's attention item
+    int32_t tbl[MG_MAX_RUN_BLOCKS];        // physical ids of the run's KV blocks
+    alignas(16) float cs[128];             // RoPE cos/sin row of the item's token
+    alignas(8) unsigned long long rkeys[MG_MAX_T][MG_MAX_E];   // routing keys (rank selection)
+    float sel[MG_MAX_T][MG_MAX_K];         // logits of the picks, in pick order
 };
 
-// x <- (layer 0: embedding rows) or (x_in + pending MoE combine), into shared xs[T][H];
-// this CTA also writes its interleaved share of x to x_out.  The combine adds the
-// assignments of a token one at a time in routing order into a zeroed sum
-// (core/src/backend/cpu_backend_moe_ops.cpp:1578-1597), then the residual add.
-__device__ __forceinline__ void assemble_x(const MegaParams& p, MegaShared& sh, float* xs, const float* x_in,
-                                           float* x_out, bool first_layer) {
-    const int H = p.H, T = p.T;
-    for (int e = threadIdx.x; e < T * H; e += MG_THREADS) {
-        const int t = e / H, dd = e - t * H;
-        float v;
-        if (first_layer) {
+// Dynamic shared memory the kernel may ask for: what the SM offers a CTA (227 KB) less the
+// kernel's static shared memory (MegaShared and its copy of the parameters).
+static constexpr uint32_t MG_DYN_LIMIT =
+    (227u * 1024u - (uint32_t)sizeof(MegaShared) - (uint32_t)sizeof(MegaParams) - 256u) & ~127u;
+
+// Hidden state -> RMSNorm -> Q8_K, one warp per (token, 256-value block), values held
+// in registers (lane l: 8 consecutive values).
+//   src 0: token-embedding rows (first layer)
+//   src 1: x_in + the pending MoE output: the token's assignments are added one at a time
+//          in routing order into a zeroed sum (core/src/backend/cpu_backend_moe_ops.cpp:1578-1597),
+//          then the residual add
+//   src 2: x_in as it is
+// The block's owner CTA also writes the assembled values to x_out.  Norm:
+// y = x / sqrt(mean(x^2) + eps) * w with the sum of squares in double
+// (core/src/llm/graph/decoder.cpp:268), then the Q8_K quantiser
+// (core/src/kernels/hwy/hwy_moe_quant.cc:103-144) straight into the activation layout;
+// xn (optional) receives the normed f32 rows in shared memory.  T * H/256 <= 32.
+// NPI (token, block) pairs per warp: T * H/256 <= 16 * NPI.
+template <int NPI>
+__device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, int src, const float* x_in, float* x_out,
+                                          const float* w, const ActSmem& act, float* xn) {
+    const int H = p.H, nb = H / DC_QK_K, pairs = p.T * nb;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float v[NPI][8];
+    float4 wv[NPI][2];
+#pragma unroll
+    for (int pi = 0; pi < NPI; ++pi) {
+        const int pr = warp + pi * MG_WARPS;
+        if (pr >= pairs) continue;
+        const int t = pr / nb, b = pr - t * nb, dd = b * DC_QK_K + 8 * lane;
+        // norm weights first: their load overlaps everything below
+        wv[pi][0] = *reinterpret_cast<const float4*>(w + dd);
+        wv[pi][1] = *reinterpret_cast<const float4*>(w + dd + 4);
+        if (src == 0) {
             int tok = __ldcg(p.tokens + t);
             if (tok < 0 || tok >= p.vocab) tok = 0;
-            v = embed_elem(p.tok_embd + (size_t)tok * p.embd_row_bytes, p.embd_type, dd);
+            const uint8_t* row = p.tok_embd + (size_t)tok * p.embd_row_bytes;
+            const Float8 e8 = embed_row8(row, p.embd_type, dd);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[pi][i] = e8.v[i];
         } else {
-            v = __ldcg(x_in + e);
-            if (sh.have_moe) {
-                float sum = 0.0f;
-                for (int k = 0; k < p.top_k; ++k) {
-                    const int a = t * p.top_k + k;
-                    const float w = sh.w[a];
-                    if (w == 0.0f) continue;
-                    sum = __fadd_rn(sum, __fmul_rn(w, __ldcg(p.dn + (size_t)a * H + dd)));
+            const float4 x0 = __ldcg(reinterpret_cast<const float4*>(x_in + (size_t)t * H + dd));
+            const float4 x1 = __ldcg(reinterpret_cast<const float4*>(x_in + (size_t)t * H + dd + 4));
+            v[pi][0] = x0.x; v[pi][1] = x0.y; v[pi][2] = x0.z; v[pi][3] = x0.w;
+            v[pi][4] = x1.x; v[pi][5] = x1.y; v[pi][6] = x1.z; v[pi][7] = x1.w;
+            if (src == 1) {
+                float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (int k0 = 0; k0 < p.top_k; k0 += 4) {
+                    float4 d0[4], d1[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {   // four experts' rows in flight
+                        const int k = min(k0 + j, p.top_k - 1);
+                        const float* dr = p.dn + (size_t)(t * p.top_k + k) * H + dd;
+                        d0[j] = __ldcg(reinterpret_cast<const float4*>(dr));
+                        d1[j] = __ldcg(reinterpret_cast<const float4*>(dr + 4));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (k0 + j < p.top_k) {
+                            const float wk = sh.w[t * p.top_k + k0 + j];
+                            if (wk != 0.0f) {
+                                sum[0] = __fadd_rn(sum[0], __fmul_rn(wk, d0[j].x));
+                                sum[1] = __fadd_rn(sum[1], __fmul_rn(wk, d0[j].y));
+                                sum[2] = __fadd_rn(sum[2], __fmul_rn(wk, d0[j].z));
+                                sum[3] = __fadd_rn(sum[3], __fmul_rn(wk, d0[j].w));
+                                sum[4] = __fadd_rn(sum[4], __fmul_rn(wk, d1[j].x));
+                                sum[5] = __fadd_rn(sum[5], __fmul_rn(wk, d1[j].y));
+                                sum[6] = __fadd_rn(sum[6], __fmul_rn(wk, d1[j].z));
+                                sum[7] = __fadd_rn(sum[7], __fmul_rn(wk, d1[j].w));
+                            }
+                        }
+                    }
                 }
-                v = __fadd_rn(v, sum);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[pi][i] = __fadd_rn(v[pi][i], sum[i]);
             }
         }
-        xs[e] = v;
-        if (x_out && (e % (int)gridDim.x) == (int)blockIdx.x) x_out[e] = v;
-    }
-    __syncthreads();
-}
-
-// RMSNorm of xs[T][H] in place (xs becomes the normed rows) and Q8_K blocks into act
-// (core/src/llm/graph/decoder.cpp:268; core/src/kernels/hwy/hwy_moe_quant.cc:103-144).
-__device__ __forceinline__ void norm_quant(const MegaParams& p, MegaShared& sh, float* xs, const float* w,
-                                           const ActSmem& act) {
-    const int H = p.H, T = p.T, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    double ss[MG_MAX_T];
-#pragma unroll
-    for (int t = 0; t < MG_MAX_T; ++t) ss[t] = 0.0;
-    for (int e = threadIdx.x; e < H; e += MG_THREADS) {
-#pragma unroll
-        for (int t = 0; t < MG_MAX_T; ++t)
-            if (t < T) {
-                const float v = xs[t * H + e];
-                ss[t] += (double)v * (double)v;
-            }
-    }
-#pragma unroll
-    for (int t = 0; t < MG_MAX_T; ++t) {
-        if (t < T) {
-            double s = ss[t];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) sh.red[warp][t] = s;
+        if (x_out && src != 2 && (pr % (int)gridDim.x) == (int)blockIdx.x) {
+            float* o = x_out + (size_t)t * H + dd;
+            *reinterpret_cast<float4*>(o) = make_float4(v[pi][0], v[pi][1], v[pi][2], v[pi][3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(v[pi][4], v[pi][5], v[pi][6], v[pi][7]);
         }
+        double ss = 0.0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += (double)v[pi][i] * (double)v[pi][i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) sh.red2[pr] = ss;
     }
     __syncthreads();
-    if (threadIdx.x < T) {
+#pragma unroll
+    for (int pi = 0; pi < NPI; ++pi) {
+        const int pr = warp + pi * MG_WARPS;
+        if (pr >= pairs) continue;
+        const int t = pr / nb, b = pr - t * nb;
         double tot = 0.0;
-        for (int i = 0; i < MG_WARPS; ++i) tot += sh.red[i][threadIdx.x];
+        for (int i = 0; i < nb; ++i) tot += sh.red2[t * nb + i];
         const float mean = (float)(tot / (double)H);
-        sh.scale[threadIdx.x] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < T * H; e += MG_THREADS) {
-        const int t = e / H, dd = e - t * H;
-        xs[e] = __fmul_rn(__fmul_rn(xs[e], sh.scale[t]), w[dd]);
-    }
-    __syncthreads();
-    const int nb = H / DC_QK_K;
-    for (int i = warp; i < T * nb; i += MG_WARPS) {
-        const int t = i / nb, b = i - t * nb;
-        const float4 a = reinterpret_cast<const float4*>(xs + t * H + b * DC_QK_K)[2 * lane];
-        const float4 c = reinterpret_cast<const float4*>(xs + t * H + b * DC_QK_K)[2 * lane + 1];
-        const float v[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
-        quantize_block_q8k_to_act(v, act, t, b, lane);
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
+        const float ww[8] = {wv[pi][0].x, wv[pi][0].y, wv[pi][0].z, wv[pi][0].w,
+                             wv[pi][1].x, wv[pi][1].y, wv[pi][1].z, wv[pi][1].w};
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(__fmul_rn(v[pi][i], scale), ww[i]);
+        if (xn) {
+            float* o = xn + t * H + b * DC_QK_K + 8 * lane;
+            *reinterpret_cast<float4*>(o) = make_float4(y[0], y[1], y[2], y[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(y[4], y[5], y[6], y[7]);
+        }
+        quantize_block_q8k_to_act(y, act, t, b, lane);
     }
     __syncthreads();
 }
 
 // ------------------------------------------------------------ attention
+__device__ __forceinline__ unsigned long long mg_now();
+#ifdef DC_MEGA_SUBMARKS
+#define MG_SUB(i)                                                             \
+    do {                                                                      \
+        if (p.phase_ns && blockIdx.x == 0 && threadIdx.x == 0) {              \
+            const unsigned long long _n = mg_now();                           \
+            p.phase_ns[i] += _n - sub_t;                                      \
+            sub_t = _n;                                                       \
+        }                                                                     \
+    } while (0)
+#define MG_SUB_BEGIN unsigned long long sub_t = mg_now()
+#else
+#define MG_SUB(i) do {} while (0)
+#define MG_SUB_BEGIN do {} while (0)
+#endif
 struct AttnItem {
     bool valid;
     int t, kvh, split, pos, ctx_len, n_blk, b0, b1;
@@ -214,6 +299,26 @@ __device__ __forceinline__ AttnItem attn_item(const MegaParams& p) {
     it.table = p.block_tables + (size_t)p.seq_ids[it.t] * p.max_blocks;
     return it;
 }
+
+// Once per step: the item of this CTA, the physical ids of its KV blocks and the
+// RoPE row of its token go to registers / shared memory, so the attention phases
+// of all layers start without dependent global loads.
+__device__ __forceinline__ AttnItem attn_step_setup(const MegaParams& p, MegaShared& sh) {
+    const AttnItem it = attn_item(p);
+    if (it.valid) {
+        for (int i = threadIdx.x; i < it.b1 - it.b0; i += MG_THREADS) sh.tbl[i] = it.table[it.b0 + i];
+        const int pos = min(it.pos, p.max_pos - 1);
+        if (threadIdx.x < 128) sh.cs[threadIdx.x] = p.cos_sin[(size_t)pos * 128 + threadIdx.x];
+    }
+    __syncthreads();
+    return it;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // One warp: RMSNorm over a 128-wide head (optional), RoPE on interleaved pairs.
 // Same steps as k_qknorm_rope_kv (core/src/llm/graph/decoder.cpp:1287-1343,
@@ -242,30 +347,83 @@ __device__ __forceinline__ void head_norm_rope(float (&v)[4], const float* nw, c
     }
 }
 
+// One K row slice (32 of 128 dims) of key kk of the run into registers.  The row of the token
+// being decoded (kpos == pos) is written by this CTA during the phase: it is flagged `late`
+// and fetched after the CTA barrier instead.
+__device__ __forceinline__ void mg_load_k(const MegaParams& p, const MegaLayer& L, const MegaShared& sh, const AttnItem& it,
+                                          int n_keys, int kk, int sub, float (&kf)[32], bool& valid, bool& late) {
+    const int blk = kk / DC_KV_BLOCK, kpos = (it.b0 + blk) * DC_KV_BLOCK + kk % DC_KV_BLOCK;
+    valid = kk < n_keys && kpos < it.ctx_len;
+    late = valid && kpos == it.pos;
+    if (valid && !late) {
+        const uint4* kp = reinterpret_cast<const uint4*>(
+            L.k_arena + (((size_t)sh.tbl[blk] * DC_KV_BLOCK + kk % DC_KV_BLOCK) * p.n_kv + it.kvh) * 128 + sub * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 u = __ldcg(kp + i);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h2[j]);
+                kf[i * 8 + 2 * j] = f.x;
+                kf[i * 8 + 2 * j + 1] = f.y;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) kf[i] = 0.0f;
+    }
+}
+
 // Phase 1: Q/K norm + RoPE, K/V of the new token into the paged cache (by the run
 // that owns its block), scores of this run into shared memory, block maxima to global.
-__device__ __forceinline__ void attn_scores_phase(const MegaParams& p, const MegaLayer& L, MegaShared& sh,
-                                                  float* s_sc) {
-    const AttnItem it = attn_item(p);
+// The run's V rows are requested here (16-byte async copies into vbuf) so that the
+// P.V phase finds them in shared memory.
+__device__ DC_HOT void attn_scores_phase(const MegaParams& p, const MegaLayer& L, MegaShared& sh,
+                                                  const AttnItem& it, float* s_sc, uint8_t* vbuf, int vcap_blocks) {
     if (!it.valid) return;
     const int g = p.n_head / p.n_kv, heads = p.n_head + 2 * p.n_kv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pos = min(it.pos, p.max_pos - 1);
-    const float* cs_row = p.cos_sin + (size_t)pos * 128;
     const float* qkv_t = p.qkv + (size_t)it.t * heads * 128;
     const bool owner = (it.pos / DC_KV_BLOCK) >= it.b0 && (it.pos / DC_KV_BLOCK) < it.b1;
+    const int nb_run = it.b1 - it.b0, n_keys = nb_run * DC_KV_BLOCK;
+    MG_SUB_BEGIN;
+    // ---- V rows of the run: block bb, slot s, 16 chunks of 16 bytes
+    {
+        const int nst = min(nb_run, vcap_blocks) * DC_KV_BLOCK * 16;
+        const uint32_t vb = smem_u32(vbuf);
+        for (int i = threadIdx.x; i < nst; i += MG_THREADS) {
+            const int bb = i >> 8, slot = (i >> 4) & 15, ch = i & 15;
+            const __half* src = L.v_arena + (((size_t)sh.tbl[bb] * DC_KV_BLOCK + slot) * p.n_kv + it.kvh) * 128 + ch * 8;
+            cp_async16(vb + (uint32_t)i * 16, src);
+        }
+        cp_async_commit();
+    }
+    MG_SUB(22);
+    // ---- first pass of K rows: history keys are loaded before anything else
+    // warp -> (group of 8 keys, group of heads): with few keys in the run the heads are spread
+    // over the warps instead, so that all 16 warps share the work
+    int KG = 1;
+    while (KG < MG_WARPS && KG * 8 < n_keys) KG <<= 1;
+    const int HG = MG_WARPS / KG, kgi = warp & (KG - 1), hgi = warp / KG;
+    const int hpg = (g + HG - 1) / HG, h0 = min(g, hgi * hpg), h1 = min(g, h0 + hpg);
+    float kf[32];
+    bool valid = false, late = false;
+    if (h0 < h1) mg_load_k(p, L, sh, it, n_keys, kgi * 8 + (lane >> 2), lane & 3, kf, valid, late);
+    MG_SUB(23);
+    // ---- q heads, and the new token's K/V rows
     if (warp < g) {
         const float4 v4 = __ldcg(reinterpret_cast<const float4*>(qkv_t + (size_t)(it.kvh * g + warp) * 128) + lane);
         float v[4] = {v4.x, v4.y, v4.z, v4.w};
-        head_norm_rope(v, L.q_norm, cs_row, p.eps, lane, true);
-        reinterpret_cast<float4*>(&sh.sq[warp][0])[lane] = make_float4(v[0], v[1], v[2], v[3]);
+        head_norm_rope(v, L.q_norm, sh.cs, p.eps, lane, true);
+        *reinterpret_cast<float4*>(&sh.sq[warp][(lane >> 3) * MG_SQ_QUARTER + (lane & 7) * 4]) = make_float4(v[0], v[1], v[2], v[3]);
     } else if (owner && (warp == g || warp == g + 1)) {
         const bool is_k = warp == g;
         const int hh = is_k ? p.n_head + it.kvh : p.n_head + p.n_kv + it.kvh;
         const float4 v4 = __ldcg(reinterpret_cast<const float4*>(qkv_t + (size_t)hh * 128) + lane);
         float v[4] = {v4.x, v4.y, v4.z, v4.w};
-        if (is_k) head_norm_rope(v, L.k_norm, cs_row, p.eps, lane, true);
-        const int blk = it.table[it.pos / DC_KV_BLOCK];
+        if (is_k) head_norm_rope(v, L.k_norm, sh.cs, p.eps, lane, true);
+        const int blk = sh.tbl[it.pos / DC_KV_BLOCK - it.b0];
         __half* dst = (is_k ? L.k_arena : L.v_arena) +
                       (((size_t)blk * DC_KV_BLOCK + it.pos % DC_KV_BLOCK) * p.n_kv + it.kvh) * 128 + 4 * lane;
         __half2 lo = __halves2half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
@@ -276,49 +434,48 @@ __device__ __forceinline__ void attn_scores_phase(const MegaParams& p, const Meg
         *reinterpret_cast<uint2*>(dst) = pk;
     }
     __syncthreads();   // sq ready; this CTA's K/V stores are visible to its own loads
-    const int n_keys = (it.b1 - it.b0) * DC_KV_BLOCK;
-    for (int k0 = 0; k0 < n_keys; k0 += MG_WARPS * 8) {
-        const int kk = k0 + warp * 8 + (lane >> 2), sub = lane & 3;
-        const int blk = it.b0 + kk / DC_KV_BLOCK, kpos = blk * DC_KV_BLOCK + kk % DC_KV_BLOCK;
-        const bool valid = kk < n_keys && kpos < it.ctx_len;
-        float kf[32];
-        if (valid) {
-            const int pb = it.table[blk];
-            const uint4* kp = reinterpret_cast<const uint4*>(
-                L.k_arena + (((size_t)pb * DC_KV_BLOCK + kk % DC_KV_BLOCK) * p.n_kv + it.kvh) * 128 + sub * 32);
+    MG_SUB(24);
+    if (h0 < h1) {
+        for (int k0 = 0; k0 + kgi * 8 < n_keys; k0 += KG * 8) {
+            const int kk = k0 + kgi * 8 + (lane >> 2), sub = lane & 3;
+            if (k0 > 0) mg_load_k(p, L, sh, it, n_keys, kk, sub, kf, valid, late);
+            if (late) {
+                const int blk = kk / DC_KV_BLOCK;
+                const uint4* kp = reinterpret_cast<const uint4*>(
+                    L.k_arena + (((size_t)sh.tbl[blk] * DC_KV_BLOCK + kk % DC_KV_BLOCK) * p.n_kv + it.kvh) * 128 + sub * 32);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint4 u = __ldcg(kp + i);
-                const __half2* h2 = reinterpret_cast<const __half2*>(&u);
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 u = __ldcg(kp + i);
+                    const __half2* h2 = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = __half22float2(h2[j]);
-                    kf[i * 8 + 2 * j] = f.x;
-                    kf[i * 8 + 2 * j + 1] = f.y;
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(h2[j]);
+                        kf[i * 8 + 2 * j] = f.x;
+                        kf[i * 8 + 2 * j + 1] = f.y;
+                    }
                 }
             }
-        } else {
+            // one head at a time, rolled: the loop body is small and stays in the instruction cache
+#pragma unroll 1
+            for (int h = h0; h < h1; ++h) {
+                const float4* qp = reinterpret_cast<const float4*>(&sh.sq[h][sub * MG_SQ_QUARTER]);
+                float dot = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) kf[i] = 0.0f;
-        }
-        for (int h = 0; h < g; ++h) {
-            float dot = 0.0f;
-            const float4* qp = reinterpret_cast<const float4*>(&sh.sq[h][sub * 32]);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 qq = qp[i];
-                dot = fmaf(qq.x, kf[4 * i], dot);
-                dot = fmaf(qq.y, kf[4 * i + 1], dot);
-                dot = fmaf(qq.z, kf[4 * i + 2], dot);
-                dot = fmaf(qq.w, kf[4 * i + 3], dot);
+                for (int i = 0; i < 8; ++i) {
+                    const float4 qq = qp[i];
+                    dot = fmaf(qq.x, kf[4 * i], dot);
+                    dot = fmaf(qq.y, kf[4 * i + 1], dot);
+                    dot = fmaf(qq.z, kf[4 * i + 2], dot);
+                    dot = fmaf(qq.w, kf[4 * i + 3], dot);
+                }
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                if (sub == 0 && kk < n_keys) s_sc[h * p.s_keys + kk] = valid ? __fmul_rn(dot, p.scale) : -INFINITY;
             }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            if (sub == 0 && kk < n_keys) s_sc[h * p.s_keys + kk] = valid ? __fmul_rn(dot, p.scale) : -INFINITY;
         }
     }
     __syncthreads();
-    const int nb_run = it.b1 - it.b0;
+    MG_SUB(25);
     for (int i = threadIdx.x; i < g * nb_run; i += MG_THREADS) {
         const int h = i / nb_run, bb = i - h * nb_run;
         float mx = -1e30f;
@@ -332,9 +489,10 @@ __device__ __forceinline__ void attn_scores_phase(const MegaParams& p, const Meg
 // blocks accumulated as the reference walks them, partial scaled by the alphas of
 // all later blocks; the last run of a (token, kv head) sums the partials and emits
 // the Q8_K blocks of the attention output (hwy_paged_attention.cc:428-629).
-__device__ __forceinline__ void attn_pv_phase(const MegaParams& p, const MegaLayer& L, MegaShared& sh,
-                                              const float* s_sc) {
-    const AttnItem it = attn_item(p);
+__device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, MegaShared& sh,
+                                              const AttnItem& it, const float* s_sc, const uint8_t* vbuf,
+                                              int vcap_blocks) {
+    cp_async_wait_all();   // this thread's V copies of the scores phase have landed
     if (!it.valid) return;
     const int g = p.n_head / p.n_kv;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -376,14 +534,27 @@ __device__ __forceinline__ void attn_pv_phase(const MegaParams& p, const MegaLay
     // thread -> (dim, two heads): heads hq and hq + 4
     const int dim = tid & 127, hq = tid >> 7;
     float acc0 = 0.0f, acc1 = 0.0f;
+    __syncthreads();   // every thread's async copies are complete and visible
+    {
+        // the new token's V row was written during the scores phase, possibly after its
+        // async copy was issued: the owning run copies that one row again
+        const int pb_new = it.pos / DC_KV_BLOCK - it.b0;
+        if (pb_new >= 0 && pb_new < it.b1 - it.b0 && pb_new < vcap_blocks && tid < 16) {
+            const int slot = it.pos % DC_KV_BLOCK;
+            const uint4* src = reinterpret_cast<const uint4*>(
+                L.v_arena + (((size_t)sh.tbl[pb_new] * DC_KV_BLOCK + slot) * p.n_kv + it.kvh) * 128) + tid;
+            reinterpret_cast<uint4*>(const_cast<uint8_t*>(vbuf))[(pb_new * DC_KV_BLOCK + slot) * 16 + tid] = __ldcg(src);
+        }
+    }
     __syncthreads();
+    const __half* vs = reinterpret_cast<const __half*>(vbuf);
     for (int blk = it.b0; blk < it.b1; ++blk) {
-        const int pb = it.table[blk];
+        const int bl = blk - it.b0;
         const int nk = min(DC_KV_BLOCK, it.ctx_len - blk * DC_KV_BLOCK);
         if (tid < 128) {
             const int h = tid >> 4, key = tid & 15;
             float s = -INFINITY;
-            if (h < g && key < nk) s = s_sc[h * p.s_keys + (blk - it.b0) * DC_KV_BLOCK + key];
+            if (h < g && key < nk) s = s_sc[h * p.s_keys + bl * DC_KV_BLOCK + key];
             float mx = fmaxf(s, -1e30f);
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -406,12 +577,22 @@ __device__ __forceinline__ void attn_pv_phase(const MegaParams& p, const MegaLay
         const bool h0 = hq < g, h1 = hq + 4 < g;
         if (h0 && sh.alpha[hq] != 1.0f) acc0 *= sh.alpha[hq];
         if (h1 && sh.alpha[hq + 4] != 1.0f) acc1 *= sh.alpha[hq + 4];
-        const __half* vb = L.v_arena + ((size_t)pb * DC_KV_BLOCK * p.n_kv + it.kvh) * 128 + dim;
-        for (int key = 0; key < nk; ++key) {
-            const float v = __half2float(
-                __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(vb + (size_t)key * p.n_kv * 128))));
-            if (h0) acc0 = fmaf(sh.p[hq][key], v, acc0);
-            if (h1) acc1 = fmaf(sh.p[hq + 4][key], v, acc1);
+        if (bl < vcap_blocks) {
+#pragma unroll 4
+            for (int key = 0; key < nk; ++key) {
+                const float v = __half2float(vs[(size_t)(bl * DC_KV_BLOCK + key) * 128 + dim]);
+                if (h0) acc0 = fmaf(sh.p[hq][key], v, acc0);
+                if (h1) acc1 = fmaf(sh.p[hq + 4][key], v, acc1);
+            }
+        } else {
+            const __half* vb = L.v_arena + ((size_t)sh.tbl[bl] * DC_KV_BLOCK * p.n_kv + it.kvh) * 128 + dim;
+#pragma unroll 4
+            for (int key = 0; key < nk; ++key) {
+                const float v = __half2float(
+                    __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(vb + (size_t)key * p.n_kv * 128))));
+                if (h0) acc0 = fmaf(sh.p[hq][key], v, acc0);
+                if (h1) acc1 = fmaf(sh.p[hq + 4][key], v, acc1);
+            }
         }
         __syncthreads();
     }
@@ -436,12 +617,25 @@ __device__ __forceinline__ void attn_pv_phase(const MegaParams& p, const MegaLay
         const int head = it.kvh * g + 2 * pb2 + (lane >> 4), d0 = (lane & 15) * 8;
         const size_t base = ((size_t)it.t * p.n_head + head) * p.nsplit;
         float v[8] = {0, 0, 0, 0, 0, 0, 0, 0}, den = 0.0f;
-        for (int s = 0; s < p.nsplit; ++s) {
-            den += __ldcg(p.part_d + base + s);
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_acc + (base + s) * 128 + d0));
-            const float4 c = __ldcg(reinterpret_cast<const float4*>(p.part_acc + (base + s) * 128 + d0 + 4));
-            v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-            v[4] += c.x; v[5] += c.y; v[6] += c.z; v[7] += c.w;
+        for (int s0 = 0; s0 < p.nsplit; s0 += 4) {
+            float dd[4];
+            float4 a[4], c[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {   // four runs' loads in flight, then added in run order
+                const bool in = s0 + j < p.nsplit;
+                const size_t bi = base + (in ? s0 + j : 0);
+                dd[j] = in ? __ldcg(p.part_d + bi) : 0.0f;
+                a[j] = in ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0)) : make_float4(0, 0, 0, 0);
+                c[j] = in ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0 + 4)) : make_float4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (s0 + j < p.nsplit) {
+                    den += dd[j];
+                    v[0] += a[j].x; v[1] += a[j].y; v[2] += a[j].z; v[3] += a[j].w;
+                    v[4] += c[j].x; v[5] += c[j].y; v[6] += c[j].z; v[7] += c[j].w;
+                }
+            }
         }
         const float inv = (den > 0.0f && isfinite(den)) ? __fdiv_rn(1.0f, __fadd_rn(den, 1e-6f)) : 0.0f;
 #pragma unroll
@@ -464,7 +658,7 @@ __device__ __forceinline__ unsigned long long mg_route_key(float v, int id) {
 
 // Router logits of this CTA's expert (expert id = blockIdx.x): each warp dots one
 // 1/16 of the F32 router row with the normed hidden state in shared memory.
-__device__ __forceinline__ void router_logits_phase(const MegaParams& p, const MegaLayer& L, MegaShared& sh,
+__device__ DC_HOT void router_logits_phase(const MegaParams& p, const MegaLayer& L, MegaShared& sh,
                                                     const float* xn) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int e = blockIdx.x; e < p.E; e += gridDim.x) {
@@ -508,74 +702,47 @@ __device__ __forceinline__ void router_logits_phase(const MegaParams& p, const M
 // Every CTA routes all tokens itself from the logits in global memory: stable top-k
 // on logits, weights over the selected experts (core/src/llm/moe/native.cpp:610-676),
 // then the expert-grouped assignment map (core/src/moe/moe_routing.cpp:534-603).
-__device__ __forceinline__ void route_phase(const MegaParams& p, MegaShared& sh) {
+__device__ DC_HOT void route_phase(const MegaParams& p, MegaShared& sh) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int t = warp; t < p.T; t += MG_WARPS) {
-        float lv[MG_MAX_E / 32];
-        bool taken[MG_MAX_E / 32];
-#pragma unroll
-        for (int j = 0; j < MG_MAX_E / 32; ++j) {
-            const int id = j * 32 + lane;
-            lv[j] = id < p.E ? __ldcg(p.router_logits + (size_t)t * p.E + id) : 0.0f;
-            taken[j] = id >= p.E;
+    // rank selection: thread (t, e) counts the candidates that precede its own
+    // ("larger logit first, then lower id, NaN last"); the k best have ranks 0..k-1
+    for (int i = threadIdx.x; i < p.T * p.E; i += MG_THREADS) {
+        const int t = i / p.E, e = i - t * p.E;
+        sh.rkeys[t][e] = mg_route_key(__ldcg(p.router_logits + i), e);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.T * p.E; i += MG_THREADS) {
+        const int t = i / p.E, e = i - t * p.E;
+        const unsigned long long mine = sh.rkeys[t][e];
+        int rank = 0;
+        for (int j = 0; j < p.E; ++j) rank += (sh.rkeys[t][j] > mine);
+        if (rank < p.top_k) {
+            sh.ids[t * p.top_k + rank] = e;
+            sh.sel[t][rank] = __ldcg(p.router_logits + i);
         }
-        float mine = 0.0f;  // lane k keeps the logit of the k-th pick
+    }
+    __syncthreads();
+    if (threadIdx.x < p.T) {
+        // weights over the selected experts, sequentially as the reference does (native.cpp:649-674)
+        const int t = threadIdx.x;
+        float mx = -INFINITY;
+        bool finite = true;
         for (int k = 0; k < p.top_k; ++k) {
-            unsigned long long best = 0ull;
-#pragma unroll
-            for (int j = 0; j < MG_MAX_E / 32; ++j) {
-                if (!taken[j]) {
-                    const unsigned long long key = mg_route_key(lv[j], j * 32 + lane);
-                    best = key > best ? key : best;
-                }
-            }
-            unsigned long long win = best;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const unsigned long long ok = __shfl_xor_sync(0xffffffffu, win, o);
-                win = ok > win ? ok : win;
-            }
-            const int wid = (int)(0xFFFFFFFFu - (uint32_t)(win & 0xFFFFFFFFull));
-            float wl = 0.0f;
-#pragma unroll
-            for (int j = 0; j < MG_MAX_E / 32; ++j)
-                if (j * 32 + lane == wid) {
-                    taken[j] = true;
-                    wl = lv[j];
-                }
-            wl = __shfl_sync(0xffffffffu, wl, wid & 31);
-            if (lane == k) mine = wl;
-            if (lane == 0) sh.ids[t * p.top_k + k] = wid;
+            const float v = sh.sel[t][k];
+            finite = finite && isfinite(v);
+            if (isfinite(v) && v > mx) mx = v;
         }
-        // weights, sequentially by lane 0 as the reference does
-        float sel[MG_MAX_K];
-#pragma unroll
-        for (int k = 0; k < MG_MAX_K; ++k) sel[k] = __shfl_sync(0xffffffffu, mine, k);
-        if (lane == 0) {
-            float mx = -INFINITY;
-            bool finite = true;
-#pragma unroll
-            for (int k = 0; k < MG_MAX_K; ++k)
-                if (k < p.top_k) {
-                    finite = finite && isfinite(sel[k]);
-                    if (isfinite(sel[k]) && sel[k] > mx) mx = sel[k];
-                }
-            float den = 0.0f, wv[MG_MAX_K];
-#pragma unroll
-            for (int k = 0; k < MG_MAX_K; ++k) {
-                wv[k] = 0.0f;
-                if (k < p.top_k && finite && isfinite(mx)) {
-                    wv[k] = expf(sel[k] - mx);
-                    den += wv[k];
-                }
+        float den = 0.0f;
+        if (finite && isfinite(mx))
+            for (int k = 0; k < p.top_k; ++k) {
+                const float ev = expf(sh.sel[t][k] - mx);
+                sh.w[t * p.top_k + k] = ev;
+                den += ev;
             }
-            const bool ok = den > 0.0f && isfinite(den);
-#pragma unroll
-            for (int k = 0; k < MG_MAX_K; ++k)
-                if (k < p.top_k) {
-                    const float w = ok ? __fdiv_rn(wv[k], den) : __fdiv_rn(1.0f, (float)p.top_k);
-                    sh.w[t * p.top_k + k] = __fmul_rn(w, p.routed_scale);
-                }
+        const bool ok = den > 0.0f && isfinite(den);
+        for (int k = 0; k < p.top_k; ++k) {
+            const float w = ok ? __fdiv_rn(sh.w[t * p.top_k + k], den) : __fdiv_rn(1.0f, (float)p.top_k);
+            sh.w[t * p.top_k + k] = __fmul_rn(w, p.routed_scale);
         }
     }
     __syncthreads();
@@ -620,7 +787,6 @@ __device__ __forceinline__ void route_phase(const MegaParams& p, MegaShared& sh)
     if (threadIdx.x == 0) {
         sh.n_active = tot_a;
         sh.uoff[tot_a] = tot_c;
-        sh.have_moe = 1;
     }
     if (blockIdx.x == 0 && threadIdx.x < A) {
         if (p.route_ids) p.route_ids[threadIdx.x] = sh.ids[threadIdx.x];
@@ -630,6 +796,21 @@ __device__ __forceinline__ void route_phase(const MegaParams& p, MegaShared& sh)
 }
 
 // ------------------------------------------------------------ the kernel
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// The whole CTA asks L2 for a small vector that a later phase will read (norm weights,
+// this CTA's router row), 128 bytes per thread.
+__device__ __forceinline__ void prefetch_vec(const void* base, size_t bytes) {
+    if (!base) return;
+    for (size_t o = (size_t)threadIdx.x * 128; o < bytes; o += (size_t)MG_THREADS * 128)
+        prefetch_l2(reinterpret_cast<const uint8_t*>(base) + o);
+}
+// Copies one layer descriptor from global memory into shared slot `slot`.
+__device__ __forceinline__ void load_layer(const MegaParams& p, MegaShared& sh, int l, int slot) {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(p.layers + l);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(&sh.layer[slot]);
+    for (int i = threadIdx.x; i < (int)(sizeof(MegaLayer) / 4); i += MG_THREADS) dst[i] = src[i];
+}
+
 __device__ __forceinline__ unsigned long long mg_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -703,11 +884,46 @@ __device__ __forceinline__ MoeMMParams mg_experts(const MegaParams& p, const Meg
     return m;
 }
 
+// The streaming matmul bodies are large; each is kept out of line and shared by all of its
+// call sites so that one layer's instruction footprint stays small (the kernel runs the same
+// code once per layer, and an instruction-cache miss costs a round trip to L2).
+__device__ __noinline__ void mg_gemv_prefill(const GemvParams& g, WarpPipe<MG_NSTAGE>& pipe, int gw, int nw, int lane) {
+    GemvStream<MG_NSTAGE> st;
+    st.begin(g, gw, nw);
+    st.prefill(g, pipe, lane);
+}
 template <int NT>
-__global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams p) {
+__device__ __noinline__ void mg_gemv_consume(const GemvParams& g, WarpPipe<MG_NSTAGE>& pipe, const ActSmem& act, int gw,
+                                             int nw, int lane) {
+    GemvStream<MG_NSTAGE> st;
+    st.resume(g, gw, nw, (int)(pipe.issued - pipe.consumed));
+    st.template consume<NT, false>(g, pipe, act, lane);
+}
+__device__ __noinline__ void mg_moe_prefill(const MoeMMParams& m, int U, WarpPipe<MG_NSTAGE>& pipe, int gw, int nw, int lane) {
+    MoeStream<MG_NSTAGE, 2> st;
+    st.begin(m, U, gw, nw);
+    st.prefill(m, pipe, lane);
+}
+template <int NT>
+__device__ __noinline__ void mg_moe_consume(const MoeMMParams& m, int U, WarpPipe<MG_NSTAGE>& pipe, const ActSmem& act,
+                                            int gw, int nw, int lane) {
+    MoeStream<MG_NSTAGE, 2> st;
+    st.resume(m, U, gw, nw, (int)(pipe.issued - pipe.consumed));
+    st.template consume<NT>(m, pipe, act, lane);
+}
+
+template <int NT>
+__global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_constant__ MegaParams gp) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ MegaShared sh;
+    __shared__ __align__(16) MegaShared sh;
+    // the parameter block is read through references by out-of-line phase functions: keep it in
+    // shared memory so that those reads are cheap shared loads rather than a per-thread local copy
+    __shared__ __align__(16) MegaParams sp;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < (int)(sizeof(MegaParams) / 4); i += MG_THREADS)
+        reinterpret_cast<uint32_t*>(&sp)[i] = reinterpret_cast<const uint32_t*>(&gp)[i];
+    __syncthreads();
+    const MegaParams& p = sp;
     const int gw = blockIdx.x * MG_WARPS + warp, nw = gridDim.x * MG_WARPS;
     WarpPipe<MG_NSTAGE> pipe;
     pipe.init(smem + p.off_pipe + (size_t)warp * MG_NSTAGE * MG_STAGE, reinterpret_cast<uint64_t*>(smem) + warp * MG_NSTAGE,
@@ -718,43 +934,47 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
     const int QD = p.n_head * 128, A = p.T * p.top_k;
     unsigned epoch = 0;
     unsigned long long t_last = mg_now();
-    if (tid == 0) sh.have_moe = 0;
-    __syncthreads();
 
+    // V rows of an attention run are staged where the activations and the hidden state live
+    // in the other phases (both are idle during attention)
+    uint8_t* vbuf = act_base;
+    const int vcap_blocks = (int)((p.off_sc - p.off_act) / (DC_KV_BLOCK * 256));
     for (int step = 0; step < p.n_steps; ++step) {
-        GemvParams gq = mg_qkv(p, p.layers[0]);
-        GemvStream<MG_NSTAGE> sq;
-        sq.begin(gq, gw, nw);
-        sq.prefill(gq, pipe, lane);
-        GemvParams glm = {};
-        GemvStream<MG_NSTAGE> slm;
+        const AttnItem item = attn_step_setup(p, sh);
+        load_layer(p, sh, 0, 0);
+        __syncthreads();
+        if (tid == 0) sh.g_qkv = mg_qkv(p, sh.layer[0]);
+        __syncthreads();
+        const GemvParams& gq = sh.g_qkv;
+        mg_gemv_prefill(gq, pipe, gw, nw, lane);
+        const GemvParams& glm = sh.g_lm;
         for (int l = 0; l < p.n_layer; ++l) {
-            const MegaLayer& L = p.layers[l];
+            const MegaLayer& L = sh.layer[l & 1];
+            if (l + 1 < p.n_layer) load_layer(p, sh, l + 1, (l + 1) & 1);   // read long before it is used
             const float* xin = (l & 1) ? p.xb : p.xa;
             float* xout = (l & 1) ? p.xa : p.xb;
             // ---- P0: hidden state, attn_norm, Q8_K, QKV rows
             MG_MARK(0);
-            assemble_x(p, sh, xs, xin, xout, l == 0);
-            if (tid == 0) sh.have_moe = 0;
-            MG_MARK(1);
             ActSmem act;
             act.bind(act_base, p.T, p.H);
-            norm_quant(p, sh, xs, L.attn_norm, act);
+            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, l == 0 ? 0 : 1, xin, xout, L.attn_norm, act, nullptr);
             MG_MARK(2);
-            sq.template consume<NT>(gq, pipe, act, lane);
+            mg_gemv_consume<NT>(gq, pipe, act, gw, nw, lane);
             MG_MARK(3);
-            GemvParams go = mg_single(p, L.wo, L.wo_type, L.wo_rb, p.H, p.rpst_o, QD, DC_EPI_ACC, xout, p.H, nullptr);
-            GemvStream<MG_NSTAGE> so;
-            so.begin(go, gw, nw);
-            so.prefill(go, pipe, lane);   // output-projection rows stream in during attention
+            if (tid == 0) sh.g_o = mg_single(p, L.wo, L.wo_type, L.wo_rb, p.H, p.rpst_o, QD, DC_EPI_ACC, xout, p.H, nullptr);
+            __syncthreads();
+            const GemvParams& go = sh.g_o;
+            mg_gemv_prefill(go, pipe, gw, nw, lane);   // output-projection rows stream in during attention
+            prefetch_vec(L.ffn_norm, (size_t)p.H * 4);
+            if ((int)blockIdx.x < p.E) prefetch_vec(L.router + (size_t)blockIdx.x * p.H, (size_t)p.H * 4);
             grid_barrier(p, epoch);
             MG_MARK(4);
             // ---- P1 / P2: attention
-            attn_scores_phase(p, L, sh, s_sc);
+            attn_scores_phase(p, L, sh, item, s_sc, vbuf, vcap_blocks);
             MG_MARK(5);
             grid_barrier(p, epoch);
             MG_MARK(6);
-            attn_pv_phase(p, L, sh, s_sc);
+            attn_pv_phase(p, L, sh, item, s_sc, vbuf, vcap_blocks);
             MG_MARK(7);
             grid_barrier(p, epoch);
             MG_MARK(8);
@@ -763,15 +983,13 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
             act.template fill<true>(p.q8_attn, p.T);
             __syncthreads();
             MG_MARK(9);
-            so.template consume<NT>(go, pipe, act, lane);
+            mg_gemv_consume<NT>(go, pipe, act, gw, nw, lane);
             MG_MARK(10);
             grid_barrier(p, epoch);
             MG_MARK(11);
             // ---- P4: ffn_norm, Q8_K, router logits
-            for (int e = tid; e < p.T * p.H; e += MG_THREADS) xs[e] = __ldcg(xout + e);
-            __syncthreads();
             act.bind(act_base, p.T, p.H);
-            norm_quant(p, sh, xs, L.ffn_norm, act);
+            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 2, xout, nullptr, L.ffn_norm, act, xs);
             MG_MARK(12);
             router_logits_phase(p, L, sh, xs);
             MG_MARK(13);
@@ -780,16 +998,25 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
             // ---- P5: routing, gate/up + SwiGLU
             route_phase(p, sh);
             MG_MARK(15);
-            MoeMMParams mgu = mg_experts(p, sh, L.gate, L.up, L.gate_type, L.gate_rb, p.F, p.H, p.rpst_gate, p.h);
-            MoeStream<MG_NSTAGE, true> sg;
-            sg.begin(mgu, sh.n_active, gw, nw);
-            sg.prefill(mgu, pipe, lane);
-            sg.template consume<NT>(mgu, pipe, act, lane);
+            if (tid == 0) {
+                sh.m_gu = mg_experts(p, sh, L.gate, L.up, L.gate_type, L.gate_rb, p.F, p.H, p.rpst_gate, p.h);
+                sh.m_dn = mg_experts(p, sh, L.down, nullptr, L.down_type, L.down_rb, p.H, p.F, p.rpst_down, p.dn);
+            }
+            __syncthreads();
+            const MoeMMParams& mgu = sh.m_gu;
+            mg_moe_prefill(mgu, sh.n_active, pipe, gw, nw, lane);
+            mg_moe_consume<NT>(mgu, sh.n_active, pipe, act, gw, nw, lane);
             MG_MARK(16);
-            MoeMMParams mdn = mg_experts(p, sh, L.down, nullptr, L.down_type, L.down_rb, p.H, p.F, p.rpst_down, p.dn);
-            MoeStream<MG_NSTAGE, false> sd;
-            sd.begin(mdn, sh.n_active, gw, nw);
-            sd.prefill(mdn, pipe, lane);  // down rows stream in across the barrier
+            const MoeMMParams& mdn = sh.m_dn;
+            mg_moe_prefill(mdn, sh.n_active, pipe, gw, nw, lane);  // down rows stream in across the barrier
+            if (l + 1 < p.n_layer) {
+                const MegaLayer& Ln = sh.layer[(l + 1) & 1];
+                prefetch_vec(Ln.attn_norm, (size_t)p.H * 4);
+                prefetch_vec(Ln.q_norm, 512);
+                prefetch_vec(Ln.k_norm, 512);
+            } else {
+                prefetch_vec(p.out_norm, (size_t)p.H * 4);
+            }
             grid_barrier(p, epoch);
             MG_MARK(17);
             // ---- P6: h -> Q8_K, down rows
@@ -797,7 +1024,9 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
             acth.bind(act_base, A, p.F);
             {
                 const int nbh = p.F / DC_QK_K;
-                for (int i = warp; i < A * nbh; i += MG_WARPS) {
+                const int rotb = (int)(blockIdx.x % (unsigned)(A * nbh));
+                for (int il = warp; il < A * nbh; il += MG_WARPS) {
+                    const int i = (il + rotb) % (A * nbh);
                     const int a = i / nbh, b = i - a * nbh;
                     const float4* src = reinterpret_cast<const float4*>(p.h + (size_t)a * p.F + b * DC_QK_K) + 2 * lane;
                     const float4 v0 = __ldcg(src), v1 = __ldcg(src + 1);
@@ -807,28 +1036,27 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const MegaParams 
             }
             __syncthreads();
             MG_MARK(18);
-            sd.template consume<NT>(mdn, pipe, acth, lane);
+            mg_moe_consume<NT>(mdn, sh.n_active, pipe, acth, gw, nw, lane);
             MG_MARK(19);
             if (l + 1 < p.n_layer) {
-                gq = mg_qkv(p, p.layers[l + 1]);
-                sq.begin(gq, gw, nw);
-                sq.prefill(gq, pipe, lane);
+                if (tid == 0) sh.g_qkv = mg_qkv(p, sh.layer[(l + 1) & 1]);
+                __syncthreads();
+                mg_gemv_prefill(gq, pipe, gw, nw, lane);
             } else {
-                glm = mg_single(p, p.out_w, p.out_type, p.out_rb, p.vocab, p.rpst_out, p.H, DC_EPI_STORE, p.logits,
-                                p.vocab, p.argmax_keys);
-                slm.begin(glm, gw, nw);
-                slm.prefill(glm, pipe, lane);
+                if (tid == 0)
+                    sh.g_lm = mg_single(p, p.out_w, p.out_type, p.out_rb, p.vocab, p.rpst_out, p.H, DC_EPI_STORE, p.logits,
+                                        p.vocab, p.argmax_keys);
+                __syncthreads();
+                mg_gemv_prefill(glm, pipe, gw, nw, lane);
             }
             grid_barrier(p, epoch);
             MG_MARK(20);
         }
         // ---- final: last MoE output + residual, output norm, lm_head with arg-max keys
-        assemble_x(p, sh, xs, (p.n_layer & 1) ? p.xb : p.xa, nullptr, false);
-        if (tid == 0) sh.have_moe = 0;
         ActSmem act;
         act.bind(act_base, p.T, p.H);
-        norm_quant(p, sh, xs, p.out_norm, act);
-        slm.template consume<NT>(glm, pipe, act, lane);
+        x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 1, (p.n_layer & 1) ? p.xb : p.xa, nullptr, p.out_norm, act, nullptr);
+        mg_gemv_consume<NT>(glm, pipe, act, gw, nw, lane);
         grid_barrier(p, epoch);
         MG_MARK(21);
         // greedy pick: first maximum wins (core/src/sampler/sampler.cpp:42-57)
@@ -881,7 +1109,7 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
     if (c.n_expert > MG_MAX_E || c.n_expert_used > MG_MAX_K) NO("too many experts");
     const int g = c.n_head / c.n_kv_head;
     if (g > 8 || (g & 1)) NO("query-head group must be even and <= 8");
-    if (c.hidden % (MG_WARPS * 4)) NO("hidden size");
+    if (c.hidden % MG_THREADS || T * (c.hidden / DC_QK_K) > 2 * MG_WARPS) NO("hidden size x streams");
     MegaParams p = {};
     const int G = m->ctx->num_sms;
     p.n_layer = c.n_layer; p.H = c.hidden; p.n_head = c.n_head; p.n_kv = c.n_kv_head; p.vocab = c.vocab;
@@ -916,15 +1144,18 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
             NO("attention tensor types vary by layer");
     }
     if (!ok) NO("a weight row does not fit a pipeline stage");
-    // gate/up pairs: halve the rows per stage until two halves fit
+    // gate/up pairs: as many outputs per stage as two halves allow (the paired half-warp path takes
+    // one output per pass; otherwise a stage holds whole passes)
     {
-        const int per_pass = 32 / dc::lanes_per_row(L0.gate_exps->type, c.hidden);
-        int r = p.rpst_gate;
+        const int G = dc::lanes_per_row(L0.gate_exps->type, c.hidden);
+        const int step = G == 16 ? 1 : 32 / G;
+        int r = p.rpst_gate / step * step;
+        if (r < step) r = step;
         uint32_t half = 0;
         for (;;) {
             half = ((uint32_t)r * (uint32_t)L0.gate_exps->row_bytes + 32 + 127) & ~127u;
-            if (2 * half <= MG_STAGE || r <= per_pass) break;
-            r -= per_pass;
+            if (2 * half <= MG_STAGE || r <= step) break;
+            r -= step;
         }
         if (2 * half > MG_STAGE) NO("a gate/up row pair does not fit a pipeline stage");
         p.rpst_gate = r;
@@ -942,10 +1173,16 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
     off += (uint32_t)((act_bytes + 127) & ~(size_t)127);
     p.off_xs = off;
     off += (uint32_t)(T * c.hidden * 4);
+    {   // V rows of an attention run are staged over act+xs: pad so a whole run fits, if there is room
+        const uint32_t want = (uint32_t)(p.s_keys / DC_KV_BLOCK) * DC_KV_BLOCK * 256;
+        const uint32_t have = off - p.off_act, sc_bytes = (uint32_t)((8 * p.s_keys * 4 + 127) & ~127);
+        if (want > have && off + (want - have) + sc_bytes <= MG_DYN_LIMIT) off += want - have;
+    }
     p.off_sc = off;
     off += (uint32_t)((8 * p.s_keys * 4 + 127) & ~127);
     p.smem_bytes = off;
-    if (off > 218 * 1024) NO("shared memory plan exceeds the 227 KB of an SM");
+    if (off > MG_DYN_LIMIT) NO("shared memory plan exceeds the 227 KB of an SM");
+    if (p.s_keys / DC_KV_BLOCK > MG_MAX_RUN_BLOCKS) NO("attention run longer than 64 KV blocks");
     *out = p;
     return true;
 #undef NO
@@ -956,7 +1193,7 @@ static int mg_launch(dc_model* m, MegaParams& p) {
     dc_ctx* ctx = m->ctx;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_decode_mega<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 218 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(k_decode_mega<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, MG_DYN_LIMIT);
         if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_decode_mega)");
         configured = true;
     }
@@ -1009,7 +1246,7 @@ int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback) {
     int st = dc_check_cuda(m->ctx, cudaMemsetAsync(m->mega_counter, 0, sizeof(unsigned), m->ctx->stream), "memset");
     if (st != DC_B200_OK) return st;
     m->last_launches = 1;
-    return T == 1 ? mg_launch<1>(m, p) : mg_launch<MG_MAX_T>(m, p);
+    return (T == 1 && m->cfg.hidden <= 4096) ? mg_launch<1>(m, p) : mg_launch<MG_MAX_T>(m, p);
 }
 
 // Device copy of the per-layer pointer table; called once when the model is finalized.

@@ -193,7 +193,8 @@ class Model:
 
     PHASES = ["(outside)", "x assemble", "attn_norm+q8", "qkv rows", "barrier", "scores", "barrier", "pv+merge", "barrier",
               "attn q8 fill", "o-proj rows", "barrier", "ffn_norm+q8", "router logits", "barrier", "top-k+buckets",
-              "gate/up rows", "barrier", "h q8", "down rows", "barrier", "lm_head+barrier"]
+              "gate/up rows", "barrier", "h q8", "down rows", "barrier", "lm_head+barrier",
+              "sub22", "sub23", "sub24", "sub25", "sub26", "sub27"]
 
     def phase_timing(self):
         """Nanoseconds per phase boundary accumulated by the persistent kernel (option phase_timing=1)."""
