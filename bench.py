@@ -42,6 +42,9 @@ METRIC = "decode tok/s (1 & 4 streams), 35B-A3B-class Q4_K_M; % HBM roofline"
 UNIT = "tok/s"
 PROMPT = 2048
 SAMPLE_LAYERS = 2          # layers of the model the CPU baseline times per sample
+# DRAM bytes (read + write) of one launch of the persistent kernel divided by its algorithmic bytes,
+# from an ncu capture of the 4-layer case (profiles/k_decode_mega_moe35b_4layers.md)
+DRAM_TRAFFIC_RATIO = 1.04
 
 
 def measured_peaks():
@@ -212,6 +215,14 @@ def main():
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-classes", action="store_true", help="print the per-kernel-class table to stderr")
+    ap.add_argument("--path", default="persistent", choices=["persistent", "per-op"],
+                    help="persistent: one cooperative kernel per decode run where the model fits its plan (default); "
+                         "per-op: one kernel per op, replayed as a CUDA graph")
+    ap.add_argument("--phase-timing", action="store_true",
+                    help="print the persistent kernel's per-phase device time (CTA 0's view) to stderr")
+    ap.add_argument("--streams", default="1,4", help="stream counts to time (the JSON line needs 1)")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed 1-stream decode run with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -245,6 +256,8 @@ def main():
         dist.broadcast(buf, 0)
         model.ep_init(bytes(buf.numpy().tobytes()), nccl_path)
     model.finalize()
+    if args.path == "per-op":
+        model.set_option("persistent", 0)
 
     rng = np.random.default_rng(0)
     seqs = [model.seq_alloc() for _ in range(4)]
@@ -265,17 +278,23 @@ def main():
 
     results = {}
     clocks = None
-    for n_streams in (1, 4):
+    stream_counts = sorted({int(x) for x in args.streams.split(",")} | {1})
+    for n_streams in stream_counts:
         sq = seqs[:n_streams]
         toks, _ = model.decode_run(sq, first[:n_streams], args.warmup)        # warm-up: eager pass, capture, replays
         sampler = ClockSampler(local_rank) if (n_streams == 1 and rank == 0) else None
         if sampler:
             sampler.start()
         barrier()
+        if args.profiler_range and n_streams == 1:
+            dc._lib.lib().dc_b200_profiler_range(1)
         t0 = time.perf_counter()
         toks, ms = model.decode_run(sq, toks[-1], args.steps)                 # K steps, device time from CUDA events
         barrier()
         wall = time.perf_counter() - t0
+        if args.profiler_range and n_streams == 1:
+            dc._lib.lib().dc_b200_profiler_range(0)
+        run_launches = model.step_stats()[0]
         if sampler:
             clocks = sampler.stop()
         ms = max_over_ranks(ms)
@@ -289,26 +308,65 @@ def main():
             last = model.decode_step(sq, last)
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
-        results[n_streams] = dict(ms=ms, wall=wall, e2e_s=e2e_s, ctx=model.seq_len(sq[0]), last=last)
+        results[n_streams] = dict(ms=ms, wall=wall, e2e_s=e2e_s, ctx=model.seq_len(sq[0]), last=last, run_launches=run_launches)
 
-    launches_per_step, weight_bytes, kv_bytes_per_tok = model.step_stats()
+    _, weight_bytes, kv_bytes_per_tok = model.step_stats()
     peak_gbs, peak_kind = measured_peaks()
-    # per-kernel-class device time of one eager step (CUDA events around every launch on the launching stream)
-    prof = model.profile_step(seqs[:1], results[1]["last"][:1])
-    prof = model.profile_step(seqs[:1], results[1]["last"][:1])
-    dom = max(prof.items(), key=lambda kv: kv[1][0])
-    dom_name, (dom_ms, dom_n, dom_bytes) = dom
+    r1 = results[1]
+    ms_per_step = r1["ms"] / args.steps
+    value = 1 * args.steps / (r1["ms"] * 1e-3)
+    # algorithmic bytes of one step: every weight byte the step must read (attention and router weights, the
+    # selected experts, lm_head) + the K and V rows of the context, at the context length mid-way through the run
+    step_bytes = weight_bytes + kv_bytes_per_tok * (r1["ctx"] - args.steps // 2)
+    persistent = r1["run_launches"] == 1
+    if persistent:
+        # one launch of the persistent kernel runs all K steps: bytes per launch = K x step bytes, duration =
+        # the run's device time (CUDA events on the launching stream around that launch)
+        achieved = step_bytes * args.steps / (r1["ms"] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "k_decode_mega", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                    "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}",
+                    "traffic": DRAM_TRAFFIC_RATIO * step_bytes * args.steps,
+                    "traffic_note": "dram__bytes_read+write of one launch measured on the 4-layer case, scaled by "
+                                    "algorithmic bytes (profiles/k_decode_mega_moe35b_4layers.md)",
+                    "launches": 1, "bytes_per_launch": step_bytes * args.steps, "us_per_launch": r1["ms"] * 1e3}
+        gpu_launches = 1
+    else:
+        # per-op path: device time of one eager step per kernel class (CUDA events around every launch)
+        prof = model.profile_step(seqs[:1], r1["last"][:1])
+        prof = model.profile_step(seqs[:1], r1["last"][:1])
+        dom_name, (dom_ms, dom_n, dom_bytes) = max(prof.items(), key=lambda kv: kv[1][0])
+        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
+        roofline = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                    "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}", "traffic": None,
+                    "launches_per_step": dom_n, "bytes_per_launch": dom_bytes / dom_n,
+                    "us_per_launch": dom_ms * 1e3 / dom_n}
+        gpu_launches = r1["run_launches"] * args.steps
+    if args.phase_timing and persistent and rank == 0:
+        for n_streams in stream_counts:
+            model.set_option("phase_timing", 1)
+            _, ms_pt = model.decode_run(seqs[:n_streams], results[n_streams]["last"], 32)
+            pt = model.phase_timing()
+            model.set_option("phase_timing", 0)
+            print(f"streams {n_streams}: {ms_pt / 32 * 1e3:.1f} us/step, {args.layers} layers; us per layer (CTA 0):", file=sys.stderr)
+            for i, (name, ns) in pt.items():
+                if ns:
+                    print(f"  {i:2d} {name:18s} {ns / 32 / args.layers / 1e3:8.2f}", file=sys.stderr)
+            arrive, release = model.barrier_trace()
+            if arrive.any():   # instrumented build only
+                print("  barriers of layer 1, first step: spread of CTA arrivals and release latency (us)", file=sys.stderr)
+                for b, name in enumerate(model.BARRIERS):
+                    a, r = arrive[b], release[b]
+                    print(f"    {name:20s} median-first {(np.median(a) - a.min()) / 1e3:6.2f}  last-median "
+                          f"{(a.max() - np.median(a)) / 1e3:6.2f}  release-last {(np.median(r) - a.max()) / 1e3:6.2f}",
+                          file=sys.stderr)
     if args.profile_classes and rank == 0:
+        prof = model.profile_step(seqs[:1], r1["last"][:1])
+        prof = model.profile_step(seqs[:1], r1["last"][:1])
         tot = sum(v[0] for v in prof.values())
         for k, (ms_, n_, b_) in sorted(prof.items(), key=lambda kv: -kv[1][0]):
             print(f"{k:22s} launches {n_:4d}  {ms_ * 1e3:9.1f} us  {ms_ / tot * 100:5.1f} %  "
                   f"{b_ / n_ / 1e6:8.2f} MB/launch  {b_ / (ms_ * 1e-3) / 1e9 if ms_ else 0:8.1f} GB/s", file=sys.stderr)
-    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
 
-    r1, r4 = results[1], results[4]
-    ms_per_step = r1["ms"] / args.steps
-    value = 1 * args.steps / (r1["ms"] * 1e-3)
-    step_bytes = weight_bytes + kv_bytes_per_tok * (r1["ctx"] - args.steps // 2)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -316,20 +374,19 @@ def main():
         "config": {"workload": "moe35b_a3b_q4km decode: 48 layers, hidden 2048, 128 experts top-8, vocab 151936; "
                                "2048-token random prompt per stream, greedy, paged fp16 KV",
                    "streams": 1, "layers": args.layers, "prompt_tokens": args.prompt, "ctx_at_timing": r1["ctx"],
-                   "parallelism": f"ep{world}",
+                   "parallelism": f"ep{world}", "path": "persistent kernel" if persistent else "per-op CUDA graph",
                    "l2": "each step reads ~1.9 GB of weights, far more than the 126 MB L2, so no flush is needed"},
         "hbm_fraction_of_step": step_bytes / (ms_per_step * 1e-3) / 1e9 / (peak_gbs * world),
-        "streams4": {"value": 4 * args.steps / (r4["ms"] * 1e-3), "ms_per_step": r4["ms"] / args.steps,
-                     "e2e": 4 * args.steps / r4["e2e_s"], "ctx_at_timing": r4["ctx"]},
         "e2e": {"value": args.steps / r1["e2e_s"], "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4,
                 "api": "dc_b200_decode_step"},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": gpu_launches,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-                     "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}", "traffic": None,
-                     "launches_per_step": dom_n, "bytes_per_launch": dom_bytes / dom_n,
-                     "us_per_launch": dom_ms * 1e3 / dom_n},
+        "roofline": roofline,
     }
+    if 4 in results:
+        r4 = results[4]
+        line["streams4"] = {"value": 4 * args.steps / (r4["ms"] * 1e-3), "ms_per_step": r4["ms"] / args.steps,
+                            "e2e": 4 * args.steps / r4["e2e_s"], "ctx_at_timing": r4["ctx"]}
     if rank == 0 and not args.no_cpu_baseline:
         from oracle import oracle as o
         o.build()

@@ -10,6 +10,9 @@
 #define MG_MAX_T 4
 #define MG_MAX_E 256
 #define MG_MAX_K 16
+// barrier counter (64 bytes) + 32 phase accumulators + a per-CTA barrier trace (14 x 160)
+#define DC_MEGA_TIMING_SLOTS (32 + 14 * 160)
+#define DC_MEGA_COUNTER_BYTES (64 + DC_MEGA_TIMING_SLOTS * 8)
 
 struct MegaLayer {
     const float *attn_norm, *q_norm, *k_norm, *ffn_norm, *router;

@@ -35,9 +35,15 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 
 // All CTAs of the (co-resident) grid meet here.  counter only grows during a
 // launch; the host zeroes it before the launch.
+__device__ __forceinline__ unsigned long long mg_now();
 __device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch) {
     __syncthreads();
     ++epoch;
+#ifdef DC_MEGA_SUBMARKS
+    // arrival and release time of every CTA at the seven barriers of the second layer
+    const bool trace = threadIdx.x == 0 && p.phase_ns && epoch > 7 && epoch <= 14;
+    if (trace) p.phase_ns[32 + (epoch - 8) * 160 + blockIdx.x] = mg_now();
+#endif
     if (threadIdx.x == 0) {
         __threadfence();
         atomicAdd(p.bar_counter, 1u);
@@ -52,6 +58,9 @@ __device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch) 
         }
         __threadfence();
     }
+#ifdef DC_MEGA_SUBMARKS
+    if (trace) p.phase_ns[32 + (7 + epoch - 8) * 160 + blockIdx.x] = mg_now();
+#endif
     __syncthreads();
 }
 
@@ -1271,8 +1280,8 @@ int dc_mega_prepare(dc_model* m) {
         d.v_arena = m->kv.v_arena + m->kv.layer_elems * il;
     }
     cudaError_t e = cudaMalloc(&m->mega_layers, v.size() * sizeof(MegaLayer));
-    if (e == cudaSuccess) e = cudaMalloc((void**)&m->mega_counter, 512);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&m->mega_counter, DC_MEGA_COUNTER_BYTES);
     if (e == cudaSuccess) e = cudaMemcpy(m->mega_layers, v.data(), v.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemset(m->mega_counter, 0, 512);
+    if (e == cudaSuccess) e = cudaMemset(m->mega_counter, 0, DC_MEGA_COUNTER_BYTES);
     return dc_check_cuda(m->ctx, e, "persistent decode set-up");
 }

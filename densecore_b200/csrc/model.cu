@@ -599,7 +599,7 @@ int dc_b200_forward_chunk(dc_model* m, int seq, const int32_t* tokens_host, int 
 void* dc_b200_model_logits_dev(dc_model* m) { return m ? m->buf.logits : nullptr; }
 
 int dc_b200_model_phase_timing(dc_model* m, uint64_t* ns_out, int n) {
-    if (!m || !ns_out || n < 1 || n > 32 || !m->mega_counter) return DC_B200_INVALID_ARGUMENT;
+    if (!m || !ns_out || n < 1 || n > DC_MEGA_TIMING_SLOTS || !m->mega_counter) return DC_B200_INVALID_ARGUMENT;
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     return dc_check_cuda(m->ctx, cudaMemcpy(ns_out, (uint8_t*)m->mega_counter + 64, (size_t)n * 8, cudaMemcpyDeviceToHost), "phase timing");
@@ -734,7 +734,7 @@ int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
     }
     if (!strcmp(name, "phase_timing")) {
         m->mega_timing = value != 0;
-        if (m->mega_counter) cudaMemsetAsync((uint8_t*)m->mega_counter + 64, 0, 32 * 8, m->ctx->stream);
+        if (m->mega_counter) cudaMemsetAsync((uint8_t*)m->mega_counter + 64, 0, DC_MEGA_TIMING_SLOTS * 8, m->ctx->stream);
         return DC_B200_OK;
     }
     return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "unknown model option '%s'", name);

@@ -201,3 +201,15 @@ class Model:
         out = np.zeros(len(self.PHASES), dtype=np.uint64)
         self._check(_lib.lib().dc_b200_model_phase_timing(self.handle, _vp(out), out.size))
         return dict(zip(range(len(self.PHASES)), zip(self.PHASES, out.tolist())))
+
+    BARRIERS = ["after qkv rows", "after scores", "after pv+merge", "after o-proj", "after router logits",
+                "after gate/up", "after down"]
+
+    def barrier_trace(self, n_cta: int = 148):
+        """(arrive, release) arrays [7, n_cta] of globaltimer nanoseconds: when each CTA reached and left the seven
+        grid barriers of the second layer in the first step of the last launch.  All zero unless the library was
+        built with -DDC_MEGA_SUBMARKS and phase_timing is on."""
+        buf = np.zeros(32 + 14 * 160, dtype=np.uint64)
+        self._check(_lib.lib().dc_b200_model_phase_timing(self.handle, _vp(buf), buf.size))
+        tr = buf[32:].reshape(14, 160)[:, :n_cta].astype(np.int64)
+        return tr[:7], tr[7:]

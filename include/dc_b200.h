@@ -251,7 +251,9 @@ DC_B200_API int dc_b200_forward_chunk(dc_model* m, int seq, const int32_t* token
 DC_B200_API void* dc_b200_model_logits_dev(dc_model* m);
 /* With model option "phase_timing" = 1 the persistent decode kernel accumulates, per phase
  * boundary, the nanoseconds CTA 0 spent since the previous boundary (work and barrier waits
- * separately); this reads the first n (<= 32) accumulators. */
+ * separately); this reads the first n accumulators (32 phases; a library built with
+ * -DDC_MEGA_SUBMARKS also fills 14 x 160 more: arrival, then release, time of every CTA at
+ * the seven barriers of the second layer; n <= 2272). */
 DC_B200_API int dc_b200_model_phase_timing(dc_model* m, uint64_t* ns_out, int n);
 /* Per-step counters of the last decode_run / decode_step: kernels launched per
  * step, bytes of weights and KV a step must read (algorithmic). */
