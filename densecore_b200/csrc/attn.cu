@@ -280,7 +280,7 @@ size_t dc_attention_scratch_bytes(int T, int n_head, int n_kv, int max_blocks, i
     n += (size_t)T * n_head * max_blocks * 4 + 256;                // bmax
     n += (size_t)T * n_head * nsplit * 128 * 4 + 256;              // part_acc
     n += (size_t)T * n_head * nsplit * 4 + 256;                    // part_d
-    n += (size_t)T * n_kv * 4 + 256;                               // tickets
+    n += (size_t)T * n_head * 4 + 256;                             // tickets (one per merge group)
     return n;
 }
 
@@ -329,5 +329,5 @@ void dc_attn_scratch_bind(dc_attn_scratch* sc, uint8_t* base, int T, int n_head,
     sc->bmax = (float*)take((size_t)T * n_head * max_blocks * 4);
     sc->part_acc = (float*)take((size_t)T * n_head * nsplit * 128 * 4);
     sc->part_d = (float*)take((size_t)T * n_head * nsplit * 4);
-    sc->tickets = (int*)take((size_t)T * n_kv * 4);
+    sc->tickets = (int*)take((size_t)T * n_head * 4);
 }

@@ -48,7 +48,8 @@ struct MegaParams {
     uint8_t* q8_attn;
     int32_t* route_ids;            // copies of the last layer's routing, for callers
     float* route_w;
-    int nsplit, s_keys;            // attention runs per (token, kv head); keys a run can hold
+    int nsplit, s_keys;            // attention runs per (token, kv head, head group); keys a run can hold
+    int n_hg;                      // head groups a kv head's query heads are split into (1, 2 or 4)
     // sync
     unsigned* bar_counter;
     int* err;

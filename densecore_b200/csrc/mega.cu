@@ -141,8 +141,7 @@ struct MegaShared {
     int wsum_a[MG_WARPS], wsum_c[MG_WARPS];
     // attention
     alignas(16) float sq[8][4 * MG_SQ_QUARTER];   // q heads; each 32-dim quarter padded (bank spread)
-    float p[8][DC_KV_BLOCK];
-    float m[8], d[8], alpha[8], suffix[8];
+    float suffix[8];
     int last;
     MegaLayer layer[2];                    // descriptor of the current layer and the next one
     // parameter blocks of the streaming phases (shared, so that no thread keeps a private copy)
@@ -285,20 +284,25 @@ __device__ __forceinline__ unsigned long long mg_now();
 #define MG_SUB(i) do {} while (0)
 #define MG_SUB_BEGIN do {} while (0)
 #endif
+// One attention run: token t, kv head kvh, head group hg (gh query heads starting at head hb of the
+// kv head's group), KV blocks [b0, b1).
 struct AttnItem {
     bool valid;
-    int t, kvh, split, pos, ctx_len, n_blk, b0, b1;
+    int t, kvh, hg, hb, gh, split, pos, ctx_len, n_blk, b0, b1;
     const int32_t* table;
 };
 
 __device__ __forceinline__ AttnItem attn_item(const MegaParams& p) {
     AttnItem it;
-    const int items = p.T * p.n_kv * p.nsplit, item = blockIdx.x;
+    const int items = p.T * p.n_kv * p.n_hg * p.nsplit, item = blockIdx.x;
     it.valid = item < items;
     const int i = it.valid ? item : 0;
-    it.t = i / (p.n_kv * p.nsplit);
-    it.kvh = (i / p.nsplit) % p.n_kv;
     it.split = i % p.nsplit;
+    it.hg = (i / p.nsplit) % p.n_hg;
+    it.kvh = (i / (p.nsplit * p.n_hg)) % p.n_kv;
+    it.t = i / (p.nsplit * p.n_hg * p.n_kv);
+    it.gh = (p.n_head / p.n_kv) / p.n_hg;
+    it.hb = it.hg * it.gh;
     it.pos = __ldcg(p.positions + it.t);
     it.ctx_len = it.pos + 1;
     it.n_blk = (it.ctx_len + DC_KV_BLOCK - 1) / DC_KV_BLOCK;
@@ -356,11 +360,12 @@ __device__ __forceinline__ void head_norm_rope(float (&v)[4], const float* nw, c
     }
 }
 
-// One K row slice (32 of 128 dims) of key kk of the run into registers.  The row of the token
-// being decoded (kpos == pos) is written by this CTA during the phase: it is flagged `late`
-// and fetched after the CTA barrier instead.
-__device__ __forceinline__ void mg_load_k(const MegaParams& p, const MegaLayer& L, const MegaShared& sh, const AttnItem& it,
-                                          int n_keys, int kk, int sub, float (&kf)[32], bool& valid, bool& late) {
+// One K row slice (32 of 128 dims) of key kk of the run, as loaded (fp16 pairs).  The row of the
+// token being decoded (kpos == pos) is written by this CTA during the phase: it is flagged `late`
+// and fetched after the CTA barrier instead.  Keys outside the run or the context read as zeros.
+__device__ __forceinline__ void mg_load_k_raw(const MegaParams& p, const MegaLayer& L, const MegaShared& sh,
+                                              const AttnItem& it, int n_keys, int kk, int sub, uint4 (&kr)[4],
+                                              bool& valid, bool& late) {
     const int blk = kk / DC_KV_BLOCK, kpos = (it.b0 + blk) * DC_KV_BLOCK + kk % DC_KV_BLOCK;
     valid = kk < n_keys && kpos < it.ctx_len;
     late = valid && kpos == it.pos;
@@ -368,19 +373,22 @@ __device__ __forceinline__ void mg_load_k(const MegaParams& p, const MegaLayer& 
         const uint4* kp = reinterpret_cast<const uint4*>(
             L.k_arena + (((size_t)sh.tbl[blk] * DC_KV_BLOCK + kk % DC_KV_BLOCK) * p.n_kv + it.kvh) * 128 + sub * 32);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 u = __ldcg(kp + i);
-            const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(h2[j]);
-                kf[i * 8 + 2 * j] = f.x;
-                kf[i * 8 + 2 * j + 1] = f.y;
-            }
-        }
+        for (int i = 0; i < 4; ++i) kr[i] = __ldcg(kp + i);
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) kf[i] = 0.0f;
+        for (int i = 0; i < 4; ++i) kr[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+__device__ __forceinline__ void mg_k_to_float(const uint4 (&kr)[4], float (&kf)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2* h2 = reinterpret_cast<const __half2*>(&kr[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h2[j]);
+            kf[i * 8 + 2 * j] = f.x;
+            kf[i * 8 + 2 * j + 1] = f.y;
+        }
     }
 }
 
@@ -391,7 +399,8 @@ __device__ __forceinline__ void mg_load_k(const MegaParams& p, const MegaLayer& 
 __device__ DC_HOT void attn_scores_phase(const MegaParams& p, const MegaLayer& L, MegaShared& sh,
                                                   const AttnItem& it, float* s_sc, uint8_t* vbuf, int vcap_blocks) {
     if (!it.valid) return;
-    const int g = p.n_head / p.n_kv, heads = p.n_head + 2 * p.n_kv;
+    // g: query heads of this run (a head group of the kv head); head0: the first of them
+    const int g = it.gh, head0 = it.kvh * (p.n_head / p.n_kv) + it.hb, heads = p.n_head + 2 * p.n_kv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float* qkv_t = p.qkv + (size_t)it.t * heads * 128;
     const bool owner = (it.pos / DC_KV_BLOCK) >= it.b0 && (it.pos / DC_KV_BLOCK) < it.b1;
@@ -416,13 +425,13 @@ __device__ DC_HOT void attn_scores_phase(const MegaParams& p, const MegaLayer& L
     while (KG < MG_WARPS && KG * 8 < n_keys) KG <<= 1;
     const int HG = MG_WARPS / KG, kgi = warp & (KG - 1), hgi = warp / KG;
     const int hpg = (g + HG - 1) / HG, h0 = min(g, hgi * hpg), h1 = min(g, h0 + hpg);
-    float kf[32];
+    uint4 kr[4];
     bool valid = false, late = false;
-    if (h0 < h1) mg_load_k(p, L, sh, it, n_keys, kgi * 8 + (lane >> 2), lane & 3, kf, valid, late);
+    if (h0 < h1) mg_load_k_raw(p, L, sh, it, n_keys, kgi * 8 + (lane >> 2), lane & 3, kr, valid, late);
     MG_SUB(23);
     // ---- q heads, and the new token's K/V rows
     if (warp < g) {
-        const float4 v4 = __ldcg(reinterpret_cast<const float4*>(qkv_t + (size_t)(it.kvh * g + warp) * 128) + lane);
+        const float4 v4 = __ldcg(reinterpret_cast<const float4*>(qkv_t + (size_t)(head0 + warp) * 128) + lane);
         float v[4] = {v4.x, v4.y, v4.z, v4.w};
         head_norm_rope(v, L.q_norm, sh.cs, p.eps, lane, true);
         *reinterpret_cast<float4*>(&sh.sq[warp][(lane >> 3) * MG_SQ_QUARTER + (lane & 7) * 4]) = make_float4(v[0], v[1], v[2], v[3]);
@@ -445,25 +454,20 @@ __device__ DC_HOT void attn_scores_phase(const MegaParams& p, const MegaLayer& L
     __syncthreads();   // sq ready; this CTA's K/V stores are visible to its own loads
     MG_SUB(24);
     if (h0 < h1) {
+        float kf[32];
         for (int k0 = 0; k0 + kgi * 8 < n_keys; k0 += KG * 8) {
             const int kk = k0 + kgi * 8 + (lane >> 2), sub = lane & 3;
-            if (k0 > 0) mg_load_k(p, L, sh, it, n_keys, kk, sub, kf, valid, late);
-            if (late) {
+            if (late) {   // this CTA wrote the row before the barrier above
                 const int blk = kk / DC_KV_BLOCK;
                 const uint4* kp = reinterpret_cast<const uint4*>(
                     L.k_arena + (((size_t)sh.tbl[blk] * DC_KV_BLOCK + kk % DC_KV_BLOCK) * p.n_kv + it.kvh) * 128 + sub * 32);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint4 u = __ldcg(kp + i);
-                    const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 f = __half22float2(h2[j]);
-                        kf[i * 8 + 2 * j] = f.x;
-                        kf[i * 8 + 2 * j + 1] = f.y;
-                    }
-                }
+                for (int i = 0; i < 4; ++i) kr[i] = __ldcg(kp + i);
             }
+            mg_k_to_float(kr, kf);
+            const bool cur_valid = valid;
+            // the next pass's rows are requested before this pass's dot products
+            if (k0 + KG * 8 + kgi * 8 < n_keys) mg_load_k_raw(p, L, sh, it, n_keys, kk + KG * 8, sub, kr, valid, late);
             // one head at a time, rolled: the loop body is small and stays in the instruction cache
 #pragma unroll 1
             for (int h = h0; h < h1; ++h) {
@@ -479,7 +483,7 @@ __device__ DC_HOT void attn_scores_phase(const MegaParams& p, const MegaLayer& L
                 }
                 dot += __shfl_xor_sync(0xffffffffu, dot, 1);
                 dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-                if (sub == 0 && kk < n_keys) s_sc[h * p.s_keys + kk] = valid ? __fmul_rn(dot, p.scale) : -INFINITY;
+                if (sub == 0 && kk < n_keys) s_sc[h * p.s_keys + kk] = cur_valid ? __fmul_rn(dot, p.scale) : -INFINITY;
             }
         }
     }
@@ -490,108 +494,138 @@ __device__ DC_HOT void attn_scores_phase(const MegaParams& p, const MegaLayer& L
         float mx = -1e30f;
 #pragma unroll
         for (int k = 0; k < DC_KV_BLOCK; ++k) mx = fmaxf(mx, s_sc[h * p.s_keys + bb * DC_KV_BLOCK + k]);
-        p.bmax[((size_t)it.t * p.n_head + it.kvh * g + h) * p.max_blocks + it.b0 + bb] = mx;
+        p.bmax[((size_t)it.t * p.n_head + head0 + h) * p.max_blocks + it.b0 + bb] = mx;
     }
 }
 
 // Phase 2: the reference's running-maximum chain from all block maxima, this run's
 // blocks accumulated as the reference walks them, partial scaled by the alphas of
-// all later blocks; the last run of a (token, kv head) sums the partials and emits
-// the Q8_K blocks of the attention output (hwy_paged_attention.cc:428-629).
+// all later blocks; the last run of a (token, kv head, head group) sums the partials and
+// emits the Q8_K blocks of the attention output (hwy_paged_attention.cc:428-629).
+// Every block's running maximum and rescale factor follow from the block maxima alone, so
+// they are computed for the whole run first (one warp per head); then all exponentials in
+// parallel; then one pass over the keys with no barrier inside.
 __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, MegaShared& sh,
                                               const AttnItem& it, const float* s_sc, const uint8_t* vbuf,
                                               int vcap_blocks) {
+#ifdef DC_MEGA_SUBMARKS
+    const unsigned long long pv_t0 = mg_now();
+#endif
     cp_async_wait_all();   // this thread's V copies of the scores phase have landed
     if (!it.valid) return;
-    const int g = p.n_head / p.n_kv;
+    const int g = it.gh, head0 = it.kvh * (p.n_head / p.n_kv) + it.hb;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nb_run = it.b1 - it.b0;
+    // per (head, block of the run): running maximum after the block, rescale factor, sum of the
+    // block's exponentials (the routing keys' space is idle during attention)
+    static_assert(sizeof(sh.rkeys) >= 3 * 8 * MG_MAX_RUN_BLOCKS * sizeof(float), "per-block attention state");
+    float* bl_mnew = reinterpret_cast<float*>(sh.rkeys);
+    float* bl_alpha = bl_mnew + 8 * MG_MAX_RUN_BLOCKS;
+    float* bl_ps = bl_alpha + 8 * MG_MAX_RUN_BLOCKS;
+    float* pw = const_cast<float*>(s_sc);   // scores become exponentials in place
     for (int h = warp; h < g; h += MG_WARPS) {
-        const float* bm = p.bmax + ((size_t)it.t * p.n_head + it.kvh * g + h) * p.max_blocks;
-        float m_start = -1e30f;
-        for (int b = lane; b < it.b0; b += 32) m_start = fmaxf(m_start, __ldcg(bm + b));
+        const float* bm = p.bmax + ((size_t)it.t * p.n_head + head0 + h) * p.max_blocks;
+        // blocks before the run only feed the running maximum; the run's blocks get their maximum and
+        // rescale factor; the factors of later blocks multiply into the suffix.  The block maxima are
+        // fetched 256 at a time so that their loads overlap.
+        float carry = -1e30f, suffix = 1.0f;
+        for (int s0 = 0; s0 < it.n_blk; s0 += 256) {
+            float vb[8];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m_start = fmaxf(m_start, __shfl_xor_sync(0xffffffffu, m_start, o));
-        float m_run = m_start;
-        for (int b = it.b0 + lane; b < it.b1; b += 32) m_run = fmaxf(m_run, __ldcg(bm + b));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m_run = fmaxf(m_run, __shfl_xor_sync(0xffffffffu, m_run, o));
-        float carry = m_run, suffix = 1.0f;
-        for (int c0 = it.b1; c0 < it.n_blk; c0 += 32) {
-            const int c = c0 + lane;
-            const float v = c < it.n_blk ? __ldcg(bm + c) : -1e30f;
-            float incl = v;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const float u = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl = fmaxf(incl, u);
+            for (int k = 0; k < 8; ++k) {
+                const int c = s0 + 32 * k + lane;
+                vb[k] = c < it.n_blk ? __ldcg(bm + c) : -1e30f;
             }
-            float excl = __shfl_up_sync(0xffffffffu, incl, 1);
-            if (lane == 0) excl = -1e30f;
-            const float m_prev = fmaxf(carry, excl), m_new = fmaxf(carry, incl);
-            float a = c < it.n_blk ? fast_exp_fma(m_prev - m_new) : 1.0f;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) a *= __shfl_xor_sync(0xffffffffu, a, o);
-            suffix *= a;
-            carry = fmaxf(carry, __shfl_sync(0xffffffffu, incl, 31));
+            for (int k = 0; k < 8; ++k) {
+                const int c0 = s0 + 32 * k, c = c0 + lane;
+                if (c0 >= it.n_blk) break;
+                if (c0 + 32 <= it.b0) {   // wholly before the run
+                    float mx = vb[k];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    carry = fmaxf(carry, mx);
+                    continue;
+                }
+                float incl = vb[k];
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const float u = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl = fmaxf(incl, u);
+                }
+                float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+                if (lane == 0) excl = -1e30f;
+                const float m_prev = fmaxf(carry, excl), m_new = fmaxf(carry, incl);
+                const float a = (c >= it.b0 && c < it.n_blk) ? fast_exp_fma(m_prev - m_new) : 1.0f;
+                if (c >= it.b0 && c < it.b1) {
+                    bl_mnew[h * MG_MAX_RUN_BLOCKS + c - it.b0] = m_new;
+                    bl_alpha[h * MG_MAX_RUN_BLOCKS + c - it.b0] = a;
+                }
+                if (c0 + 32 > it.b1) {   // the chunk reaches past the run
+                    float later = c >= it.b1 ? a : 1.0f;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) later *= __shfl_xor_sync(0xffffffffu, later, o);
+                    suffix *= later;
+                }
+                carry = fmaxf(carry, __shfl_sync(0xffffffffu, incl, 31));
+            }
         }
-        if (lane == 0) {
-            sh.suffix[h] = suffix;
-            sh.m[h] = m_start;
-            sh.d[h] = 0.0f;
-        }
+        if (lane == 0) sh.suffix[h] = suffix;
     }
-    // thread -> (dim, two heads): heads hq and hq + 4
-    const int dim = tid & 127, hq = tid >> 7;
-    float acc0 = 0.0f, acc1 = 0.0f;
-    __syncthreads();   // every thread's async copies are complete and visible
+    __syncthreads();   // every thread's async copies are complete and visible; block state is set
     {
         // the new token's V row was written during the scores phase, possibly after its
         // async copy was issued: the owning run copies that one row again
         const int pb_new = it.pos / DC_KV_BLOCK - it.b0;
-        if (pb_new >= 0 && pb_new < it.b1 - it.b0 && pb_new < vcap_blocks && tid < 16) {
+        if (pb_new >= 0 && pb_new < nb_run && pb_new < vcap_blocks && tid < 16) {
             const int slot = it.pos % DC_KV_BLOCK;
             const uint4* src = reinterpret_cast<const uint4*>(
                 L.v_arena + (((size_t)sh.tbl[pb_new] * DC_KV_BLOCK + slot) * p.n_kv + it.kvh) * 128) + tid;
             reinterpret_cast<uint4*>(const_cast<uint8_t*>(vbuf))[(pb_new * DC_KV_BLOCK + slot) * 16 + tid] = __ldcg(src);
         }
     }
-    __syncthreads();
-    const __half* vs = reinterpret_cast<const __half*>(vbuf);
-    for (int blk = it.b0; blk < it.b1; ++blk) {
-        const int bl = blk - it.b0;
-        const int nk = min(DC_KV_BLOCK, it.ctx_len - blk * DC_KV_BLOCK);
-        if (tid < 128) {
-            const int h = tid >> 4, key = tid & 15;
-            float s = -INFINITY;
-            if (h < g && key < nk) s = s_sc[h * p.s_keys + bl * DC_KV_BLOCK + key];
-            float mx = fmaxf(s, -1e30f);
+    // exponentials: 16 lanes per (head, block)
+    for (int base = 0; base < g * nb_run; base += MG_THREADS / 16) {
+        const int pair = base + (tid >> 4), key = tid & 15;
+        const bool in = pair < g * nb_run;
+        const int h = in ? pair / nb_run : 0, bl = in ? pair - h * nb_run : 0;
+        const int nk = min(DC_KV_BLOCK, it.ctx_len - (it.b0 + bl) * DC_KV_BLOCK);
+        const float s = (in && key < nk) ? pw[h * p.s_keys + bl * DC_KV_BLOCK + key] : -INFINITY;
+        const float pr = (s == -INFINITY) ? 0.0f : fast_exp_fma(s - bl_mnew[h * MG_MAX_RUN_BLOCKS + bl]);
+        float ps = pr;
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float m_prev = h < g ? sh.m[h] : -1e30f;
-            const float m_new = fmaxf(m_prev, mx);
-            const float pr = (s == -INFINITY) ? 0.0f : fast_exp_fma(s - m_new);
-            float ps = pr;
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-            if (h < g) sh.p[h][key] = pr;
-            __syncwarp();
-            if (h < g && key == 0) {
-                const float alpha = fast_exp_fma(m_prev - m_new);
-                sh.alpha[h] = alpha;
-                sh.d[h] = sh.d[h] * alpha + ps;
-                sh.m[h] = m_new;
-            }
+        for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        if (in) {
+            pw[h * p.s_keys + bl * DC_KV_BLOCK + key] = pr;
+            if (key == 0) bl_ps[h * MG_MAX_RUN_BLOCKS + bl] = ps;
         }
-        __syncthreads();
-        const bool h0 = hq < g, h1 = hq + 4 < g;
-        if (h0 && sh.alpha[hq] != 1.0f) acc0 *= sh.alpha[hq];
-        if (h1 && sh.alpha[hq + 4] != 1.0f) acc1 *= sh.alpha[hq + 4];
+    }
+    __syncthreads();
+    // thread -> (dim, two heads): heads hq and hq + 4
+    const int dim = tid & 127, hq = tid >> 7;
+    const bool h0 = hq < g, h1 = hq + 4 < g;
+    float acc0 = 0.0f, acc1 = 0.0f, d0 = 0.0f, d1 = 0.0f;
+    const __half* vs = reinterpret_cast<const __half*>(vbuf);
+    const float* p0 = pw + hq * p.s_keys;
+    const float* p1 = pw + (hq + 4) * p.s_keys;
+    for (int bl = 0; bl < nb_run; ++bl) {
+        const int nk = min(DC_KV_BLOCK, it.ctx_len - (it.b0 + bl) * DC_KV_BLOCK);
+        if (h0) {
+            const float a = bl_alpha[hq * MG_MAX_RUN_BLOCKS + bl];
+            if (a != 1.0f) acc0 *= a;
+            if (dim == 0) d0 = d0 * a + bl_ps[hq * MG_MAX_RUN_BLOCKS + bl];
+        }
+        if (h1) {
+            const float a = bl_alpha[(hq + 4) * MG_MAX_RUN_BLOCKS + bl];
+            if (a != 1.0f) acc1 *= a;
+            if (dim == 0) d1 = d1 * a + bl_ps[(hq + 4) * MG_MAX_RUN_BLOCKS + bl];
+        }
         if (bl < vcap_blocks) {
 #pragma unroll 4
             for (int key = 0; key < nk; ++key) {
                 const float v = __half2float(vs[(size_t)(bl * DC_KV_BLOCK + key) * 128 + dim]);
-                if (h0) acc0 = fmaf(sh.p[hq][key], v, acc0);
-                if (h1) acc1 = fmaf(sh.p[hq + 4][key], v, acc1);
+                if (h0) acc0 = fmaf(p0[bl * DC_KV_BLOCK + key], v, acc0);
+                if (h1) acc1 = fmaf(p1[bl * DC_KV_BLOCK + key], v, acc1);
             }
         } else {
             const __half* vb = L.v_arena + ((size_t)sh.tbl[bl] * DC_KV_BLOCK * p.n_kv + it.kvh) * 128 + dim;
@@ -599,58 +633,75 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
             for (int key = 0; key < nk; ++key) {
                 const float v = __half2float(
                     __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(vb + (size_t)key * p.n_kv * 128))));
-                if (h0) acc0 = fmaf(sh.p[hq][key], v, acc0);
-                if (h1) acc1 = fmaf(sh.p[hq + 4][key], v, acc1);
+                if (h0) acc0 = fmaf(p0[bl * DC_KV_BLOCK + key], v, acc0);
+                if (h1) acc1 = fmaf(p1[bl * DC_KV_BLOCK + key], v, acc1);
             }
         }
-        __syncthreads();
     }
-    if (hq < g) {
-        const size_t idx = ((size_t)it.t * p.n_head + it.kvh * g + hq) * p.nsplit + it.split;
+    if (h0) {
+        const size_t idx = ((size_t)it.t * p.n_head + head0 + hq) * p.nsplit + it.split;
         p.part_acc[idx * 128 + dim] = acc0 * sh.suffix[hq];
-        if (dim == 0) p.part_d[idx] = sh.d[hq] * sh.suffix[hq];
+        if (dim == 0) p.part_d[idx] = d0 * sh.suffix[hq];
     }
-    if (hq + 4 < g) {
-        const size_t idx = ((size_t)it.t * p.n_head + it.kvh * g + hq + 4) * p.nsplit + it.split;
+    if (h1) {
+        const size_t idx = ((size_t)it.t * p.n_head + head0 + hq + 4) * p.nsplit + it.split;
         p.part_acc[idx * 128 + dim] = acc1 * sh.suffix[hq + 4];
-        if (dim == 0) p.part_d[idx] = sh.d[hq + 4] * sh.suffix[hq + 4];
+        if (dim == 0) p.part_d[idx] = d1 * sh.suffix[hq + 4];
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) sh.last = (atomicAdd(p.tickets + it.t * p.n_kv + it.kvh, 1) == p.nsplit - 1);
+    int* ticket = p.tickets + (it.t * p.n_kv + it.kvh) * p.n_hg + it.hg;
+    if (tid == 0) sh.last = (atomicAdd(ticket, 1) == p.nsplit - 1);
     __syncthreads();
     if (!sh.last) return;
     __threadfence();
-    if (tid == 0) p.tickets[it.t * p.n_kv + it.kvh] = 0;
-    for (int pb2 = warp; pb2 < g / 2; pb2 += MG_WARPS) {
-        const int head = it.kvh * g + 2 * pb2 + (lane >> 4), d0 = (lane & 15) * 8;
-        const size_t base = ((size_t)it.t * p.n_head + head) * p.nsplit;
-        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0}, den = 0.0f;
-        for (int s0 = 0; s0 < p.nsplit; s0 += 4) {
-            float dd[4];
-            float4 a[4], c[4];
+    if (tid == 0) *ticket = 0;
+#ifdef DC_MEGA_SUBMARKS
+    const unsigned long long merge_t0 = mg_now();
+#endif
+    // every thread sums two neighbouring outputs of one head over the runs in run order, with 16 runs'
+    // loads in flight at a time; the sums meet in shared memory (the score buffer is idle by now) and
+    // one warp per 256-value block quantises them
+    float* merged = const_cast<float*>(s_sc);
+    for (int o2 = tid; o2 < g * 64; o2 += MG_THREADS) {
+        const int h = o2 >> 6, d0 = (o2 & 63) * 2;
+        const size_t base = ((size_t)it.t * p.n_head + head0 + h) * p.nsplit;
+        float v0 = 0.0f, v1 = 0.0f, den = 0.0f;
+        for (int s0 = 0; s0 < p.nsplit; s0 += 16) {
+            float dd[16];
+            float2 a[16];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {   // four runs' loads in flight, then added in run order
+            for (int j = 0; j < 16; ++j) {
                 const bool in = s0 + j < p.nsplit;
                 const size_t bi = base + (in ? s0 + j : 0);
-                dd[j] = in ? __ldcg(p.part_d + bi) : 0.0f;
-                a[j] = in ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0)) : make_float4(0, 0, 0, 0);
-                c[j] = in ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0 + 4)) : make_float4(0, 0, 0, 0);
+                dd[j] = __ldcg(p.part_d + bi);
+                a[j] = __ldcg(reinterpret_cast<const float2*>(p.part_acc + bi * 128 + d0));
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 16; ++j) {
                 if (s0 + j < p.nsplit) {
                     den += dd[j];
-                    v[0] += a[j].x; v[1] += a[j].y; v[2] += a[j].z; v[3] += a[j].w;
-                    v[4] += c[j].x; v[5] += c[j].y; v[6] += c[j].z; v[7] += c[j].w;
+                    v0 += a[j].x;
+                    v1 += a[j].y;
                 }
             }
         }
         const float inv = (den > 0.0f && isfinite(den)) ? __fdiv_rn(1.0f, __fadd_rn(den, 1e-6f)) : 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= inv;
-        quantize_block_q8k_regs(v, p.q8_attn + ((size_t)it.t * (p.n_head / 2) + it.kvh * (g / 2) + pb2) * DC_Q8K_BYTES, lane);
+        *reinterpret_cast<float2*>(merged + h * 128 + d0) = make_float2(v0 * inv, v1 * inv);
     }
+    __syncthreads();
+    for (int pb2 = warp; pb2 < g / 2; pb2 += MG_WARPS) {
+        const float4 x0 = *reinterpret_cast<const float4*>(merged + pb2 * 256 + lane * 8);
+        const float4 x1 = *reinterpret_cast<const float4*>(merged + pb2 * 256 + lane * 8 + 4);
+        const float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        quantize_block_q8k_regs(v, p.q8_attn + ((size_t)it.t * (p.n_head / 2) + head0 / 2 + pb2) * DC_Q8K_BYTES, lane);
+    }
+#ifdef DC_MEGA_SUBMARKS
+    if (p.phase_ns && tid == 0 && it.t == 0 && it.kvh == 0 && it.hg == 0) {
+        p.phase_ns[26] += mg_now() - merge_t0;      // the merge itself
+        p.phase_ns[27] += merge_t0 - pv_t0;         // from the start of the phase to the ticket
+    }
+#endif
 }
 
 // ------------------------------------------------------------- routing
@@ -720,38 +771,47 @@ __device__ DC_HOT void route_phase(const MegaParams& p, MegaShared& sh) {
         sh.rkeys[t][e] = mg_route_key(__ldcg(p.router_logits + i), e);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < p.T * p.E; i += MG_THREADS) {
-        const int t = i / p.E, e = i - t * p.E;
-        const unsigned long long mine = sh.rkeys[t][e];
-        int rank = 0;
-        for (int j = 0; j < p.E; ++j) rank += (sh.rkeys[t][j] > mine);
-        if (rank < p.top_k) {
-            sh.ids[t * p.top_k + rank] = e;
-            sh.sel[t][rank] = __ldcg(p.router_logits + i);
+    {
+        // Q neighbouring lanes share one candidate: each counts part of the row, a shuffle adds up
+        const int TE = p.T * p.E;
+        int Q = 1;
+        while (Q < 32 && TE * Q * 2 <= MG_THREADS) Q <<= 1;
+        for (int base = 0; base < TE; base += MG_THREADS / Q) {
+            const int i = base + (int)threadIdx.x / Q, part = (int)threadIdx.x % Q;
+            const bool in = i < TE;
+            const int t = in ? i / p.E : 0, e = in ? i - t * p.E : 0;
+            const unsigned long long mine = sh.rkeys[t][e];
+            int rank = 0;
+            if (in)
+                for (int j = part; j < p.E; j += Q) rank += (sh.rkeys[t][j] > mine);
+            for (int o = Q >> 1; o > 0; o >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+            if (in && part == 0 && rank < p.top_k) {
+                sh.ids[t * p.top_k + rank] = e;
+                // the logit back out of the key (NaN stays NaN; -0 was made +0, which exp treats alike)
+                const uint32_t u = (uint32_t)(mine >> 32);
+                sh.sel[t][rank] = __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
+            }
         }
     }
     __syncthreads();
-    if (threadIdx.x < p.T) {
-        // weights over the selected experts, sequentially as the reference does (native.cpp:649-674)
-        const int t = threadIdx.x;
-        float mx = -INFINITY;
-        bool finite = true;
-        for (int k = 0; k < p.top_k; ++k) {
-            const float v = sh.sel[t][k];
-            finite = finite && isfinite(v);
-            if (isfinite(v) && v > mx) mx = v;
-        }
+    if (warp < p.T) {
+        // weights over the selected experts (native.cpp:649-674): exponentials side by side, the sum in
+        // pick order as the reference adds them
+        const int t = warp;
+        const float v = lane < p.top_k ? sh.sel[t][lane] : -INFINITY;
+        const bool fin_l = lane >= p.top_k || isfinite(v);
+        const bool finite = __all_sync(0xffffffffu, fin_l);
+        float mx = (lane < p.top_k && isfinite(v)) ? v : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const bool use = finite && isfinite(mx);
+        const float ev = (use && lane < p.top_k) ? expf(v - mx) : 0.0f;
         float den = 0.0f;
-        if (finite && isfinite(mx))
-            for (int k = 0; k < p.top_k; ++k) {
-                const float ev = expf(sh.sel[t][k] - mx);
-                sh.w[t * p.top_k + k] = ev;
-                den += ev;
-            }
+        for (int k = 0; k < p.top_k; ++k) den += __shfl_sync(0xffffffffu, ev, k);
         const bool ok = den > 0.0f && isfinite(den);
-        for (int k = 0; k < p.top_k; ++k) {
-            const float w = ok ? __fdiv_rn(sh.w[t * p.top_k + k], den) : __fdiv_rn(1.0f, (float)p.top_k);
-            sh.w[t * p.top_k + k] = __fmul_rn(w, p.routed_scale);
+        if (lane < p.top_k) {
+            const float w = ok ? __fdiv_rn(ev, den) : __fdiv_rn(1.0f, (float)p.top_k);
+            sh.w[t * p.top_k + lane] = __fmul_rn(w, p.routed_scale);
         }
     }
     __syncthreads();
@@ -1100,6 +1160,13 @@ static int mg_rows_per_stage(int type, int K, int row_bytes) {
     return r < per_pass ? per_pass : r;
 }
 
+// Score buffer of an attention run: 8 heads x s_keys floats, and at least 8 x 128 floats because
+// the merging run reuses it for the merged heads.
+static uint32_t mg_sc_bytes(int s_keys) {
+    const int keys = s_keys < 128 ? 128 : s_keys;
+    return (uint32_t)((8 * keys * 4 + 127) & ~127);
+}
+
 // Decides whether the persistent kernel can run this model for T streams and fills
 // the parameter block.  Returns false (with a reason) when the shapes do not fit
 // its fixed shared-memory plan; the caller then uses the per-op kernels.
@@ -1124,7 +1191,12 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
     p.n_layer = c.n_layer; p.H = c.hidden; p.n_head = c.n_head; p.n_kv = c.n_kv_head; p.vocab = c.vocab;
     p.E = c.n_expert; p.top_k = c.n_expert_used; p.F = c.expert_ffn; p.T = T;
     p.eps = c.rms_eps; p.scale = 1.0f / sqrtf((float)c.head_dim); p.routed_scale = c.routed_scale;
-    p.nsplit = G / (T * c.n_kv_head);
+    // attention runs: (stream, kv head, head group, split).  More head groups mean fewer, longer runs per
+    // group and a shorter merge (the merging CTA adds nsplit partials per output); K/V rows are then read
+    // once per head group (from L2).  Groups hold an even number of heads (a Q8_K block spans two).
+    p.n_hg = 1;
+    while (p.n_hg < 4 && G / (T * c.n_kv_head * p.n_hg) > 20 && (g / (2 * p.n_hg)) % 2 == 0 && g / (2 * p.n_hg) >= 2) p.n_hg *= 2;
+    p.nsplit = G / (T * c.n_kv_head * p.n_hg);
     if (p.nsplit < 1) NO("fewer SMs than (stream, kv head) pairs");
     const int max_blocks = m->kv.max_blocks_per_seq;
     if (p.nsplit > max_blocks) p.nsplit = max_blocks;
@@ -1184,11 +1256,11 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
     off += (uint32_t)(T * c.hidden * 4);
     {   // V rows of an attention run are staged over act+xs: pad so a whole run fits, if there is room
         const uint32_t want = (uint32_t)(p.s_keys / DC_KV_BLOCK) * DC_KV_BLOCK * 256;
-        const uint32_t have = off - p.off_act, sc_bytes = (uint32_t)((8 * p.s_keys * 4 + 127) & ~127);
+        const uint32_t have = off - p.off_act, sc_bytes = mg_sc_bytes(p.s_keys);
         if (want > have && off + (want - have) + sc_bytes <= MG_DYN_LIMIT) off += want - have;
     }
     p.off_sc = off;
-    off += (uint32_t)((8 * p.s_keys * 4 + 127) & ~127);
+    off += mg_sc_bytes(p.s_keys);
     p.smem_bytes = off;
     if (off > MG_DYN_LIMIT) NO("shared memory plan exceeds the 227 KB of an SM");
     if (p.s_keys / DC_KV_BLOCK > MG_MAX_RUN_BLOCKS) NO("attention run longer than 64 KV blocks");

@@ -158,7 +158,7 @@ static int alloc_step_buffers(dc_model* m) {
     const size_t att_bytes = dc_attention_scratch_bytes((int)T, c.n_head, c.n_kv_head, m->kv.max_blocks_per_seq, m->nsplit);
     DC_TRY(dev_alloc(ctx, &b.attn_mem, att_bytes));
     dc_attn_scratch_bind(&b.attn, b.attn_mem, (int)T, c.n_head, c.n_kv_head, m->kv.max_blocks_per_seq, m->nsplit);
-    DC_TRY(dc_check_cuda(ctx, cudaMemsetAsync(b.attn.tickets, 0, T * c.n_kv_head * 4, ctx->stream), "memset"));
+    DC_TRY(dc_check_cuda(ctx, cudaMemsetAsync(b.attn.tickets, 0, T * c.n_head * 4, ctx->stream), "memset"));
     DC_TRY(dev_alloc(ctx, &b.q8_x, T * (H / 256) * 292));
     DC_TRY(dev_alloc(ctx, &b.q8_attn, T * (QD / 256) * 292));
     DC_TRY(dev_alloc(ctx, &b.q8_h, A * (F / 256) * 292));
