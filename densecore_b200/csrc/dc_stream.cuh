@@ -194,9 +194,32 @@ struct MoeStream {
     }
     MoeIter prod, cons;
     size_t estride;
+    // Flattened row index (unit * N + row) at weighted position x, where a row of a unit with nt
+    // tokens weighs 1 + nt (one decode plus one dot per token).
+    __device__ __forceinline__ static int row_at(const MoeMMParams& p, int U, long long x) {
+        long long cum = 0;
+        for (int u = 0; u < U; ++u) {
+            const int w = 1 + (p.uoff[u + 1] - p.uoff[u]);
+            const long long span = (long long)p.N * w;
+            if (x < cum + span) return u * p.N + (int)((x - cum) / w);
+            cum += span;
+        }
+        return U * p.N;
+    }
+    // Each warp takes a contiguous range of the active experts' rows; ranges are balanced by weight so
+    // that experts serving several tokens do not make their warps the last to finish.
     __device__ __forceinline__ void begin(const MoeMMParams& p, int U, int gw, int nw) {
-        const int total = U * p.N;
-        const int r0 = (int)((long long)gw * total / nw), r1 = (int)((long long)(gw + 1) * total / nw);
+        const int A = p.uoff[U];   // assignments in all units
+        int r0, r1;
+        if (A == U) {              // one token per expert everywhere: plain even split
+            const int total = U * p.N;
+            r0 = (int)((long long)gw * total / nw);
+            r1 = (int)((long long)(gw + 1) * total / nw);
+        } else {
+            const long long total_w = (long long)p.N * (U + A);
+            r0 = row_at(p, U, (long long)gw * total_w / nw);
+            r1 = gw + 1 == nw ? U * p.N : row_at(p, U, (long long)(gw + 1) * total_w / nw);
+        }
         prod = MoeIter{r0, r1, p.N, p.rpst};
         cons = MoeIter{r0, r1, p.N, p.rpst};
         estride = (size_t)p.N * p.row_bytes;
@@ -219,11 +242,51 @@ struct MoeStream {
             for (int s = 0; s < NSTAGE; ++s) issue_next(p, pipe);
         }
     }
+    // The rows of one stage for the first NTT token slots of tok/asg.
+    template <int NTT>
+    __device__ __forceinline__ static void stage_rows(const MoeMMParams& p, const ActSmem& act, uint32_t buf, uint32_t skew0,
+                                                      uint32_t skew1, int nhalf, int r, int n, int nt, const int* tok_in,
+                                                      const int* asg_in, int G, int grp, int lig) {
+        const int rows_per_pass = 32 / G;
+        int tok[NTT], asg[NTT];
+#pragma unroll
+        for (int s = 0; s < NTT; ++s) {
+            tok[s] = tok_in[s];
+            asg[s] = asg_in[s];
+        }
+        for (int rr0 = 0; rr0 < n; rr0 += rows_per_pass) {
+            const int rr = rr0 + grp;
+            const bool active = rr < n;
+            float v[NTT];
+#pragma unroll
+            for (int s = 0; s < NTT; ++s) v[s] = 0.0f;
+            // gate row first, then (pairs) the up row of the same output through the same code
+#pragma unroll 1
+            for (int half = 0; half < nhalf; ++half) {
+                float acc[NTT];
+#pragma unroll
+                for (int s = 0; s < NTT; ++s) acc[s] = 0.0f;
+                if (active)
+                    row_dot_partial<NTT>(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, lig, G, act, nt, tok, acc);
+#pragma unroll
+                for (int s = 0; s < NTT; ++s) {
+                    if (s < nt) {
+                        const float sum = group_sum_rt(acc[s], G);
+                        v[s] = half ? __fmul_rn(silu_fast(v[s]), sum) : sum;
+                    }
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < NTT; ++s)
+                if (s < nt && active && lig == (s & (G - 1))) p.out[(size_t)asg[s] * p.N + r + rr] = v[s];
+        }
+    }
+
     template <int NT>
     __device__ DC_HOT void consume(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
         const bool pair = is_pair(p);
         const int G = lanes_per_row(p.type, p.K);
-        const int rows_per_pass = 32 / G, grp = lane / G, lig = lane % G;
+        const int grp = lane / G, lig = lane % G;
         const int nhalf = pair ? 2 : 1;
         int u, r, n;
         while (cons.next(u, r, n)) {
@@ -238,32 +301,9 @@ struct MoeStream {
                 asg[s] = s < nt ? p.uassign[a0 + s] : 0;
                 tok[s] = pair ? asg[s] / p.top_k : asg[s];
             }
-            for (int rr0 = 0; rr0 < n; rr0 += rows_per_pass) {
-                const int rr = rr0 + grp;
-                const bool active = rr < n;
-                float v[NT];
-#pragma unroll
-                for (int s = 0; s < NT; ++s) v[s] = 0.0f;
-                // gate row first, then (pairs) the up row of the same output through the same code
-#pragma unroll 1
-                for (int half = 0; half < nhalf; ++half) {
-                    float acc[NT];
-#pragma unroll
-                    for (int s = 0; s < NT; ++s) acc[s] = 0.0f;
-                    if (active)
-                        row_dot_partial<NT>(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, lig, G, act, nt, tok, acc);
-#pragma unroll
-                    for (int s = 0; s < NT; ++s) {
-                        if (s < nt) {
-                            const float sum = group_sum_rt(acc[s], G);
-                            v[s] = half ? __fmul_rn(silu_fast(v[s]), sum) : sum;
-                        }
-                    }
-                }
-#pragma unroll
-                for (int s = 0; s < NT; ++s)
-                    if (s < nt && active && lig == (s & (G - 1))) p.out[(size_t)asg[s] * p.N + r + rr] = v[s];
-            }
+            // most experts of a step serve a single token: that case runs the one-token body
+            if (NT > 1 && nt == 1) stage_rows<1>(p, act, buf, skew0, skew1, nhalf, r, n, nt, tok, asg, G, grp, lig);
+            else stage_rows<NT>(p, act, buf, skew0, skew1, nhalf, r, n, nt, tok, asg, G, grp, lig);
             pipe.release();
             if (lane == 0) issue_next(p, pipe);
         }
