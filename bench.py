@@ -220,6 +220,9 @@ def main():
                          "per-op: one kernel per op, replayed as a CUDA graph")
     ap.add_argument("--phase-timing", action="store_true",
                     help="print the persistent kernel's per-phase device time (CTA 0's view) to stderr")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: peer = the persistent kernel stores expert outputs into all GPUs' buffers over NVLink "
+                         "(default); nccl = per-op kernels with one all-reduce per layer")
     ap.add_argument("--streams", default="1,4", help="stream counts to time (the JSON line needs 1)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed 1-stream decode run with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
@@ -255,6 +258,14 @@ def main():
             buf = torch.frombuffer(bytearray(raw.raw), dtype=torch.uint8).clone()
         dist.broadcast(buf, 0)
         model.ep_init(bytes(buf.numpy().tobytes()), nccl_path)
+        if args.ep_exchange == "peer":
+            # exchange buffers of the persistent kernel: every rank's handle to every rank
+            mine = torch.frombuffer(bytearray(model.ep_export()), dtype=torch.uint8).clone()
+            allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+            dist.all_gather(allh, mine)
+            for r in range(world):
+                if r != rank:
+                    model.ep_import(r, bytes(allh[r].numpy().tobytes()))
     model.finalize()
     if args.path == "per-op":
         model.set_option("persistent", 0)

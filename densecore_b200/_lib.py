@@ -116,6 +116,8 @@ def _signatures() -> dict:
         "dc_b200_kernel_class_name": (cstr, [i32]),
         "dc_b200_ep_unique_id": (i32, [vp, cstr, vp]),
         "dc_b200_model_ep_init": (i32, [vp, cstr, vp]),
+        "dc_b200_model_ep_export": (i32, [vp, vp]),
+        "dc_b200_model_ep_import": (i32, [vp, i32, vp]),
     }
 
 

@@ -10,6 +10,8 @@
 #define MG_MAX_T 4
 #define MG_MAX_E 256
 #define MG_MAX_K 16
+#define MG_MAX_RANKS 8
+#define MG_XCH_FLAG_BYTES 256   // flag array at the head of an exchange buffer
 // barrier counter (64 bytes) + 32 phase accumulators + a per-CTA barrier trace (14 x 160)
 #define DC_MEGA_TIMING_SLOTS (32 + 14 * 160)
 #define DC_MEGA_COUNTER_BYTES (64 + DC_MEGA_TIMING_SLOTS * 8)
@@ -50,6 +52,14 @@ struct MegaParams {
     float* route_w;
     int nsplit, s_keys;            // attention runs per (token, kv head, head group); keys a run can hold
     int n_hg;                      // head groups a kv head's query heads are split into (1, 2 or 4)
+    // expert parallel (ep_size > 1): experts [e_lo, e_hi) live here.  Every rank stores the rows its experts
+    // produce in the down projection into all ranks' exchange buffers (peer stores over NVLink), then the ranks
+    // meet once per layer through flags in each other's memory; the combine then reads local memory only.
+    int ep_rank, ep_size, e_lo, e_hi;
+    float* xdn[MG_MAX_RANKS];        // rank r's exchange rows: two halves of [MG_MAX_T * MG_MAX_K][H] floats
+    unsigned* xflag[MG_MAX_RANKS];   // in rank r's memory: the flag this rank raises there
+    unsigned* my_flags;              // this rank's flags, one per peer
+    unsigned xepoch0;                // exchanges completed before this launch
     // sync
     unsigned* bar_counter;
     int* err;

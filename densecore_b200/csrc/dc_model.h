@@ -71,6 +71,12 @@ struct dc_model {
     bool ep_ready = false;
     void* ep_comm = nullptr;     // ncclComm_t
     void* ep_lib = nullptr;      // dlopen handle of libnccl
+    // exchange buffer of the persistent kernel's expert-parallel path: flags, then two halves of rows;
+    // xch_peer[r] is rank r's buffer mapped into this process (own rank: xch itself)
+    uint8_t* xch = nullptr;
+    uint8_t* xch_peer[8] = {};
+    int xch_connected = 0;       // peers mapped so far
+    unsigned xepoch = 0;         // exchanges completed by earlier launches
 };
 
 // ---- synth.cu ----
@@ -78,6 +84,7 @@ int dc_launch_synth_quantized(dc_ctx* ctx, int type, uint64_t seed, int64_t firs
                               uint8_t* out);
 int dc_launch_synth_f32(dc_ctx* ctx, uint64_t seed, int64_t n, float sigma, float offset, float* out);
 // ---- mega.cu ----
+void dc_mega_release_xch(dc_model* m);
 struct MegaParams;
 bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why);
 int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback);

@@ -168,6 +168,8 @@ struct MoeMMParams {
     const int32_t* uoff;
     const int32_t* uassign;
     float* out;           // [assignment][N]
+    float* peer_out[7];   // the same array in other GPUs' memory: results are stored there too
+    int n_peer;
     int rpst;
     uint32_t stage_bytes, up_off;
     int* err;
@@ -278,7 +280,11 @@ struct MoeStream {
             }
 #pragma unroll
             for (int s = 0; s < NTT; ++s)
-                if (s < nt && active && lig == (s & (G - 1))) p.out[(size_t)asg[s] * p.N + r + rr] = v[s];
+                if (s < nt && active && lig == (s & (G - 1))) {
+                    const size_t oi = (size_t)asg[s] * p.N + r + rr;
+                    p.out[oi] = v[s];
+                    for (int q = 0; q < p.n_peer; ++q) p.peer_out[q][oi] = v[s];
+                }
         }
     }
 

@@ -14,6 +14,7 @@
 // mbarrier that does not complete within its poll limit records an error code
 // and the kernel carries on to its end.
 #include <cooperative_groups.h>
+#include <string.h>
 
 #include "dc_common.cuh"
 #include "dc_internal.h"
@@ -36,7 +37,7 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 // All CTAs of the (co-resident) grid meet here.  counter only grows during a
 // launch; the host zeroes it before the launch.
 __device__ __forceinline__ unsigned long long mg_now();
-__device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch) {
+__device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch, bool sys_scope = false) {
     __syncthreads();
     ++epoch;
 #ifdef DC_MEGA_SUBMARKS
@@ -45,7 +46,8 @@ __device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch) 
     if (trace) p.phase_ns[32 + (epoch - 8) * 160 + blockIdx.x] = mg_now();
 #endif
     if (threadIdx.x == 0) {
-        __threadfence();
+        if (sys_scope) __threadfence_system();   // this CTA's stores to other GPUs are performed first
+        else __threadfence();
         atomicAdd(p.bar_counter, 1u);
         const unsigned target = epoch * gridDim.x;
         unsigned polls = 0;
@@ -61,6 +63,44 @@ __device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch) 
 #ifdef DC_MEGA_SUBMARKS
     if (trace) p.phase_ns[32 + (7 + epoch - 8) * 160 + blockIdx.x] = mg_now();
 #endif
+    __syncthreads();
+}
+
+// Expert-parallel meeting point, once per layer, after a grid barrier with system-scope fences: CTA 0
+// raises this rank's flag in every peer's memory; every CTA then waits until all peers have raised theirs
+// here (their rows for this layer are then in this GPU's exchange buffer).  The wait gives up after two
+// seconds, or at once if an error is already recorded, and records DC_ERR_EP_WAIT.
+#define DC_ERR_EP_WAIT 3
+#define MG_EP_WAIT_NS 2000000000ull
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __noinline__ void ep_exchange(const MegaParams& p, unsigned value) {
+    if (threadIdx.x == 0) {
+        if (blockIdx.x == 0) {
+            __threadfence_system();
+            for (int r = 0; r < p.ep_size; ++r)
+                if (r != p.ep_rank) st_release_sys_u32(p.xflag[r], value);
+        }
+        const unsigned long long t0 = mg_now();
+        for (int r = 0; r < p.ep_size; ++r) {
+            if (r == p.ep_rank) continue;
+            // flags only grow; the difference is taken modulo 2^32
+            while ((int)(ld_acquire_sys_u32(p.my_flags + r) - value) < 0) {
+                if (*reinterpret_cast<volatile int*>(p.err) != 0) break;
+                if (mg_now() - t0 > MG_EP_WAIT_NS) {
+                    atomicExch(p.err, DC_ERR_EP_WAIT);
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+    }
     __syncthreads();
 }
 
@@ -174,7 +214,7 @@ static constexpr uint32_t MG_DYN_LIMIT =
 // NPI (token, block) pairs per warp: T * H/256 <= 16 * NPI.
 template <int NPI>
 __device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, int src, const float* x_in, float* x_out,
-                                          const float* w, const ActSmem& act, float* xn) {
+                                          const float* w, const ActSmem& act, float* xn, const float* dn) {
     const int H = p.H, nb = H / DC_QK_K, pairs = p.T * nb;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float v[NPI][8];
@@ -206,7 +246,7 @@ __device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, i
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {   // four experts' rows in flight
                         const int k = min(k0 + j, p.top_k - 1);
-                        const float* dr = p.dn + (size_t)(t * p.top_k + k) * H + dd;
+                        const float* dr = dn + (size_t)(t * p.top_k + k) * H + dd;
                         d0[j] = __ldcg(reinterpret_cast<const float4*>(dr));
                         d1[j] = __ldcg(reinterpret_cast<const float4*>(dr + 4));
                     }
@@ -854,7 +894,7 @@ __device__ DC_HOT void route_phase(const MegaParams& p, MegaShared& sh) {
     // bucketing: thread e owns expert e (E <= 256 < 512 threads)
     const int A = p.T * p.top_k, me = threadIdx.x;
     int cnt = 0;
-    if (me < p.E)
+    if (me >= p.e_lo && me < p.e_hi)   // experts stored on this GPU
         for (int i = 0; i < A; ++i) cnt += (sh.ids[i] == me);
     const int act = cnt > 0 ? 1 : 0;
     int sa = act, scn = cnt;
@@ -977,7 +1017,8 @@ __device__ __forceinline__ MoeMMParams mg_experts(const MegaParams& p, const Meg
     m.N = N;
     m.K = K;
     m.top_k = p.top_k;
-    m.e_base = 0;
+    m.e_base = p.e_lo;
+    m.n_peer = 0;
     m.uexp = sh.uexp;
     m.uoff = sh.uoff;
     m.uassign = sh.uassign;
@@ -1044,6 +1085,11 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
     // in the other phases (both are idle during attention)
     uint8_t* vbuf = act_base;
     const int vcap_blocks = (int)((p.off_sc - p.off_act) / (DC_KV_BLOCK * 256));
+    // expert parallel: rows of the down projection go to the exchange buffers, alternating halves by layer
+    const bool ep = p.ep_size > 1;
+    const size_t xhalf = (size_t)MG_MAX_T * MG_MAX_K * p.H;
+    unsigned xe = p.xepoch0;           // exchanges done so far (all ranks count alike)
+    const float* dn_r = p.dn;          // where the pending MoE output is read from
     for (int step = 0; step < p.n_steps; ++step) {
         const AttnItem item = attn_step_setup(p, sh);
         load_layer(p, sh, 0, 0);
@@ -1062,7 +1108,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             MG_MARK(0);
             ActSmem act;
             act.bind(act_base, p.T, p.H);
-            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, l == 0 ? 0 : 1, xin, xout, L.attn_norm, act, nullptr);
+            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, l == 0 ? 0 : 1, xin, xout, L.attn_norm, act, nullptr, dn_r);
             MG_MARK(2);
             mg_gemv_consume<NT>(gq, pipe, act, gw, nw, lane);
             MG_MARK(3);
@@ -1094,7 +1140,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             MG_MARK(11);
             // ---- P4: ffn_norm, Q8_K, router logits
             act.bind(act_base, p.T, p.H);
-            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 2, xout, nullptr, L.ffn_norm, act, xs);
+            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 2, xout, nullptr, L.ffn_norm, act, xs, nullptr);
             MG_MARK(12);
             router_logits_phase(p, L, sh, xs);
             MG_MARK(13);
@@ -1103,9 +1149,16 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             // ---- P5: routing, gate/up + SwiGLU
             route_phase(p, sh);
             MG_MARK(15);
+            float* dn_w = ep ? p.xdn[p.ep_rank] + (xe & 1u) * xhalf : p.dn;
             if (tid == 0) {
                 sh.m_gu = mg_experts(p, sh, L.gate, L.up, L.gate_type, L.gate_rb, p.F, p.H, p.rpst_gate, p.h);
-                sh.m_dn = mg_experts(p, sh, L.down, nullptr, L.down_type, L.down_rb, p.H, p.F, p.rpst_down, p.dn);
+                sh.m_dn = mg_experts(p, sh, L.down, nullptr, L.down_type, L.down_rb, p.H, p.F, p.rpst_down, dn_w);
+                if (ep) {   // the same rows in every peer's exchange buffer
+                    int q = 0;
+                    for (int r = 0; r < p.ep_size; ++r)
+                        if (r != p.ep_rank) sh.m_dn.peer_out[q++] = p.xdn[r] + (xe & 1u) * xhalf;
+                    sh.m_dn.n_peer = q;
+                }
             }
             __syncthreads();
             const MoeMMParams& mgu = sh.m_gu;
@@ -1154,13 +1207,16 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
                 __syncthreads();
                 mg_gemv_prefill(glm, pipe, gw, nw, lane);
             }
-            grid_barrier(p, epoch);
+            grid_barrier(p, epoch, ep);
+            if (ep) ep_exchange(p, xe + 1);
+            ++xe;
+            dn_r = dn_w;
             MG_MARK(20);
         }
         // ---- final: last MoE output + residual, output norm, lm_head with arg-max keys
         ActSmem act;
         act.bind(act_base, p.T, p.H);
-        x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 1, (p.n_layer & 1) ? p.xb : p.xa, nullptr, p.out_norm, act, nullptr);
+        x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 1, (p.n_layer & 1) ? p.xb : p.xa, nullptr, p.out_norm, act, nullptr, dn_r);
         mg_gemv_consume<NT>(glm, pipe, act, gw, nw, lane);
         grid_barrier(p, epoch);
         MG_MARK(21);
@@ -1216,7 +1272,8 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
         return false;  \
     } while (0)
     if (c.n_expert <= 0) NO("dense FFN models use the per-op kernels");
-    if (c.ep_size > 1) NO("expert-parallel runs use the per-op kernels");
+    if (c.ep_size > 1 && (c.ep_size > MG_MAX_RANKS || m->xch_connected != c.ep_size - 1))
+        NO("expert-parallel exchange buffers are not connected (dc_b200_model_ep_export / _import)");
     if (T < 1 || T > MG_MAX_T || T * c.n_expert_used > MG_MAX_T * 8) NO("more than 4 streams or 32 assignments");
     if (c.n_expert > MG_MAX_E || c.n_expert_used > MG_MAX_K) NO("too many experts");
     const int g = c.n_head / c.n_kv_head;
@@ -1357,6 +1414,16 @@ int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback) {
     p.q8_attn = b.q8_attn;
     p.route_ids = b.route.ids;
     p.route_w = b.route.weights;
+    p.ep_rank = m->cfg.ep_rank; p.ep_size = m->cfg.ep_size; p.e_lo = m->ep_lo; p.e_hi = m->ep_hi;
+    if (p.ep_size > 1) {
+        for (int r = 0; r < p.ep_size; ++r) {
+            p.xdn[r] = (float*)(m->xch_peer[r] + MG_XCH_FLAG_BYTES);
+            p.xflag[r] = (unsigned*)m->xch_peer[r] + p.ep_rank;
+        }
+        p.my_flags = (unsigned*)m->xch;
+        p.xepoch0 = m->xepoch;
+        m->xepoch += (unsigned)(m->cfg.n_layer * n_steps);
+    }
     p.bar_counter = m->mega_counter;
     p.err = m->ctx->d_err;
     p.phase_ns = m->mega_timing ? (unsigned long long*)((uint8_t*)m->mega_counter + 64) : nullptr;
@@ -1392,4 +1459,56 @@ int dc_mega_prepare(dc_model* m) {
     if (e == cudaSuccess) e = cudaMemcpy(m->mega_layers, v.data(), v.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemset(m->mega_counter, 0, DC_MEGA_COUNTER_BYTES);
     return dc_check_cuda(m->ctx, e, "persistent decode set-up");
+}
+
+// ---- expert-parallel exchange buffers (one process per GPU; handles travel through the caller) ----
+size_t dc_mega_xch_bytes(const dc_model* m) {
+    return MG_XCH_FLAG_BYTES + 2 * (size_t)MG_MAX_T * MG_MAX_K * m->cfg.hidden * sizeof(float);
+}
+
+extern "C" {
+
+int dc_b200_model_ep_export(dc_model* m, void* handle_out_64) {
+    if (!m || !handle_out_64) return DC_B200_INVALID_ARGUMENT;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaSetDevice(m->ctx->device);
+    if (!m->xch) {
+        cudaError_t e = cudaMalloc((void**)&m->xch, dc_mega_xch_bytes(m));
+        if (e == cudaSuccess) e = cudaMemset(m->xch, 0, dc_mega_xch_bytes(m));
+        if (e != cudaSuccess) return dc_check_cuda(m->ctx, e, "exchange buffer");
+        m->xch_peer[m->cfg.ep_rank] = m->xch;
+    }
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, m->xch);
+    if (e != cudaSuccess) return dc_check_cuda(m->ctx, e, "cudaIpcGetMemHandle");
+    memcpy(handle_out_64, &h, 64);
+    return DC_B200_OK;
+}
+
+int dc_b200_model_ep_import(dc_model* m, int rank, const void* handle_64) {
+    if (!m || !handle_64 || rank < 0 || rank >= m->cfg.ep_size || rank >= MG_MAX_RANKS || rank == m->cfg.ep_rank)
+        return DC_B200_INVALID_ARGUMENT;
+    if (!m->xch) return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "ep_import before ep_export");
+    if (m->xch_peer[rank]) return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "rank %d is already connected", rank);
+    cudaSetDevice(m->ctx->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle_64, 64);
+    void* ptr = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return dc_check_cuda(m->ctx, e, "cudaIpcOpenMemHandle");
+    m->xch_peer[rank] = (uint8_t*)ptr;
+    m->xch_connected++;
+    return DC_B200_OK;
+}
+
+}  // extern "C"
+
+void dc_mega_release_xch(dc_model* m) {
+    for (int r = 0; r < 8; ++r) {
+        if (m->xch_peer[r] && m->xch_peer[r] != m->xch) cudaIpcCloseMemHandle(m->xch_peer[r]);
+        m->xch_peer[r] = nullptr;
+    }
+    if (m->xch) cudaFree(m->xch);
+    m->xch = nullptr;
+    m->xch_connected = 0;
 }

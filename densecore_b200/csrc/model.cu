@@ -453,6 +453,7 @@ void dc_b200_model_destroy(dc_model* m) {
         if (p) cudaFree(p);
     if (m->mega_layers) cudaFree(m->mega_layers);
     if (m->mega_counter) cudaFree(m->mega_counter);
+    dc_mega_release_xch(m);
     if (m->h_stage) cudaFreeHost(m->h_stage);
     dc_kv_release(&m->kv);
     delete m;

@@ -116,6 +116,16 @@ class Model:
         buf = (C.c_char * 128).from_buffer_copy(unique_id)
         self._check(_lib.lib().dc_b200_model_ep_init(self.handle, nccl_path.encode() if nccl_path else None, buf))
 
+    def ep_export(self) -> bytes:
+        """64-byte handle of this rank's exchange buffer (hand it to every other rank)."""
+        buf = (C.c_char * 64)()
+        self._check(_lib.lib().dc_b200_model_ep_export(self.handle, buf))
+        return bytes(buf.raw)
+
+    def ep_import(self, rank: int, handle: bytes):
+        buf = (C.c_char * 64).from_buffer_copy(handle)
+        self._check(_lib.lib().dc_b200_model_ep_import(self.handle, rank, buf))
+
     def finalize(self):
         self._check(_lib.lib().dc_b200_model_finalize(self.handle))
 

@@ -284,6 +284,19 @@ DC_B200_API int dc_b200_model_set_option(dc_model* m, const char* name, int valu
  * of libnccl.so.2, or NULL to use the loader's search path. */
 DC_B200_API int dc_b200_ep_unique_id(dc_ctx* ctx, const char* nccl_path, void* id_out_128);
 DC_B200_API int dc_b200_model_ep_init(dc_model* m, const char* nccl_path, const void* id_128);
+/* Exchange buffers of the persistent decode kernel's expert-parallel path (one process per GPU of one
+ * node).  Each rank exports a 64-byte handle of its buffer (cudaIpcGetMemHandle), the launcher hands
+ * every rank's handle to every other rank, and each rank imports its ep_size - 1 peers.  With all peers
+ * connected, decode steps of up to 4 streams run in the persistent kernel: every GPU stores the rows its
+ * experts produce straight into all GPUs' buffers over NVLink and the GPUs meet once per layer through
+ * flags in each other's memory, so the weighted combine runs in routing order on local memory and the
+ * result is bit-identical to a single GPU's (the NCCL all-reduce of the per-op path is only tolerance-
+ * equal).  Every rank must then make the same sequence of decode calls.  A rank whose peers do not
+ * arrive gives up after two seconds and the call returns DC_B200_BACKEND_ERROR.  Without these calls
+ * expert-parallel decode uses the per-op kernels and NCCL.  No counterpart in the reference (its experts
+ * share one address space). */
+DC_B200_API int dc_b200_model_ep_export(dc_model* m, void* handle_out_64);
+DC_B200_API int dc_b200_model_ep_import(dc_model* m, int rank, const void* handle_64);
 
 #ifdef __cplusplus
 }
