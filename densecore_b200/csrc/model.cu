@@ -343,9 +343,11 @@ static int upload_step_inputs(dc_model* m, const int32_t* tokens, const int32_t*
     return DC_B200_OK;
 }
 
-// The persistent kernel serves 1..4 decode streams of a single-GPU MoE model.
+// The persistent kernel serves decode steps of MoE models.  With 3-4 streams every phase is bound by
+// instruction issue and the per-op kernels (more resident warps per SM) are as fast or faster, so the
+// default sends only 1-2 streams to it.
 static bool mega_ok(dc_model* m, int T) {
-    if (!m->use_mega) return false;
+    if (!m->use_mega || (m->use_mega == 1 && T > 2)) return false;
     MegaParams p;
     const char* why = "";
     return dc_mega_plan(m, T, &p, &why);
@@ -730,7 +732,7 @@ int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
         return DC_B200_OK;
     }
     if (!strcmp(name, "persistent")) {
-        m->use_mega = value != 0;
+        m->use_mega = value < 0 ? 0 : value > 2 ? 2 : value;
         return DC_B200_OK;
     }
     if (!strcmp(name, "phase_timing")) {

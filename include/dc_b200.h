@@ -270,8 +270,9 @@ DC_B200_API int dc_b200_model_profile_step(dc_model* m, const int32_t* seqs, int
                                            int n_classes, float* ms_out, int* launches_out, double* bytes_out);
 DC_B200_API const char* dc_b200_kernel_class_name(int cls);
 /* "graphs" 0/1: replay each step shape as a CUDA graph (default 1).
- * "persistent" 0/1: decode steps of 1..4 streams of a single-GPU MoE model run in one
- * persistent cooperative kernel with grid barriers between phases (default 1). */
+ * "persistent" 0/1/2: decode steps of MoE models run in one persistent cooperative kernel with grid
+ * barriers between phases: 0 never, 1 for 1-2 streams (default: with 3-4 streams the per-op kernels are as
+ * fast), 2 for every stream count it supports (1-4). */
 DC_B200_API int dc_b200_model_set_option(dc_model* m, const char* name, int value);
 
 /* ---- expert parallelism over the GPUs of one node ---------------------------- */

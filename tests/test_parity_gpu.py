@@ -457,6 +457,32 @@ def test_decoder_two_streams_are_independent(ctx):
     m.close()
 
 
+def test_persistent_kernel_matches_per_op_kernels(ctx):
+    """The persistent cooperative kernel and the per-op kernels compute the same step: identical picked
+    tokens and bit-identical logits for 1, 2 and 4 streams (short contexts, where both split the KV alike)."""
+    cfg = tiny_cfg(True)
+    cfg.max_seqs = 4
+    m = dc.Model(ctx, cfg)
+    m.init_synthetic(42, 0.05)
+    m.finalize()
+    for T in (1, 2, 4):
+        res = {}
+        for mode in (0, 2):
+            m.set_option("persistent", mode)
+            seqs = [m.seq_alloc() for _ in range(T)]
+            rng = np.random.default_rng(5)
+            first = [m.prefill(s, rng.integers(0, cfg.vocab, size=19 + 3 * i)) for i, s in enumerate(seqs)]
+            out, lg = m.decode_step(seqs, first, want_logits=True)
+            run, _ = m.decode_run(seqs, out, 6)
+            res[mode] = (out.copy(), lg.copy(), run.copy(), m.step_stats()[0])
+            for s in seqs:
+                m.seq_free(s)
+        assert res[2][3] == 1 and res[0][3] > 1, "the two runs must have taken different paths"
+        assert np.array_equal(res[0][0], res[2][0]) and np.array_equal(res[0][2], res[2][2]), T
+        assert np.array_equal(res[0][1], res[2][1]), T
+    m.close()
+
+
 def test_model_error_behaviour(ctx):
     cfg = tiny_cfg(False)
     m = dc.Model(ctx, cfg)
