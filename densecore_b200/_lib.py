@@ -117,6 +117,9 @@ def _signatures() -> dict:
         "dc_b200_ep_unique_id": (i32, [vp, cstr, vp]),
         "dc_b200_model_ep_init": (i32, [vp, cstr, vp]),
         "dc_b200_model_ep_export": (i32, [vp, vp]),
+        "dc_b200_model_tensor_names": (i32, [vp, vp, i32, vp]),
+        "dc_b200_model_get_config": (i32, [vp, vp]),
+        "dc_b200_model_from_gguf": (i32, [vp, cstr, i32, i32, i32, i32, vp]),
         "dc_b200_model_ep_import": (i32, [vp, i32, vp]),
     }
 

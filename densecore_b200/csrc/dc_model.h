@@ -47,6 +47,7 @@ struct dc_model {
     dc_weight *tok_embd = nullptr, *out_norm = nullptr, *output = nullptr;
     std::vector<dc_weight*> owned;
     std::map<std::string, dc_weight*> names;
+    std::vector<std::string> all_names;   // every tensor the decoder needs, in load order
     dc_kv_cache kv;
     dc_step_buffers buf;
     int nsplit = 16;

@@ -461,6 +461,21 @@ void dc_b200_model_destroy(dc_model* m) {
     delete m;
 }
 
+int dc_b200_model_get_config(dc_model* m, dc_model_config* out) {
+    if (!m || !out) return DC_B200_INVALID_ARGUMENT;
+    *out = m->cfg;
+    return DC_B200_OK;
+}
+
+int dc_b200_model_tensor_names(dc_model* m, const char** names_out, int capacity, int* n_out) {
+    if (!m || !n_out) return DC_B200_INVALID_ARGUMENT;
+    if (m->all_names.empty()) m->all_names = tensor_names(m);
+    *n_out = (int)m->all_names.size();
+    if (names_out)
+        for (int i = 0; i < capacity && i < *n_out; ++i) names_out[i] = m->all_names[i].c_str();
+    return DC_B200_OK;
+}
+
 int dc_b200_model_set_tensor(dc_model* m, const char* name, int ggml_type, const int64_t ne[4], const void* data_host) {
     if (!m || !name || !ne || !data_host) return DC_B200_INVALID_ARGUMENT;
     cudaSetDevice(m->ctx->device);

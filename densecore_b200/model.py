@@ -75,6 +75,28 @@ class Model:
         ctx._check(_lib.lib().dc_b200_model_create(ctx.handle, C.byref(cc), C.byref(h)))
         self.handle = h
 
+    @classmethod
+    def from_gguf(cls, ctx: Context, path: str, max_seqs: int = 4, max_ctx: int = 0, ep_rank: int = 0, ep_size: int = 1):
+        """Model with configuration and tensors read from a GGUF file (not yet finalized)."""
+        h = C.c_void_p()
+        ctx._check(_lib.lib().dc_b200_model_from_gguf(ctx.handle, path.encode(), max_seqs, max_ctx, ep_rank, ep_size,
+                                                      C.byref(h)))
+        cc = _lib.ModelConfig()
+        ctx._check(_lib.lib().dc_b200_model_get_config(h, C.byref(cc)))
+        self = cls.__new__(cls)
+        self.ctx, self.handle = ctx, h
+        kw = {name: getattr(cc, name) for name, _ in _lib.ModelConfig._fields_}
+        kw["tie_embeddings"], kw["qk_norm"] = bool(kw["tie_embeddings"]), bool(kw["qk_norm"])
+        self.cfg = Config(**kw)
+        return self
+
+    def tensor_names(self):
+        n = C.c_int(0)
+        self._check(_lib.lib().dc_b200_model_tensor_names(self.handle, None, 0, C.byref(n)))
+        arr = (C.c_char_p * n.value)()
+        self._check(_lib.lib().dc_b200_model_tensor_names(self.handle, arr, n.value, C.byref(n)))
+        return [a.decode() for a in arr]
+
     def close(self):
         if self.handle:
             _lib.lib().dc_b200_model_destroy(self.handle)

@@ -220,6 +220,20 @@ DC_B200_API int dc_b200_model_set_tensor(dc_model* m, const char* name, int ggml
  * router F32).  sigma is the weight standard deviation. */
 DC_B200_API int dc_b200_model_init_synthetic(dc_model* m, uint64_t seed, float sigma);
 /* Looks a tensor up: type, shape, device address, bytes. */
+/* The model's configuration (as given to model_create, or as read from a GGUF file). */
+DC_B200_API int dc_b200_model_get_config(dc_model* m, dc_model_config* out);
+/* Names of all tensors the decoder needs (GGUF names: "token_embd.weight", "blk.0.attn_q.weight" ...).
+ * *n_out receives their number; up to `capacity` pointers (owned by the model) are written. */
+DC_B200_API int dc_b200_model_tensor_names(dc_model* m, const char** names_out, int capacity, int* n_out);
+/* Creates a model from a GGUF v2/v3 file: configuration from the metadata ("<arch>.block_count",
+ * ".embedding_length", ".attention.head_count[_kv]", ".attention.key_length",
+ * ".attention.layer_norm_rms_epsilon", ".rope.freq_base", ".expert_count", ".expert_used_count",
+ * ".expert_feed_forward_length", ".feed_forward_length"; the keys core/src/models/model_loader.cpp:2555-2829
+ * reads), tensors uploaded with their file bytes (Q4_K / Q6_K matrices, F32 vectors and router).
+ * max_seqs / max_ctx are run-time sizes (0: 4 streams, the file's context_length).  The model still needs
+ * dc_b200_model_ep_init (expert-parallel runs) and dc_b200_model_finalize. */
+DC_B200_API int dc_b200_model_from_gguf(dc_ctx* ctx, const char* path, int max_seqs, int max_ctx, int ep_rank,
+                                        int ep_size, dc_model** out_model);
 DC_B200_API int dc_b200_model_get_tensor(dc_model* m, const char* name, int* ggml_type, int64_t ne[4], void** dev,
                                          size_t* bytes);
 DC_B200_API int dc_b200_model_finalize(dc_model* m);
