@@ -371,12 +371,15 @@ def main():
                           f"{(a.max() - np.median(a)) / 1e3:6.2f}  release-last {(np.median(r) - a.max()) / 1e3:6.2f}",
                           file=sys.stderr)
     if args.profile_classes and rank == 0:
-        prof = model.profile_step(seqs[:1], r1["last"][:1])
-        prof = model.profile_step(seqs[:1], r1["last"][:1])
-        tot = sum(v[0] for v in prof.values())
-        for k, (ms_, n_, b_) in sorted(prof.items(), key=lambda kv: -kv[1][0]):
-            print(f"{k:22s} launches {n_:4d}  {ms_ * 1e3:9.1f} us  {ms_ / tot * 100:5.1f} %  "
-                  f"{b_ / n_ / 1e6:8.2f} MB/launch  {b_ / (ms_ * 1e-3) / 1e9 if ms_ else 0:8.1f} GB/s", file=sys.stderr)
+        for n_streams in stream_counts:
+            last = results[n_streams]["last"][:n_streams]
+            prof = model.profile_step(seqs[:n_streams], last)
+            prof = model.profile_step(seqs[:n_streams], last)
+            tot = sum(v[0] for v in prof.values())
+            print(f"per-op kernels, one eager step, {n_streams} stream(s): {tot * 1e3:.1f} us in kernels", file=sys.stderr)
+            for k, (ms_, n_, b_) in sorted(prof.items(), key=lambda kv: -kv[1][0]):
+                print(f"  {k:22s} launches {n_:4d}  {ms_ * 1e3:9.1f} us  {ms_ / tot * 100:5.1f} %  "
+                      f"{b_ / n_ / 1e6:8.2f} MB/launch  {b_ / (ms_ * 1e-3) / 1e9 if ms_ else 0:8.1f} GB/s", file=sys.stderr)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

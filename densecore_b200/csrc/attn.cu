@@ -52,7 +52,9 @@ __device__ __forceinline__ void split_range(int pos, int split, int nsplit, int&
 }
 
 __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
-    __shared__ __align__(16) float sq[ATT_MAX_GROUP][128];
+    // a q head as four 32-dim quarters 36 floats apart: the four lanes of a key read the same offset of
+    // different quarters, which then fall into different banks
+    __shared__ __align__(16) float sq[ATT_MAX_GROUP][4 * 36];
     __shared__ float sc[ATT_MAX_GROUP][ATT_TILE];
     __shared__ int s_blk[ATT_TILE / DC_KV_BLOCK];
     pdl_launch_dependents();
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
     if (b0 >= b1) return;
     const int32_t* table = p.block_tables + (size_t)p.seq_ids[t] * p.max_blocks;
     for (int i = tid; i < g * 128; i += 128)
-        sq[i >> 7][i & 127] = p.q[((size_t)t * p.n_head + kvh * g + (i >> 7)) * 128 + (i & 127)];
+        sq[i >> 7][((i & 127) >> 5) * 36 + (i & 31)] = p.q[((size_t)t * p.n_head + kvh * g + (i >> 7)) * 128 + (i & 127)];
     __syncthreads();
     const size_t ctx_pad = (size_t)p.max_blocks * DC_KV_BLOCK;
     for (int blk = b0; blk < b1; blk += ATT_TILE / DC_KV_BLOCK) {
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
             }
             for (int h = 0; h < g; ++h) {
                 float dot = 0.0f;
-                const float4* qp = reinterpret_cast<const float4*>(&sq[h][sub * 32]);
+                const float4* qp = reinterpret_cast<const float4*>(&sq[h][sub * 36]);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float4 qq = qp[i];
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
 
 __global__ void __launch_bounds__(128) k_attn_pv(const AttnParams p) {
     __shared__ float s_p[ATT_MAX_GROUP][DC_KV_BLOCK];
-    __shared__ float s_mstart[ATT_MAX_GROUP], s_suffix[ATT_MAX_GROUP];
+    __shared__ float s_suffix[ATT_MAX_GROUP];
     __shared__ float s_m[ATT_MAX_GROUP], s_d[ATT_MAX_GROUP], s_alpha[ATT_MAX_GROUP];
     __shared__ int s_last;
     pdl_launch_dependents();
@@ -153,7 +155,13 @@ __global__ void __launch_bounds__(128) k_attn_pv(const AttnParams p) {
     for (int h = warp; h < g; h += 4) {
         const float* bm = p.bmax + ((size_t)t * p.n_head + kvh * g + h) * p.max_blocks;
         float m_start = -1e30f;
-        for (int b = lane; b < b0; b += 32) m_start = fmaxf(m_start, bm[b]);
+        for (int b = lane; b < b0; b += 256) {   // eight loads in flight per lane
+            float vb8[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) vb8[k] = b + 32 * k < b0 ? bm[b + 32 * k] : -1e30f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m_start = fmaxf(m_start, vb8[k]);
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m_start = fmaxf(m_start, __shfl_xor_sync(0xffffffffu, m_start, o));
         float m_run = m_start;
@@ -181,7 +189,6 @@ __global__ void __launch_bounds__(128) k_attn_pv(const AttnParams p) {
             carry = fmaxf(carry, __shfl_sync(0xffffffffu, incl, 31));
         }
         if (lane == 0) {
-            s_mstart[h] = m_start;
             s_suffix[h] = suffix;
             s_m[h] = m_start;
             s_d[h] = 0.0f;
@@ -224,11 +231,18 @@ __global__ void __launch_bounds__(128) k_attn_pv(const AttnParams p) {
         for (int h = 0; h < ATT_MAX_GROUP; ++h)
             if (h < g && s_alpha[h] != 1.0f) acc[h] *= s_alpha[h];
         const __half* vb = p.v_arena + ((size_t)pb * DC_KV_BLOCK * p.n_kv + kvh) * 128 + tid;
-        for (int key = 0; key < nk; ++key) {
-            const float v = __half2float(vb[(size_t)key * p.n_kv * 128]);
+        // the block's 16 V values are requested together (rows beyond nk exist in the arena and are not used)
+        __half vv[DC_KV_BLOCK];
 #pragma unroll
-            for (int h = 0; h < ATT_MAX_GROUP; ++h)
-                if (h < g) acc[h] = fmaf(s_p[h][key], v, acc[h]);
+        for (int key = 0; key < DC_KV_BLOCK; ++key) vv[key] = vb[(size_t)key * p.n_kv * 128];
+#pragma unroll
+        for (int key = 0; key < DC_KV_BLOCK; ++key) {
+            if (key < nk) {
+                const float v = __half2float(vv[key]);
+#pragma unroll
+                for (int h = 0; h < ATT_MAX_GROUP; ++h)
+                    if (h < g) acc[h] = fmaf(s_p[h][key], v, acc[h]);
+            }
         }
         __syncthreads();
     }
@@ -254,12 +268,24 @@ __global__ void __launch_bounds__(128) k_attn_pv(const AttnParams p) {
         const int head = kvh * g + 2 * pb2 + (lane >> 4), d0 = (lane & 15) * 8;
         const size_t base = ((size_t)t * p.n_head + head) * p.nsplit;
         float v[8] = {0, 0, 0, 0, 0, 0, 0, 0}, den = 0.0f;
-        for (int s = 0; s < p.nsplit; ++s) {
-            den += __ldcg(p.part_d + base + s);
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_acc + (base + s) * 128 + d0));
-            const float4 c = __ldcg(reinterpret_cast<const float4*>(p.part_acc + (base + s) * 128 + d0 + 4));
-            v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-            v[4] += c.x; v[5] += c.y; v[6] += c.z; v[7] += c.w;
+        for (int s0 = 0; s0 < p.nsplit; s0 += 8) {
+            float dd[8];
+            float4 a[8], c[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {   // eight runs' loads in flight, then added in run order
+                const size_t bi = base + (s0 + j < p.nsplit ? s0 + j : 0);
+                dd[j] = __ldcg(p.part_d + bi);
+                a[j] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0));
+                c[j] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0 + 4));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (s0 + j < p.nsplit) {
+                    den += dd[j];
+                    v[0] += a[j].x; v[1] += a[j].y; v[2] += a[j].z; v[3] += a[j].w;
+                    v[4] += c[j].x; v[5] += c[j].y; v[6] += c[j].z; v[7] += c[j].w;
+                }
+            }
         }
         const float inv = (den > 0.0f && isfinite(den)) ? __fdiv_rn(1.0f, __fadd_rn(den, 1e-6f)) : 0.0f;
 #pragma unroll

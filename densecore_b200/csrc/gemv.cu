@@ -34,18 +34,20 @@ int dc_launch_quantize_q8k(dc_ctx* ctx, const float* x, int rows, int K, uint8_t
 }
 
 // ------------------------------------------------------------------- GEMV
-template <int NT>
+// NSTAGE: pipeline depth per warp (2 where that lets more CTAs share an SM: the row decode is bound by
+// instruction issue, so resident warps matter more than bytes in flight per warp).
+template <int NT, int NSTAGE>
 __global__ void __launch_bounds__(DC_WARPS * 32) k_gemv(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * DC_NSTAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * NSTAGE;
     uint8_t* act_base = smem + DC_WARPS * DC_NSTAGE * 8;
     const size_t act_bytes = (ActSmem::bytes(p.T, p.K) + 127) & ~(size_t)127;
-    uint8_t* bufs = act_base + act_bytes + (size_t)warp * DC_NSTAGE * p.stage_bytes;
+    uint8_t* bufs = act_base + act_bytes + (size_t)warp * NSTAGE * p.stage_bytes;
 
-    WarpPipe<DC_NSTAGE> pipe;
+    WarpPipe<NSTAGE> pipe;
     pipe.init(bufs, bars, p.stage_bytes, p.err);
-    GemvStream<DC_NSTAGE> st;
+    GemvStream<NSTAGE> st;
     st.begin(p, blockIdx.x * DC_WARPS + warp, gridDim.x * DC_WARPS);
     // Weights do not depend on the previous kernel: start streaming before waiting for it.
     st.prefill(p, pipe, lane);
@@ -67,12 +69,12 @@ static int rows_per_stage(int type, int K, int row_bytes) {
     return r < per_pass ? per_pass : r;
 }
 
-template <int NT>
-static int launch_gemv_nt(dc_ctx* ctx, const GemvParams& p, int grid, size_t smem) {
+template <int NT, int NSTAGE>
+static int launch_gemv_ns(dc_ctx* ctx, const GemvParams& p, int grid, size_t smem) {
     static bool configured = false;
     cudaError_t e = cudaSuccess;
     if (!configured) {
-        e = cudaFuncSetAttribute(k_gemv<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        e = cudaFuncSetAttribute(k_gemv<NT, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_gemv)");
         configured = true;
     }
@@ -86,8 +88,41 @@ static int launch_gemv_nt(dc_ctx* ctx, const GemvParams& p, int grid, size_t sme
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, k_gemv<NT>, p);
+    e = cudaLaunchKernelEx(&cfg, k_gemv<NT, NSTAGE>, p);
     return dc_check_cuda(ctx, e, "k_gemv");
+}
+
+static size_t gemv_smem(size_t act_bytes, uint32_t stage, int ns) {
+    return DC_WARPS * DC_NSTAGE * 8 + act_bytes + (size_t)DC_WARPS * ns * stage;
+}
+// CTAs of that size an SM holds (227 KB of shared memory, 1 KB reserved per CTA), at most 4.
+static int gemv_ctas_per_sm(size_t smem) {
+    if (smem > 200 * 1024) return 0;
+    const int n = (int)((227u * 1024u) / (smem + 1024));
+    return n > 4 ? 4 : n;
+}
+
+// Grid: a multiple of the SM count, no more warps than row groups; two stages per warp wherever that
+// puts more CTAs on an SM.
+template <int NT>
+static int launch_gemv_nt(dc_ctx* ctx, const GemvParams& p, size_t act_bytes, int total_rows) {
+    const size_t s4 = gemv_smem(act_bytes, p.stage_bytes, DC_NSTAGE), s2 = gemv_smem(act_bytes, p.stage_bytes, 2);
+    // resident CTAs per SM by shared memory, then by the kernel's registers (asked once per instance)
+    static int reg_limit4 = 0, reg_limit2 = 0;
+    if (!reg_limit4) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reg_limit4, k_gemv<NT, DC_NSTAGE>, DC_WARPS * 32, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reg_limit2, k_gemv<NT, 2>, DC_WARPS * 32, 0);
+        if (reg_limit4 < 1) reg_limit4 = 1;
+        if (reg_limit2 < 1) reg_limit2 = 1;
+    }
+    int n4 = gemv_ctas_per_sm(s4), n2 = gemv_ctas_per_sm(s2);
+    if (n4 > reg_limit4) n4 = reg_limit4;
+    if (n2 > reg_limit2) n2 = reg_limit2;
+    const bool two = n2 > n4;
+    int grid = ctx->num_sms * (two ? n2 : n4);
+    const int max_useful = (total_rows + DC_WARPS - 1) / DC_WARPS;
+    if (grid > max_useful) grid = max_useful < 1 ? 1 : max_useful;
+    return two ? launch_gemv_ns<NT, 2>(ctx, p, grid, s2) : launch_gemv_ns<NT, DC_NSTAGE>(ctx, p, grid, s4);
 }
 
 int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, const uint8_t* act_q8, int T, int K,
@@ -124,10 +159,10 @@ int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, con
     p.total_rows = total;
     p.stage_bytes = stage;
     const size_t act_bytes = (ActSmem::bytes(T, K) + 127) & ~(size_t)127;
-    const size_t smem = DC_WARPS * DC_NSTAGE * 8 + act_bytes + (size_t)DC_WARPS * DC_NSTAGE * stage;
-    if (smem > 200 * 1024) {
+    if (gemv_smem(act_bytes, stage, 2) > 200 * 1024) {
         // activations of all T tokens do not fit beside the weight pipeline: run the tokens in two halves
-        if (T == 1 || argmax) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemv: shared memory need %zu too large", smem);
+        if (T == 1 || argmax)
+            return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemv: shared memory need %zu too large", gemv_smem(act_bytes, stage, 2));
         const int T0 = T / 2;
         dc_gemv_seg second[3];
         for (int i = 0; i < n_seg; ++i) {
@@ -138,15 +173,10 @@ int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, con
         if (st != DC_B200_OK) return st;
         return dc_launch_gemv(ctx, second, n_seg, epi, act_q8 + (size_t)T0 * (K / DC_QK_K) * DC_Q8K_BYTES, T - T0, K, nullptr);
     }
-    // persistent-style grid: a multiple of the SM count, no more warps than row groups
-    int ctas_per_sm = smem <= 100 * 1024 ? 2 : 1;
-    int grid = ctx->num_sms * ctas_per_sm;
-    const int max_useful = (total + DC_WARPS - 1) / DC_WARPS;
-    if (grid > max_useful) grid = max_useful < 1 ? 1 : max_useful;
-    if (T == 1) return launch_gemv_nt<1>(ctx, p, grid, smem);
-    if (T <= 4) return launch_gemv_nt<4>(ctx, p, grid, smem);
-    if (T <= 8) return launch_gemv_nt<8>(ctx, p, grid, smem);
-    return launch_gemv_nt<16>(ctx, p, grid, smem);
+    if (T == 1) return launch_gemv_nt<1>(ctx, p, act_bytes, total);
+    if (T <= 4) return launch_gemv_nt<4>(ctx, p, act_bytes, total);
+    if (T <= 8) return launch_gemv_nt<8>(ctx, p, act_bytes, total);
+    return launch_gemv_nt<16>(ctx, p, act_bytes, total);
 }
 
 // ------------------------------------------------ per-block integer sums

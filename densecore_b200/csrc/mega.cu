@@ -27,6 +27,9 @@ using namespace dc;
 #define MG_BAR_LIMIT (1u << 21)
 #define MG_MAX_RUN_BLOCKS 64
 #define DC_ERR_GRID_BARRIER 2
+#ifndef MG_BAR_SLEEP
+#define MG_BAR_SLEEP 32   // nanoseconds between polls of the barrier counter
+#endif
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     unsigned v;
@@ -56,7 +59,7 @@ __device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch, 
                 atomicExch(p.err, DC_ERR_GRID_BARRIER);
                 break;
             }
-            __nanosleep(32);
+            if (MG_BAR_SLEEP) __nanosleep(MG_BAR_SLEEP);
         }
         __threadfence();
     }
@@ -1058,6 +1061,29 @@ __device__ __noinline__ void mg_moe_consume(const MoeMMParams& m, int U, WarpPip
     st.template consume<NT>(m, pipe, act, lane);
 }
 
+// Expert activations h [A][F] (written by all CTAs in the gate/up phase) -> Q8_K in shared memory,
+// one warp per 256-value block, two blocks per pass so that both loads are in flight together.
+__device__ __noinline__ void mg_h_quant(const MegaParams& p, const ActSmem& acth, int A) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nbh = p.F / DC_QK_K;
+    const int rotb = (int)(blockIdx.x % (unsigned)(A * nbh));
+    for (int il = warp; il < A * nbh; il += 2 * MG_WARPS) {
+        const int i0 = (il + rotb) % (A * nbh), il1 = il + MG_WARPS;
+        const bool two = il1 < A * nbh;
+        const int i1 = two ? (il1 + rotb) % (A * nbh) : i0;
+        const int a0 = i0 / nbh, b0 = i0 - a0 * nbh, a1 = i1 / nbh, b1 = i1 - a1 * nbh;
+        const float4* s0 = reinterpret_cast<const float4*>(p.h + (size_t)a0 * p.F + b0 * DC_QK_K) + 2 * lane;
+        const float4* s1 = reinterpret_cast<const float4*>(p.h + (size_t)a1 * p.F + b1 * DC_QK_K) + 2 * lane;
+        const float4 v0 = __ldcg(s0), v1 = __ldcg(s0 + 1), w0 = __ldcg(s1), w1 = __ldcg(s1 + 1);
+        const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        quantize_block_q8k_to_act(v, acth, a0, b0, lane);
+        if (two) {
+            const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            quantize_block_q8k_to_act(w, acth, a1, b1, lane);
+        }
+    }
+}
+
 template <int NT>
 __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_constant__ MegaParams gp) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -1144,11 +1170,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             MG_MARK(12);
             router_logits_phase(p, L, sh, xs);
             MG_MARK(13);
-            grid_barrier(p, epoch);
-            MG_MARK(14);
-            // ---- P5: routing, gate/up + SwiGLU
-            route_phase(p, sh);
-            MG_MARK(15);
+            // parameter blocks of the two expert phases: they depend on the layer, not on the routing, so
+            // they are built while this CTA would otherwise wait at the barrier
             float* dn_w = ep ? p.xdn[p.ep_rank] + (xe & 1u) * xhalf : p.dn;
             if (tid == 0) {
                 sh.m_gu = mg_experts(p, sh, L.gate, L.up, L.gate_type, L.gate_rb, p.F, p.H, p.rpst_gate, p.h);
@@ -1160,7 +1183,11 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
                     sh.m_dn.n_peer = q;
                 }
             }
-            __syncthreads();
+            grid_barrier(p, epoch);
+            MG_MARK(14);
+            // ---- P5: routing, gate/up + SwiGLU
+            route_phase(p, sh);   // ends with a CTA barrier: the blocks above are visible too
+            MG_MARK(15);
             const MoeMMParams& mgu = sh.m_gu;
             mg_moe_prefill(mgu, sh.n_active, pipe, gw, nw, lane);
             mg_moe_consume<NT>(mgu, sh.n_active, pipe, act, gw, nw, lane);
@@ -1180,18 +1207,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             // ---- P6: h -> Q8_K, down rows
             ActSmem acth;
             acth.bind(act_base, A, p.F);
-            {
-                const int nbh = p.F / DC_QK_K;
-                const int rotb = (int)(blockIdx.x % (unsigned)(A * nbh));
-                for (int il = warp; il < A * nbh; il += MG_WARPS) {
-                    const int i = (il + rotb) % (A * nbh);
-                    const int a = i / nbh, b = i - a * nbh;
-                    const float4* src = reinterpret_cast<const float4*>(p.h + (size_t)a * p.F + b * DC_QK_K) + 2 * lane;
-                    const float4 v0 = __ldcg(src), v1 = __ldcg(src + 1);
-                    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                    quantize_block_q8k_to_act(v, acth, a, b, lane);
-                }
-            }
+            mg_h_quant(p, acth, A);
             __syncthreads();
             MG_MARK(18);
             mg_moe_consume<NT>(mdn, sh.n_active, pipe, acth, gw, nw, lane);

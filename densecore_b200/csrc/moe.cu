@@ -50,7 +50,7 @@ __device__ __forceinline__ unsigned long long route_key(float v, int id) {
 __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
     __shared__ int s_last;
     __shared__ int32_t s_ids[DC_MAX_T * MOE_MAX_K];
-    __shared__ int s_cnt[MOE_MAX_E], s_wsum_a[8], s_wsum_c[8];
+    __shared__ int s_wsum_a[8], s_wsum_c[8];
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,20 +224,22 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
 }
 
 // --------------------------------------------------- expert matmul kernel
-template <int NT, bool PAIR>
+// NSTAGE: pipeline depth per warp.  Fewer, smaller rings let more CTAs share an SM: the row decode is
+// bound by instruction issue, so resident warps matter more than bytes in flight per warp.
+template <int NT, bool PAIR, int NSTAGE>
 __global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * DC_NSTAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * NSTAGE;
     uint8_t* act_base = smem + DC_WARPS * DC_NSTAGE * 8;
     const size_t act_bytes = (ActSmem::bytes(p.act_rows, p.K) + 127) & ~(size_t)127;
-    uint8_t* bufs = act_base + act_bytes + (size_t)warp * DC_NSTAGE * p.stage_bytes;
-    WarpPipe<DC_NSTAGE> pipe;
+    uint8_t* bufs = act_base + act_bytes + (size_t)warp * NSTAGE * p.stage_bytes;
+    WarpPipe<NSTAGE> pipe;
     pipe.init(bufs, bars, p.stage_bytes, p.err);
     pdl_launch_dependents();
     pdl_wait();  // expert ids come from the router kernel: nothing can be fetched before this
 
-    MoeStream<DC_NSTAGE, PAIR> st;
+    MoeStream<NSTAGE, PAIR> st;
     st.begin(p, *p.n_active, blockIdx.x * DC_WARPS + warp, gridDim.x * DC_WARPS);
     st.prefill(p, pipe, lane);
     ActSmem act;
@@ -247,15 +249,45 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
     st.template consume<NT>(p, pipe, act, lane);
 }
 
-template <int NT, bool PAIR>
-static int launch_moe_mm(dc_ctx* ctx, const MoeMMParams& p, int grid, size_t smem) {
+template <int NT, bool PAIR, int NSTAGE>
+static int launch_moe_mm_ns(dc_ctx* ctx, const MoeMMParams& p, int grid, size_t smem) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_moe_mm<NT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(k_moe_mm<NT, PAIR, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_moe_mm)");
         configured = true;
     }
-    return dc_launch(ctx, "k_moe_mm", k_moe_mm<NT, PAIR>, dim3(grid), dim3(DC_WARPS * 32), smem, p);
+    return dc_launch(ctx, "k_moe_mm", k_moe_mm<NT, PAIR, NSTAGE>, dim3(grid), dim3(DC_WARPS * 32), smem, p);
+}
+
+// Shared memory of one CTA with `ns` stages per warp.
+static size_t moe_smem(size_t act_bytes, uint32_t stage, int ns) {
+    return DC_WARPS * DC_NSTAGE * 8 + act_bytes + (size_t)DC_WARPS * ns * stage;
+}
+// CTAs of that size an SM holds (227 KB of shared memory, 1 KB reserved per CTA), at most 4.
+static int moe_ctas_per_sm(size_t smem) {
+    const int n = (int)((227u * 1024u) / (smem + 1024));
+    return n > 4 ? 4 : n;
+}
+
+template <int NT, bool PAIR>
+static int launch_moe_mm(dc_ctx* ctx, const MoeMMParams& p, size_t act_bytes) {
+    // two stages per warp wherever that puts more CTAs on an SM, else the full depth
+    const size_t s4 = moe_smem(act_bytes, p.stage_bytes, DC_NSTAGE), s2 = moe_smem(act_bytes, p.stage_bytes, 2);
+    // resident CTAs per SM by shared memory, then by the kernel's registers (asked once per instance)
+    static int reg_limit4 = 0, reg_limit2 = 0;
+    if (!reg_limit4) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reg_limit4, k_moe_mm<NT, PAIR, DC_NSTAGE>, DC_WARPS * 32, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reg_limit2, k_moe_mm<NT, PAIR, 2>, DC_WARPS * 32, 0);
+        if (reg_limit4 < 1) reg_limit4 = 1;
+        if (reg_limit2 < 1) reg_limit2 = 1;
+    }
+    int n4 = s4 <= 200 * 1024 ? moe_ctas_per_sm(s4) : 0, n2 = s2 <= 200 * 1024 ? moe_ctas_per_sm(s2) : 0;
+    if (n4 > reg_limit4) n4 = reg_limit4;
+    if (n2 > reg_limit2) n2 = reg_limit2;
+    if (n4 < 1 && n2 < 1) return dc_fail(ctx, DC_B200_UNSUPPORTED, "moe: shared memory need %zu too large", s2);
+    if (n2 > n4) return launch_moe_mm_ns<NT, PAIR, 2>(ctx, p, ctx->num_sms * n2, s2);
+    return launch_moe_mm_ns<NT, PAIR, DC_NSTAGE>(ctx, p, ctx->num_sms * n4, s4);
 }
 
 static int rows_per_stage_moe(int type, int K, int row_bytes) {
@@ -299,19 +331,16 @@ int dc_launch_moe_mm(dc_ctx* ctx, bool pair, const dc_weight* w0, const dc_weigh
     p.stage_bytes = stage;
     p.err = ctx->d_err;
     const size_t act_bytes = (ActSmem::bytes(act_rows, p.K) + 127) & ~(size_t)127;
-    const size_t smem = DC_WARPS * DC_NSTAGE * 8 + act_bytes + (size_t)DC_WARPS * DC_NSTAGE * stage;
-    if (smem > 200 * 1024) return dc_fail(ctx, DC_B200_UNSUPPORTED, "moe: shared memory need %zu too large", smem);
-    const int grid = ctx->num_sms * (smem <= 100 * 1024 ? 2 : 1);
     if (pair) {
-        if (T == 1) return launch_moe_mm<1, true>(ctx, p, grid, smem);
-        if (T <= 4) return launch_moe_mm<4, true>(ctx, p, grid, smem);
-        if (T <= 8) return launch_moe_mm<8, true>(ctx, p, grid, smem);
-        return launch_moe_mm<16, true>(ctx, p, grid, smem);
+        if (T == 1) return launch_moe_mm<1, true>(ctx, p, act_bytes);
+        if (T <= 4) return launch_moe_mm<4, true>(ctx, p, act_bytes);
+        if (T <= 8) return launch_moe_mm<8, true>(ctx, p, act_bytes);
+        return launch_moe_mm<16, true>(ctx, p, act_bytes);
     }
-    if (T == 1) return launch_moe_mm<1, false>(ctx, p, grid, smem);
-    if (T <= 4) return launch_moe_mm<4, false>(ctx, p, grid, smem);
-    if (T <= 8) return launch_moe_mm<8, false>(ctx, p, grid, smem);
-    return launch_moe_mm<16, false>(ctx, p, grid, smem);
+    if (T == 1) return launch_moe_mm<1, false>(ctx, p, act_bytes);
+    if (T <= 4) return launch_moe_mm<4, false>(ctx, p, act_bytes);
+    if (T <= 8) return launch_moe_mm<8, false>(ctx, p, act_bytes);
+    return launch_moe_mm<16, false>(ctx, p, act_bytes);
 }
 
 int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_expert, int T, int top_k, float scale,
