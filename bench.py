@@ -357,12 +357,15 @@ def main():
             model.set_option("phase_timing", 1)
             _, ms_pt = model.decode_run(seqs[:n_streams], results[n_streams]["last"], 32)
             pt = model.phase_timing()
+            arrive, release = model.barrier_trace()
             model.set_option("phase_timing", 0)
+            if model.step_stats()[0] != 1:
+                print(f"streams {n_streams}: per-op path ({ms_pt / 32 * 1e3:.1f} us/step), no phases", file=sys.stderr)
+                continue
             print(f"streams {n_streams}: {ms_pt / 32 * 1e3:.1f} us/step, {args.layers} layers; us per layer (CTA 0):", file=sys.stderr)
             for i, (name, ns) in pt.items():
                 if ns:
                     print(f"  {i:2d} {name:18s} {ns / 32 / args.layers / 1e3:8.2f}", file=sys.stderr)
-            arrive, release = model.barrier_trace()
             if arrive.any():   # instrumented build only
                 print("  barriers of layer 1, first step: spread of CTA arrivals and release latency (us)", file=sys.stderr)
                 for b, name in enumerate(model.BARRIERS):
