@@ -41,7 +41,8 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tok/s (1 & 4 streams), 35B-A3B-class Q4_K_M; % HBM roofline"
 UNIT = "tok/s"
 PROMPT = 2048
-SAMPLE_LAYERS = 2          # layers of the model the CPU baseline times per sample
+SAMPLE_LAYERS = 4          # layers of the model the CPU baseline times per sample
+SAMPLE_REPS = 12           # repeats of the sample (median taken)
 # DRAM bytes (read + write) of one launch of the persistent kernel divided by its algorithmic bytes,
 # from an ncu capture of the 4-layer case (profiles/k_decode_mega_moe35b_4layers.md)
 DRAM_TRAFFIC_RATIO = 1.04
@@ -411,10 +412,11 @@ def main():
         o.set_threads(threads)
         S = cpu_sample_setup(SAMPLE_LAYERS, r1["ctx"])
         cpu_sample_run(o, S, 1, rng)
-        v, step_s = cpu_tok_s(o, S, 1, 3, rng)
+        cpu_sample_run(o, S, 1, rng)
+        v, step_s = cpu_tok_s(o, S, 1, SAMPLE_REPS, rng)
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                                 "sample": f"{SAMPLE_LAYERS} of 48 layers + lm_head of one batch-1 decode step at ctx "
-                                          f"{r1['ctx']}, 3 repeats, scaled to 48 layers; CPU restatement of DenseCore's "
+                                          f"{r1['ctx']}, median of {SAMPLE_REPS} repeats, scaled to 48 layers; CPU restatement of DenseCore's "
                                           f"ggml path"}
     if rank == 0:
         print(json.dumps(line))
