@@ -224,6 +224,10 @@ def main():
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: peer = the persistent kernel stores expert outputs into all GPUs' buffers over NVLink "
                          "(default); nccl = per-op kernels with one all-reduce per layer")
+    ap.add_argument("--spec-sweep", action="store_true",
+                    help="after the decode runs: speculative decoding (target = this model, draft = the dense 0.8B-class "
+                         "model, gamma 4, greedy accept), with the draft model's own proposals and with synthetic drafts "
+                         "at forced 0/50/100 %% acceptance; table to stderr")
     ap.add_argument("--streams", default="1,4", help="stream counts to time (the JSON line needs 1)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed 1-stream decode run with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
@@ -374,6 +378,34 @@ def main():
                     print(f"    {name:20s} median-first {(np.median(a) - a.min()) / 1e3:6.2f}  last-median "
                           f"{(a.max() - np.median(a)) / 1e3:6.2f}  release-last {(np.median(r) - a.max()) / 1e3:6.2f}",
                           file=sys.stderr)
+    if args.spec_sweep and world == 1:
+        dcfg = dc.dense_0p8b(max_seqs=2, max_ctx=1024 + 512)
+        draft = dc.Model(ctx, dcfg)
+        draft.init_synthetic(4321, 0.02)
+        draft.finalize()
+        prompt = rng.integers(0, cfg.vocab, size=1024)
+        n_out, gamma = 128, 4
+        want, st0 = dc.speculative_decode(model, draft, prompt, n_out + gamma + 1, gamma=gamma)
+        print(f"speculative decoding, gamma {gamma}, greedy accept, 1024-token prompt, {n_out} output tokens:", file=sys.stderr)
+        print(f"  draft model's proposals: acceptance {st0.acceptance * 100:5.1f} %  {st0.tokens_per_step:4.2f} tokens/step  "
+              f"{st0.emitted / st0.seconds:7.1f} tok/s  {st0.seconds / st0.steps * 1e3:6.2f} ms/step", file=sys.stderr)
+
+        def forced(rate):
+            def f(pos, g):
+                true = want[pos:pos + g].copy()
+                if rate == 0.0:
+                    true[0] = (true[0] + 1) % cfg.vocab
+                elif rate == 0.5:
+                    true[g // 2] = (true[g // 2] + 1) % cfg.vocab
+                return true
+            return f
+        for rate in (0.0, 0.5, 1.0):
+            got, st = dc.speculative_decode(model, draft, prompt, n_out, gamma=gamma, forced_drafts=forced(rate))
+            ok = bool(np.array_equal(got, want[:n_out]))
+            print(f"  synthetic drafts {rate * 100:3.0f} %:  acceptance {st.acceptance * 100:5.1f} %  {st.tokens_per_step:4.2f} "
+                  f"tokens/step  {st.emitted / st.seconds:7.1f} tok/s  {st.seconds / st.steps * 1e3:6.2f} ms/verify step  "
+                  f"tokens equal the target's greedy stream: {ok}", file=sys.stderr)
+        draft.close()
     if args.profile_classes and rank == 0:
         for n_streams in stream_counts:
             last = results[n_streams]["last"][:n_streams]

@@ -92,6 +92,7 @@ def _signatures() -> dict:
         "dc_b200_argmax": (i32, [vp, vp, i32, i32, vp]),
         "dc_b200_verify_accept": (i32, [vp, vp, vp, vp, vp, u64, u32, i32, i32, i32, f32, pi, pi]),
         "dc_b200_verify_uniforms": (i32, [vp, u64, u32, i32, vp]),
+        "dc_b200_verify_accept_dev": (i32, [vp, vp, vp, vp, vp, u64, u32, i32, i32, i32, f32, pi, pi]),
         "dc_b200_softmax": (i32, [vp, vp, i32, i32, f32, vp]),
         "dc_b200_model_create": (i32, [vp, C.POINTER(ModelConfig), pp]),
         "dc_b200_model_destroy": (None, [vp]),

@@ -134,6 +134,55 @@ __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
     }
 }
 
+// Tail of both P.V kernels: the run's partials are in global memory; the last run of the (token, kv head)
+// to get here sums all runs in run order, normalises and emits (no run waits for another).
+__device__ __forceinline__ void attn_merge_tail(const AttnParams& p, int t, int kvh, int g, int tid, int warp, int lane,
+                                                int& s_last) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(p.tickets + t * p.n_kv + kvh, 1) == p.nsplit - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) p.tickets[t * p.n_kv + kvh] = 0;
+    // ---- last run of this (token, kv head): sum the runs in run order, normalise, emit.
+    // One warp per 256 outputs (two heads) = one Q8_K block of the o-projection input.
+    for (int pb2 = warp; pb2 < g / 2; pb2 += 4) {
+        const int head = kvh * g + 2 * pb2 + (lane >> 4), d0 = (lane & 15) * 8;
+        const size_t base = ((size_t)t * p.n_head + head) * p.nsplit;
+        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0}, den = 0.0f;
+        for (int s0 = 0; s0 < p.nsplit; s0 += 8) {
+            float dd[8];
+            float4 a[8], c[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {   // eight runs' loads in flight, then added in run order
+                const size_t bi = base + (s0 + j < p.nsplit ? s0 + j : 0);
+                dd[j] = __ldcg(p.part_d + bi);
+                a[j] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0));
+                c[j] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0 + 4));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (s0 + j < p.nsplit) {
+                    den += dd[j];
+                    v[0] += a[j].x; v[1] += a[j].y; v[2] += a[j].z; v[3] += a[j].w;
+                    v[4] += c[j].x; v[5] += c[j].y; v[6] += c[j].z; v[7] += c[j].w;
+                }
+            }
+        }
+        const float inv = (den > 0.0f && isfinite(den)) ? __fdiv_rn(1.0f, __fadd_rn(den, 1e-6f)) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= inv;
+        if (p.out) {
+            float* o = p.out + ((size_t)t * p.n_head + head) * 128 + d0;
+            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+        if (p.q8_out)
+            quantize_block_q8k_regs(v, p.q8_out + ((size_t)t * (p.n_head / 2) + kvh * (g / 2) + pb2) * DC_Q8K_BYTES, lane);
+    }
+}
+
 __global__ void __launch_bounds__(128) k_attn_pv(const AttnParams p) {
     __shared__ float s_p[ATT_MAX_GROUP][DC_KV_BLOCK];
     __shared__ float s_suffix[ATT_MAX_GROUP];
@@ -255,49 +304,134 @@ __global__ void __launch_bounds__(128) k_attn_pv(const AttnParams p) {
             if (tid == 0) p.part_d[idx] = s_d[h] * s_suffix[h];
         }
     }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(p.tickets + t * p.n_kv + kvh, 1) == p.nsplit - 1);
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    if (tid == 0) p.tickets[t * p.n_kv + kvh] = 0;
-    // ---- last run of this (token, kv head): sum the runs in run order, normalise, emit.
-    // One warp per 256 outputs (two heads) = one Q8_K block of the o-projection input.
-    for (int pb2 = warp; pb2 < g / 2; pb2 += 4) {
-        const int head = kvh * g + 2 * pb2 + (lane >> 4), d0 = (lane & 15) * 8;
-        const size_t base = ((size_t)t * p.n_head + head) * p.nsplit;
-        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0}, den = 0.0f;
-        for (int s0 = 0; s0 < p.nsplit; s0 += 8) {
-            float dd[8];
-            float4 a[8], c[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {   // eight runs' loads in flight, then added in run order
-                const size_t bi = base + (s0 + j < p.nsplit ? s0 + j : 0);
-                dd[j] = __ldcg(p.part_d + bi);
-                a[j] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0));
-                c[j] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + bi * 128 + d0 + 4));
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (s0 + j < p.nsplit) {
-                    den += dd[j];
-                    v[0] += a[j].x; v[1] += a[j].y; v[2] += a[j].z; v[3] += a[j].w;
-                    v[4] += c[j].x; v[5] += c[j].y; v[6] += c[j].z; v[7] += c[j].w;
-                }
-            }
-        }
-        const float inv = (den > 0.0f && isfinite(den)) ? __fdiv_rn(1.0f, __fadd_rn(den, 1e-6f)) : 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= inv;
-        if (p.out) {
-            float* o = p.out + ((size_t)t * p.n_head + head) * 128 + d0;
-            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-            *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
-        }
-        if (p.q8_out)
-            quantize_block_q8k_regs(v, p.q8_out + ((size_t)t * (p.n_head / 2) + kvh * (g / 2) + pb2) * DC_Q8K_BYTES, lane);
+    attn_merge_tail(p, t, kvh, g, tid, warp, lane, s_last);
+}
+
+// Same result as k_attn_pv for runs of at most ATT_MAX_RUN KV blocks, organised for latency: every
+// block's running maximum and rescale factor follow from the block maxima alone, so they are computed
+// for the whole run first (one batched load, prefix maxima by shuffles); then all exponentials of the
+// run at once; then one pass over the keys with no CTA barrier inside.
+#define ATT_MAX_RUN 64
+__global__ void __launch_bounds__(128) k_attn_pv_run(const AttnParams p) {
+    __shared__ float s_pw[ATT_MAX_GROUP * ATT_MAX_RUN * DC_KV_BLOCK];   // scores of the run, then exponentials
+    __shared__ float s_mnew[ATT_MAX_GROUP][ATT_MAX_RUN], s_alpha[ATT_MAX_GROUP][ATT_MAX_RUN], s_ps[ATT_MAX_GROUP][ATT_MAX_RUN];
+    __shared__ float s_suffix[ATT_MAX_GROUP];
+    __shared__ int s_blk[ATT_MAX_RUN];
+    __shared__ int s_last;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int g = p.n_head / p.n_kv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pos = p.positions[t], ctx_len = pos + 1;
+    int n_blk, b0, b1;
+    split_range(pos, split, p.nsplit, n_blk, b0, b1);
+    const int32_t* table = p.block_tables + (size_t)p.seq_ids[t] * p.max_blocks;
+    const size_t ctx_pad = (size_t)p.max_blocks * DC_KV_BLOCK;
+    const int nb = b1 - b0, stride = nb * DC_KV_BLOCK;
+    for (int i = tid; i < g * stride; i += 128) {
+        const int h = i / stride, k = i - h * stride;
+        s_pw[i] = p.scores[((size_t)t * p.n_head + kvh * g + h) * ctx_pad + (size_t)b0 * DC_KV_BLOCK + k];
     }
+    for (int i = tid; i < nb; i += 128) s_blk[i] = table[b0 + i];
+    for (int h = warp; h < g; h += 4) {
+        const float* bm = p.bmax + ((size_t)t * p.n_head + kvh * g + h) * p.max_blocks;
+        float carry = -1e30f, suffix = 1.0f;
+        for (int s0 = 0; s0 < n_blk; s0 += 256) {
+            float vb[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int c = s0 + 32 * k + lane;
+                vb[k] = c < n_blk ? bm[c] : -1e30f;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int c0 = s0 + 32 * k, c = c0 + lane;
+                if (c0 >= n_blk) break;
+                if (c0 + 32 <= b0) {   // wholly before the run: only the running maximum
+                    float mx = vb[k];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    carry = fmaxf(carry, mx);
+                    continue;
+                }
+                float incl = vb[k];
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const float u = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl = fmaxf(incl, u);
+                }
+                float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+                if (lane == 0) excl = -1e30f;
+                const float m_prev = fmaxf(carry, excl), m_new = fmaxf(carry, incl);
+                const float a = (c >= b0 && c < n_blk) ? fast_exp_fma(m_prev - m_new) : 1.0f;
+                if (c >= b0 && c < b1) {
+                    s_mnew[h][c - b0] = m_new;
+                    s_alpha[h][c - b0] = a;
+                }
+                if (c0 + 32 > b1) {   // the chunk reaches past the run: those factors go into the suffix
+                    float later = c >= b1 ? a : 1.0f;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) later *= __shfl_xor_sync(0xffffffffu, later, o);
+                    suffix *= later;
+                }
+                carry = fmaxf(carry, __shfl_sync(0xffffffffu, incl, 31));
+            }
+        }
+        if (lane == 0) s_suffix[h] = suffix;
+    }
+    __syncthreads();
+    // exponentials: 16 lanes per (head, block)
+    for (int base = 0; base < g * nb; base += 8) {
+        const int pair = base + (tid >> 4), key = tid & 15;
+        const bool in = pair < g * nb;
+        const int h = in ? pair / nb : 0, bl = in ? pair - h * nb : 0;
+        const int nk = min(DC_KV_BLOCK, ctx_len - (b0 + bl) * DC_KV_BLOCK);
+        const float s = (in && key < nk) ? s_pw[h * stride + bl * DC_KV_BLOCK + key] : -INFINITY;
+        const float pr = (s == -INFINITY) ? 0.0f : fast_exp_fma(s - s_mnew[h][bl]);
+        float ps = pr;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        if (in) {
+            s_pw[h * stride + bl * DC_KV_BLOCK + key] = pr;
+            if (key == 0) s_ps[h][bl] = ps;
+        }
+    }
+    __syncthreads();
+    // thread = dim; one accumulator per head; thread h also carries head h's denominator
+    float acc[ATT_MAX_GROUP];
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h) acc[h] = 0.0f;
+    float den = 0.0f;
+    for (int bl = 0; bl < nb; ++bl) {
+        const int nk = min(DC_KV_BLOCK, ctx_len - (b0 + bl) * DC_KV_BLOCK);
+        const __half* vb = p.v_arena + ((size_t)s_blk[bl] * DC_KV_BLOCK * p.n_kv + kvh) * 128 + tid;
+        __half vv[DC_KV_BLOCK];   // requested together; rows beyond nk exist in the arena and are not used
+#pragma unroll
+        for (int key = 0; key < DC_KV_BLOCK; ++key) vv[key] = vb[(size_t)key * p.n_kv * 128];
+        if (tid < g) den = den * s_alpha[tid][bl] + s_ps[tid][bl];
+#pragma unroll
+        for (int h = 0; h < ATT_MAX_GROUP; ++h)
+            if (h < g && s_alpha[h][bl] != 1.0f) acc[h] *= s_alpha[h][bl];
+#pragma unroll
+        for (int key = 0; key < DC_KV_BLOCK; ++key) {
+            if (key < nk) {
+                const float v = __half2float(vv[key]);
+#pragma unroll
+                for (int h = 0; h < ATT_MAX_GROUP; ++h)
+                    if (h < g) acc[h] = fmaf(s_pw[h * stride + bl * DC_KV_BLOCK + key], v, acc[h]);
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+        if (h < g) {
+            const size_t idx = ((size_t)t * p.n_head + kvh * g + h) * p.nsplit + split;
+            p.part_acc[idx * 128 + tid] = acc[h] * s_suffix[h];
+        }
+    }
+    if (tid < g) p.part_d[((size_t)t * p.n_head + kvh * g + tid) * p.nsplit + split] = den * s_suffix[tid];
+    attn_merge_tail(p, t, kvh, g, tid, warp, lane, s_last);
 }
 
 size_t dc_attention_scratch_bytes(int T, int n_head, int n_kv, int max_blocks, int nsplit) {
@@ -341,6 +475,9 @@ int dc_launch_attention(dc_ctx* ctx, const float* q, const void* k_arena, const 
     p.q8_out = q8_out;
     int st = dc_launch(ctx, "k_attn_scores", k_attn_scores, dim3(nsplit, n_kv, T), dim3(128), 0, p);
     if (st != DC_B200_OK) return st;
+    // runs short enough for the kernel that keeps a whole run's scores in shared memory
+    if ((max_blocks + nsplit - 1) / nsplit <= ATT_MAX_RUN)
+        return dc_launch(ctx, "k_attn_pv_run", k_attn_pv_run, dim3(nsplit, n_kv, T), dim3(128), 0, p);
     return dc_launch(ctx, "k_attn_pv", k_attn_pv, dim3(nsplit, n_kv, T), dim3(128), 0, p);
 }
 

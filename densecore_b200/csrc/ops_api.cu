@@ -276,4 +276,42 @@ int dc_b200_verify_accept(dc_ctx* ctx, const float* target_logits_host, const in
     return DC_B200_OK;
 }
 
+// Device-resident variant: target logits [gamma+1, vocab] (for example dc_b200_model_logits_dev after a
+// forward_chunk) and, in mode 1, draft probabilities [gamma, vocab] are already on this GPU; only the draft
+// token ids go in and the two result ints come out.
+int dc_b200_verify_accept_dev(dc_ctx* ctx, const float* target_logits_dev, const int32_t* draft_tokens,
+                              const float* draft_probs_dev, const float* uniforms, uint64_t seed, uint32_t step,
+                              int gamma, int vocab, int mode, float temperature, int32_t* n_accepted,
+                              int32_t* next_token) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!target_logits_dev || !draft_tokens || !n_accepted || !next_token || gamma < 1 || gamma > 16 || vocab < 2 ||
+        (mode != 0 && mode != 1) || (mode == 1 && !draft_probs_dev))
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "verify_accept_dev: bad argument");
+    for (int i = 0; i < gamma; ++i)
+        if (draft_tokens[i] < 0 || draft_tokens[i] >= vocab)
+            return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "verify_accept_dev: draft token %d out of range", i);
+    cudaSetDevice(ctx->device);
+    const size_t row = (size_t)vocab * 4;
+    uint8_t* s = dc_scratch(ctx, row * (gamma + 1) + 4096);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
+    Bump b{s};
+    float* probs = b.take<float>((size_t)(gamma + 1) * vocab);
+    int32_t* dt = b.take<int32_t>(gamma);
+    float* u = b.take<float>(gamma + 1);
+    int32_t* am = b.take<int32_t>(gamma + 1);
+    int32_t* res = b.take<int32_t>(2);
+    DC_TRY(h2d(ctx, dt, draft_tokens, (size_t)gamma * 4));
+    if (mode == 1) {
+        if (uniforms) DC_TRY(h2d(ctx, u, uniforms, (size_t)(gamma + 1) * 4));
+        else DC_TRY(dc_launch_verify_uniforms(ctx, seed, step, gamma + 1, u));
+    }
+    DC_TRY(dc_launch_verify(ctx, mode, gamma, vocab, target_logits_dev, dt, draft_probs_dev, u, temperature, am, probs, res));
+    int32_t out[2] = {0, 0};
+    DC_TRY(d2h(ctx, out, res, 8));
+    DC_TRY(dc_b200_synchronize(ctx));
+    *n_accepted = out[0];
+    *next_token = out[1];
+    return DC_B200_OK;
+}
+
 }  // extern "C"

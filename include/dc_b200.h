@@ -183,6 +183,12 @@ DC_B200_API int dc_b200_verify_accept(dc_ctx* ctx, const float* target_logits_ho
                                       const float* draft_probs_host, const float* uniforms, uint64_t seed,
                                       uint32_t step, int gamma, int vocab, int mode, float temperature,
                                       int32_t* n_accepted, int32_t* next_token);
+/* The same step with target logits (and, in mode 1, draft probabilities) already on this GPU, e.g.
+ * dc_b200_model_logits_dev after dc_b200_forward_chunk: only the draft ids go in and two ints come out. */
+DC_B200_API int dc_b200_verify_accept_dev(dc_ctx* ctx, const float* target_logits_dev, const int32_t* draft_tokens,
+                                          const float* draft_probs_dev, const float* uniforms, uint64_t seed,
+                                          uint32_t step, int gamma, int vocab, int mode, float temperature,
+                                          int32_t* n_accepted, int32_t* next_token);
 DC_B200_API int dc_b200_verify_uniforms(dc_ctx* ctx, uint64_t seed, uint32_t step, int n, float* out_host);
 DC_B200_API int dc_b200_softmax(dc_ctx* ctx, const float* logits_host, int rows, int n, float temperature,
                                 float* probs_host);
