@@ -385,6 +385,7 @@ def main():
         draft.finalize()
         prompt = rng.integers(0, cfg.vocab, size=1024)
         n_out, gamma = 128, 4
+        model.seq_free(seqs[3])   # the decode runs hold all four sequence slots
         want, st0 = dc.speculative_decode(model, draft, prompt, n_out + gamma + 1, gamma=gamma)
         print(f"speculative decoding, gamma {gamma}, greedy accept, 1024-token prompt, {n_out} output tokens:", file=sys.stderr)
         print(f"  draft model's proposals: acceptance {st0.acceptance * 100:5.1f} %  {st0.tokens_per_step:4.2f} tokens/step  "
