@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(128) k_attn_pv(const AttnParams p) {
 // run at once; then one pass over the keys with no CTA barrier inside.
 #define ATT_MAX_RUN 64
 __global__ void __launch_bounds__(128) k_attn_pv_run(const AttnParams p) {
-    __shared__ float s_pw[ATT_MAX_GROUP * ATT_MAX_RUN * DC_KV_BLOCK];   // scores of the run, then exponentials
+    __shared__ __align__(16) float s_pw[ATT_MAX_GROUP * ATT_MAX_RUN * DC_KV_BLOCK];   // scores of the run, then exponentials
     __shared__ float s_mnew[ATT_MAX_GROUP][ATT_MAX_RUN], s_alpha[ATT_MAX_GROUP][ATT_MAX_RUN], s_ps[ATT_MAX_GROUP][ATT_MAX_RUN];
     __shared__ float s_suffix[ATT_MAX_GROUP];
     __shared__ int s_blk[ATT_MAX_RUN];
@@ -413,13 +413,21 @@ __global__ void __launch_bounds__(128) k_attn_pv_run(const AttnParams p) {
 #pragma unroll
         for (int h = 0; h < ATT_MAX_GROUP; ++h)
             if (h < g && s_alpha[h][bl] != 1.0f) acc[h] *= s_alpha[h][bl];
+        float vf[DC_KV_BLOCK];
 #pragma unroll
-        for (int key = 0; key < DC_KV_BLOCK; ++key) {
-            if (key < nk) {
-                const float v = __half2float(vv[key]);
+        for (int key = 0; key < DC_KV_BLOCK; ++key) vf[key] = __half2float(vv[key]);
+        // per head: the block's 16 exponentials in four 128-bit loads, then the FMA chain in key order
 #pragma unroll
-                for (int h = 0; h < ATT_MAX_GROUP; ++h)
-                    if (h < g) acc[h] = fmaf(s_pw[h * stride + bl * DC_KV_BLOCK + key], v, acc[h]);
+        for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+            if (h < g) {
+                float pp[DC_KV_BLOCK];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    *reinterpret_cast<float4*>(&pp[4 * q]) =
+                        *reinterpret_cast<const float4*>(&s_pw[h * stride + bl * DC_KV_BLOCK + 4 * q]);
+#pragma unroll
+                for (int key = 0; key < DC_KV_BLOCK; ++key)
+                    if (key < nk) acc[h] = fmaf(pp[key], vf[key], acc[h]);
             }
         }
     }

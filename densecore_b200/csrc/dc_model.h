@@ -66,7 +66,7 @@ struct dc_model {
     // persistent decode kernel (mega.cu)
     void* mega_layers = nullptr;     // device array of MegaLayer
     unsigned* mega_counter = nullptr;
-    int use_mega = 1;            // 0 never, 1 for 1-2 streams (where it is the faster path), 2 wherever it fits
+    int use_mega = 1;            // 0 never, 1 for one stream (where it is the faster path), 2 wherever it fits
     bool mega_timing = false;
     // expert parallel
     bool ep_ready = false;

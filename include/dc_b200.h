@@ -291,8 +291,8 @@ DC_B200_API int dc_b200_model_profile_step(dc_model* m, const int32_t* seqs, int
 DC_B200_API const char* dc_b200_kernel_class_name(int cls);
 /* "graphs" 0/1: replay each step shape as a CUDA graph (default 1).
  * "persistent" 0/1/2: decode steps of MoE models run in one persistent cooperative kernel with grid
- * barriers between phases: 0 never, 1 for 1-2 streams (default: with 3-4 streams the per-op kernels are as
- * fast), 2 for every stream count it supports (1-4). */
+ * barriers between phases: 0 never, 1 for one stream (default: with more streams the per-op kernels are
+ * faster), 2 for every stream count it supports (1-4). */
 DC_B200_API int dc_b200_model_set_option(dc_model* m, const char* name, int value);
 
 /* ---- expert parallelism over the GPUs of one node ---------------------------- */
