@@ -403,12 +403,24 @@ __global__ void __launch_bounds__(128) k_attn_pv_run(const AttnParams p) {
 #pragma unroll
     for (int h = 0; h < ATT_MAX_GROUP; ++h) acc[h] = 0.0f;
     float den = 0.0f;
+    // a block's 16 V values are requested together, one block ahead of the FMAs (rows beyond nk exist in
+    // the arena and are not used)
+    __half vn[DC_KV_BLOCK];
+    if (nb > 0) {
+        const __half* vb = p.v_arena + ((size_t)s_blk[0] * DC_KV_BLOCK * p.n_kv + kvh) * 128 + tid;
+#pragma unroll
+        for (int key = 0; key < DC_KV_BLOCK; ++key) vn[key] = vb[(size_t)key * p.n_kv * 128];
+    }
     for (int bl = 0; bl < nb; ++bl) {
         const int nk = min(DC_KV_BLOCK, ctx_len - (b0 + bl) * DC_KV_BLOCK);
-        const __half* vb = p.v_arena + ((size_t)s_blk[bl] * DC_KV_BLOCK * p.n_kv + kvh) * 128 + tid;
-        __half vv[DC_KV_BLOCK];   // requested together; rows beyond nk exist in the arena and are not used
+        __half vv[DC_KV_BLOCK];
 #pragma unroll
-        for (int key = 0; key < DC_KV_BLOCK; ++key) vv[key] = vb[(size_t)key * p.n_kv * 128];
+        for (int key = 0; key < DC_KV_BLOCK; ++key) vv[key] = vn[key];
+        if (bl + 1 < nb) {
+            const __half* vb = p.v_arena + ((size_t)s_blk[bl + 1] * DC_KV_BLOCK * p.n_kv + kvh) * 128 + tid;
+#pragma unroll
+            for (int key = 0; key < DC_KV_BLOCK; ++key) vn[key] = vb[(size_t)key * p.n_kv * 128];
+        }
         if (tid < g) den = den * s_alpha[tid][bl] + s_ps[tid][bl];
 #pragma unroll
         for (int h = 0; h < ATT_MAX_GROUP; ++h)

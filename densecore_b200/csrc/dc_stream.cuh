@@ -52,8 +52,39 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int row) {
 template <int NSTAGE>
 struct GemvStream {
     StageIter prod, cons;
+    // A Q6_K row takes about twice the instructions of a Q4_K row of the same K.
+    __device__ __forceinline__ static int row_weight(int type) { return type == DC_TYPE_Q6_K ? 2 : 1; }
+    // Flattened row index at weighted position x (segments in order, each row weighing row_weight).
+    __device__ __forceinline__ static int row_at(const GemvParams& p, int nseg, long long x) {
+        long long cum = 0;
+        int base = 0;
+        for (int s = 0; s < nseg; ++s) {
+            const int w = row_weight(p.seg[s].type);
+            const long long span = (long long)p.seg[s].n_rows * w;
+            if (x < cum + span) return base + (int)((x - cum) / w);
+            cum += span;
+            base += p.seg[s].n_rows;
+        }
+        return base;
+    }
+    // Each warp takes a contiguous range of rows; with segments of different types the ranges are balanced
+    // by weight, so that the warps holding the costlier rows are not the last to finish.
     __device__ __forceinline__ void begin(const GemvParams& p, int gw, int nw) {
-        const int r0 = (int)((long long)gw * p.total_rows / nw), r1 = (int)((long long)(gw + 1) * p.total_rows / nw);
+        const int nseg = p.epi == DC_EPI_SWIGLU ? 1 : p.n_seg;
+        bool mixed = false;
+        long long total_w = 0;
+        for (int s = 0; s < nseg; ++s) {
+            mixed |= p.seg[s].type != p.seg[0].type;
+            total_w += (long long)p.seg[s].n_rows * row_weight(p.seg[s].type);
+        }
+        int r0, r1;
+        if (!mixed) {
+            r0 = (int)((long long)gw * p.total_rows / nw);
+            r1 = (int)((long long)(gw + 1) * p.total_rows / nw);
+        } else {
+            r0 = row_at(p, nseg, (long long)gw * total_w / nw);
+            r1 = gw + 1 == nw ? p.total_rows : row_at(p, nseg, (long long)(gw + 1) * total_w / nw);
+        }
         prod = StageIter{r0, r1};
         cons = StageIter{r0, r1};
     }

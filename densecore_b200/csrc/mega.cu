@@ -894,8 +894,38 @@ __device__ DC_HOT void route_phase(const MegaParams& p, MegaShared& sh) {
         }
     }
     __syncthreads();
-    // bucketing: thread e owns expert e (E <= 256 < 512 threads)
     const int A = p.T * p.top_k, me = threadIdx.x;
+    if (p.T == 1) {
+        // one token: its experts are distinct, so each local one is a unit of its own; units are ordered by
+        // expert id (position = number of local picks with a smaller id)
+        if (me < p.top_k) {
+            const int e = sh.ids[me];
+            const bool local = e >= p.e_lo && e < p.e_hi;
+            int posn = 0, n_local = 0;
+            for (int j = 0; j < p.top_k; ++j) {
+                const int ej = sh.ids[j];
+                const bool lj = ej >= p.e_lo && ej < p.e_hi;
+                n_local += lj;
+                posn += (lj && ej < e);
+            }
+            if (local) {
+                sh.uexp[posn] = e;
+                sh.uoff[posn] = posn;
+                sh.uassign[posn] = me;
+            }
+            if (me == 0) {
+                sh.n_active = n_local;
+                sh.uoff[n_local] = n_local;
+            }
+        }
+        if (blockIdx.x == 0 && me < A) {
+            if (p.route_ids) p.route_ids[me] = sh.ids[me];
+            if (p.route_w) p.route_w[me] = sh.w[me];
+        }
+        __syncthreads();
+        return;
+    }
+    // bucketing: thread e owns expert e (E <= 256 < 512 threads)
     int cnt = 0;
     if (me >= p.e_lo && me < p.e_hi)   // experts stored on this GPU
         for (int i = 0; i < A; ++i) cnt += (sh.ids[i] == me);

@@ -308,7 +308,7 @@ DC_B200_API int dc_b200_model_ep_init(dc_model* m, const char* nccl_path, const 
 /* Exchange buffers of the persistent decode kernel's expert-parallel path (one process per GPU of one
  * node).  Each rank exports a 64-byte handle of its buffer (cudaIpcGetMemHandle), the launcher hands
  * every rank's handle to every other rank, and each rank imports its ep_size - 1 peers.  With all peers
- * connected, decode steps of up to 4 streams run in the persistent kernel: every GPU stores the rows its
+ * connected, decode steps the persistent kernel serves (option "persistent") run in it: every GPU stores the rows its
  * experts produce straight into all GPUs' buffers over NVLink and the GPUs meet once per layer through
  * flags in each other's memory, so the weighted combine runs in routing order on local memory and the
  * result is bit-identical to a single GPU's (the NCCL all-reduce of the per-op path is only tolerance-
