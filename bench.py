@@ -45,7 +45,7 @@ SAMPLE_LAYERS = 4          # layers of the model the CPU baseline times per samp
 SAMPLE_REPS = 12           # repeats of the sample (median taken)
 # DRAM bytes (read + write) of one launch of the persistent kernel divided by its algorithmic bytes,
 # from an ncu capture of the 4-layer case (profiles/k_decode_mega_moe35b_4layers.md)
-DRAM_TRAFFIC_RATIO = 1.04
+DRAM_TRAFFIC_RATIO = 1.03
 
 
 def measured_peaks():
