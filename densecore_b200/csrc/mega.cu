@@ -554,15 +554,8 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
 #ifdef DC_MEGA_SUBMARKS
     const unsigned long long pv_t0 = mg_now();
 #endif
-#ifdef DC_SUB_PV
-    unsigned long long sub_t = mg_now();
-#define PVSUB(i) do { if (p.phase_ns && blockIdx.x == 0 && threadIdx.x == 0) { const unsigned long long _n = mg_now(); p.phase_ns[i] += _n - sub_t; sub_t = _n; } } while (0)
-#else
-#define PVSUB(i) do {} while (0)
-#endif
     cp_async_wait_all();   // this thread's V copies of the scores phase have landed
     if (!it.valid) return;
-    PVSUB(22);
     const int g = it.gh, head0 = it.kvh * (p.n_head / p.n_kv) + it.hb;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb_run = it.b1 - it.b0;
@@ -623,7 +616,6 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
         if (lane == 0) sh.suffix[h] = suffix;
     }
     __syncthreads();   // every thread's async copies are complete and visible; block state is set
-    PVSUB(23);
     {
         // the new token's V row was written during the scores phase, possibly after its
         // async copy was issued: the owning run copies that one row again
@@ -652,7 +644,6 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
         }
     }
     __syncthreads();
-    PVSUB(24);
     // thread -> (dim, two heads): heads hq and hq + 4
     const int dim = tid & 127, hq = tid >> 7;
     const bool h0 = hq < g, h1 = hq + 4 < g;
@@ -661,9 +652,6 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
     const float* p0 = pw + hq * p.s_keys;
     const float* p1 = pw + (hq + 4) * p.s_keys;
     for (int bl = 0; bl < nb_run; ++bl) {
-#ifdef DC_SUB_PV
-        const long long ck0 = clock64();
-#endif
         const int nk = min(DC_KV_BLOCK, it.ctx_len - (it.b0 + bl) * DC_KV_BLOCK);
         if (h0) {
             const float a = bl_alpha[hq * MG_MAX_RUN_BLOCKS + bl];
@@ -675,9 +663,6 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
             if (a != 1.0f) acc1 *= a;
             if (dim == 0) d1 = d1 * a + bl_ps[(hq + 4) * MG_MAX_RUN_BLOCKS + bl];
         }
-#ifdef DC_SUB_PV
-        const long long ck1 = clock64();
-#endif
         if (bl < vcap_blocks) {
             // all 16 V values and exponentials of the block are fetched first, then added in key order
             const __half* vrow = vs + (size_t)bl * DC_KV_BLOCK * 128 + dim;
@@ -702,9 +687,6 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
                 for (int key = 0; key < DC_KV_BLOCK; ++key)
                     if (key < nk) acc1 = fmaf(pp[key], vv[key], acc1);
             }
-#ifdef DC_SUB_PV
-            if (p.phase_ns && blockIdx.x == 0 && threadIdx.x == 0) { const long long ck2 = clock64(); p.phase_ns[26] += (ck1 - ck0) / 2; p.phase_ns[27] += (ck2 - ck1) / 2; }
-#endif
         } else {
             const __half* vb = L.v_arena + ((size_t)sh.tbl[bl] * DC_KV_BLOCK * p.n_kv + it.kvh) * 128 + dim;
 #pragma unroll 4
@@ -728,7 +710,6 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
     }
     __threadfence();
     __syncthreads();
-    PVSUB(25);
     int* ticket = p.tickets + (it.t * p.n_kv + it.kvh) * p.n_hg + it.hg;
     if (tid == 0) sh.last = (atomicAdd(ticket, 1) == p.nsplit - 1);
     __syncthreads();
