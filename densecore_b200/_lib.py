@@ -103,6 +103,10 @@ def _signatures() -> dict:
         "dc_b200_model_weight_bytes": (sz, [vp]),
         "dc_b200_seq_alloc": (i32, [vp, pi]),
         "dc_b200_seq_free": (i32, [vp, i32]),
+        "dc_b200_seq_fork": (i32, [vp, i32, pi]),
+        "dc_b200_model_free_blocks": (i32, [vp]),
+        "dc_b200_kv_seq_fork": (i32, [vp, i32, pi]),
+        "dc_b200_kv_block_refcount": (i32, [vp, i32]),
         "dc_b200_seq_len": (i32, [vp, i32]),
         "dc_b200_seq_truncate": (i32, [vp, i32, i32]),
         "dc_b200_prefill": (i32, [vp, i32, vp, i32, vp, pi]),

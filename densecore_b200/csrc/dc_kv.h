@@ -21,6 +21,7 @@ struct dc_kv_cache {
     __half* v_arena = nullptr;
     int32_t* d_tables = nullptr; // [max_seqs][max_blocks_per_seq]
     std::vector<int> free_list;
+    std::vector<int> ref;        // references per physical block (sequences sharing it after a fork)
     std::vector<dc_kv_seq> seqs;
     int stage_off = 0;
 };
@@ -31,3 +32,4 @@ void dc_kv_release(dc_kv_cache* kv);
 int dc_kv_seq_alloc(dc_kv_cache* kv, int* out_seq);
 int dc_kv_seq_free(dc_kv_cache* kv, int seq);
 int dc_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens);
+int dc_kv_seq_fork(dc_kv_cache* kv, int src_seq, int* out_seq);

@@ -31,6 +31,7 @@ int dc_kv_init(dc_ctx* ctx, dc_kv_cache* kv, int n_layer, int n_kv_head, int hea
     if (e != cudaSuccess) return dc_check_cuda(ctx, e, "kv_create");
     kv->free_list.clear();
     for (int b = max_blocks - 1; b >= 0; --b) kv->free_list.push_back(b);
+    kv->ref.assign(max_blocks, 0);
     kv->seqs.assign(max_seqs, dc_kv_seq());
     return DC_B200_OK;
 }
@@ -59,13 +60,65 @@ int dc_kv_seq_alloc(dc_kv_cache* kv, int* out_seq) {
 int dc_kv_seq_free(dc_kv_cache* kv, int seq) {
     if (seq < 0 || seq >= kv->max_seqs || !kv->seqs[seq].used)
         return dc_fail(kv->ctx, DC_B200_INVALID_ARGUMENT, "kv: sequence %d is not allocated", seq);
-    for (int b : kv->seqs[seq].blocks) kv->free_list.push_back(b);
+    // a block returns to the free list when its last reference goes (kv_cache.h:140)
+    for (int b : kv->seqs[seq].blocks)
+        if (--kv->ref[b] <= 0) {
+            kv->ref[b] = 0;
+            kv->free_list.push_back(b);
+        }
     kv->seqs[seq] = dc_kv_seq();
     return DC_B200_OK;
 }
 
-// Makes sure blocks exist for positions [0, n_tokens) and mirrors new table
-// entries to the device (ordered on the context's stream).
+// One block of every layer, K and V: src -> dst.
+__global__ void __launch_bounds__(256) k_kv_copy_block(__half* k_arena, __half* v_arena, size_t layer_elems,
+                                                       size_t block_elems, int src, int dst) {
+    __half* arena = blockIdx.y ? v_arena : k_arena;
+    const uint4* s = reinterpret_cast<const uint4*>(arena + layer_elems * blockIdx.x + block_elems * src);
+    uint4* d = reinterpret_cast<uint4*>(arena + layer_elems * blockIdx.x + block_elems * dst);
+    for (size_t i = threadIdx.x; i < block_elems / 8; i += blockDim.x) d[i] = s[i];
+}
+
+// Staged upload of `n` table entries of a sequence starting at logical block `first`.
+static int upload_table(dc_kv_cache* kv, int seq, int first, int n) {
+    if (n <= 0) return DC_B200_OK;
+    int32_t* stage = (int32_t*)dc_pinned(kv->ctx, 64 * 1024);
+    if (!stage) return DC_B200_OUT_OF_MEMORY;
+    if (n > 16 * 1024) return dc_fail(kv->ctx, DC_B200_UNSUPPORTED, "kv: too many new blocks at once");
+    if (kv->stage_off + n > 16 * 1024) {   // a small pinned ring keeps the async copy source valid
+        cudaStreamSynchronize(kv->ctx->stream);
+        kv->stage_off = 0;
+    }
+    memcpy(stage + kv->stage_off, kv->seqs[seq].blocks.data() + first, (size_t)n * sizeof(int32_t));
+    cudaError_t e = cudaMemcpyAsync(kv->d_tables + (size_t)seq * kv->max_blocks_per_seq + first, stage + kv->stage_off,
+                                    (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice, kv->ctx->stream);
+    kv->stage_off += n;
+    return dc_check_cuda(kv->ctx, e, "kv: block table upload");
+}
+
+// New sequence that shares every block of src (Fork, kv_cache.h:151-156): nothing is copied now; a shared
+// block is copied when one of its owners is about to write into it (copy-on-write, :158-161).
+int dc_kv_seq_fork(dc_kv_cache* kv, int src_seq, int* out_seq) {
+    if (src_seq < 0 || src_seq >= kv->max_seqs || !kv->seqs[src_seq].used)
+        return dc_fail(kv->ctx, DC_B200_INVALID_ARGUMENT, "kv: sequence %d is not allocated", src_seq);
+    int dst = -1;
+    int st = dc_kv_seq_alloc(kv, &dst);
+    if (st != DC_B200_OK) return st;
+    kv->seqs[dst].blocks = kv->seqs[src_seq].blocks;
+    kv->seqs[dst].len = kv->seqs[src_seq].len;
+    for (int b : kv->seqs[dst].blocks) ++kv->ref[b];
+    st = upload_table(kv, dst, 0, (int)kv->seqs[dst].blocks.size());
+    if (st != DC_B200_OK) {
+        dc_kv_seq_free(kv, dst);
+        return st;
+    }
+    *out_seq = dst;
+    return DC_B200_OK;
+}
+
+// Makes sure blocks exist for positions [0, n_tokens), that the blocks the next writes touch (positions
+// from the sequence's length on) are not shared with another sequence, and mirrors new table entries to
+// the device (ordered on the context's stream).
 int dc_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens) {
     if (seq < 0 || seq >= kv->max_seqs || !kv->seqs[seq].used)
         return dc_fail(kv->ctx, DC_B200_INVALID_ARGUMENT, "kv: sequence %d is not allocated", seq);
@@ -75,28 +128,34 @@ int dc_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens) {
         return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: sequence %d needs %d blocks, table holds %d", seq, need,
                        kv->max_blocks_per_seq);
     const int have = (int)s.blocks.size();
+    // copy-on-write of shared blocks in the range about to be written
+    for (int lb = s.len / DC_KV_BLOCK; lb < have && lb < need; ++lb) {
+        const int old = s.blocks[lb];
+        if (kv->ref[old] <= 1) continue;
+        if (kv->free_list.empty()) return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: out of blocks (copy-on-write)");
+        const int fresh = kv->free_list.back();
+        kv->free_list.pop_back();
+        kv->ref[fresh] = 1;
+        --kv->ref[old];
+        const size_t be = (size_t)DC_KV_BLOCK * kv->n_kv * kv->head_dim;
+        k_kv_copy_block<<<dim3(kv->n_layer, 2), 256, 0, kv->ctx->stream>>>(kv->k_arena, kv->v_arena, kv->layer_elems, be, old, fresh);
+        int st = dc_check_cuda(kv->ctx, cudaGetLastError(), "k_kv_copy_block");
+        if (st != DC_B200_OK) return st;
+        s.blocks[lb] = fresh;
+        st = upload_table(kv, seq, lb, 1);
+        if (st != DC_B200_OK) return st;
+    }
     if (need <= have) return DC_B200_OK;
     if ((int)kv->free_list.size() < need - have)
         return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: out of blocks (%d free, %d needed)",
                        (int)kv->free_list.size(), need - have);
     for (int i = have; i < need; ++i) {
-        s.blocks.push_back(kv->free_list.back());
+        const int b = kv->free_list.back();
         kv->free_list.pop_back();
+        kv->ref[b] = 1;
+        s.blocks.push_back(b);
     }
-    // staged through a small pinned ring so the async copy source stays valid
-    int32_t* stage = (int32_t*)dc_pinned(kv->ctx, 64 * 1024);
-    if (!stage) return DC_B200_OUT_OF_MEMORY;
-    const int n_new = need - have;
-    if (kv->stage_off + n_new > 16 * 1024) {
-        cudaStreamSynchronize(kv->ctx->stream);
-        kv->stage_off = 0;
-    }
-    if (n_new > 16 * 1024) return dc_fail(kv->ctx, DC_B200_UNSUPPORTED, "kv: too many new blocks at once");
-    memcpy(stage + kv->stage_off, s.blocks.data() + have, (size_t)n_new * sizeof(int32_t));
-    cudaError_t e = cudaMemcpyAsync(kv->d_tables + (size_t)seq * kv->max_blocks_per_seq + have, stage + kv->stage_off,
-                                    (size_t)n_new * sizeof(int32_t), cudaMemcpyHostToDevice, kv->ctx->stream);
-    kv->stage_off += n_new;
-    return dc_check_cuda(kv->ctx, e, "kv: block table upload");
+    return upload_table(kv, seq, have, need - have);
 }
 
 extern "C" {
@@ -142,6 +201,14 @@ int dc_b200_kv_block_table(dc_kv_cache* kv, int seq, int32_t* out_blocks, int ca
     if (out_blocks)
         for (int i = 0; i < n && i < capacity; ++i) out_blocks[i] = kv->seqs[seq].blocks[i];
     return DC_B200_OK;
+}
+int dc_b200_kv_seq_fork(dc_kv_cache* kv, int src_seq, int* out_seq) {
+    if (!kv || !out_seq) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(kv->ctx->device);
+    return dc_kv_seq_fork(kv, src_seq, out_seq);
+}
+int dc_b200_kv_block_refcount(dc_kv_cache* kv, int block) {
+    return (kv && block >= 0 && block < kv->max_blocks) ? kv->ref[block] : DC_B200_INVALID_ARGUMENT;
 }
 int dc_b200_kv_free_blocks(dc_kv_cache* kv) { return kv ? (int)kv->free_list.size() : DC_B200_INVALID_ARGUMENT; }
 

@@ -570,6 +570,12 @@ size_t dc_b200_model_weight_bytes(dc_model* m) {
 
 int dc_b200_seq_alloc(dc_model* m, int* out_seq) { return (m && out_seq) ? dc_kv_seq_alloc(&m->kv, out_seq) : DC_B200_INVALID_ARGUMENT; }
 int dc_b200_seq_free(dc_model* m, int seq) { return m ? dc_kv_seq_free(&m->kv, seq) : DC_B200_INVALID_ARGUMENT; }
+int dc_b200_seq_fork(dc_model* m, int src_seq, int* out_seq) {
+    if (!m || !out_seq) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(m->ctx->device);
+    return dc_kv_seq_fork(&m->kv, src_seq, out_seq);
+}
+int dc_b200_model_free_blocks(dc_model* m) { return m ? (int)m->kv.free_list.size() : DC_B200_INVALID_ARGUMENT; }
 int dc_b200_seq_len(dc_model* m, int seq) {
     if (!m || seq < 0 || seq >= m->kv.max_seqs || !m->kv.seqs[seq].used) return DC_B200_INVALID_ARGUMENT;
     return m->kv.seqs[seq].len;

@@ -159,6 +159,15 @@ class Model:
         self._check(_lib.lib().dc_b200_seq_alloc(self.handle, C.byref(s)))
         return s.value
 
+    def seq_fork(self, seq: int) -> int:
+        """New sequence sharing seq's KV blocks (copy-on-write)."""
+        s = C.c_int(-1)
+        self._check(_lib.lib().dc_b200_seq_fork(self.handle, seq, C.byref(s)))
+        return s.value
+
+    def free_blocks(self) -> int:
+        return _lib.lib().dc_b200_model_free_blocks(self.handle)
+
     def seq_free(self, seq: int):
         self._check(_lib.lib().dc_b200_seq_free(self.handle, seq))
 

@@ -159,6 +159,13 @@ DC_B200_API int dc_b200_kv_seq_free(dc_kv_cache* kv, int seq);
 DC_B200_API int dc_b200_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens);
 DC_B200_API int dc_b200_kv_block_table(dc_kv_cache* kv, int seq, int32_t* out_blocks, int capacity, int* out_n);
 DC_B200_API int dc_b200_kv_free_blocks(dc_kv_cache* kv);
+/* Fork (BlockManager::Fork / CopyOnWrite, core/include/densecore/memory/kv_cache.h:151-166): a new
+ * sequence that shares every block of src_seq and has its length.  Nothing is copied at the fork; when a
+ * sequence is about to write into a block that another one still references (kv_seq_reserve, or a model
+ * step), that block is first copied to a fresh one on the device (all layers, K and V).  Blocks return
+ * to the free list when their last reference goes. */
+DC_B200_API int dc_b200_kv_seq_fork(dc_kv_cache* kv, int src_seq, int* out_seq);
+DC_B200_API int dc_b200_kv_block_refcount(dc_kv_cache* kv, int block);
 /* cb_paged_attention_decode (core/src/llm/attention/paged_exec.cpp:343): writes
  * the T current tokens' K/V (f32 [T, n_kv, hd]) into the cache at positions[t]
  * of sequence seq_ids[t], then attends q [T, n_head, hd] over keys
@@ -247,6 +254,10 @@ DC_B200_API size_t dc_b200_model_weight_bytes(dc_model* m);
 /* Sequences (KV slots). */
 DC_B200_API int dc_b200_seq_alloc(dc_model* m, int* out_seq);
 DC_B200_API int dc_b200_seq_free(dc_model* m, int seq);
+/* A new sequence sharing src_seq's KV blocks (a common prompt prefilled once, then several continuations);
+ * copy-on-write as dc_b200_kv_seq_fork.  dc_b200_model_free_blocks: blocks not referenced by any sequence. */
+DC_B200_API int dc_b200_seq_fork(dc_model* m, int src_seq, int* out_seq);
+DC_B200_API int dc_b200_model_free_blocks(dc_model* m);
 DC_B200_API int dc_b200_seq_len(dc_model* m, int seq);
 DC_B200_API int dc_b200_seq_truncate(dc_model* m, int seq, int new_len);
 /* Runs n tokens of one sequence through the model in chunks of <= 16 and
