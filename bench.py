@@ -263,16 +263,30 @@ def main():
             buf = torch.frombuffer(bytearray(raw.raw), dtype=torch.uint8).clone()
         dist.broadcast(buf, 0)
         model.ep_init(bytes(buf.numpy().tobytes()), nccl_path)
-        if args.ep_exchange == "peer":
+        peer_ok = args.ep_exchange == "peer"
+        if peer_ok:
             # exchange buffers of the persistent kernel: every rank's handle to every rank
-            mine = torch.frombuffer(bytearray(model.ep_export()), dtype=torch.uint8).clone()
+            try:
+                mine = torch.frombuffer(bytearray(model.ep_export()), dtype=torch.uint8).clone()
+            except dc.DcError as e:
+                print(f"rank {rank}: ep_export failed: {e}", file=sys.stderr)
+                mine, peer_ok = torch.zeros(64, dtype=torch.uint8), False
             allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
             dist.all_gather(allh, mine)
             for r in range(world):
-                if r != rank:
-                    model.ep_import(r, bytes(allh[r].numpy().tobytes()))
+                if r != rank and peer_ok:
+                    try:
+                        model.ep_import(r, bytes(allh[r].numpy().tobytes()))
+                    except dc.DcError as e:
+                        print(f"rank {rank}: ep_import({r}) failed: {e}", file=sys.stderr)
+                        peer_ok = False
+            # all ranks must take the same path: one failure sends everyone to the per-op kernels and NCCL
+            flag = torch.tensor([1 if peer_ok else 0], dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            peer_ok = bool(flag.item())
+        ep_force_per_op = not peer_ok
     model.finalize()
-    if args.path == "per-op":
+    if args.path == "per-op" or (world > 1 and ep_force_per_op):
         model.set_option("persistent", 0)
 
     rng = np.random.default_rng(0)
