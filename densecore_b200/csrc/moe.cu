@@ -147,7 +147,10 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
 #pragma unroll
             for (int j = 0; j < MOE_MAX_E / 32; ++j)
                 if (j * 32 + lane == wid) taken[j] = true;
-            const float wl = __ldcg(p.logits + (size_t)t * p.E + wid);
+            // the winner's logit back out of its key (NaN stays NaN; -0 was made +0, which exp treats alike):
+            // no load per round
+            const uint32_t ku = (uint32_t)(win >> 32);
+            const float wl = __uint_as_float((ku & 0x80000000u) ? (ku & 0x7FFFFFFFu) : ~ku);
             if (k < MOE_MAX_K) sel_l[k] = wl;
             if (lane == 0) {
                 p.ids[t * p.top_k + k] = wid;
