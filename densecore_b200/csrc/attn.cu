@@ -58,15 +58,44 @@ __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
     __shared__ float sc[ATT_MAX_GROUP][ATT_TILE];
     __shared__ int s_blk[ATT_TILE / DC_KV_BLOCK];
     pdl_launch_dependents();
-    pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int g = p.n_head / p.n_kv;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int pos = p.positions[t], ctx_len = pos + 1;
+    // positions, sequence ids and block tables were settled before this step began, and K rows of earlier
+    // positions are not written during it: the first tile's history rows are fetched while this kernel
+    // still waits for the one that writes the new token's row and the q heads
+    // (in an eager chain of steps the position may still be the previous step's here: everything is
+    // recomputed after the wait and the early rows are dropped if the run moved)
+    const int32_t* table = p.block_tables + (size_t)p.seq_ids[t] * p.max_blocks;
+    uint4 kr0[4];
+    bool pre = false;
+    int pre_b0;
+    {
+        const int pos0 = p.positions[t];
+        // rows written during this step: this token's, and those of earlier tokens of the same sequence
+        // in a multi-token chunk; only rows before the first of them are safe to read early
+        int stable = pos0;
+        const int sid = p.seq_ids[t];
+        for (int u = 0; u < p.T; ++u)
+            if (p.seq_ids[u] == sid) stable = min(stable, p.positions[u]);
+        int nb0, e1;
+        split_range(pos0, split, p.nsplit, nb0, pre_b0, e1);
+        const int key = warp * 8 + (lane >> 2), sub = lane & 3, blk = pre_b0 + key / DC_KV_BLOCK;
+        const int kpos = pre_b0 * DC_KV_BLOCK + key;
+        if (pos0 >= 0 && blk < e1 && kpos < stable) {
+            const uint4* kp = reinterpret_cast<const uint4*>(
+                p.k_arena + (((size_t)table[blk] * DC_KV_BLOCK + key % DC_KV_BLOCK) * p.n_kv + kvh) * 128 + sub * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) kr0[i] = kp[i];
+            pre = true;
+        }
+    }
+    pdl_wait();
+    const int pos = *reinterpret_cast<const volatile int32_t*>(p.positions + t), ctx_len = pos + 1;
     int n_blk, b0, b1;
     split_range(pos, split, p.nsplit, n_blk, b0, b1);
+    if (b0 != pre_b0) pre = false;
     if (b0 >= b1) return;
-    const int32_t* table = p.block_tables + (size_t)p.seq_ids[t] * p.max_blocks;
     for (int i = tid; i < g * 128; i += 128)
         sq[i >> 7][((i & 127) >> 5) * 36 + (i & 31)] = p.q[((size_t)t * p.n_head + kvh * g + (i >> 7)) * 128 + (i & 127)];
     __syncthreads();
@@ -83,9 +112,10 @@ __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
             if (valid) {
                 const uint4* kp = reinterpret_cast<const uint4*>(
                     p.k_arena + (((size_t)pb * DC_KV_BLOCK + key % DC_KV_BLOCK) * p.n_kv + kvh) * 128 + sub * 32);
+                const bool have = pre && blk == b0;   // fetched before the wait
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint4 u = kp[i];
+                    const uint4 u = have ? kr0[i] : kp[i];
                     const __half2* h2 = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {

@@ -73,6 +73,14 @@ __global__ void __launch_bounds__(256) k_rmsnorm_q8k(float* __restrict__ x, cons
     extern __shared__ __align__(16) float sx[];
     __shared__ double red[8];
     pdl_launch_dependents();
+    // the norm weights do not depend on the previous kernel: they are fetched (first touch comes from HBM)
+    // while this kernel still waits for it
+    float wreg[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = threadIdx.x + i * 256;
+        wreg[i] = e < H ? w[e] : 0.0f;
+    }
     pdl_wait();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* xr = x + (size_t)t * H;
@@ -97,7 +105,16 @@ __global__ void __launch_bounds__(256) k_rmsnorm_q8k(float* __restrict__ x, cons
     for (int i = 0; i < 8; ++i) tot += red[i];
     const float mean = (float)(tot / (double)H);
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-    for (int e = threadIdx.x; e < H; e += blockDim.x) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = threadIdx.x + i * 256;
+        if (e < H) {
+            const float v = __fmul_rn(__fmul_rn(sx[e], scale), wreg[i]);
+            sx[e] = v;
+            if (xn_out) xn_out[(size_t)t * H + e] = v;
+        }
+    }
+    for (int e = threadIdx.x + 8 * 256; e < H; e += 256) {
         const float v = __fmul_rn(__fmul_rn(sx[e], scale), w[e]);
         sx[e] = v;
         if (xn_out) xn_out[(size_t)t * H + e] = v;

@@ -52,10 +52,22 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
     __shared__ int32_t s_ids[DC_MAX_T * MOE_MAX_K];
     __shared__ int s_wsum_a[8], s_wsum_c[8];
     pdl_launch_dependents();
-    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // logits: two experts per CTA, four warps per expert, each warp a quarter of the row
-    // with all of its loads issued before the first use
+    // with all of its loads issued before the first use.  The router weights do not depend on the
+    // previous kernel: the first batch is fetched while this kernel still waits for it.
+    float4 wv0[4];
+    {
+        const int e = blockIdx.x * 2 + (warp >> 2), quarter = warp & 3, seg = p.H / 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = j * 32 + lane;
+            wv0[j] = (p.wr && e < p.E && i < seg / 4)
+                         ? reinterpret_cast<const float4*>(p.wr + (size_t)e * p.H + quarter * seg)[i]
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    pdl_wait();
     if (p.wr) {
         __shared__ float s_part[8][DC_MAX_T];
         const int e = blockIdx.x * 2 + (warp >> 2), quarter = warp & 3;
@@ -70,7 +82,7 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int i = i0 + j * 32 + lane;
-                    wv[j] = i < seg / 4 ? w4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    wv[j] = i0 == 0 ? wv0[j] : (i < seg / 4 ? w4[i] : make_float4(0.f, 0.f, 0.f, 0.f));
                 }
 #pragma unroll
                 for (int t = 0; t < DC_MAX_T; ++t) {
