@@ -252,11 +252,19 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
     WarpPipe<NSTAGE> pipe;
     pipe.init(bufs, bars, p.stage_bytes, p.err);
     pdl_launch_dependents();
-    pdl_wait();  // expert ids come from the router kernel: nothing can be fetched before this
-
     MoeStream<NSTAGE, PAIR> st;
-    st.begin(p, *p.n_active, blockIdx.x * DC_WARPS + warp, gridDim.x * DC_WARPS);
-    st.prefill(p, pipe, lane);
+    if (PAIR) {
+        pdl_wait();  // expert ids come from the router kernel just before: nothing can be fetched earlier
+        st.begin(p, *p.n_active, blockIdx.x * DC_WARPS + warp, gridDim.x * DC_WARPS);
+        st.prefill(p, pipe, lane);
+    } else {
+        // down projection: the routing was final before the gate/up kernel ran, and the kernel just before
+        // this one (the quantiser of h, an ordinary launch) started only after gate/up had completed, so
+        // the expert rows can be requested while this kernel still waits for the quantiser's output
+        st.begin(p, *p.n_active, blockIdx.x * DC_WARPS + warp, gridDim.x * DC_WARPS);
+        st.prefill(p, pipe, lane);
+        pdl_wait();
+    }
     ActSmem act;
     act.bind(act_base, p.act_rows, p.K);
     act.fill(p.act_q8, p.act_rows);
