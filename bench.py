@@ -44,7 +44,7 @@ PROMPT = 2048
 SAMPLE_LAYERS = 4          # layers of the model the CPU baseline times per sample
 SAMPLE_REPS = 12           # repeats of the sample (median taken)
 # DRAM bytes (read + write) of one launch of the persistent kernel divided by its algorithmic bytes,
-# from an ncu capture of the 4-layer case (profiles/k_decode_mega_moe35b_4layers.md)
+# measured with one ncu capture of the model cut to 4 layers (traffic is the weights, which scale with the layers)
 DRAM_TRAFFIC_RATIO = 1.03
 
 
@@ -356,8 +356,8 @@ def main():
         roofline = {"bound": "hbm", "kernel": "k_decode_mega", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                     "frac": achieved / peak_gbs, "peak_kind": f"of {peak_kind}",
                     "traffic": DRAM_TRAFFIC_RATIO * step_bytes * args.steps,
-                    "traffic_note": "dram__bytes_read+write of one launch measured on the 4-layer case, scaled by "
-                                    "algorithmic bytes (profiles/k_decode_mega_moe35b_4layers.md)",
+                    "traffic_note": "dram__bytes_read+write of one launch from an ncu capture of the model cut to 4 layers, "
+                                    "scaled by algorithmic bytes",
                     "launches": 1, "bytes_per_launch": step_bytes * args.steps, "us_per_launch": r1["ms"] * 1e3}
         gpu_launches = 1
     else:

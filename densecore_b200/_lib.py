@@ -126,6 +126,8 @@ def _signatures() -> dict:
         "dc_b200_model_get_config": (i32, [vp, vp]),
         "dc_b200_model_from_gguf": (i32, [vp, cstr, i32, i32, i32, i32, vp]),
         "dc_b200_model_ep_import": (i32, [vp, i32, vp]),
+        "dc_b200_model_read_layer_input": (i32, [vp, i32, i32, vp]),
+        "dc_b200_model_read_kv": (i32, [vp, i32, i32, i32, i32, vp, vp]),
     }
 
 

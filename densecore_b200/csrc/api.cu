@@ -5,6 +5,9 @@
 #include <string.h>
 #include <cuda_profiler_api.h>
 
+#include <map>
+#include <tuple>
+
 #include "dc_common.cuh"
 #include "dc_internal.h"
 
@@ -24,6 +27,39 @@ int dc_check_cuda(dc_ctx* ctx, cudaError_t e, const char* what) {
     if (e == cudaSuccess) return DC_B200_OK;
     return dc_fail(ctx, e == cudaErrorMemoryAllocation ? DC_B200_OUT_OF_MEMORY : DC_B200_BACKEND_ERROR, "%s: %s", what,
                    cudaGetErrorString(e));
+}
+
+// Kernel attributes and occupancy answers belong to a device, not to the process: a second context on
+// another GPU must opt its own kernels into large dynamic shared memory.  Both tables are keyed by
+// (device, kernel) and guarded by one mutex, so contexts on several GPUs and several host threads can
+// launch at once.
+static std::mutex g_kernel_mu;
+static std::map<std::pair<int, const void*>, int> g_kernel_smem;                    // opted-in bytes
+static std::map<std::tuple<int, const void*, int, size_t>, int> g_kernel_occupancy;
+
+int dc_kernel_setup(dc_ctx* ctx, const void* func, int max_dyn_smem, const char* name) {
+    std::lock_guard<std::mutex> lk(g_kernel_mu);
+    auto key = std::make_pair(ctx->device, func);
+    auto it = g_kernel_smem.find(key);
+    if (it != g_kernel_smem.end() && it->second >= max_dyn_smem) return DC_B200_OK;
+    cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn_smem);
+    if (e != cudaSuccess) return dc_check_cuda(ctx, e, name);
+    g_kernel_smem[key] = max_dyn_smem;
+    return DC_B200_OK;
+}
+
+int dc_kernel_occupancy(dc_ctx* ctx, const void* func, int threads, size_t dyn_smem) {
+    std::lock_guard<std::mutex> lk(g_kernel_mu);
+    auto key = std::make_tuple(ctx->device, func, threads, dyn_smem);
+    auto it = g_kernel_occupancy.find(key);
+    if (it != g_kernel_occupancy.end()) return it->second;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, func, threads, dyn_smem) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    g_kernel_occupancy[key] = n;
+    return n;
 }
 
 uint8_t* dc_scratch(dc_ctx* ctx, size_t bytes) {
@@ -134,6 +170,11 @@ int dc_b200_set_option(dc_ctx* ctx, const char* name, int value) {
     if (!ctx || !name) return DC_B200_INVALID_ARGUMENT;
     if (!strcmp(name, "pdl")) {
         ctx->use_pdl = value ? 1 : 0;
+        return DC_B200_OK;
+    }
+    if (!strcmp(name, "route_mode")) {
+        if (value != DC_ROUTE_STABLE && value != DC_ROUTE_SOFTMAX) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "route_mode must be 0 or 1");
+        ctx->route_mode = value;
         return DC_B200_OK;
     }
     return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "unknown option '%s'", name);
@@ -288,13 +329,17 @@ int dc_b200_mul_mat_block_sums(dc_ctx* ctx, const dc_weight* w, const float* x_h
     const size_t xb = ((size_t)M * K * 4 + 255) & ~(size_t)255;
     const size_t qb = ((size_t)M * nb * DC_Q8K_BYTES + 255) & ~(size_t)255;
     const size_t ib = ((size_t)M * w->N * nb * 4 + 255) & ~(size_t)255;
-    uint8_t* s = dc_scratch(ctx, xb + qb + 2 * ib);
+    const size_t yb = ((size_t)M * w->N * 4 + 255) & ~(size_t)255;
+    uint8_t* s = dc_scratch(ctx, xb + qb + 2 * ib + yb);
     if (!s) return DC_B200_OUT_OF_MEMORY;
     int32_t* Id = (int32_t*)(s + xb + qb);
     int32_t* Md = (int32_t*)(s + xb + qb + ib);
+    float* yd = (float*)(s + xb + qb + 2 * ib);
     DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(s, x_host, (size_t)M * K * 4, cudaMemcpyHostToDevice, ctx->stream), "H2D x"));
     DC_TRY(dc_launch_quantize_q8k(ctx, (const float*)s, M, K, s + xb));
-    DC_TRY(dc_launch_block_sums(ctx, w, s + xb, M, Id, Md));
+    // the production GEMV kernel itself, asked to store the integer sums it forms on the way
+    dc_gemv_seg seg = {w->dev, w->type, (int)w->N, (int)w->row_bytes, yd, (int)w->N};
+    DC_TRY(dc_launch_gemv(ctx, &seg, 1, DC_EPI_STORE, s + xb, M, K, nullptr, Id, w->type == DC_TYPE_Q4_K ? Md : nullptr));
     DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(I_host, Id, (size_t)M * w->N * nb * 4, cudaMemcpyDeviceToHost, ctx->stream), "D2H I"));
     if (Mn_host && w->type == DC_TYPE_Q4_K)
         DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(Mn_host, Md, (size_t)M * w->N * nb * 4, cudaMemcpyDeviceToHost, ctx->stream), "D2H M"));

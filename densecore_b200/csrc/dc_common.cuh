@@ -180,6 +180,11 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
 // 32-bit load from a 2-byte aligned shared address.
 __device__ __forceinline__ uint32_t lds32_a2(uint32_t a) { return lds16(a) | (lds16(a + 2) << 16); }
 
@@ -393,12 +398,24 @@ struct Q6Item {
     int sc[4];
     float d;
 };
+// Eight consecutive bytes from a 2-byte aligned shared address as two 32-bit words: two aligned
+// 64-bit loads and funnel shifts (instead of four 16-bit loads).  Reads up to a + 15.
+__device__ __forceinline__ uint2 lds64_a2(uint32_t a) {
+    const uint32_t a0 = a & ~7u, o = a & 7u;   // o in {0, 2, 4, 6}
+    const uint2 lo = lds64(a0), hi = lds64(a0 + 8);
+    const uint32_t sh = (o & 3u) * 8u;         // 0 or 16 bits
+    const bool up = o >= 4u;
+    const uint32_t w0 = up ? lo.y : lo.x, w1 = up ? hi.x : lo.y, w2 = up ? hi.y : hi.x;
+    return make_uint2(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh));
+}
 __device__ __forceinline__ void q6k_load_item(uint32_t row, int b, int j, int t, Q6Item& it) {
     const uint32_t blk = row + b * DC_Q6K_BYTES;
     const uint32_t ql0 = blk + 64 * j + 8 * t, ql1 = ql0 + 32, qh = blk + 128 + 32 * j + 8 * t;
+    // every range read below ends at most 15 bytes after its start, inside the 210-byte block
+    const uint2 A = lds64_a2(ql0), C = lds64_a2(ql1), H = lds64_a2(qh);
 #pragma unroll
     for (int w = 0; w < 2; ++w) {
-        const uint32_t a = lds32_a2(ql0 + 4 * w), c = lds32_a2(ql1 + 4 * w), h = lds32_a2(qh + 4 * w);
+        const uint32_t a = w ? A.y : A.x, c = w ? C.y : C.x, h = w ? H.y : H.x;
         // per byte: q in 0..63 -> q - 32 as a signed byte.  With bit 7 set no byte borrows from its
         // neighbour, so one 32-bit subtraction does all four: ((q | 0x80) - 0x20) ^ 0x80.
         it.q[0 + w] = q6_signed((a & 0x0F0F0F0F) | ((h << 4) & 0x30303030));
@@ -413,17 +430,17 @@ __device__ __forceinline__ void q6k_load_item(uint32_t row, int b, int j, int t,
 }
 // yq: shared address of the activation code at element 256b + 128j + 8t.  Quadrant qd
 // is 32*qd elements further on: same 64-value chunk for odd qd, next chunk (80 bytes on) for qd >= 2.
-__device__ __forceinline__ int q6k_item_int(const Q6Item& it, uint32_t yq) {
-    int I = 0;
+// I0 takes bytes 8t..8t+3 of every quadrant, I1 bytes 8t+4..8t+7: they belong to the partials 2t and
+// 2t+1 of core/src/llm/matmul/q6_small_batch.h:62-83.
+__device__ __forceinline__ void q6k_item_ints(const Q6Item& it, uint32_t yq, int& I0, int& I1) {
+    I0 = I1 = 0;
 #pragma unroll
     for (int qd = 0; qd < 4; ++qd) {
         const uint32_t a = yq + (qd >> 1) * 80 + (qd & 1) * 32;
-        const uint32_t y0 = lds32(a), y1 = lds32(a + 4);
-        int s = __dp4a((int)it.q[2 * qd], (int)y0, 0);
-        s = __dp4a((int)it.q[2 * qd + 1], (int)y1, s);
-        I += it.sc[qd] * s;
+        const uint2 y = lds64(a);
+        I0 += it.sc[qd] * __dp4a((int)it.q[2 * qd], (int)y.x, 0);
+        I1 += it.sc[qd] * __dp4a((int)it.q[2 * qd + 1], (int)y.y, 0);
     }
-    return I;
 }
 
 // Sum over the G lanes of a power-of-two lane group (all 32 lanes call it).
@@ -434,44 +451,149 @@ __device__ __forceinline__ float group_sum(float v) {
     return v;
 }
 
-// Row dot for up to NT tokens: weights decoded once per item and reused for
-// each token.  G lanes cooperate on one row.  tok[s] = row of the activation
-// arrays in shared memory used by token slot s (slots >= nt are skipped).
-// acc[] receives each lane's float partial; callers reduce with group_sum.
+// Optional capture of the exact per-block integer sums a row dot forms (parity checks):
+// I[(t * N + row) * nb + b], M likewise (Q4_K only).  Null in production launches.
+struct BlockSumDump {
+    int32_t* I;
+    int32_t* M;
+    int N;   // rows of the whole matrix (stride of a token)
+};
+
+// Row dot for up to NT tokens, in the float order of the CPU kernels it stands in for, so that the
+// result is bit-identical to them:
+//   Q4_K (core/src/kernels/hwy/hwy_moe_quant.cc:218-253): per super-block the exact int32 sums
+//     I = sum_s scale_s * dot_s and M = sum_g bsums_g * min_(g/2), then in block order
+//     sumf += (d * yd) * float(I);  sumf -= (dmin * yd) * float(M).
+//   Q6_K (core/src/llm/matmul/q6_small_batch.h:62-103): per super-block eight int32 partials (partial L
+//     collects bytes 4L..4L+3 of every 32-value quadrant, times the group scales), then per partial
+//     acc[L] = fma(yd * d, float(partial L), acc[L]) in block order, and at the end
+//     ((a0 + a4) + (a2 + a6)) + ((a1 + a5) + (a3 + a7)).
+// Weights are decoded once per item and reused for every token.  G lanes cooperate on one row and ALL 32
+// lanes of the warp must call (the exchanges are full-warp shuffles); `active` = this lane's row exists.
+// On return every lane of the group holds the row's result for each token.
+// tok[s] = row of the activation arrays in shared memory used by token slot s (slots >= nt are skipped).
 template <int NT>
-__device__ DC_HOT void row_dot_partial(int type, uint32_t row, int lane_in_group, int G, const ActSmem& act,
-                                                int nt, const int (&tok)[NT], float (&acc)[NT]) {
+__device__ DC_HOT void row_dot_exact(int type, uint32_t row, bool active, int lane, int G, const ActSmem& act, int nt,
+                                     const int (&tok)[NT], float (&out)[NT], const BlockSumDump* dump = nullptr,
+                                     int dump_row = 0) {
     const int nb = act.nb;
+    const int lig = lane & (G - 1), gbase = lane & ~(G - 1);
     if (type == DC_TYPE_Q4_K) {
-        for (int i = lane_in_group; i < nb * 4; i += G) {
-            const int b = i >> 2, c = i & 3;
+        float acc[NT];
+#pragma unroll
+        for (int s = 0; s < NT; ++s) acc[s] = 0.0f;
+        const int n_items = nb * 4, bpp = G >> 2;   // blocks per pass
+        for (int i0 = 0; i0 < n_items; i0 += G) {
+            const int i = i0 + lig, b = i >> 2, c = i & 3;
+            const bool on = active && i < n_items;
             Q4Item it;
-            q4k_load_item(row, b, c, it);
+            if (on) q4k_load_item(row, b, c, it);
+            float tI[NT], tM[NT];
 #pragma unroll
             for (int s = 0; s < NT; ++s) {
+                tI[s] = tM[s] = 0.0f;
                 if (s < nt) {
                     const int t = tok[s];
-                    int I, M;
-                    q4k_item_ints(it, act.q(t, b * 256 + 64 * c), act.bs + (t * nb + b) * 32 + 8 * c, I, M);
-                    const float yd = __int_as_float(lds32(act.d + (t * nb + b) * 4));
-                    acc[s] += yd * (it.d * (float)I - it.dmin * (float)M);
+                    int I = 0, M = 0;
+                    float yd = 0.0f;
+                    if (on) {
+                        q4k_item_ints(it, act.q(t, b * 256 + 64 * c), act.bs + (t * nb + b) * 32 + 8 * c, I, M);
+                        yd = __int_as_float(lds32(act.d + (t * nb + b) * 4));
+                    }
+                    // the block's four chunks sit in four neighbouring lanes
+                    I += __shfl_xor_sync(0xffffffffu, I, 1);
+                    M += __shfl_xor_sync(0xffffffffu, M, 1);
+                    I += __shfl_xor_sync(0xffffffffu, I, 2);
+                    M += __shfl_xor_sync(0xffffffffu, M, 2);
+                    if (on) {
+                        tI[s] = __fmul_rn(__fmul_rn(it.d, yd), (float)I);
+                        tM[s] = __fmul_rn(__fmul_rn(it.dmin, yd), (float)M);
+                        if (dump && c == 0) {
+                            const size_t di = ((size_t)t * dump->N + dump_row) * nb + b;
+                            dump->I[di] = I;
+                            if (dump->M) dump->M[di] = M;
+                        }
+                    }
+                }
+            }
+            // block order: the terms of the pass's blocks are fetched side by side, then added one by one
+#pragma unroll 1
+            for (int bb = 0; bb < bpp; ++bb) {
+                if ((i0 >> 2) + bb >= nb) break;
+#pragma unroll
+                for (int s = 0; s < NT; ++s) {
+                    if (s < nt) {
+                        const float a = __shfl_sync(0xffffffffu, tI[s], gbase + 4 * bb);
+                        const float m = __shfl_sync(0xffffffffu, tM[s], gbase + 4 * bb);
+                        acc[s] = __fsub_rn(__fadd_rn(acc[s], a), m);
+                    }
                 }
             }
         }
+#pragma unroll
+        for (int s = 0; s < NT; ++s) out[s] = acc[s];
     } else {
-        for (int i = lane_in_group; i < nb * 8; i += G) {
-            const int b = i >> 3, j = (i >> 2) & 1, tq = i & 3;
+        // lane -> (block, half j, eighth tq); the lanes with the same tq carry the chains of partials 2tq, 2tq+1
+        float a0[NT], a1[NT];
+#pragma unroll
+        for (int s = 0; s < NT; ++s) a0[s] = a1[s] = 0.0f;
+        const int n_items = nb * 8, bpp = G >> 3;
+        for (int i0 = 0; i0 < n_items; i0 += G) {
+            const int i = i0 + lig, b = i >> 3, j = (i >> 2) & 1, tq = i & 3;
+            const bool on = active && i < n_items;
             Q6Item it;
-            q6k_load_item(row, b, j, tq, it);
+            if (on) q6k_load_item(row, b, j, tq, it);
+            int I0[NT], I1[NT];
+            float sc[NT];
 #pragma unroll
             for (int s = 0; s < NT; ++s) {
+                I0[s] = I1[s] = 0;
+                sc[s] = 0.0f;
                 if (s < nt) {
                     const int t = tok[s];
-                    const int I = q6k_item_int(it, act.q(t, b * 256 + 128 * j + 8 * tq));
-                    const float yd = __int_as_float(lds32(act.d + (t * nb + b) * 4));
-                    acc[s] += (yd * it.d) * (float)I;
+                    if (on) {
+                        q6k_item_ints(it, act.q(t, b * 256 + 128 * j + 8 * tq), I0[s], I1[s]);
+                        sc[s] = __fmul_rn(__int_as_float(lds32(act.d + (t * nb + b) * 4)), it.d);
+                    }
+                    // the two halves of a block are four lanes apart
+                    I0[s] += __shfl_xor_sync(0xffffffffu, I0[s], 4);
+                    I1[s] += __shfl_xor_sync(0xffffffffu, I1[s], 4);
+                    if (dump) {
+                        int tot = I0[s] + I1[s];
+                        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+                        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+                        if (on && j == 0 && tq == 0) dump->I[((size_t)t * dump->N + dump_row) * nb + b] = tot;
+                    }
                 }
             }
+#pragma unroll 1
+            for (int bb = 0; bb < bpp; ++bb) {
+                if ((i0 >> 3) + bb >= nb) break;
+                const int src = gbase + 8 * bb + (lig & 3);
+#pragma unroll
+                for (int s = 0; s < NT; ++s) {
+                    if (s < nt) {
+                        const float f = __shfl_sync(0xffffffffu, sc[s], src);
+                        const int v0 = __shfl_sync(0xffffffffu, I0[s], src);
+                        const int v1 = __shfl_sync(0xffffffffu, I1[s], src);
+                        a0[s] = __fmaf_rn(f, (float)v0, a0[s]);
+                        a1[s] = __fmaf_rn(f, (float)v1, a1[s]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int s = 0; s < NT; ++s) {
+            float r = 0.0f;
+            if (s < nt) {
+                // lanes tq = 0..3 hold (a0,a1), (a2,a3), (a4,a5), (a6,a7)
+                const float x0 = __fadd_rn(a0[s], __shfl_xor_sync(0xffffffffu, a0[s], 2));   // a0+a4 | a2+a6
+                const float x1 = __fadd_rn(a1[s], __shfl_xor_sync(0xffffffffu, a1[s], 2));   // a1+a5 | a3+a7
+                const float y0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 1));         // (a0+a4)+(a2+a6)
+                const float y1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 1));         // (a1+a5)+(a3+a7)
+                r = __fadd_rn(y0, y1);
+            }
+            out[s] = r;
         }
     }
 }

@@ -37,6 +37,7 @@ struct dc_ctx {
     void* pinned = nullptr;        // small pinned staging area for host<->device results
     size_t pinned_bytes = 0;
     int use_pdl = 1;
+    int route_mode = 0;            // router variant of the op-level MoE calls (DC_ROUTE_*)
 };
 
 int dc_fail(dc_ctx* ctx, int status, const char* fmt, ...);
@@ -44,6 +45,10 @@ int dc_check_cuda(dc_ctx* ctx, cudaError_t e, const char* what);
 uint8_t* dc_scratch(dc_ctx* ctx, size_t bytes);   // returns nullptr on failure (error recorded)
 void* dc_pinned(dc_ctx* ctx, size_t bytes);
 int dc_check_device_error(dc_ctx* ctx);            // reads d_err after a sync
+// One-time, per-device kernel set-up (thread-safe): opt `func` into max_dyn_smem bytes of dynamic shared
+// memory on ctx's device; cached occupancy (resident CTAs per SM) of `func` on that device.
+int dc_kernel_setup(dc_ctx* ctx, const void* func, int max_dyn_smem, const char* name);
+int dc_kernel_occupancy(dc_ctx* ctx, const void* func, int threads, size_t dyn_smem);
 
 // ---- launch helpers implemented in the kernel translation units ----
 struct dc_gemv_seg {
@@ -60,12 +65,12 @@ enum { DC_EPI_STORE = 0, DC_EPI_ACC = 1, DC_EPI_SWIGLU = 2 };
 // n_seg 1..3 segments share the activations.  DC_EPI_SWIGLU: seg[0]=gate, seg[1]=up,
 // result silu(gate.x)*(up.x) stored to seg[0].out.  argmax (optional, [T] u64 keys,
 // zeroed by the caller) receives the packed (value,row) maximum of the stored rows.
+// dump_I / dump_M (parity checks, single segment): receive the exact int32 block sums the kernel forms,
+// [T][n_rows][K/256] (M for Q4_K only).
 int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, const uint8_t* act_q8, int T, int K,
-                   unsigned long long* argmax);
+                   unsigned long long* argmax, int32_t* dump_I = nullptr, int32_t* dump_M = nullptr);
 // rows x K f32 -> native Q8_K blocks (row stride K/256*292)
 int dc_launch_quantize_q8k(dc_ctx* ctx, const float* x, int rows, int K, uint8_t* out);
-// per-block integer sums of W x (debug/parity): I[T][N][nb], M[T][N][nb] (M only for Q4_K)
-int dc_launch_block_sums(dc_ctx* ctx, const dc_weight* w, const uint8_t* act_q8, int T, int32_t* I, int32_t* M);
 
 // ---- misc.cu ----
 int dc_launch_embed(dc_ctx* ctx, const dc_weight* w, const int32_t* tokens, int T, float* x);
@@ -106,8 +111,12 @@ struct dc_moe_route {
     int32_t* uoff;     // [E+1]
     int32_t* uassign;  // [T*top_k]
 };
+// mode: DC_ROUTE_STABLE = top-k on the logits with the stable comparator, weights over the picks
+// (core/src/llm/moe/native.cpp:610-676); DC_ROUTE_SOFTMAX = softmax over all experts, top-k on the
+// probabilities with strict '>', renormalise (core/src/moe/moe_routing.cpp:53-101).
+enum { DC_ROUTE_STABLE = 0, DC_ROUTE_SOFTMAX = 1 };
 int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_expert, int T, int top_k, float scale,
-                     int ep_lo, int ep_hi, const dc_moe_route* rt);
+                     int ep_lo, int ep_hi, const dc_moe_route* rt, int mode = DC_ROUTE_STABLE);
 // carves a dc_moe_route for (T, E, top_k) out of a byte buffer; returns bytes used
 size_t dc_moe_route_bind(dc_moe_route* rt, uint8_t* base, int T, int E, int top_k);
 int dc_launch_moe_mm(dc_ctx* ctx, bool pair, const dc_weight* w0, const dc_weight* w1, const uint8_t* act_q8,

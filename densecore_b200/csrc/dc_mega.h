@@ -60,6 +60,10 @@ struct MegaParams {
     unsigned* xflag[MG_MAX_RANKS];   // in rank r's memory: the flag this rank raises there
     unsigned* my_flags;              // this rank's flags, one per peer
     unsigned xepoch0;                // exchanges completed before this launch
+    int route_mode;                  // DC_ROUTE_STABLE / DC_ROUTE_SOFTMAX
+    float* dbg_x;                    // optional capture of every layer's input [n_layer + 1][DC_MAX_T][H]
+    unsigned bar_polls;              // poll limit of a grid barrier
+    unsigned long long ep_wait_ns;   // time limit of the expert-parallel meeting
     // sync
     unsigned* bar_counter;
     int* err;

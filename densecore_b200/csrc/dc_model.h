@@ -68,6 +68,13 @@ struct dc_model {
     unsigned* mega_counter = nullptr;
     int use_mega = 1;            // 0 never, 1 for one stream (where it is the faster path), 2 wherever it fits
     bool mega_timing = false;
+    int route_mode = 0;          // DC_ROUTE_STABLE / DC_ROUTE_SOFTMAX
+    // parity aid: the hidden state entering every layer (slot il) and the output norm (slot n_layer) of the
+    // last step, [n_layer + 1][DC_MAX_T][hidden] floats; allocated by option "capture_layer_inputs"
+    float* dbg_x = nullptr;
+    // bounded-wait test hooks: poll limits of the persistent kernel's waits (0 = the defaults)
+    unsigned test_barrier_polls = 0;
+    unsigned long long test_ep_wait_ns = 0;
     // expert parallel
     bool ep_ready = false;
     void* ep_comm = nullptr;     // ncclComm_t

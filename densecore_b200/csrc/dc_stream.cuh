@@ -20,6 +20,7 @@ struct GemvParams {
     uint32_t up_off;  // SwiGLU: offset of the up rows inside a stage
     unsigned long long* argmax;
     int* err;
+    BlockSumDump dump;   // parity checks only: where the exact block sums go (I == nullptr: nowhere)
 };
 
 // Walks a warp's contiguous flattened row range stage by stage.
@@ -132,27 +133,22 @@ struct GemvStream {
             const uint32_t skew = (uint32_t)(((uintptr_t)s.w + (size_t)lr * s.row_bytes) & 15);
             const uint32_t skew_up =
                 (SWIGLU && p.epi == DC_EPI_SWIGLU) ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
+            const BlockSumDump* dump = p.dump.I ? &p.dump : nullptr;
             for (int r = 0; r < n; r += rows_per_pass) {
                 const int rr = r + grp;
                 const bool active = rr < n;
                 float acc[NT], acc2[NT];
-#pragma unroll
-                for (int t = 0; t < NT; ++t) acc[t] = acc2[t] = 0.0f;
-                if (active) {
-                    row_dot_partial<NT>(s.type, buf + skew + rr * s.row_bytes, lig, G, act, p.T, tok, acc);
-                    if ((SWIGLU && p.epi == DC_EPI_SWIGLU))
-                        row_dot_partial<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, lig, G, act, p.T, tok,
-                                            acc2);
-                }
-                // every lane runs the reductions; lane (t mod G) of the row's group stores token t
+                // every lane takes part in the row dots (full-warp exchanges inside); all lanes of a row's
+                // group end up with the row's result, and lane (t mod G) of the group stores token t
+                row_dot_exact<NT>(s.type, buf + skew + rr * s.row_bytes, active, lane, G, act, p.T, tok, acc, dump, lr + rr);
+                if ((SWIGLU && p.epi == DC_EPI_SWIGLU))
+                    row_dot_exact<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, active, lane, G, act, p.T, tok,
+                                      acc2);
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
                     if (t < p.T) {
-                        float v = group_sum_rt(acc[t], G);
-                        if ((SWIGLU && p.epi == DC_EPI_SWIGLU)) {
-                            const float u = group_sum_rt(acc2[t], G);
-                            v = __fmul_rn(silu_fast(v), u);
-                        }
+                        float v = acc[t];
+                        if ((SWIGLU && p.epi == DC_EPI_SWIGLU)) v = __fmul_rn(silu_fast(v), acc2[t]);
                         if (active && lig == (t & (G - 1))) {
                             const int row = lr + rr;
                             float* o = s.out + (size_t)t * s.ldo + row;
@@ -279,7 +275,7 @@ struct MoeStream {
     template <int NTT>
     __device__ __forceinline__ static void stage_rows(const MoeMMParams& p, const ActSmem& act, uint32_t buf, uint32_t skew0,
                                                       uint32_t skew1, int nhalf, int r, int n, int nt, const int* tok_in,
-                                                      const int* asg_in, int G, int grp, int lig) {
+                                                      const int* asg_in, int G, int grp, int lig, int lane) {
         const int rows_per_pass = 32 / G;
         int tok[NTT], asg[NTT];
 #pragma unroll
@@ -297,17 +293,10 @@ struct MoeStream {
 #pragma unroll 1
             for (int half = 0; half < nhalf; ++half) {
                 float acc[NTT];
+                row_dot_exact<NTT>(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, active, lane, G, act, nt, tok, acc);
 #pragma unroll
-                for (int s = 0; s < NTT; ++s) acc[s] = 0.0f;
-                if (active)
-                    row_dot_partial<NTT>(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, lig, G, act, nt, tok, acc);
-#pragma unroll
-                for (int s = 0; s < NTT; ++s) {
-                    if (s < nt) {
-                        const float sum = group_sum_rt(acc[s], G);
-                        v[s] = half ? __fmul_rn(silu_fast(v[s]), sum) : sum;
-                    }
-                }
+                for (int s = 0; s < NTT; ++s)
+                    if (s < nt) v[s] = half ? __fmul_rn(silu_fast(v[s]), acc[s]) : acc[s];
             }
 #pragma unroll
             for (int s = 0; s < NTT; ++s)
@@ -339,8 +328,8 @@ struct MoeStream {
                 tok[s] = pair ? asg[s] / p.top_k : asg[s];
             }
             // most experts of a step serve a single token: that case runs the one-token body
-            if (NT > 1 && nt == 1) stage_rows<1>(p, act, buf, skew0, skew1, nhalf, r, n, nt, tok, asg, G, grp, lig);
-            else stage_rows<NT>(p, act, buf, skew0, skew1, nhalf, r, n, nt, tok, asg, G, grp, lig);
+            if (NT > 1 && nt == 1) stage_rows<1>(p, act, buf, skew0, skew1, nhalf, r, n, nt, tok, asg, G, grp, lig, lane);
+            else stage_rows<NT>(p, act, buf, skew0, skew1, nhalf, r, n, nt, tok, asg, G, grp, lig, lane);
             pipe.release();
             if (lane == 0) issue_next(p, pipe);
         }

@@ -71,13 +71,8 @@ static int rows_per_stage(int type, int K, int row_bytes) {
 
 template <int NT, int NSTAGE>
 static int launch_gemv_ns(dc_ctx* ctx, const GemvParams& p, int grid, size_t smem) {
-    static bool configured = false;
-    cudaError_t e = cudaSuccess;
-    if (!configured) {
-        e = cudaFuncSetAttribute(k_gemv<NT, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_gemv)");
-        configured = true;
-    }
+    int st = dc_kernel_setup(ctx, (const void*)k_gemv<NT, NSTAGE>, 200 * 1024, "cudaFuncSetAttribute(k_gemv)");
+    if (st != DC_B200_OK) return st;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(DC_WARPS * 32);
@@ -88,8 +83,7 @@ static int launch_gemv_ns(dc_ctx* ctx, const GemvParams& p, int grid, size_t sme
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, k_gemv<NT, NSTAGE>, p);
-    return dc_check_cuda(ctx, e, "k_gemv");
+    return dc_check_cuda(ctx, cudaLaunchKernelEx(&cfg, k_gemv<NT, NSTAGE>, p), "k_gemv");
 }
 
 static size_t gemv_smem(size_t act_bytes, uint32_t stage, int ns) {
@@ -107,14 +101,11 @@ static int gemv_ctas_per_sm(size_t smem) {
 template <int NT>
 static int launch_gemv_nt(dc_ctx* ctx, const GemvParams& p, size_t act_bytes, int total_rows) {
     const size_t s4 = gemv_smem(act_bytes, p.stage_bytes, DC_NSTAGE), s2 = gemv_smem(act_bytes, p.stage_bytes, 2);
-    // resident CTAs per SM by shared memory, then by the kernel's registers (asked once per instance)
-    static int reg_limit4 = 0, reg_limit2 = 0;
-    if (!reg_limit4) {
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reg_limit4, k_gemv<NT, DC_NSTAGE>, DC_WARPS * 32, 0);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reg_limit2, k_gemv<NT, 2>, DC_WARPS * 32, 0);
-        if (reg_limit4 < 1) reg_limit4 = 1;
-        if (reg_limit2 < 1) reg_limit2 = 1;
-    }
+    // resident CTAs per SM by shared memory, then by the kernel's registers (asked once per device and instance)
+    int reg_limit4 = dc_kernel_occupancy(ctx, (const void*)k_gemv<NT, DC_NSTAGE>, DC_WARPS * 32, 0);
+    int reg_limit2 = dc_kernel_occupancy(ctx, (const void*)k_gemv<NT, 2>, DC_WARPS * 32, 0);
+    if (reg_limit4 < 1) reg_limit4 = 1;
+    if (reg_limit2 < 1) reg_limit2 = 1;
     int n4 = gemv_ctas_per_sm(s4), n2 = gemv_ctas_per_sm(s2);
     if (n4 > reg_limit4) n4 = reg_limit4;
     if (n2 > reg_limit2) n2 = reg_limit2;
@@ -126,7 +117,7 @@ static int launch_gemv_nt(dc_ctx* ctx, const GemvParams& p, size_t act_bytes, in
 }
 
 int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, const uint8_t* act_q8, int T, int K,
-                   unsigned long long* argmax) {
+                   unsigned long long* argmax, int32_t* dump_I, int32_t* dump_M) {
     if (n_seg < 1 || n_seg > 3 || T < 1 || T > DC_MAX_T || K % DC_QK_K)
         return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemv: bad shape (n_seg=%d T=%d K=%d)", n_seg, T, K);
     GemvParams p = {};
@@ -137,6 +128,10 @@ int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, con
     p.K = K;
     p.argmax = argmax;
     p.err = ctx->d_err;
+    if (dump_I) {
+        if (n_seg != 1 || epi != DC_EPI_STORE) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemv: block-sum capture takes one plain segment");
+        p.dump = BlockSumDump{dump_I, dump_M, segs[0].n_rows};
+    }
     uint32_t stage = 0;
     int total = 0;
     for (int i = 0; i < n_seg; ++i) {
@@ -161,7 +156,7 @@ int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, con
     const size_t act_bytes = (ActSmem::bytes(T, K) + 127) & ~(size_t)127;
     if (gemv_smem(act_bytes, stage, 2) > 200 * 1024) {
         // activations of all T tokens do not fit beside the weight pipeline: run the tokens in two halves
-        if (T == 1 || argmax)
+        if (T == 1 || argmax || dump_I)
             return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemv: shared memory need %zu too large", gemv_smem(act_bytes, stage, 2));
         const int T0 = T / 2;
         dc_gemv_seg second[3];
@@ -179,78 +174,3 @@ int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, con
     return launch_gemv_nt<16>(ctx, p, act_bytes, total);
 }
 
-// ------------------------------------------------ per-block integer sums
-// Parity/debug path: writes the exact int32 block sums the GEMV forms
-// (I and M of core/src/kernels/hwy/hwy_moe_quant.cc:218-246; I of
-// core/src/llm/matmul/q6_small_batch.h:62-83).  Same decoders as k_gemv, plain
-// (non-pipelined) staging since speed does not matter here.
-__global__ void __launch_bounds__(256) k_block_sums(const uint8_t* __restrict__ w, int type, int N, int K,
-                                                    int row_bytes, const uint8_t* __restrict__ act_q8, int T,
-                                                    int32_t* __restrict__ I_out, int32_t* __restrict__ M_out) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nb = K / DC_QK_K;
-    ActSmem act;
-    act.bind(smem, T, K);
-    act.fill(act_q8, T);
-    const size_t act_bytes = (ActSmem::bytes(T, K) + 127) & ~(size_t)127;
-    const int row_pad = (row_bytes + 15) & ~15;
-    uint8_t* rowbuf = smem + act_bytes + (size_t)warp * row_pad;
-    __syncthreads();
-    const int gw = blockIdx.x * 8 + warp, nw = gridDim.x * 8;
-    const int ipb = type == DC_TYPE_Q4_K ? 4 : 8;
-    for (int n = gw; n < N; n += nw) {
-        const uint8_t* src = w + (size_t)n * row_bytes;
-        for (int i = lane; i < row_bytes / 2; i += 32)
-            reinterpret_cast<uint16_t*>(rowbuf)[i] = reinterpret_cast<const uint16_t*>(src)[i];
-        __syncwarp();
-        const uint32_t row = smem_u32(rowbuf);
-        for (int t = 0; t < T; ++t) {
-            for (int i0 = 0; i0 < nb * ipb; i0 += 32) {
-                const int i = i0 + lane;
-                int I = 0, M = 0;
-                if (i < nb * ipb) {
-                    if (type == DC_TYPE_Q4_K) {
-                        const int b = i >> 2, c = i & 3;
-                        Q4Item it;
-                        q4k_load_item(row, b, c, it);
-                        q4k_item_ints(it, act.q(t, b * 256 + 64 * c), act.bs + (t * nb + b) * 32 + 8 * c, I, M);
-                    } else {
-                        const int b = i >> 3, j = (i >> 2) & 1, tq = i & 3;
-                        Q6Item it;
-                        q6k_load_item(row, b, j, tq, it);
-                        I = q6k_item_int(it, act.q(t, b * 256 + 128 * j + 8 * tq));
-                    }
-                }
-                for (int o = 1; o < ipb; o <<= 1) {
-                    I += __shfl_xor_sync(0xffffffffu, I, o);
-                    M += __shfl_xor_sync(0xffffffffu, M, o);
-                }
-                if (i < nb * ipb && (lane % ipb) == 0) {
-                    const size_t idx = ((size_t)t * N + n) * nb + i / ipb;
-                    I_out[idx] = I;
-                    if (M_out) M_out[idx] = M;
-                }
-            }
-        }
-        __syncwarp();
-    }
-}
-
-int dc_launch_block_sums(dc_ctx* ctx, const dc_weight* w, const uint8_t* act_q8, int T, int32_t* I, int32_t* M) {
-    const int K = (int)w->K, N = (int)(w->N * w->E);
-    const size_t act_bytes = (ActSmem::bytes(T, K) + 127) & ~(size_t)127;
-    const size_t smem = act_bytes + 8 * (((size_t)w->row_bytes + 15) & ~(size_t)15);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_block_sums, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_block_sums)");
-        configured = true;
-    }
-    if (smem > 200 * 1024) return dc_fail(ctx, DC_B200_UNSUPPORTED, "block_sums: shape too large");
-    int grid = (N + 7) / 8;
-    if (grid > ctx->num_sms * 2) grid = ctx->num_sms * 2;
-    k_block_sums<<<grid, 256, smem, ctx->stream>>>(w->dev, w->type, N, K, (int)w->row_bytes, act_q8, T, I,
-                                                   w->type == DC_TYPE_Q4_K ? M : nullptr);
-    return dc_check_cuda(ctx, cudaGetLastError(), "k_block_sums");
-}

@@ -55,7 +55,7 @@ __device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch, 
         const unsigned target = epoch * gridDim.x;
         unsigned polls = 0;
         while (ld_acquire_u32(p.bar_counter) < target) {
-            if (++polls > MG_BAR_LIMIT) {
+            if (++polls > p.bar_polls) {
                 atomicExch(p.err, DC_ERR_GRID_BARRIER);
                 break;
             }
@@ -96,7 +96,7 @@ __device__ __noinline__ void ep_exchange(const MegaParams& p, unsigned value) {
             // flags only grow; the difference is taken modulo 2^32
             while ((int)(ld_acquire_sys_u32(p.my_flags + r) - value) < 0) {
                 if (*reinterpret_cast<volatile int*>(p.err) != 0) break;
-                if (mg_now() - t0 > MG_EP_WAIT_NS) {
+                if (mg_now() - t0 > p.ep_wait_ns) {
                     atomicExch(p.err, DC_ERR_EP_WAIT);
                     break;
                 }
@@ -194,7 +194,8 @@ struct MegaShared {
     int32_t tbl[MG_MAX_RUN_BLOCKS];        // physical ids of the run's KV blocks
     alignas(16) float cs[128];             // RoPE cos/sin row of the item's token
     alignas(8) unsigned long long rkeys[MG_MAX_T][MG_MAX_E];   // routing keys (rank selection)
-    float sel[MG_MAX_T][MG_MAX_K];         // logits of the picks, in pick order
+    float sel[MG_MAX_T][MG_MAX_K];         // logits (or probabilities) of the picks, in pick order
+    float prob[MG_MAX_T][MG_MAX_E];        // generic router: exponentials of all experts
 };
 
 // Dynamic shared memory the kernel may ask for: what the SM offers a CTA (227 KB) less the
@@ -217,7 +218,8 @@ static constexpr uint32_t MG_DYN_LIMIT =
 // NPI (token, block) pairs per warp: T * H/256 <= 16 * NPI.
 template <int NPI>
 __device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, int src, const float* x_in, float* x_out,
-                                          const float* w, const ActSmem& act, float* xn, const float* dn) {
+                                          const float* w, const ActSmem& act, float* xn, const float* dn,
+                                          float* dbg = nullptr) {
     const int H = p.H, nb = H / DC_QK_K, pairs = p.T * nb;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float v[NPI][8];
@@ -274,10 +276,17 @@ __device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, i
                 for (int i = 0; i < 8; ++i) v[pi][i] = __fadd_rn(v[pi][i], sum[i]);
             }
         }
-        if (x_out && src != 2 && (pr % (int)gridDim.x) == (int)blockIdx.x) {
-            float* o = x_out + (size_t)t * H + dd;
-            *reinterpret_cast<float4*>(o) = make_float4(v[pi][0], v[pi][1], v[pi][2], v[pi][3]);
-            *reinterpret_cast<float4*>(o + 4) = make_float4(v[pi][4], v[pi][5], v[pi][6], v[pi][7]);
+        if (src != 2 && (pr % (int)gridDim.x) == (int)blockIdx.x) {
+            if (x_out) {
+                float* o = x_out + (size_t)t * H + dd;
+                *reinterpret_cast<float4*>(o) = make_float4(v[pi][0], v[pi][1], v[pi][2], v[pi][3]);
+                *reinterpret_cast<float4*>(o + 4) = make_float4(v[pi][4], v[pi][5], v[pi][6], v[pi][7]);
+            }
+            if (dbg) {
+                float* o = dbg + (size_t)t * H + dd;
+                *reinterpret_cast<float4*>(o) = make_float4(v[pi][0], v[pi][1], v[pi][2], v[pi][3]);
+                *reinterpret_cast<float4*>(o + 4) = make_float4(v[pi][4], v[pi][5], v[pi][6], v[pi][7]);
+            }
         }
         double ss = 0.0;
 #pragma unroll
@@ -826,9 +835,30 @@ __device__ DC_HOT void route_phase(const MegaParams& p, MegaShared& sh) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // rank selection: thread (t, e) counts the candidates that precede its own
     // ("larger logit first, then lower id, NaN last"); the k best have ranks 0..k-1
-    for (int i = threadIdx.x; i < p.T * p.E; i += MG_THREADS) {
-        const int t = i / p.E, e = i - t * p.E;
-        sh.rkeys[t][e] = mg_route_key(__ldcg(p.router_logits + i), e);
+    if (p.route_mode == DC_ROUTE_SOFTMAX) {
+        // softmax over all experts first (expf(x - max), sum in index order, times 1/sum:
+        // core/include/densecore/simd/simd_ops.h:1171-1195); the ranks are then taken on the probabilities
+        if (warp < p.T) {
+            const int t = warp;
+            float mx = -INFINITY;
+            for (int e = lane; e < p.E; e += 32) mx = fmaxf(mx, __ldcg(p.router_logits + t * p.E + e));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            for (int e = lane; e < p.E; e += 32)
+                sh.prob[t][e] = (float)exp((double)__fsub_rn(__ldcg(p.router_logits + t * p.E + e), mx));
+            __syncwarp();
+            float sum = 0.0f;
+            if (lane == 0)
+                for (int e = 0; e < p.E; ++e) sum = __fadd_rn(sum, sh.prob[t][e]);
+            sum = __shfl_sync(0xffffffffu, sum, 0);
+            const float inv = __fdiv_rn(1.0f, sum);
+            for (int e = lane; e < p.E; e += 32) sh.rkeys[t][e] = mg_route_key(__fmul_rn(sh.prob[t][e], inv), e);
+        }
+    } else {
+        for (int i = threadIdx.x; i < p.T * p.E; i += MG_THREADS) {
+            const int t = i / p.E, e = i - t * p.E;
+            sh.rkeys[t][e] = mg_route_key(__ldcg(p.router_logits + i), e);
+        }
     }
     __syncthreads();
     {
@@ -859,6 +889,15 @@ __device__ DC_HOT void route_phase(const MegaParams& p, MegaShared& sh) {
         // pick order as the reference adds them
         const int t = warp;
         const float v = lane < p.top_k ? sh.sel[t][lane] : -INFINITY;
+        if (p.route_mode == DC_ROUTE_SOFTMAX) {
+            // renormalise over the picks in pick order, w * (1 / sum) (core/src/moe/moe_routing.cpp:90-101)
+            float sum = 0.0f;
+            for (int k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, v, k));
+            if (lane < p.top_k) {
+                const float w = sum > 0.0f ? __fmul_rn(v, __fdiv_rn(1.0f, sum)) : v;
+                sh.w[t * p.top_k + lane] = __fmul_rn(w, p.routed_scale);
+            }
+        } else {
         const bool fin_l = lane >= p.top_k || isfinite(v);
         const bool finite = __all_sync(0xffffffffu, fin_l);
         float mx = (lane < p.top_k && isfinite(v)) ? v : -INFINITY;
@@ -872,6 +911,7 @@ __device__ DC_HOT void route_phase(const MegaParams& p, MegaShared& sh) {
         if (lane < p.top_k) {
             const float w = ok ? __fdiv_rn(ev, den) : __fdiv_rn(1.0f, (float)p.top_k);
             sh.w[t * p.top_k + lane] = __fmul_rn(w, p.routed_scale);
+        }
         }
     }
     __syncthreads();
@@ -1145,7 +1185,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             MG_MARK(0);
             ActSmem act;
             act.bind(act_base, p.T, p.H);
-            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, l == 0 ? 0 : 1, xin, xout, L.attn_norm, act, nullptr, dn_r);
+            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, l == 0 ? 0 : 1, xin, xout, L.attn_norm, act, nullptr, dn_r,
+                                           p.dbg_x ? p.dbg_x + (size_t)l * DC_MAX_T * p.H : nullptr);
             MG_MARK(2);
             mg_gemv_consume<NT>(gq, pipe, act, gw, nw, lane);
             MG_MARK(3);
@@ -1243,7 +1284,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
         // ---- final: last MoE output + residual, output norm, lm_head with arg-max keys
         ActSmem act;
         act.bind(act_base, p.T, p.H);
-        x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 1, (p.n_layer & 1) ? p.xb : p.xa, nullptr, p.out_norm, act, nullptr, dn_r);
+        x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 1, (p.n_layer & 1) ? p.xb : p.xa, nullptr, p.out_norm, act, nullptr, dn_r,
+                                       p.dbg_x ? p.dbg_x + (size_t)p.n_layer * DC_MAX_T * p.H : nullptr);
         mg_gemv_consume<NT>(glm, pipe, act, gw, nw, lane);
         grid_barrier(p, epoch);
         MG_MARK(21);
@@ -1392,15 +1434,10 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
 template <int NT>
 static int mg_launch(dc_model* m, MegaParams& p) {
     dc_ctx* ctx = m->ctx;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_decode_mega<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, MG_DYN_LIMIT);
-        if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_decode_mega)");
-        configured = true;
-    }
-    int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_mega<NT>, MG_THREADS, p.smem_bytes);
-    if (e != cudaSuccess) return dc_check_cuda(ctx, e, "occupancy query");
+    int st = dc_kernel_setup(ctx, (const void*)k_decode_mega<NT>, MG_DYN_LIMIT, "cudaFuncSetAttribute(k_decode_mega)");
+    if (st != DC_B200_OK) return st;
+    const int per_sm = dc_kernel_occupancy(ctx, (const void*)k_decode_mega<NT>, MG_THREADS, p.smem_bytes);
+    cudaError_t e;
     if (per_sm < 1) return dc_fail(ctx, DC_B200_UNSUPPORTED, "persistent decode kernel does not fit on an SM");
     void* args[] = {&p};
     e = cudaLaunchCooperativeKernel((void*)k_decode_mega<NT>, dim3(ctx->num_sms), dim3(MG_THREADS), args, p.smem_bytes,
@@ -1451,6 +1488,10 @@ int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback) {
         p.xepoch0 = m->xepoch;
         m->xepoch += (unsigned)(m->cfg.n_layer * n_steps);
     }
+    p.route_mode = m->route_mode;
+    p.dbg_x = m->dbg_x;
+    p.bar_polls = m->test_barrier_polls ? m->test_barrier_polls : MG_BAR_LIMIT;
+    p.ep_wait_ns = m->test_ep_wait_ns ? m->test_ep_wait_ns : MG_EP_WAIT_NS;
     p.bar_counter = m->mega_counter;
     p.err = m->ctx->d_err;
     p.phase_ns = m->mega_timing ? (unsigned long long*)((uint8_t*)m->mega_counter + 64) : nullptr;

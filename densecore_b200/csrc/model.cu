@@ -220,6 +220,8 @@ static int enqueue_forward(dc_model* m, int T, int lm_mode, bool feedback) {
         L(DC_K_RMSNORM, xb + q8x + H * 4, 1,
           dc_launch_rmsnorm_q8k(ctx, b.x, pending, (const float*)Ly.attn_norm->dev, T, H, c.rms_eps, nullptr, b.q8_x));
         pending = nullptr;
+        if (m->dbg_x)
+            DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(m->dbg_x + (size_t)il * DC_MAX_T * H, b.x, (size_t)T * H * 4, cudaMemcpyDeviceToDevice, ctx->stream), "capture"));
         dc_gemv_seg qkv[3] = {
             {Ly.wq->dev, Ly.wq->type, QD, (int)Ly.wq->row_bytes, b.qkv, QKV},
             {Ly.wk->dev, Ly.wk->type, KD, (int)Ly.wk->row_bytes, b.qkv + QD, QKV},
@@ -250,7 +252,7 @@ static int enqueue_forward(dc_model* m, int T, int lm_mode, bool feedback) {
             const double U = T == 1 ? top_k : (A < E ? A : E);
             const double local = (double)(ep_hi - ep_lo) / E;
             L(DC_K_ROUTER, (double)Ly.router->bytes + xb, 1,
-              dc_launch_router(ctx, Ly.router, b.xn, E, T, top_k, c.routed_scale, ep_lo, ep_hi, &b.route));
+              dc_launch_router(ctx, Ly.router, b.xn, E, T, top_k, c.routed_scale, ep_lo, ep_hi, &b.route, m->route_mode));
             L(DC_K_MOE_GATEUP, U * local * 2.0 * F * Ly.gate_exps->row_bytes + q8x + (double)A * F * 4, 1,
               dc_launch_moe_mm(ctx, true, Ly.gate_exps, Ly.up_exps, b.q8_x, T, T, top_k, ep_lo, &b.route, b.h));
             L(DC_K_QUANT_H, (double)A * F * 4 + (double)A * (F / 256) * 292, 1,
@@ -280,6 +282,8 @@ static int enqueue_forward(dc_model* m, int T, int lm_mode, bool feedback) {
         L(DC_K_RMSNORM, (double)rows * H * 4 * 2 + (double)rows * (H / 256) * 292, 1,
           dc_launch_rmsnorm_q8k(ctx, b.x + (size_t)first * H, pending ? pending + (size_t)first * H : nullptr,
                                 (const float*)m->out_norm->dev, rows, H, c.rms_eps, nullptr, b.q8_x));
+        if (m->dbg_x)
+            DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(m->dbg_x + ((size_t)c.n_layer * DC_MAX_T + first) * H, b.x + (size_t)first * H, (size_t)rows * H * 4, cudaMemcpyDeviceToDevice, ctx->stream), "capture"));
         const dc_weight* out_w = c.tie_embeddings ? m->tok_embd : m->output;
         dc_gemv_seg lm = {out_w->dev, out_w->type, c.vocab, (int)out_w->row_bytes, b.logits, c.vocab};
         L(DC_K_LM_HEAD, (double)out_w->bytes + (double)rows * (H / 256) * 292 + (double)rows * c.vocab * 4, 1,
@@ -297,7 +301,7 @@ static int enqueue_forward(dc_model* m, int T, int lm_mode, bool feedback) {
 // Captured once per (T, lm_mode, feedback); replayed afterwards.
 static int run_forward(dc_model* m, int T, int lm_mode, bool feedback) {
     dc_ctx* ctx = m->ctx;
-    if (!m->use_graphs) return enqueue_forward(m, T, lm_mode, feedback);
+    if (!m->use_graphs || m->dbg_x) return enqueue_forward(m, T, lm_mode, feedback);
     const int key = T * 8 + lm_mode * 2 + (feedback ? 1 : 0);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
@@ -453,6 +457,7 @@ void dc_b200_model_destroy(dc_model* m) {
                     b.route_mem, b.cos_sin, b.verify_mem};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+    if (m->dbg_x) cudaFree(m->dbg_x);
     if (m->mega_layers) cudaFree(m->mega_layers);
     if (m->mega_counter) cudaFree(m->mega_counter);
     dc_mega_release_xch(m);
@@ -670,6 +675,9 @@ int dc_b200_decode_run(dc_model* m, const int32_t* seqs, int n_seq, const int32_
     int32_t pos[DC_MAX_T];
     for (int i = 0; i < n_seq; ++i) {
         DC_TRY(check_seq(m, seqs[i]));
+        for (int j = 0; j < i; ++j)
+            if (seqs[j] == seqs[i]) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "decode_run: sequence %d appears twice", seqs[i]);
+        if (first_tokens_host[i] < 0 || first_tokens_host[i] >= m->cfg.vocab) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "decode_run: token id out of range");
         dc_kv_seq& s = m->kv.seqs[seqs[i]];
         if (s.len + n_steps > m->cfg.max_ctx) return dc_fail(ctx, DC_B200_OUT_OF_MEMORY, "decode_run: sequence %d would exceed max_ctx", seqs[i]);
         DC_TRY(dc_kv_seq_reserve(&m->kv, seqs[i], s.len + n_steps));
@@ -756,12 +764,82 @@ int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
         m->use_mega = value < 0 ? 0 : value > 2 ? 2 : value;
         return DC_B200_OK;
     }
+    if (!strcmp(name, "route_mode")) {
+        if (value != DC_ROUTE_STABLE && value != DC_ROUTE_SOFTMAX) return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "route_mode must be 0 or 1");
+        if (value != m->route_mode) {   // captured step graphs hold the old launch parameters
+            cudaStreamSynchronize(m->ctx->stream);
+            for (auto& kvp : m->graphs) cudaGraphExecDestroy(kvp.second.exec);
+            m->graphs.clear();
+        }
+        m->route_mode = value;
+        return DC_B200_OK;
+    }
+    if (!strcmp(name, "capture_layer_inputs")) {
+        cudaSetDevice(m->ctx->device);
+        cudaStreamSynchronize(m->ctx->stream);
+        if (value && !m->dbg_x) {
+            const size_t n = (size_t)(m->cfg.n_layer + 1) * DC_MAX_T * m->cfg.hidden;
+            cudaError_t e = cudaMalloc((void**)&m->dbg_x, n * sizeof(float));
+            if (e == cudaSuccess) e = cudaMemset(m->dbg_x, 0, n * sizeof(float));
+            if (e != cudaSuccess) {
+                m->dbg_x = nullptr;
+                return dc_check_cuda(m->ctx, e, "capture buffer");
+            }
+        } else if (!value && m->dbg_x) {
+            cudaFree(m->dbg_x);
+            m->dbg_x = nullptr;
+        }
+        return DC_B200_OK;
+    }
+    // Test hooks for the bounded waits of the persistent kernel: a limit small enough to run out, so that
+    // the error path (status code, usable context afterwards) can be exercised without any real failure.
+    if (!strcmp(name, "test_barrier_polls")) {
+        m->test_barrier_polls = value < 0 ? 0u : (unsigned)value;
+        return DC_B200_OK;
+    }
+    if (!strcmp(name, "test_ep_wait_us")) {
+        m->test_ep_wait_ns = value < 0 ? 0ull : (unsigned long long)value * 1000ull;
+        return DC_B200_OK;
+    }
     if (!strcmp(name, "phase_timing")) {
         m->mega_timing = value != 0;
         if (m->mega_counter) cudaMemsetAsync((uint8_t*)m->mega_counter + 64, 0, DC_MEGA_TIMING_SLOTS * 8, m->ctx->stream);
         return DC_B200_OK;
     }
     return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "unknown model option '%s'", name);
+}
+
+int dc_b200_model_read_layer_input(dc_model* m, int layer, int n_tokens, float* x_host) {
+    if (!m || !x_host) return DC_B200_INVALID_ARGUMENT;
+    if (!m->dbg_x) return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "read_layer_input: set option capture_layer_inputs first");
+    if (layer < 0 || layer > m->cfg.n_layer || n_tokens < 1 || n_tokens > DC_MAX_T)
+        return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "read_layer_input: layer %d / %d tokens out of range", layer, n_tokens);
+    cudaSetDevice(m->ctx->device);
+    DC_TRY(dc_check_cuda(m->ctx, cudaMemcpyAsync(x_host, m->dbg_x + (size_t)layer * DC_MAX_T * m->cfg.hidden, (size_t)n_tokens * m->cfg.hidden * 4,
+                                                 cudaMemcpyDeviceToHost, m->ctx->stream), "D2H layer input"));
+    return dc_b200_synchronize(m->ctx);
+}
+
+int dc_b200_model_read_kv(dc_model* m, int layer, int seq, int first, int n_tokens, void* k_host, void* v_host) {
+    if (!m || !k_host || !v_host) return DC_B200_INVALID_ARGUMENT;
+    DC_TRY(check_seq(m, seq));
+    const dc_kv_seq& s = m->kv.seqs[seq];
+    if (layer < 0 || layer >= m->cfg.n_layer || first < 0 || n_tokens < 1 || first + n_tokens > (int)s.blocks.size() * DC_KV_BLOCK)
+        return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "read_kv: layer %d, tokens [%d, %d) out of range", layer, first, first + n_tokens);
+    cudaSetDevice(m->ctx->device);
+    const size_t row = (size_t)m->cfg.n_kv_head * 128;   // fp16 elements per token
+    const __half* ka = m->kv.k_arena + m->kv.layer_elems * layer;
+    const __half* va = m->kv.v_arena + m->kv.layer_elems * layer;
+    for (int t = first; t < first + n_tokens;) {
+        const int blk = s.blocks[t / DC_KV_BLOCK], slot = t % DC_KV_BLOCK;
+        int n = DC_KV_BLOCK - slot;
+        if (n > first + n_tokens - t) n = first + n_tokens - t;
+        const size_t src = ((size_t)blk * DC_KV_BLOCK + slot) * row, dst = (size_t)(t - first) * row * 2;
+        DC_TRY(dc_check_cuda(m->ctx, cudaMemcpyAsync((uint8_t*)k_host + dst, ka + src, (size_t)n * row * 2, cudaMemcpyDeviceToHost, m->ctx->stream), "D2H K"));
+        DC_TRY(dc_check_cuda(m->ctx, cudaMemcpyAsync((uint8_t*)v_host + dst, va + src, (size_t)n * row * 2, cudaMemcpyDeviceToHost, m->ctx->stream), "D2H V"));
+        t += n;
+    }
+    return dc_b200_synchronize(m->ctx);
 }
 
 int dc_b200_model_step_stats(dc_model* m, int* kernels_per_step, double* weight_bytes_per_step, double* kv_bytes_per_token_ctx) {

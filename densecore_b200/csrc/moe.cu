@@ -25,6 +25,7 @@ struct RouterParams {
     const float* xn;      // [T][H] f32 (normed hidden state)
     int E, H, T, top_k;
     float scale;          // moe_routed_scaling_factor
+    int mode;             // DC_ROUTE_STABLE (top-k on logits) or DC_ROUTE_SOFTMAX (softmax over all experts first)
     int ep_lo, ep_hi;     // experts owned by this GPU
     float* logits;        // [T][E]
     int32_t* ids;         // [T][top_k]
@@ -47,8 +48,15 @@ __device__ __forceinline__ unsigned long long route_key(float v, int id) {
     return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)id);
 }
 
+// expf rounded as the host library rounds it: the double-precision exponential (1 ulp of double) rounded once
+// to float is the correctly rounded float result except on a 2^-29 sliver of arguments, and so is glibc's expf.
+// The generic router compares probabilities for equality (ties go to the lower expert id), so its
+// exponentials must be the CPU's bit for bit.
+__device__ __forceinline__ float expf_cr(float x) { return (float)exp((double)x); }
+
 __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
     __shared__ int s_last;
+    __shared__ float s_prob[8][MOE_MAX_E];
     __shared__ int32_t s_ids[DC_MAX_T * MOE_MAX_K];
     __shared__ int s_wsum_a[8], s_wsum_c[8];
     pdl_launch_dependents();
@@ -138,6 +146,33 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
             lv[j] = id < p.E ? __ldcg(p.logits + (size_t)t * p.E + id) : 0.0f;
             taken[j] = id >= p.E;
         }
+        if (p.mode == DC_ROUTE_SOFTMAX) {
+            // softmax over all experts: expf(x - max), sum in index order, times 1/sum
+            // (core/include/densecore/simd/simd_ops.h:1171-1195); selection then runs on the probabilities
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < MOE_MAX_E / 32; ++j)
+                if (!taken[j]) mx = fmaxf(mx, lv[j]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+#pragma unroll
+            for (int j = 0; j < MOE_MAX_E / 32; ++j) {
+                if (!taken[j]) {
+                    lv[j] = expf_cr(__fsub_rn(lv[j], mx));
+                    s_prob[warp][j * 32 + lane] = lv[j];
+                }
+            }
+            __syncwarp();
+            float sum = 0.0f;
+            if (lane == 0)
+                for (int e = 0; e < p.E; ++e) sum = __fadd_rn(sum, s_prob[warp][e]);
+            sum = __shfl_sync(0xffffffffu, sum, 0);
+            const float inv = __fdiv_rn(1.0f, sum);
+#pragma unroll
+            for (int j = 0; j < MOE_MAX_E / 32; ++j)
+                if (!taken[j]) lv[j] = __fmul_rn(lv[j], inv);
+            __syncwarp();
+        }
         float sel_l[MOE_MAX_K];
         for (int k = 0; k < p.top_k; ++k) {
             unsigned long long best = 0ull;
@@ -159,7 +194,7 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
 #pragma unroll
             for (int j = 0; j < MOE_MAX_E / 32; ++j)
                 if (j * 32 + lane == wid) taken[j] = true;
-            // the winner's logit back out of its key (NaN stays NaN; -0 was made +0, which exp treats alike):
+            // the winner's value back out of its key (NaN stays NaN; -0 was made +0, which exp treats alike):
             // no load per round
             const uint32_t ku = (uint32_t)(win >> 32);
             const float wl = __uint_as_float((ku & 0x80000000u) ? (ku & 0x7FFFFFFFu) : ~ku);
@@ -169,7 +204,15 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
                 s_ids[t * p.top_k + k] = wid;
             }
         }
-        if (lane == 0) {
+        if (lane == 0 && p.mode == DC_ROUTE_SOFTMAX) {
+            // renormalise over the picks in pick order: w * (1 / sum) (core/src/moe/moe_routing.cpp:90-101),
+            // then the routed scaling factor (core/src/llm/moe/exec.cpp:764-768)
+            float sum = 0.0f;
+            for (int k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, sel_l[k]);
+            const float is = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 1.0f;
+            for (int k = 0; k < p.top_k; ++k)
+                p.weights[t * p.top_k + k] = __fmul_rn(sum > 0.0f ? __fmul_rn(sel_l[k], is) : sel_l[k], p.scale);
+        } else if (lane == 0) {
             // weights over the selected experts only (native.cpp:649-674)
             float mx = -INFINITY;
             bool finite = true;
@@ -274,12 +317,8 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_moe_mm(const MoeMMParams p) {
 
 template <int NT, bool PAIR, int NSTAGE>
 static int launch_moe_mm_ns(dc_ctx* ctx, const MoeMMParams& p, int grid, size_t smem) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_moe_mm<NT, PAIR, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return dc_check_cuda(ctx, e, "cudaFuncSetAttribute(k_moe_mm)");
-        configured = true;
-    }
+    int st = dc_kernel_setup(ctx, (const void*)k_moe_mm<NT, PAIR, NSTAGE>, 200 * 1024, "cudaFuncSetAttribute(k_moe_mm)");
+    if (st != DC_B200_OK) return st;
     return dc_launch(ctx, "k_moe_mm", k_moe_mm<NT, PAIR, NSTAGE>, dim3(grid), dim3(DC_WARPS * 32), smem, p);
 }
 
@@ -297,14 +336,11 @@ template <int NT, bool PAIR>
 static int launch_moe_mm(dc_ctx* ctx, const MoeMMParams& p, size_t act_bytes) {
     // two stages per warp wherever that puts more CTAs on an SM, else the full depth
     const size_t s4 = moe_smem(act_bytes, p.stage_bytes, DC_NSTAGE), s2 = moe_smem(act_bytes, p.stage_bytes, 2);
-    // resident CTAs per SM by shared memory, then by the kernel's registers (asked once per instance)
-    static int reg_limit4 = 0, reg_limit2 = 0;
-    if (!reg_limit4) {
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reg_limit4, k_moe_mm<NT, PAIR, DC_NSTAGE>, DC_WARPS * 32, 0);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reg_limit2, k_moe_mm<NT, PAIR, 2>, DC_WARPS * 32, 0);
-        if (reg_limit4 < 1) reg_limit4 = 1;
-        if (reg_limit2 < 1) reg_limit2 = 1;
-    }
+    // resident CTAs per SM by shared memory, then by the kernel's registers (asked once per device and instance)
+    int reg_limit4 = dc_kernel_occupancy(ctx, (const void*)k_moe_mm<NT, PAIR, DC_NSTAGE>, DC_WARPS * 32, 0);
+    int reg_limit2 = dc_kernel_occupancy(ctx, (const void*)k_moe_mm<NT, PAIR, 2>, DC_WARPS * 32, 0);
+    if (reg_limit4 < 1) reg_limit4 = 1;
+    if (reg_limit2 < 1) reg_limit2 = 1;
     int n4 = s4 <= 200 * 1024 ? moe_ctas_per_sm(s4) : 0, n2 = s2 <= 200 * 1024 ? moe_ctas_per_sm(s2) : 0;
     if (n4 > reg_limit4) n4 = reg_limit4;
     if (n2 > reg_limit2) n2 = reg_limit2;
@@ -367,7 +403,7 @@ int dc_launch_moe_mm(dc_ctx* ctx, bool pair, const dc_weight* w0, const dc_weigh
 }
 
 int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_expert, int T, int top_k, float scale,
-                     int ep_lo, int ep_hi, const dc_moe_route* rt) {
+                     int ep_lo, int ep_hi, const dc_moe_route* rt, int mode) {
     // wr == nullptr: rt->logits already holds the router logits (routing only)
     if (wr && wr->type != DC_TYPE_F32) return dc_fail(ctx, DC_B200_UNSUPPORTED, "router weight must be F32");
     const int E = wr ? (int)wr->N : n_expert;
@@ -381,6 +417,7 @@ int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_ex
     p.T = T;
     p.top_k = top_k;
     p.scale = scale;
+    p.mode = mode;
     p.ep_lo = ep_lo;
     p.ep_hi = ep_hi;
     p.logits = rt->logits;

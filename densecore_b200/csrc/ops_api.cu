@@ -76,16 +76,22 @@ int dc_b200_copy_from_device(dc_ctx* ctx, void* dst_host, const void* src_dev, s
 
 int dc_b200_moe_route(dc_ctx* ctx, const float* logits_host, int T, int n_expert, int top_k, float routed_scale,
                       int32_t* ids_out, float* weights_out) {
-    if (!ctx || !logits_host || !ids_out || !weights_out || T < 1 || T > DC_MAX_T)
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!logits_host || !ids_out || !weights_out || T < 1 || T > DC_MAX_T)
         return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "moe_route: bad argument");
+    // checked before anything is carved, cleared or copied: the scratch is sized from these
+    if (n_expert < 1 || n_expert > 256 || top_k < 1 || top_k > 16 || top_k > n_expert)
+        return dc_fail(ctx, DC_B200_UNSUPPORTED, "moe_route: n_expert=%d top_k=%d out of range (1..256 experts, top_k <= min(16, n_expert))",
+                       n_expert, top_k);
     cudaSetDevice(ctx->device);
-    uint8_t* s = dc_scratch(ctx, 1 << 20);
-    if (!s) return DC_B200_OUT_OF_MEMORY;
     dc_moe_route rt;
+    const size_t need = dc_moe_route_bind(&rt, nullptr, T, n_expert, top_k);
+    uint8_t* s = dc_scratch(ctx, need + 256);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
     dc_moe_route_bind(&rt, s, T, n_expert, top_k);
     DC_TRY(dc_check_cuda(ctx, cudaMemsetAsync(rt.ticket, 0, sizeof(int), ctx->stream), "memset"));
     DC_TRY(h2d(ctx, rt.logits, logits_host, (size_t)T * n_expert * 4));
-    DC_TRY(dc_launch_router(ctx, nullptr, nullptr, n_expert, T, top_k, routed_scale, 0, n_expert, &rt));
+    DC_TRY(dc_launch_router(ctx, nullptr, nullptr, n_expert, T, top_k, routed_scale, 0, n_expert, &rt, ctx->route_mode));
     DC_TRY(d2h(ctx, ids_out, rt.ids, (size_t)T * top_k * 4));
     DC_TRY(d2h(ctx, weights_out, rt.weights, (size_t)T * top_k * 4));
     return dc_b200_synchronize(ctx);
@@ -105,10 +111,14 @@ int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* ga
     if (router->K != H || router->N != E || up->K != H || up->N != F || up->E != E || down->K != F || down->N != H ||
         down->E != E)
         return fail_closed(dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: tensor shapes do not agree"));
+    if (E < 1 || E > 256 || top_k < 1 || top_k > 16 || top_k > E)
+        return fail_closed(dc_fail(ctx, DC_B200_UNSUPPORTED, "mul_mat_id: n_expert=%d top_k=%d out of range (1..256 experts, top_k <= min(16, n_expert))", E, top_k));
+    if (H % 256 || F % 256) return fail_closed(dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: hidden and ffn sizes must be multiples of 256"));
     cudaSetDevice(ctx->device);
     const int A = T * top_k;
+    dc_moe_route rt_size;
     const size_t need = (size_t)T * H * 4 * 3 + (size_t)T * (H / 256) * 292 + (size_t)A * F * 4 +
-                        (size_t)A * (F / 256) * 292 + (size_t)A * H * 4 + (1 << 20);
+                        (size_t)A * (F / 256) * 292 + (size_t)A * H * 4 + dc_moe_route_bind(&rt_size, nullptr, T, E, top_k) + 4096;
     uint8_t* s = dc_scratch(ctx, need);
     if (!s) return fail_closed(DC_B200_OUT_OF_MEMORY);
     Bump b{s};
@@ -122,7 +132,7 @@ int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* ga
     dc_moe_route_bind(&rt, s + b.off, T, E, top_k);
     int st = dc_check_cuda(ctx, cudaMemsetAsync(rt.ticket, 0, sizeof(int), ctx->stream), "memset");
     if (st == DC_B200_OK) st = h2d(ctx, x, x_host, (size_t)T * H * 4);
-    if (st == DC_B200_OK) st = dc_launch_router(ctx, router, x, E, T, top_k, routed_scale, 0, E, &rt);
+    if (st == DC_B200_OK) st = dc_launch_router(ctx, router, x, E, T, top_k, routed_scale, 0, E, &rt, ctx->route_mode);
     if (st == DC_B200_OK) st = dc_launch_quantize_q8k(ctx, x, T, H, xq);
     if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, true, gate, up, xq, T, T, top_k, 0, &rt, h);
     if (st == DC_B200_OK) st = dc_launch_quantize_q8k(ctx, h, A, F, hq);

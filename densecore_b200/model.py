@@ -208,6 +208,20 @@ class Model:
         self._check(_lib.lib().dc_b200_forward_chunk(self.handle, seq, _vp(tokens), tokens.size, _vp(logits)))
         return logits
 
+    def read_layer_input(self, layer: int, n_tokens: int = 1) -> np.ndarray:
+        """Hidden state that entered `layer` in the last step (layer == n_layer: what entered the output norm).
+        Needs set_option("capture_layer_inputs", 1) before the step."""
+        out = np.zeros((n_tokens, self.cfg.hidden), dtype=np.float32)
+        self._check(_lib.lib().dc_b200_model_read_layer_input(self.handle, layer, n_tokens, _vp(out)))
+        return out
+
+    def read_kv(self, layer: int, seq: int, first: int, n_tokens: int):
+        """fp16 K and V rows [n_tokens, n_kv_head, 128] (as uint16) of positions first.. of a sequence."""
+        k = np.zeros((n_tokens, self.cfg.n_kv_head, 128), dtype=np.uint16)
+        v = np.zeros_like(k)
+        self._check(_lib.lib().dc_b200_model_read_kv(self.handle, layer, seq, first, n_tokens, _vp(k), _vp(v)))
+        return k, v
+
     def step_stats(self):
         k = C.c_int(0)
         wb = C.c_double(0.0)

@@ -65,7 +65,12 @@ DC_B200_API void* dc_b200_stream(dc_ctx* ctx);
 /* Waits for the stream and reports any error a kernel recorded (bounded waits
  * that ran out). */
 DC_B200_API int dc_b200_synchronize(dc_ctx* ctx);
-/* 0/1: programmatic dependent launch between consecutive kernels (default 1). */
+/* "pdl" 0/1: programmatic dependent launch between consecutive kernels (default 1).
+ * "route_mode" 0/1: router of the op-level MoE calls (dc_b200_moe_route, dc_b200_mul_mat_id): 0 = top-k on
+ * the logits with the stable comparator, weights over the picks (ComputeQwenNativeMoEStableTopK,
+ * core/src/llm/moe/native.cpp:610-676; default); 1 = softmax over all experts, top-k on the probabilities
+ * with strict '>', weights renormalised (SoftmaxRow / TopKSelect / NormalizeWeights,
+ * core/src/moe/moe_routing.cpp:53-101). */
 DC_B200_API int dc_b200_set_option(dc_ctx* ctx, const char* name, int value);
 
 /* cudaProfilerStart (1) / cudaProfilerStop (0): brackets the region a profiler
@@ -107,8 +112,10 @@ DC_B200_API int dc_b200_mul_mat_dev(dc_ctx* ctx, const dc_weight* w, const float
  * (each GPU that loads the library keeps it until exit).  Limits: M <= 16 and
  * K <= 16384, larger shapes are refused with DC_B200_UNSUPPORTED.  No
  * cudaMalloc/cudaFree or allocating routine is called.  The first call on a
- * GPU looks up the array's device address (cudaGetSymbolAddress); make that
- * call before any stream capture begins.  All calls on a GPU share the array
+ * GPU looks up the array's device address (cudaGetSymbolAddress), and the first
+ * call for each row-count class (1, 2-4, 5-8, 9-16) and weight shape also
+ * configures its kernel instance (shared-memory opt-in, occupancy query) on
+ * that GPU; make one such call before any stream capture begins.  All calls on a GPU share the array
  * and it keeps the previous call's contents (each call overwrites what it
  * reads), so two calls whose kernels can overlap on the GPU, e.g. from two
  * contexts or streams, race: serialise them.  Enqueues on the context's stream. */
@@ -138,8 +145,9 @@ DC_B200_API int dc_b200_copy_from_device(dc_ctx* ctx, void* dst_host, const void
 DC_B200_API int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
                                    const dc_weight* down, const float* x_host, int T, int top_k, float routed_scale,
                                    float* y_host, int32_t* ids_out, float* weights_out);
-/* Routing alone from given logits [T, n_expert] (RouteMoESoftmaxTopK,
- * core/src/llm/moe/exec.cpp:734; stable comparator of core/src/llm/moe/native.cpp:610-676). */
+/* Routing alone from given logits [T, n_expert] (RouteMoESoftmaxTopK, core/src/llm/moe/exec.cpp:734);
+ * which of the reference's two routers runs is the context option "route_mode".  1 <= n_expert <= 256,
+ * 1 <= top_k <= min(16, n_expert), else DC_B200_UNSUPPORTED with nothing launched. */
 DC_B200_API int dc_b200_moe_route(dc_ctx* ctx, const float* logits_host, int T, int n_expert, int top_k,
                                   float routed_scale, int32_t* ids_out, float* weights_out);
 
@@ -300,7 +308,21 @@ DC_B200_API int dc_b200_model_step_stats(dc_model* m, int* kernels_per_step, dou
 DC_B200_API int dc_b200_model_profile_step(dc_model* m, const int32_t* seqs, int n_seq, const int32_t* tokens_host,
                                            int n_classes, float* ms_out, int* launches_out, double* bytes_out);
 DC_B200_API const char* dc_b200_kernel_class_name(int cls);
+/* Parity aids.  With model option "capture_layer_inputs" = 1 every step also stores the hidden state that
+ * enters each layer (after the previous layer's MoE/FFN output and residual were added) and the one that
+ * enters the output norm; read_layer_input copies layer `layer`'s (layer == n_layer: the output norm's) rows
+ * of the last step, [n_tokens, hidden] f32.  read_kv copies the fp16 K and V rows [n_tokens, n_kv_head,
+ * head_dim] of positions first .. first + n_tokens of a sequence in one layer.  With these a CPU checker
+ * can redo any single layer from exactly the inputs the GPU had. */
+DC_B200_API int dc_b200_model_read_layer_input(dc_model* m, int layer, int n_tokens, float* x_host);
+DC_B200_API int dc_b200_model_read_kv(dc_model* m, int layer, int seq, int first, int n_tokens, void* k_host,
+                                      void* v_host);
 /* "graphs" 0/1: replay each step shape as a CUDA graph (default 1).
+ * "route_mode" 0/1: which router the MoE layers use (see dc_b200_set_option; default 0).
+ * "capture_layer_inputs" 0/1: see dc_b200_model_read_layer_input (steps then run without graphs).
+ * "test_barrier_polls" n, "test_ep_wait_us" n: shorten the poll limit of the persistent kernel's grid
+ * barrier / the time limit of its expert-parallel meeting (0 restores the defaults), so that a test can
+ * make a bounded wait run out and check the status that comes back.
  * "persistent" 0/1/2: decode steps of MoE models run in one persistent cooperative kernel with grid
  * barriers between phases: 0 never, 1 for one stream (default: with more streams the per-op kernels are
  * faster), 2 for every stream count it supports (1-4). */

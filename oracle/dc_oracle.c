@@ -1025,6 +1025,28 @@ DCO_API void dco_det_softmax(const float* logits, int n, float temperature, floa
     for (int i = 0; i < n; ++i) p[i] *= inv;
 }
 
+/* The sampler's own temperature softmax, step for step (core/src/sampler/sampler.cpp:235-262):
+ * v = logit * (1/T) with T clamped as ClampTemperature does (:21-26), running maximum of v,
+ * e = exp(v - max) with the C library's expf, sum in index order, then * (1/sum). */
+DCO_API void dco_softmax_temperature(const float* logits, int n, float temperature, float* p) {
+    if (!(temperature > 0.0f)) temperature = 1.0f;
+    if (temperature < 1e-6f) temperature = 1e-6f;
+    const float inv_t = 1.0f / temperature;
+    float mx = -INFINITY;
+    for (int i = 0; i < n; ++i) {
+        const float v = logits[i] * inv_t;
+        if (v > mx) mx = v;
+    }
+    float sum = 0.0f;
+    for (int i = 0; i < n; ++i) {
+        const float v = logits[i] * inv_t;
+        p[i] = expf(v - mx);
+        sum += p[i];
+    }
+    const float inv = 1.0f / sum;
+    for (int i = 0; i < n; ++i) p[i] *= inv;
+}
+
 /* Inverse CDF in index order over non-negative weights w (not normalised).
  * Sums have a fixed shape: a "run" is 32 consecutive elements added in index
  * order starting from 0; a chunk sum adds its 32 run sums in order; the total

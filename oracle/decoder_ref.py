@@ -60,48 +60,56 @@ class RefModel:
         row = np.ascontiguousarray(data.reshape(N, rb)[tok])
         return o.dequantize(ty, row, 1, K)[0]
 
-    def step(self, seq: int, tok: int, want_logits: bool = True):
+    def layer(self, il: int, x: np.ndarray, pos: int, k_arena: np.ndarray, v_arena: np.ndarray, table: np.ndarray,
+              route_mode: str = "stable"):
+        """One decoder layer for one token at position `pos`: x [hidden] -> x_out [hidden].  The token's K/V
+        row is written into (k_arena, v_arena) at `pos` through `table`; earlier rows are whatever the arenas
+        hold.  Also records the router logits and the routing of the layer in self.last_route."""
+        c = self.cfg
+        p = f"blk.{il}."
+        scale = F32(1.0 / np.sqrt(np.float32(c.head_dim)))
+        xn = o.rms_norm(x, self.vec(p + "attn_norm.weight"), c.rms_eps)
+        q = self.mm(p + "attn_q.weight", xn).reshape(c.n_head, 128)
+        k = self.mm(p + "attn_k.weight", xn).reshape(c.n_kv_head, 128)
+        v = self.mm(p + "attn_v.weight", xn).reshape(c.n_kv_head, 128)
+        if c.qk_norm:
+            qw, kw = self.vec(p + "attn_q_norm.weight"), self.vec(p + "attn_k_norm.weight")
+            q = np.stack([o.rms_norm(h, qw, c.rms_eps) for h in q])
+            k = np.stack([o.rms_norm(h, kw, c.rms_eps) for h in k])
+        q = o.rope(q, self.rope[pos])
+        k = o.rope(k, self.rope[pos])
+        o.kv_write(k_arena, v_arena, table, pos, c.n_kv_head, 128, k, v)
+        att = o.paged_attention(q, k_arena, v_arena, table, pos, c.n_head, c.n_kv_head, 128, float(scale),
+                                mode="blockwise")
+        x = (x + self.mm(p + "attn_output.weight", att.reshape(-1))).astype(F32)
+        xn = o.rms_norm(x, self.vec(p + "ffn_norm.weight"), c.rms_eps)
+        if c.n_expert > 0:
+            rl = self.mm(p + "ffn_gate_inp.weight", xn)
+            ids, w = o.route(rl, c.n_expert_used, mode=route_mode, scale=c.routed_scale)
+            self.last_route = (rl, ids, w)
+            gt, _, gd = self.t[p + "ffn_gate_exps.weight"]
+            ut, _, ud = self.t[p + "ffn_up_exps.weight"]
+            dt, _, dd = self.t[p + "ffn_down_exps.weight"]
+            y = o.moe_forward((gt, ut, dt), gd, ud, dd, c.n_expert, c.hidden, c.expert_ffn, xn.reshape(1, -1), ids,
+                              w, fast_exp=True)[0]
+            return (x + y).astype(F32)
+        gate = self.mm(p + "ffn_gate.weight", xn)
+        up = self.mm(p + "ffn_up.weight", xn)
+        h = (silu_fast_np(gate) * up).astype(F32)
+        return (x + self.mm(p + "ffn_down.weight", h)).astype(F32)
+
+    def head(self, x: np.ndarray) -> np.ndarray:
+        """Output norm and lm_head: x [hidden] -> logits [vocab]."""
+        c = self.cfg
+        xn = o.rms_norm(x, self.vec("output_norm.weight"), c.rms_eps)
+        return self.mm("token_embd.weight" if c.tie_embeddings else "output.weight", xn)
+
+    def step(self, seq: int, tok: int, want_logits: bool = True, route_mode: str = "stable"):
         c = self.cfg
         pos = self.lens.get(seq, 0)
         table = self.table(seq)
         x = self.embed(tok)
-        g = c.n_head // c.n_kv_head
-        scale = F32(1.0 / np.sqrt(np.float32(c.head_dim)))
         for il in range(c.n_layer):
-            p = f"blk.{il}."
-            xn = o.rms_norm(x, self.vec(p + "attn_norm.weight"), c.rms_eps)
-            q = self.mm(p + "attn_q.weight", xn).reshape(c.n_head, 128)
-            k = self.mm(p + "attn_k.weight", xn).reshape(c.n_kv_head, 128)
-            v = self.mm(p + "attn_v.weight", xn).reshape(c.n_kv_head, 128)
-            if c.qk_norm:
-                qw, kw = self.vec(p + "attn_q_norm.weight"), self.vec(p + "attn_k_norm.weight")
-                q = np.stack([o.rms_norm(h, qw, c.rms_eps) for h in q])
-                k = np.stack([o.rms_norm(h, kw, c.rms_eps) for h in k])
-            q = o.rope(q, self.rope[pos])
-            k = o.rope(k, self.rope[pos])
-            o.kv_write(self.k[il], self.v[il], table, pos, c.n_kv_head, 128, k, v)
-            att = o.paged_attention(q, self.k[il], self.v[il], table, pos, c.n_head, c.n_kv_head, 128, float(scale),
-                                    mode="blockwise")
-            x = (x + self.mm(p + "attn_output.weight", att.reshape(-1))).astype(F32)
-            xn = o.rms_norm(x, self.vec(p + "ffn_norm.weight"), c.rms_eps)
-            if c.n_expert > 0:
-                rl = self.mm(p + "ffn_gate_inp.weight", xn)
-                ids, w = o.route(rl, c.n_expert_used, mode="stable", scale=c.routed_scale)
-                self.last_route = (rl, ids, w)
-                gt, _, gd = self.t[p + "ffn_gate_exps.weight"]
-                ut, _, ud = self.t[p + "ffn_up_exps.weight"]
-                dt, _, dd = self.t[p + "ffn_down_exps.weight"]
-                y = o.moe_forward((gt, ut, dt), gd, ud, dd, c.n_expert, c.hidden, c.expert_ffn, xn.reshape(1, -1), ids,
-                                  w, fast_exp=True)[0]
-                x = (x + y).astype(F32)
-            else:
-                gate = self.mm(p + "ffn_gate.weight", xn)
-                up = self.mm(p + "ffn_up.weight", xn)
-                h = (silu_fast_np(gate) * up).astype(F32)
-                x = (x + self.mm(p + "ffn_down.weight", h)).astype(F32)
+            x = self.layer(il, x, pos, self.k[il], self.v[il], table, route_mode)
         self.lens[seq] = pos + 1
-        if not want_logits:
-            return None
-        xn = o.rms_norm(x, self.vec("output_norm.weight"), c.rms_eps)
-        name = "token_embd.weight" if c.tie_embeddings else "output.weight"
-        return self.mm(name, xn)
+        return self.head(x) if want_logits else None

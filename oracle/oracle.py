@@ -28,6 +28,65 @@ def build(force: bool = False) -> str:
     return _SO
 
 
+# ---- the reference's own code where it compiles here (oracle/ref_shim.cpp -> oracle/_ref/libdc_ref.so) ----
+_REF_SO = os.path.join(_HERE, "_ref", "libdc_ref.so")
+_ref = None
+
+
+def default_reference_root() -> str:
+    """Where a DenseCore checkout is looked for: $DENSECORE_SRC, else a directory named
+    `reference` beside this repository."""
+    return os.environ.get("DENSECORE_SRC") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
+def build_ref(reference_root: str | None = None, force: bool = False) -> str | None:
+    """Compiles the reference's sampler and Q6_K small-batch kernel from a DenseCore checkout.
+    Returns the library path, or None when no checkout is present (a prebuilt library is then used as is)."""
+    root = reference_root or default_reference_root()
+    if not os.path.isdir(os.path.join(root, "core", "src", "sampler")):
+        return _REF_SO if os.path.exists(_REF_SO) else None
+    args = ["make", "-C", _HERE, "DENSECORE_SRC=" + root, "_ref/libdc_ref.so"]
+    if force:
+        args.insert(3, "-B")
+    subprocess.check_call(args, stdout=subprocess.DEVNULL)
+    return _REF_SO
+
+
+def ref_lib():
+    """ctypes handle of the compiled reference pieces, or None if they were never built."""
+    global _ref
+    if _ref is None and os.path.exists(_REF_SO):
+        _ref = C.CDLL(_REF_SO)
+    return _ref
+
+
+def ref_argmax(v) -> int:
+    v = _f32(v)
+    return int(ref_lib().dcref_argmax(_p(v), v.size))
+
+
+def ref_softmax_temperature(logits, temperature, seed: int = 42):
+    """(probabilities, sampled token) of the reference's SampleTopP with top_p = 1."""
+    logits = _f32(logits)
+    p = np.zeros_like(logits)
+    tok = ref_lib().dcref_softmax_temperature(_p(logits), logits.size, C.c_float(temperature), C.c_uint64(seed), _p(p))
+    return p, int(tok)
+
+
+def ref_q6k_q8k_m4(w_row: np.ndarray, q8_rows: np.ndarray, K: int) -> np.ndarray:
+    """One Q6_K row against four Q8_K rows ([4, K/256*292] bytes) through the reference's AVX2 kernel."""
+    q8 = np.ascontiguousarray(q8_rows, dtype=np.uint8)
+    assert q8.shape[0] == 4
+    # the kernel wants 4-byte aligned activation rows and a 2-byte aligned weight row
+    wbuf = np.zeros(w_row.size + 8, dtype=np.uint8)
+    off = (-wbuf.ctypes.data) % 8
+    wbuf[off:off + w_row.size] = w_row
+    out = np.zeros(4, dtype=np.float32)
+    ok = ref_lib().dcref_q6k_q8k_m4(C.c_void_p(wbuf.ctypes.data + off), _p(q8), C.c_uint64(q8.shape[1]), int(K), _p(out))
+    assert ok, "the reference kernel refused its arguments"
+    return out
+
+
 _lib = None
 
 
@@ -251,6 +310,14 @@ def det_softmax(logits, temperature):
     logits = _f32(logits)
     p = np.zeros_like(logits)
     lib().dco_det_softmax(_p(logits), logits.size, C.c_float(temperature), _p(p))
+    return p
+
+
+def softmax_temperature(logits, temperature):
+    """The sampler's temperature softmax with the C library's expf (sampler.cpp:235-262)."""
+    logits = _f32(logits)
+    p = np.zeros_like(logits)
+    lib().dco_softmax_temperature(_p(logits), logits.size, C.c_float(temperature), _p(p))
     return p
 
 

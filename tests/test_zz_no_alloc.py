@@ -46,6 +46,17 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row(ctx):
         W.free()
 
 
+def test_noalloc_at_the_full_extent_of_its_scratch(ctx):
+    """16 rows of 16384 values fill the built-in array exactly (and make the kernel split the rows in two
+    halves, which do not fit shared memory together)."""
+    rng = np.random.default_rng(79)
+    t, N, K = B.GGML_TYPE_Q4_K, 64, 16384
+    W = ctx.upload_weight(t, B.random_weight(rng, t, N, K), K, N)
+    x = rng.normal(size=(16, K)).astype(np.float32)
+    assert np.array_equal(_run(ctx, W, x, noalloc=True), _run(ctx, W, x, noalloc=False))
+    W.free()
+
+
 def test_noalloc_refuses_shapes_beyond_its_scratch(ctx):
     rng = np.random.default_rng(78)
     W = ctx.upload_weight(B.GGML_TYPE_Q4_K, B.random_q4k(rng, 8, 256), 256, 8)
@@ -53,6 +64,15 @@ def test_noalloc_refuses_shapes_beyond_its_scratch(ctx):
     with pytest.raises(dc.DcError) as e:
         ctx.mul_mat_dev(W, xd, 17, yd, noalloc=True)        # more than 16 rows
     assert e.value.status == -7 and "16 rows" in e.value.message
+    ctx.free(xd)
+    ctx.free(yd)
+    W.free()
+    K = 16640                                               # one super-block more than the array holds
+    W = ctx.upload_weight(B.GGML_TYPE_Q4_K, B.random_q4k(rng, 2, K), K, 2)
+    xd, yd = ctx.alloc(K * 4), ctx.alloc(2 * 4)
+    with pytest.raises(dc.DcError) as e:
+        ctx.mul_mat_dev(W, xd, 1, yd, noalloc=True)
+    assert e.value.status == -7
     ctx.free(xd)
     ctx.free(yd)
     W.free()
