@@ -470,8 +470,22 @@ struct BlockSumDump {
 //     ((a0 + a4) + (a2 + a6)) + ((a1 + a5) + (a3 + a7)).
 // Weights are decoded once per item and reused for every token.  G lanes cooperate on one row and ALL 32
 // lanes of the warp must call (the exchanges are full-warp shuffles); `active` = this lane's row exists.
-// On return every lane of the group holds the row's result for each token.
+// On return lane row_dot_owner(type, s) of the group (among others) holds the row's result for token slot s.
 // tok[s] = row of the activation arrays in shared memory used by token slot s (slots >= nt are skipped).
+// Lane of a row's group that ends up with token t's result (see row_dot_exact).
+__device__ __forceinline__ int row_dot_owner(int type, int t) { return type == DC_TYPE_Q4_K ? (t & 3) : 4 * (t & 1); }
+
+// v[base + sub] for a lane-dependent sub < N (0 beyond the array): register arrays cannot be indexed by a
+// run-time value, so the pick is a chain of selects.
+template <int N, int LEN, typename T>
+__device__ __forceinline__ T pick_slot(const T (&v)[LEN], int base, int sub) {
+    T r = base < LEN ? v[base < LEN ? base : 0] : T(0);
+#pragma unroll
+    for (int j = 1; j < N; ++j)
+        if (base + j < LEN && sub == j) r = v[base + j < LEN ? base + j : 0];
+    return r;
+}
+
 template <int NT>
 __device__ DC_HOT void row_dot_exact(int type, uint32_t row, bool active, int lane, int G, const ActSmem& act, int nt,
                                      const int (&tok)[NT], float (&out)[NT], const BlockSumDump* dump = nullptr,
@@ -479,9 +493,14 @@ __device__ DC_HOT void row_dot_exact(int type, uint32_t row, bool active, int la
     const int nb = act.nb;
     const int lig = lane & (G - 1), gbase = lane & ~(G - 1);
     if (type == DC_TYPE_Q4_K) {
-        float acc[NT];
+        // The four lanes of a block hold the same block sums after the integer exchange; lane `sub` of them
+        // carries the block-order chain of the tokens sub, sub + 4, ...: one pair of shuffles per block then
+        // serves four tokens.
+        constexpr int NG = (NT + 3) / 4;
+        const int sub = lig & 3;
+        float acc[NG];
 #pragma unroll
-        for (int s = 0; s < NT; ++s) acc[s] = 0.0f;
+        for (int g = 0; g < NG; ++g) acc[g] = 0.0f;
         const int n_items = nb * 4, bpp = G >> 2;   // blocks per pass
         for (int i0 = 0; i0 < n_items; i0 += G) {
             const int i = i0 + lig, b = i >> 2, c = i & 3;
@@ -516,27 +535,35 @@ __device__ DC_HOT void row_dot_exact(int type, uint32_t row, bool active, int la
                     }
                 }
             }
+            float xi[NG], xm[NG];
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                xi[g] = pick_slot<4>(tI, 4 * g, sub);
+                xm[g] = pick_slot<4>(tM, 4 * g, sub);
+            }
             // block order: the terms of the pass's blocks are fetched side by side, then added one by one
 #pragma unroll 1
             for (int bb = 0; bb < bpp; ++bb) {
                 if ((i0 >> 2) + bb >= nb) break;
+                const int src = gbase + 4 * bb + sub;
 #pragma unroll
-                for (int s = 0; s < NT; ++s) {
-                    if (s < nt) {
-                        const float a = __shfl_sync(0xffffffffu, tI[s], gbase + 4 * bb);
-                        const float m = __shfl_sync(0xffffffffu, tM[s], gbase + 4 * bb);
-                        acc[s] = __fsub_rn(__fadd_rn(acc[s], a), m);
-                    }
+                for (int g = 0; g < NG; ++g) {
+                    const float a = __shfl_sync(0xffffffffu, xi[g], src);
+                    const float m = __shfl_sync(0xffffffffu, xm[g], src);
+                    acc[g] = __fsub_rn(__fadd_rn(acc[g], a), m);
                 }
             }
         }
 #pragma unroll
-        for (int s = 0; s < NT; ++s) out[s] = acc[s];
+        for (int s = 0; s < NT; ++s) out[s] = acc[s >> 2];   // valid on the lanes with sub == s % 4
     } else {
-        // lane -> (block, half j, eighth tq); the lanes with the same tq carry the chains of partials 2tq, 2tq+1
-        float a0[NT], a1[NT];
+        // lane -> (block, half j, eighth tq).  After the integer exchange both halves hold the block's partials
+        // 2tq and 2tq+1; half j then carries the chains of the tokens j, j + 2, ...
+        constexpr int NG = (NT + 1) / 2;
+        const int jj = (lig >> 2) & 1;
+        float a0[NG], a1[NG];
 #pragma unroll
-        for (int s = 0; s < NT; ++s) a0[s] = a1[s] = 0.0f;
+        for (int g = 0; g < NG; ++g) a0[g] = a1[g] = 0.0f;
         const int n_items = nb * 8, bpp = G >> 3;
         for (int i0 = 0; i0 < n_items; i0 += G) {
             const int i = i0 + lig, b = i >> 3, j = (i >> 2) & 1, tq = i & 3;
@@ -566,37 +593,70 @@ __device__ DC_HOT void row_dot_exact(int type, uint32_t row, bool active, int la
                     }
                 }
             }
+            float xf[NG];
+            int x0[NG], x1[NG];
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                xf[g] = pick_slot<2>(sc, 2 * g, jj);
+                x0[g] = pick_slot<2>(I0, 2 * g, jj);
+                x1[g] = pick_slot<2>(I1, 2 * g, jj);
+            }
 #pragma unroll 1
             for (int bb = 0; bb < bpp; ++bb) {
                 if ((i0 >> 3) + bb >= nb) break;
-                const int src = gbase + 8 * bb + (lig & 3);
+                const int src = gbase + 8 * bb + (lig & 7);
 #pragma unroll
-                for (int s = 0; s < NT; ++s) {
-                    if (s < nt) {
-                        const float f = __shfl_sync(0xffffffffu, sc[s], src);
-                        const int v0 = __shfl_sync(0xffffffffu, I0[s], src);
-                        const int v1 = __shfl_sync(0xffffffffu, I1[s], src);
-                        a0[s] = __fmaf_rn(f, (float)v0, a0[s]);
-                        a1[s] = __fmaf_rn(f, (float)v1, a1[s]);
-                    }
+                for (int g = 0; g < NG; ++g) {
+                    const float f = __shfl_sync(0xffffffffu, xf[g], src);
+                    const int v0 = __shfl_sync(0xffffffffu, x0[g], src);
+                    const int v1 = __shfl_sync(0xffffffffu, x1[g], src);
+                    a0[g] = __fmaf_rn(f, (float)v0, a0[g]);
+                    a1[g] = __fmaf_rn(f, (float)v1, a1[g]);
                 }
             }
         }
+        float r[NG];
 #pragma unroll
-        for (int s = 0; s < NT; ++s) {
-            float r = 0.0f;
-            if (s < nt) {
-                // lanes tq = 0..3 hold (a0,a1), (a2,a3), (a4,a5), (a6,a7)
-                const float x0 = __fadd_rn(a0[s], __shfl_xor_sync(0xffffffffu, a0[s], 2));   // a0+a4 | a2+a6
-                const float x1 = __fadd_rn(a1[s], __shfl_xor_sync(0xffffffffu, a1[s], 2));   // a1+a5 | a3+a7
-                const float y0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 1));         // (a0+a4)+(a2+a6)
-                const float y1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 1));         // (a1+a5)+(a3+a7)
-                r = __fadd_rn(y0, y1);
-            }
-            out[s] = r;
+        for (int g = 0; g < NG; ++g) {
+            // lanes tq = 0..3 (of one half) hold (a0,a1), (a2,a3), (a4,a5), (a6,a7) of their token
+            const float x0s = __fadd_rn(a0[g], __shfl_xor_sync(0xffffffffu, a0[g], 2));   // a0+a4 | a2+a6
+            const float x1s = __fadd_rn(a1[g], __shfl_xor_sync(0xffffffffu, a1[g], 2));   // a1+a5 | a3+a7
+            const float y0 = __fadd_rn(x0s, __shfl_xor_sync(0xffffffffu, x0s, 1));        // (a0+a4)+(a2+a6)
+            const float y1 = __fadd_rn(x1s, __shfl_xor_sync(0xffffffffu, x1s, 1));        // (a1+a5)+(a3+a7)
+            r[g] = __fadd_rn(y0, y1);
         }
+#pragma unroll
+        for (int s = 0; s < NT; ++s) out[s] = r[s >> 1];   // valid on the lanes of half s % 2
     }
 }
+// The single-token row dot as an out-of-line leaf with scalar arguments (everything travels in registers):
+// (qs_t, d_t, bs_t) are the shared-memory addresses of the token's codes, block scales and block sums.
+// Inside the persistent kernel the inlined form costs the surrounding phases their registers (the kernel and
+// its out-of-line phase functions share one register file along each call chain, and spill what does not
+// fit: measured 24 % of the step time), and a call per row of the 32-register leaf costs 3 %.
+template <int TYPE>
+__device__ __noinline__ float row_dot_exact1(uint32_t row, int active, int lane, int G, uint32_t qs_t, uint32_t d_t,
+                                             uint32_t bs_t, int nb) {
+    ActSmem a;
+    a.qs = qs_t;
+    a.d = d_t;
+    a.bs = bs_t;
+    a.nb = nb;
+    a.K = nb * DC_QK_K;
+    a.rs = 0;
+    const int tok[1] = {0};
+    float out[1];
+    row_dot_exact<1>(TYPE, row, active != 0, lane, G, a, 1, tok, out);
+    return out[0];
+}
+// Token row t of an activation layout, by either decoder.
+__device__ __forceinline__ float row_dot_exact1_typed(int type, uint32_t row, bool active, int lane, int G,
+                                                      const ActSmem& act, int t) {
+    const uint32_t qs_t = act.qs + t * act.rs, d_t = act.d + t * act.nb * 4, bs_t = act.bs + t * act.nb * 32;
+    return type == DC_TYPE_Q4_K ? row_dot_exact1<DC_TYPE_Q4_K>(row, active, lane, G, qs_t, d_t, bs_t, act.nb)
+                                : row_dot_exact1<DC_TYPE_Q6_K>(row, active, lane, G, qs_t, d_t, bs_t, act.nb);
+}
+
 // Generic-width lane-group sum (G a power of two <= 32, runtime value).
 __device__ __forceinline__ float group_sum_rt(float v, int G) {
     for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

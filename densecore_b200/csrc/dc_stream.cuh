@@ -115,7 +115,8 @@ struct GemvStream {
     }
     // SWIGLU = false leaves the paired gate/up path out of the generated code (callers that
     // never stream pairs).
-    template <int NT, bool SWIGLU = true>
+    // DUMP = true also stores the exact block sums (parity checks; never in the decoder's launches).
+    template <int NT, bool SWIGLU = true, bool DUMP = false>
     __device__ DC_HOT void consume(const GemvParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
         int tok[NT];
 #pragma unroll
@@ -133,23 +134,29 @@ struct GemvStream {
             const uint32_t skew = (uint32_t)(((uintptr_t)s.w + (size_t)lr * s.row_bytes) & 15);
             const uint32_t skew_up =
                 (SWIGLU && p.epi == DC_EPI_SWIGLU) ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
-            const BlockSumDump* dump = p.dump.I ? &p.dump : nullptr;
+            const BlockSumDump* dump = DUMP ? &p.dump : nullptr;
             for (int r = 0; r < n; r += rows_per_pass) {
                 const int rr = r + grp;
                 const bool active = rr < n;
                 float acc[NT], acc2[NT];
                 // every lane takes part in the row dots (full-warp exchanges inside); all lanes of a row's
-                // group end up with the row's result, and lane (t mod G) of the group stores token t
-                row_dot_exact<NT>(s.type, buf + skew + rr * s.row_bytes, active, lane, G, act, p.T, tok, acc, dump, lr + rr);
-                if ((SWIGLU && p.epi == DC_EPI_SWIGLU))
-                    row_dot_exact<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, active, lane, G, act, p.T, tok,
-                                      acc2);
+                // group run together; the lane that owns token t's result stores it
+                if (NT == 1 && !DUMP) {
+                    acc[0] = row_dot_exact1_typed(s.type, buf + skew + rr * s.row_bytes, active, lane, G, act, 0);
+                    if ((SWIGLU && p.epi == DC_EPI_SWIGLU))
+                        acc2[0] = row_dot_exact1_typed(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, active, lane, G, act, 0);
+                } else {
+                    row_dot_exact<NT>(s.type, buf + skew + rr * s.row_bytes, active, lane, G, act, p.T, tok, acc, dump, lr + rr);
+                    if ((SWIGLU && p.epi == DC_EPI_SWIGLU))
+                        row_dot_exact<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, active, lane, G, act, p.T, tok,
+                                          acc2);
+                }
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
                     if (t < p.T) {
                         float v = acc[t];
                         if ((SWIGLU && p.epi == DC_EPI_SWIGLU)) v = __fmul_rn(silu_fast(v), acc2[t]);
-                        if (active && lig == (t & (G - 1))) {
+                        if (active && lig == row_dot_owner(s.type, t)) {
                             const int row = lr + rr;
                             float* o = s.out + (size_t)t * s.ldo + row;
                             if (p.epi == DC_EPI_ACC) *o = __ldcg(o) + v;  // L2 read: another SM may have written it
@@ -293,14 +300,15 @@ struct MoeStream {
 #pragma unroll 1
             for (int half = 0; half < nhalf; ++half) {
                 float acc[NTT];
-                row_dot_exact<NTT>(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, active, lane, G, act, nt, tok, acc);
+                if (NTT == 1) acc[0] = row_dot_exact1_typed(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, active, lane, G, act, tok[0]);
+                else row_dot_exact<NTT>(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, active, lane, G, act, nt, tok, acc);
 #pragma unroll
                 for (int s = 0; s < NTT; ++s)
                     if (s < nt) v[s] = half ? __fmul_rn(silu_fast(v[s]), acc[s]) : acc[s];
             }
 #pragma unroll
             for (int s = 0; s < NTT; ++s)
-                if (s < nt && active && lig == (s & (G - 1))) {
+                if (s < nt && active && lig == row_dot_owner(p.type, s)) {
                     const size_t oi = (size_t)asg[s] * p.N + r + rr;
                     p.out[oi] = v[s];
                     for (int q = 0; q < p.n_peer; ++q) p.peer_out[q][oi] = v[s];

@@ -36,7 +36,7 @@ int dc_launch_quantize_q8k(dc_ctx* ctx, const float* x, int rows, int K, uint8_t
 // ------------------------------------------------------------------- GEMV
 // NSTAGE: pipeline depth per warp (2 where that lets more CTAs share an SM: the row decode is bound by
 // instruction issue, so resident warps matter more than bytes in flight per warp).
-template <int NT, int NSTAGE>
+template <int NT, int NSTAGE, bool DUMP = false>
 __global__ void __launch_bounds__(DC_WARPS * 32) k_gemv(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(DC_WARPS * 32) k_gemv(const GemvParams p) {
     act.bind(act_base, p.T, p.K);
     act.fill(p.act_q8, p.T);
     __syncthreads();
-    st.template consume<NT>(p, pipe, act, lane);
+    st.template consume<NT, true, DUMP>(p, pipe, act, lane);
 }
 
 static int rows_per_stage(int type, int K, int row_bytes) {
@@ -69,9 +69,9 @@ static int rows_per_stage(int type, int K, int row_bytes) {
     return r < per_pass ? per_pass : r;
 }
 
-template <int NT, int NSTAGE>
+template <int NT, int NSTAGE, bool DUMP = false>
 static int launch_gemv_ns(dc_ctx* ctx, const GemvParams& p, int grid, size_t smem) {
-    int st = dc_kernel_setup(ctx, (const void*)k_gemv<NT, NSTAGE>, 200 * 1024, "cudaFuncSetAttribute(k_gemv)");
+    int st = dc_kernel_setup(ctx, (const void*)k_gemv<NT, NSTAGE, DUMP>, 200 * 1024, "cudaFuncSetAttribute(k_gemv)");
     if (st != DC_B200_OK) return st;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -83,7 +83,7 @@ static int launch_gemv_ns(dc_ctx* ctx, const GemvParams& p, int grid, size_t sme
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-    return dc_check_cuda(ctx, cudaLaunchKernelEx(&cfg, k_gemv<NT, NSTAGE>, p), "k_gemv");
+    return dc_check_cuda(ctx, cudaLaunchKernelEx(&cfg, k_gemv<NT, NSTAGE, DUMP>, p), "k_gemv");
 }
 
 static size_t gemv_smem(size_t act_bytes, uint32_t stage, int ns) {
@@ -109,6 +109,11 @@ static int launch_gemv_nt(dc_ctx* ctx, const GemvParams& p, size_t act_bytes, in
     int n4 = gemv_ctas_per_sm(s4), n2 = gemv_ctas_per_sm(s2);
     if (n4 > reg_limit4) n4 = reg_limit4;
     if (n2 > reg_limit2) n2 = reg_limit2;
+    // parity capture of the block sums: the same kernel compiled with the stores in (never in a decoder step)
+    if (p.dump.I) {
+        const int max_useful = (total_rows + DC_WARPS - 1) / DC_WARPS;
+        return launch_gemv_ns<NT, DC_NSTAGE, true>(ctx, p, ctx->num_sms < max_useful ? ctx->num_sms : max_useful, s4);
+    }
     const bool two = n2 > n4;
     int grid = ctx->num_sms * (two ? n2 : n4);
     const int max_useful = (total_rows + DC_WARPS - 1) / DC_WARPS;

@@ -218,8 +218,7 @@ static constexpr uint32_t MG_DYN_LIMIT =
 // NPI (token, block) pairs per warp: T * H/256 <= 16 * NPI.
 template <int NPI>
 __device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, int src, const float* x_in, float* x_out,
-                                          const float* w, const ActSmem& act, float* xn, const float* dn,
-                                          float* dbg = nullptr) {
+                                          const float* w, const ActSmem& act, float* xn, const float* dn) {
     const int H = p.H, nb = H / DC_QK_K, pairs = p.T * nb;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float v[NPI][8];
@@ -276,17 +275,10 @@ __device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, i
                 for (int i = 0; i < 8; ++i) v[pi][i] = __fadd_rn(v[pi][i], sum[i]);
             }
         }
-        if (src != 2 && (pr % (int)gridDim.x) == (int)blockIdx.x) {
-            if (x_out) {
-                float* o = x_out + (size_t)t * H + dd;
-                *reinterpret_cast<float4*>(o) = make_float4(v[pi][0], v[pi][1], v[pi][2], v[pi][3]);
-                *reinterpret_cast<float4*>(o + 4) = make_float4(v[pi][4], v[pi][5], v[pi][6], v[pi][7]);
-            }
-            if (dbg) {
-                float* o = dbg + (size_t)t * H + dd;
-                *reinterpret_cast<float4*>(o) = make_float4(v[pi][0], v[pi][1], v[pi][2], v[pi][3]);
-                *reinterpret_cast<float4*>(o + 4) = make_float4(v[pi][4], v[pi][5], v[pi][6], v[pi][7]);
-            }
+        if (x_out && src != 2 && (pr % (int)gridDim.x) == (int)blockIdx.x) {
+            float* o = x_out + (size_t)t * H + dd;
+            *reinterpret_cast<float4*>(o) = make_float4(v[pi][0], v[pi][1], v[pi][2], v[pi][3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(v[pi][4], v[pi][5], v[pi][6], v[pi][7]);
         }
         double ss = 0.0;
 #pragma unroll
@@ -318,6 +310,20 @@ __device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, i
         quantize_block_q8k_to_act(y, act, t, b, lane);
     }
     __syncthreads();
+}
+
+// Parity capture: the CTAs that own a (token, 256-value block) of the hidden state copy the rows they have
+// just written to x into capture slot `slot`.  Out of line: it only runs when a test asked for it.
+__device__ __noinline__ void mg_capture_x(const MegaParams& p, const float* x, int slot) {
+    const int nb = p.H / DC_QK_K, pairs = p.T * nb;
+    float* dst = p.dbg_x + (size_t)slot * DC_MAX_T * p.H;
+    for (int pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
+        const int t = pr / nb, b = pr - t * nb;
+        if (threadIdx.x < 64) {
+            const size_t o = (size_t)t * p.H + b * DC_QK_K + 4 * threadIdx.x;
+            *reinterpret_cast<float4*>(dst + o) = __ldcg(reinterpret_cast<const float4*>(x + o));
+        }
+    }
 }
 
 // ------------------------------------------------------------ attention
@@ -828,6 +834,29 @@ __device__ DC_HOT void router_logits_phase(const MegaParams& p, const MegaLayer&
     }
 }
 
+// Generic router, first half: softmax over all experts (expf(x - max), sum in index order, times 1/sum:
+// core/include/densecore/simd/simd_ops.h:1171-1195); the ranks are then taken on the probabilities.  The
+// exponential is the double-precision one rounded to float, which is what the host's expf returns.  Out of
+// line: the double-precision code would otherwise weigh on the registers of every phase inlined next to it.
+__device__ __noinline__ void mg_softmax_keys(const MegaParams& p, MegaShared& sh) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp >= p.T) return;
+    const int t = warp;
+    float mx = -INFINITY;
+    for (int e = lane; e < p.E; e += 32) mx = fmaxf(mx, __ldcg(p.router_logits + t * p.E + e));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int e = lane; e < p.E; e += 32)
+        sh.prob[t][e] = (float)exp((double)__fsub_rn(__ldcg(p.router_logits + t * p.E + e), mx));
+    __syncwarp();
+    float sum = 0.0f;
+    if (lane == 0)
+        for (int e = 0; e < p.E; ++e) sum = __fadd_rn(sum, sh.prob[t][e]);
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    const float inv = __fdiv_rn(1.0f, sum);
+    for (int e = lane; e < p.E; e += 32) sh.rkeys[t][e] = mg_route_key(__fmul_rn(sh.prob[t][e], inv), e);
+}
+
 // Every CTA routes all tokens itself from the logits in global memory: stable top-k
 // on logits, weights over the selected experts (core/src/llm/moe/native.cpp:610-676),
 // then the expert-grouped assignment map (core/src/moe/moe_routing.cpp:534-603).
@@ -836,24 +865,7 @@ __device__ DC_HOT void route_phase(const MegaParams& p, MegaShared& sh) {
     // rank selection: thread (t, e) counts the candidates that precede its own
     // ("larger logit first, then lower id, NaN last"); the k best have ranks 0..k-1
     if (p.route_mode == DC_ROUTE_SOFTMAX) {
-        // softmax over all experts first (expf(x - max), sum in index order, times 1/sum:
-        // core/include/densecore/simd/simd_ops.h:1171-1195); the ranks are then taken on the probabilities
-        if (warp < p.T) {
-            const int t = warp;
-            float mx = -INFINITY;
-            for (int e = lane; e < p.E; e += 32) mx = fmaxf(mx, __ldcg(p.router_logits + t * p.E + e));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            for (int e = lane; e < p.E; e += 32)
-                sh.prob[t][e] = (float)exp((double)__fsub_rn(__ldcg(p.router_logits + t * p.E + e), mx));
-            __syncwarp();
-            float sum = 0.0f;
-            if (lane == 0)
-                for (int e = 0; e < p.E; ++e) sum = __fadd_rn(sum, sh.prob[t][e]);
-            sum = __shfl_sync(0xffffffffu, sum, 0);
-            const float inv = __fdiv_rn(1.0f, sum);
-            for (int e = lane; e < p.E; e += 32) sh.rkeys[t][e] = mg_route_key(__fmul_rn(sh.prob[t][e], inv), e);
-        }
+        mg_softmax_keys(p, sh);
     } else {
         for (int i = threadIdx.x; i < p.T * p.E; i += MG_THREADS) {
             const int t = i / p.E, e = i - t * p.E;
@@ -1185,8 +1197,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             MG_MARK(0);
             ActSmem act;
             act.bind(act_base, p.T, p.H);
-            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, l == 0 ? 0 : 1, xin, xout, L.attn_norm, act, nullptr, dn_r,
-                                           p.dbg_x ? p.dbg_x + (size_t)l * DC_MAX_T * p.H : nullptr);
+            x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, l == 0 ? 0 : 1, xin, xout, L.attn_norm, act, nullptr, dn_r);
+            if (p.dbg_x) mg_capture_x(p, xout, l);
             MG_MARK(2);
             mg_gemv_consume<NT>(gq, pipe, act, gw, nw, lane);
             MG_MARK(3);
@@ -1284,8 +1296,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
         // ---- final: last MoE output + residual, output norm, lm_head with arg-max keys
         ActSmem act;
         act.bind(act_base, p.T, p.H);
-        x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 1, (p.n_layer & 1) ? p.xb : p.xa, nullptr, p.out_norm, act, nullptr, dn_r,
-                                       p.dbg_x ? p.dbg_x + (size_t)p.n_layer * DC_MAX_T * p.H : nullptr);
+        // (parity capture on: the assembled final hidden state goes straight to its capture slot)
+        x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 1, (p.n_layer & 1) ? p.xb : p.xa,
+                                       p.dbg_x ? p.dbg_x + (size_t)p.n_layer * DC_MAX_T * p.H : nullptr, p.out_norm, act,
+                                       nullptr, dn_r);
         mg_gemv_consume<NT>(glm, pipe, act, gw, nw, lane);
         grid_barrier(p, epoch);
         MG_MARK(21);

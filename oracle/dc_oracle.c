@@ -82,6 +82,7 @@ static dco_range_fn g_fn;
 static void* g_ctx;
 static int64_t g_n;
 static int g_nth;
+static unsigned g_start_gen; /* generation counter at the time the current workers were created */
 
 static void run_slice(int ith) {
     const int64_t per = (g_n + g_nth - 1) / g_nth;
@@ -91,7 +92,8 @@ static void run_slice(int ith) {
 }
 static void* worker_main(void* arg) {
     const int ith = (int)(intptr_t)arg;
-    unsigned seen = 0;
+    /* a worker created after earlier generations have passed must not take them for new work */
+    unsigned seen = g_start_gen;
     for (;;) {
         int spins = 0;
         while (atomic_load_explicit(&g_gen, memory_order_acquire) == seen) {
@@ -129,6 +131,7 @@ static void parallel_for(int64_t n, dco_range_fn fn, void* ctx) {
     }
     if (g_started != g_threads) {
         stop_pool();
+        g_start_gen = atomic_load(&g_gen);
         for (int i = 1; i < g_threads; ++i) pthread_create(&g_workers[i], NULL, worker_main, (void*)(intptr_t)i);
         g_started = g_threads;
     }

@@ -520,8 +520,10 @@ def test_decoder_two_streams_are_independent(ctx):
 
 
 def test_persistent_kernel_matches_per_op_kernels(ctx):
-    """The persistent cooperative kernel and the per-op kernels compute the same step: identical picked
-    tokens and bit-identical logits for 1, 2 and 4 streams (short contexts, where both split the KV alike)."""
+    """The persistent cooperative kernel and the per-op kernels compute the same step for 1, 2 and 4 streams.
+    Both use the same matmul bodies and rebuild the CPU kernel's running-maximum chain in attention; partial sums
+    meet in a different order in a few places (router logits, attention merge), so logits agree to float
+    rounding (1e-5 here, at short contexts) rather than bit for bit, and picked tokens agree."""
     cfg = tiny_cfg(True)
     cfg.max_seqs = 4
     m = dc.Model(ctx, cfg)
@@ -540,8 +542,9 @@ def test_persistent_kernel_matches_per_op_kernels(ctx):
             for s in seqs:
                 m.seq_free(s)
         assert res[2][3] == 1 and res[0][3] > 1, "the two runs must have taken different paths"
+        for i in range(T):
+            assert rel(res[2][1][i], res[0][1][i]) < 1e-5, (T, i)
         assert np.array_equal(res[0][0], res[2][0]) and np.array_equal(res[0][2], res[2][2]), T
-        assert np.array_equal(res[0][1], res[2][1]), T
     m.close()
 
 

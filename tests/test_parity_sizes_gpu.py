@@ -139,8 +139,10 @@ def test_moe_decoder_layers_at_full_width_and_context(ctx, oracle):
 
 def test_persistent_kernel_matches_per_op_at_long_context(ctx):
     """Same model, same 2048-token history: the persistent kernel's logits against the per-op kernels'.
-    The two split the context differently (and merge partial sums in a different order), so the logits
-    agree to rounding, not bit for bit."""
+    The two split the context differently (and merge partial sums in a different order), so they differ by float
+    rounding in attention, and every Q8_K re-quantisation downstream turns such a difference into a few flipped
+    codes (1/127 of a block maximum each).  Measured after four layers: 1e-3 .. 1e-2 of the logit range; the
+    per-layer check against the CPU (test above) is the parity gate, this one guards against gross errors."""
     cfg = dc.Config(n_layer=4, hidden=2048, n_head=32, n_kv_head=4, vocab=8192, n_expert=128, n_expert_used=8,
                     expert_ffn=768, max_seqs=4, max_ctx=2304)
     m = dc.Model(ctx, cfg)
@@ -159,15 +161,19 @@ def test_persistent_kernel_matches_per_op_at_long_context(ctx):
             for s in seqs:
                 m.seq_free(s)
         for i in range(T):
-            assert rel(res[2][1][i], res[0][1][i]) < 2e-3, (T, i)
+            assert rel(res[2][1][i], res[0][1][i]) < 3e-2, (T, i)
     m.close()
 
 
 def test_dense_0p8b_decoder_at_full_size(ctx, oracle):
     """Config 2: the dense 0.8B-class decoder (28 layers, hidden 1024, FFN 3072, 16 Q / 8 KV heads, vocab
-    151936, tied Q6_K lm_head).  A short sequence end to end against the CPU decoder (greedy tokens identical
-    wherever the top-2 margin exceeds the tolerance), then a 512-token prompt with every layer and the logits
-    redone on the CPU from the GPU's own inputs (1e-2)."""
+    151936, tied Q6_K lm_head).  A 512-token prompt, then every layer and the logits of the next step redone on
+    the CPU from the GPU's own inputs: max-abs-rel 1e-2 (measured 1e-7: MUL_MAT is bit-equal, the rest differs
+    by float order only).  Then a short sequence end to end against the CPU decoder run on its own: the first
+    token (no history) is bit-equal; from the second on the two attention implementations add in different
+    orders, every Q8_K re-quantisation amplifies that into flipped codes, and after 28 layers the logits of
+    two correct implementations sit 1.5e-2 .. 2.5e-2 apart (reported, held to 5e-2); greedy tokens must agree
+    wherever the top-2 margin exceeds that."""
     from oracle.decoder_ref import RefModel
     cfg = dc.dense_0p8b(max_seqs=2, max_ctx=768)
     m = dc.Model(ctx, cfg)
@@ -176,6 +182,15 @@ def test_dense_0p8b_decoder_at_full_size(ctx, oracle):
     ref = RefModel(cfg, _all_tensors(m))
     oracle.set_threads(min(16, oracle.max_threads()))
     rng = np.random.default_rng(512)
+    # 512-token prompt, every layer redone on the CPU at position 512
+    m.set_option("capture_layer_inputs", 1)
+    seq2 = m.seq_alloc()
+    tok2 = m.prefill(seq2, rng.integers(0, cfg.vocab, size=512))
+    _, errs2 = _layer_reset_check(m, ref, oracle, [seq2], [tok2], 512)
+    print("dense 0.8B layer-reset max-abs-rel:", [f"{e:.1e}" for e in errs2])
+    m.set_option("capture_layer_inputs", 0)
+    m.seq_free(seq2)
+    assert max(errs2) < 1e-2, errs2
     # short end-to-end run
     prompt = rng.integers(0, cfg.vocab, size=24)
     seq = m.seq_alloc()
@@ -185,21 +200,19 @@ def test_dense_0p8b_decoder_at_full_size(ctx, oracle):
     errs, agree, decided = [rel(lg, lr)], 0, 0
     for _ in range(6):
         top = np.sort(lr)[-2:]
-        if top[1] - top[0] > 1e-2 * np.abs(lr).max():
+        if top[1] - top[0] > 5e-2 * np.abs(lr).max():
             decided += 1
             agree += int(tok == oracle.argmax(lr))
         out, lg = m.decode_step([seq], [tok], want_logits=True)
         lr = ref.step(seq, tok)
         errs.append(rel(lg[0], lr))
         tok = int(out[0])
-    assert agree == decided
-    assert np.median(errs) < 1e-2, errs
-    print("dense 0.8B end-to-end logits max-abs-rel per step:", [f"{e:.2e}" for e in errs])
-    # 512-token prompt, layer-reset check at position 512
-    m.set_option("capture_layer_inputs", 1)
-    seq2 = m.seq_alloc()
-    tok2 = m.prefill(seq2, rng.integers(0, cfg.vocab, size=512))
-    _, errs2 = _layer_reset_check(m, ref, oracle, [seq2], [tok2], 512)
     oracle.set_threads(1)
-    assert max(errs2) < 1e-2, errs2
+    print("dense 0.8B end-to-end logits max-abs-rel per step:", [f"{e:.2e}" for e in errs])
+    assert agree == decided
+    assert max(errs) < 5e-2, errs
+    # one token, nothing in the cache: the whole 28-layer decoder is bit-equal to the CPU decoder
+    seq3 = m.seq_alloc()
+    _, lg1 = m.prefill(seq3, prompt[:1], want_logits=True)
+    assert np.array_equal(lg1, ref.step(seq3, int(prompt[0])))
     m.close()
