@@ -205,6 +205,79 @@ def reference_arm(args):
     return 0
 
 
+# ------------------------------------------------------- single-op timing
+def _stream_of(ctx):
+    import torch
+    import densecore_b200 as dc
+    return torch.cuda.ExternalStream(dc._lib.lib().dc_b200_stream(ctx.handle))
+
+
+def _time_graph(ctx, enqueue, reps: int, warm: int = 3):
+    """Device time of `enqueue()` (library calls on the context's stream), captured once as a CUDA graph and
+    replayed `reps` times back to back: microseconds per replay from CUDA events on that stream."""
+    import torch
+    st = _stream_of(ctx)
+    enqueue()                                   # eager: kernel attributes, scratch growth
+    ctx.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=st):
+        enqueue()
+    for _ in range(warm):
+        g.replay()
+    ctx.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(st):
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def op_gemv(ctx, ggml_type: int, N: int, K: int, M: int, ring: int, reps: int, peak_gbs: float) -> dict:
+    """MUL_MAT of one [N x K] K-quant matrix with M activation rows, over a ring of distinct weight copies
+    (larger than L2 together) so that every launch reads its weights from HBM.  One op = Q8_K quantiser +
+    GEMV kernel, as dc_b200_mul_mat_dev enqueues them."""
+    from densecore_b200 import blocks as B
+    rng = np.random.default_rng(1234)
+    ws = [ctx.upload_weight(ggml_type, B.random_weight(rng, ggml_type, N, K), K, N) for _ in range(ring)]
+    x = rng.normal(size=(M, K)).astype(np.float32)
+    xd, yd = ctx.alloc(x.nbytes), ctx.alloc(M * N * 4)
+    ctx.to_device(xd, x)
+
+    def enqueue():
+        for w in ws:
+            ctx.mul_mat_dev(w, xd, M, yd)
+    us = _time_graph(ctx, enqueue, reps) / ring
+    nbytes = B.row_bytes(ggml_type, K) * N + M * K * 4 + M * N * 4
+    for w in ws:
+        w.free()
+    ctx.free(xd)
+    ctx.free(yd)
+    return {"us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak_gbs,
+            "floor_us": nbytes / peak_gbs / 1e3, "ring_copies": ring, "M": M}
+
+
+def run_single_op(args) -> int:
+    """--op: one operator alone (for profiling runs and for the per-config figures of the main line)."""
+    import densecore_b200 as dc
+    from densecore_b200 import blocks as B
+    ctx = dc.Context(0)
+    peak, _ = measured_peaks()
+    if args.op == "gemv-config1":
+        out = op_gemv(ctx, B.GGML_TYPE_Q4_K, 6144, 2048, 1, 64, args.steps, peak)
+    elif args.op == "gemv-q4-big":
+        out = op_gemv(ctx, B.GGML_TYPE_Q4_K, 65536, 2048, 1, 4, args.steps, peak)
+    elif args.op == "gemv-lm-head":
+        out = op_gemv(ctx, B.GGML_TYPE_Q6_K, 151936, 2048, 1, 2, args.steps, peak)
+    else:
+        raise SystemExit(f"unknown --op {args.op}")
+    print(json.dumps({"op": args.op, **out}))
+    ctx.close()
+    return 0
+
+
 # -------------------------------------------------------------- our arm
 def main():
     ap = argparse.ArgumentParser()
@@ -231,9 +304,13 @@ def main():
     ap.add_argument("--streams", default="1,4", help="stream counts to time (the JSON line needs 1)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed 1-stream decode run with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--op", default=None, choices=["gemv-config1", "gemv-lm-head", "gemv-q4-big"],
+                    help="time one operator alone and print its own JSON line (not the benchmark line)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.op:
+        return run_single_op(args)
     if args.impl == "reference":
         return reference_arm(args)
 

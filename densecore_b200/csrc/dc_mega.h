@@ -12,8 +12,11 @@
 #define MG_MAX_K 16
 #define MG_MAX_RANKS 8
 #define MG_XCH_FLAG_BYTES 256   // flag array at the head of an exchange buffer
-// barrier counter (64 bytes) + 32 phase accumulators + a per-CTA barrier trace (14 x 160)
-#define DC_MEGA_TIMING_SLOTS (32 + 14 * 160)
+// barrier counter (64 bytes) + 32 phase accumulators + a per-CTA barrier trace (14 x 160) + a per-warp trace
+// of MG_WTRACE_POINTS points of the second layer (instrumented builds only; 160 CTAs x 16 warps each)
+#define MG_WTRACE_POINTS 18
+#define MG_WTRACE_BASE (32 + 14 * 160)
+#define DC_MEGA_TIMING_SLOTS (MG_WTRACE_BASE + MG_WTRACE_POINTS * 2560)
 #define DC_MEGA_COUNTER_BYTES (64 + DC_MEGA_TIMING_SLOTS * 8)
 
 struct MegaLayer {

@@ -56,36 +56,45 @@ struct GemvStream {
     // A Q6_K row takes about twice the instructions of a Q4_K row of the same K.
     __device__ __forceinline__ static int row_weight(int type) { return type == DC_TYPE_Q6_K ? 2 : 1; }
     // Flattened row index at weighted position x (segments in order, each row weighing row_weight).
-    __device__ __forceinline__ static int row_at(const GemvParams& p, int nseg, long long x) {
-        long long cum = 0;
+    __device__ __forceinline__ static int row_at(const GemvParams& p, int nseg, unsigned x) {
+        unsigned cum = 0;
         int base = 0;
         for (int s = 0; s < nseg; ++s) {
-            const int w = row_weight(p.seg[s].type);
-            const long long span = (long long)p.seg[s].n_rows * w;
+            const unsigned w = (unsigned)row_weight(p.seg[s].type);
+            const unsigned span = (unsigned)p.seg[s].n_rows * w;
             if (x < cum + span) return base + (int)((x - cum) / w);
             cum += span;
             base += p.seg[s].n_rows;
         }
         return base;
     }
+    // gw * total / nw without 64-bit division where the product fits 32 bits (every shape of a decoder step;
+    // the wide form is kept for safety)
+    __device__ __forceinline__ static unsigned share(unsigned gw, unsigned total, unsigned nw) {
+        if ((unsigned long long)nw * total < 0xFFFFFFFFull) return gw * total / nw;
+        return (unsigned)((unsigned long long)gw * total / nw);
+    }
     // Each warp takes a contiguous range of rows; with segments of different types the ranges are balanced
     // by weight, so that the warps holding the costlier rows are not the last to finish.
-    __device__ __forceinline__ void begin(const GemvParams& p, int gw, int nw) {
+    __device__ __forceinline__ static void range(const GemvParams& p, int gw, int nw, int& r0, int& r1) {
         const int nseg = p.epi == DC_EPI_SWIGLU ? 1 : p.n_seg;
         bool mixed = false;
-        long long total_w = 0;
+        unsigned total_w = 0;
         for (int s = 0; s < nseg; ++s) {
             mixed |= p.seg[s].type != p.seg[0].type;
-            total_w += (long long)p.seg[s].n_rows * row_weight(p.seg[s].type);
+            total_w += (unsigned)p.seg[s].n_rows * (unsigned)row_weight(p.seg[s].type);
         }
-        int r0, r1;
         if (!mixed) {
-            r0 = (int)((long long)gw * p.total_rows / nw);
-            r1 = (int)((long long)(gw + 1) * p.total_rows / nw);
+            r0 = (int)share((unsigned)gw, (unsigned)p.total_rows, (unsigned)nw);
+            r1 = (int)share((unsigned)gw + 1u, (unsigned)p.total_rows, (unsigned)nw);
         } else {
-            r0 = row_at(p, nseg, (long long)gw * total_w / nw);
-            r1 = gw + 1 == nw ? p.total_rows : row_at(p, nseg, (long long)(gw + 1) * total_w / nw);
+            r0 = row_at(p, nseg, share((unsigned)gw, total_w, (unsigned)nw));
+            r1 = gw + 1 == nw ? p.total_rows : row_at(p, nseg, share((unsigned)gw + 1u, total_w, (unsigned)nw));
         }
+    }
+    __device__ __forceinline__ void begin(const GemvParams& p, int gw, int nw) {
+        int r0, r1;
+        range(p, gw, nw, r0, r1);
         prod = StageIter{r0, r1};
         cons = StageIter{r0, r1};
     }
@@ -93,6 +102,13 @@ struct GemvStream {
     // (by prefill in an earlier phase), so that no iterator has to stay live in between.
     __device__ __forceinline__ void resume(const GemvParams& p, int gw, int nw, int inflight) {
         begin(p, gw, nw);
+        int sg, lr, n;
+        for (int i = 0; i < inflight; ++i) prod.next(p, sg, lr, n);
+    }
+    // The same from a row range the caller kept (no partition arithmetic).
+    __device__ __forceinline__ void resume_range(const GemvParams& p, int r0, int r1, int inflight) {
+        prod = StageIter{r0, r1};
+        cons = StageIter{r0, r1};
         int sg, lr, n;
         for (int i = 0; i < inflight; ++i) prod.next(p, sg, lr, n);
     }
@@ -209,14 +225,25 @@ struct MoeMMParams {
     int* err;
 };
 
+// Walks a flattened range of (unit, row) pairs stage by stage; the unit and the row inside it are carried
+// along (one division when the walk starts, none per stage).
 struct MoeIter {
-    int cur, end, N, rpst;
+    int cur, end, N, rpst, cu, cr;
+    __device__ __forceinline__ static MoeIter make(int r0, int r1, int N, int rpst) {
+        const int u = r0 / N;
+        return MoeIter{r0, r1, N, rpst, u, r0 - u * N};
+    }
     __device__ __forceinline__ bool next(int& u, int& r, int& n) {
         if (cur >= end) return false;
-        u = cur / N;
-        r = cur - u * N;
-        n = min(rpst, min(N - r, end - cur));
+        u = cu;
+        r = cr;
+        n = min(rpst, min(N - cr, end - cur));
         cur += n;
+        cr += n;
+        if (cr == N) {
+            cr = 0;
+            ++cu;
+        }
         return true;
     }
 };
@@ -232,36 +259,47 @@ struct MoeStream {
     size_t estride;
     // Flattened row index (unit * N + row) at weighted position x, where a row of a unit with nt
     // tokens weighs 1 + nt (one decode plus one dot per token).
-    __device__ __forceinline__ static int row_at(const MoeMMParams& p, int U, long long x) {
-        long long cum = 0;
+    __device__ __forceinline__ static int row_at(const MoeMMParams& p, int U, unsigned x) {
+        unsigned cum = 0;
         for (int u = 0; u < U; ++u) {
-            const int w = 1 + (p.uoff[u + 1] - p.uoff[u]);
-            const long long span = (long long)p.N * w;
+            const unsigned w = 1u + (unsigned)(p.uoff[u + 1] - p.uoff[u]);
+            const unsigned span = (unsigned)p.N * w;
             if (x < cum + span) return u * p.N + (int)((x - cum) / w);
             cum += span;
         }
         return U * p.N;
     }
+    // (rows x weights of one MoE layer stay far below 2^32 / warps: 32-bit arithmetic throughout)
+    __device__ __forceinline__ static void range(const MoeMMParams& p, int U, int gw, int nw, int& r0, int& r1) {
+        const int A = p.uoff[U];   // assignments in all units
+        if (A == U) {              // one token per expert everywhere: plain even split
+            const unsigned total = (unsigned)(U * p.N);
+            r0 = (int)((unsigned)gw * total / (unsigned)nw);
+            r1 = (int)(((unsigned)gw + 1u) * total / (unsigned)nw);
+        } else {
+            const unsigned total_w = (unsigned)p.N * (unsigned)(U + A);
+            r0 = row_at(p, U, (unsigned)gw * total_w / (unsigned)nw);
+            r1 = gw + 1 == nw ? U * p.N : row_at(p, U, ((unsigned)gw + 1u) * total_w / (unsigned)nw);
+        }
+    }
     // Each warp takes a contiguous range of the active experts' rows; ranges are balanced by weight so
     // that experts serving several tokens do not make their warps the last to finish.
     __device__ __forceinline__ void begin(const MoeMMParams& p, int U, int gw, int nw) {
-        const int A = p.uoff[U];   // assignments in all units
         int r0, r1;
-        if (A == U) {              // one token per expert everywhere: plain even split
-            const int total = U * p.N;
-            r0 = (int)((long long)gw * total / nw);
-            r1 = (int)((long long)(gw + 1) * total / nw);
-        } else {
-            const long long total_w = (long long)p.N * (U + A);
-            r0 = row_at(p, U, (long long)gw * total_w / nw);
-            r1 = gw + 1 == nw ? U * p.N : row_at(p, U, (long long)(gw + 1) * total_w / nw);
-        }
-        prod = MoeIter{r0, r1, p.N, p.rpst};
-        cons = MoeIter{r0, r1, p.N, p.rpst};
+        range(p, U, gw, nw, r0, r1);
+        prod = MoeIter::make(r0, r1, p.N, p.rpst);
+        cons = prod;
         estride = (size_t)p.N * p.row_bytes;
     }
     __device__ __forceinline__ void resume(const MoeMMParams& p, int U, int gw, int nw, int inflight) {
         begin(p, U, gw, nw);
+        int u, r, n;
+        for (int i = 0; i < inflight; ++i) prod.next(u, r, n);
+    }
+    __device__ __forceinline__ void resume_range(const MoeMMParams& p, int r0, int r1, int inflight) {
+        prod = MoeIter::make(r0, r1, p.N, p.rpst);
+        cons = prod;
+        estride = (size_t)p.N * p.row_bytes;
         int u, r, n;
         for (int i = 0; i < inflight; ++i) prod.next(u, r, n);
     }

@@ -40,7 +40,10 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 // All CTAs of the (co-resident) grid meet here.  counter only grows during a
 // launch; the host zeroes it before the launch.
 __device__ __forceinline__ unsigned long long mg_now();
-__device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch, bool sys_scope = false) {
+// Split in two so that work that does not depend on the other CTAs (asking for the next phase's weight rows,
+// prefetches) runs between a CTA's arrival and its release instead of in front of the arrival: issuing those
+// copies takes a warp longer than the barrier's own release latency.
+__device__ __noinline__ void grid_arrive(const MegaParams& p, unsigned& epoch, bool sys_scope = false) {
     __syncthreads();
     ++epoch;
 #ifdef DC_MEGA_SUBMARKS
@@ -52,6 +55,10 @@ __device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch, 
         if (sys_scope) __threadfence_system();   // this CTA's stores to other GPUs are performed first
         else __threadfence();
         atomicAdd(p.bar_counter, 1u);
+    }
+}
+__device__ __noinline__ void grid_wait(const MegaParams& p, unsigned epoch) {
+    if (threadIdx.x == 0) {
         const unsigned target = epoch * gridDim.x;
         unsigned polls = 0;
         while (ld_acquire_u32(p.bar_counter) < target) {
@@ -64,9 +71,13 @@ __device__ __noinline__ void grid_barrier(const MegaParams& p, unsigned& epoch, 
         __threadfence();
     }
 #ifdef DC_MEGA_SUBMARKS
-    if (trace) p.phase_ns[32 + (7 + epoch - 8) * 160 + blockIdx.x] = mg_now();
+    if (threadIdx.x == 0 && p.phase_ns && epoch > 7 && epoch <= 14) p.phase_ns[32 + (7 + epoch - 8) * 160 + blockIdx.x] = mg_now();
 #endif
     __syncthreads();
+}
+__device__ __forceinline__ void grid_barrier(const MegaParams& p, unsigned& epoch, bool sys_scope = false) {
+    grid_arrive(p, epoch, sys_scope);
+    grid_wait(p, epoch);
 }
 
 // Expert-parallel meeting point, once per layer, after a grid barrier with system-scope fences: CTA 0
@@ -196,6 +207,7 @@ struct MegaShared {
     alignas(8) unsigned long long rkeys[MG_MAX_T][MG_MAX_E];   // routing keys (rank selection)
     float sel[MG_MAX_T][MG_MAX_K];         // logits (or probabilities) of the picks, in pick order
     float prob[MG_MAX_T][MG_MAX_E];        // generic router: exponentials of all experts
+    int rng[MG_WARPS][2];                  // row range of each warp's stream between its prefill and its consume
 };
 
 // Dynamic shared memory the kernel may ask for: what the SM offers a CTA (227 KB) less the
@@ -338,7 +350,14 @@ __device__ __forceinline__ unsigned long long mg_now();
         }                                                                     \
     } while (0)
 #define MG_SUB_BEGIN unsigned long long sub_t = mg_now()
+// when every warp of every CTA passes point i of the second layer in the first step of a launch
+#define MG_WTRACE(i)                                                                                       \
+    do {                                                                                                   \
+        if (p.phase_ns && lane == 0 && l == 1 && step == 0)                                                \
+            p.phase_ns[MG_WTRACE_BASE + (i) * 2560 + blockIdx.x * MG_WARPS + warp] = mg_now();             \
+    } while (0)
 #else
+#define MG_WTRACE(i) do {} while (0)
 #define MG_SUB(i) do {} while (0)
 #define MG_SUB_BEGIN do {} while (0)
 #endif
@@ -1099,28 +1118,46 @@ __device__ __forceinline__ MoeMMParams mg_experts(const MegaParams& p, const Meg
 // The streaming matmul bodies are large; each is kept out of line and shared by all of its
 // call sites so that one layer's instruction footprint stays small (the kernel runs the same
 // code once per layer, and an instruction-cache miss costs a round trip to L2).
-__device__ __noinline__ void mg_gemv_prefill(const GemvParams& g, WarpPipe<MG_NSTAGE>& pipe, int gw, int nw, int lane) {
-    GemvStream<MG_NSTAGE> st;
-    st.begin(g, gw, nw);
-    st.prefill(g, pipe, lane);
-}
-template <int NT>
-__device__ __noinline__ void mg_gemv_consume(const GemvParams& g, WarpPipe<MG_NSTAGE>& pipe, const ActSmem& act, int gw,
+// A stream's row range is worked out once, when its first stages are requested, and kept in shared memory
+// until the consuming phase picks it up (the partition arithmetic costs as much as a weight row).
+__device__ __noinline__ void mg_gemv_prefill(const GemvParams& g, WarpPipe<MG_NSTAGE>& pipe, MegaShared& sh, int gw,
                                              int nw, int lane) {
     GemvStream<MG_NSTAGE> st;
-    st.resume(g, gw, nw, (int)(pipe.issued - pipe.consumed));
-    st.template consume<NT, false>(g, pipe, act, lane);
-}
-__device__ __noinline__ void mg_moe_prefill(const MoeMMParams& m, int U, WarpPipe<MG_NSTAGE>& pipe, int gw, int nw, int lane) {
-    MoeStream<MG_NSTAGE, 2> st;
-    st.begin(m, U, gw, nw);
-    st.prefill(m, pipe, lane);
+    int r0, r1;
+    GemvStream<MG_NSTAGE>::range(g, gw, nw, r0, r1);
+    st.resume_range(g, r0, r1, 0);
+    st.prefill(g, pipe, lane);
+    if (lane == 0) {
+        sh.rng[gw % MG_WARPS][0] = r0;
+        sh.rng[gw % MG_WARPS][1] = r1;
+    }
+    __syncwarp();
 }
 template <int NT>
-__device__ __noinline__ void mg_moe_consume(const MoeMMParams& m, int U, WarpPipe<MG_NSTAGE>& pipe, const ActSmem& act,
-                                            int gw, int nw, int lane) {
+__device__ __noinline__ void mg_gemv_consume(const GemvParams& g, WarpPipe<MG_NSTAGE>& pipe, const ActSmem& act,
+                                             const MegaShared& sh, int gw, int lane) {
+    GemvStream<MG_NSTAGE> st;
+    st.resume_range(g, sh.rng[gw % MG_WARPS][0], sh.rng[gw % MG_WARPS][1], (int)(pipe.issued - pipe.consumed));
+    st.template consume<NT, false>(g, pipe, act, lane);
+}
+__device__ __noinline__ void mg_moe_prefill(const MoeMMParams& m, int U, WarpPipe<MG_NSTAGE>& pipe, MegaShared& sh, int gw,
+                                            int nw, int lane) {
     MoeStream<MG_NSTAGE, 2> st;
-    st.resume(m, U, gw, nw, (int)(pipe.issued - pipe.consumed));
+    int r0, r1;
+    MoeStream<MG_NSTAGE, 2>::range(m, U, gw, nw, r0, r1);
+    st.resume_range(m, r0, r1, 0);
+    st.prefill(m, pipe, lane);
+    if (lane == 0) {
+        sh.rng[gw % MG_WARPS][0] = r0;
+        sh.rng[gw % MG_WARPS][1] = r1;
+    }
+    __syncwarp();
+}
+template <int NT>
+__device__ __noinline__ void mg_moe_consume(const MoeMMParams& m, WarpPipe<MG_NSTAGE>& pipe, const ActSmem& act,
+                                            const MegaShared& sh, int gw, int lane) {
+    MoeStream<MG_NSTAGE, 2> st;
+    st.resume_range(m, sh.rng[gw % MG_WARPS][0], sh.rng[gw % MG_WARPS][1], (int)(pipe.issued - pipe.consumed));
     st.template consume<NT>(m, pipe, act, lane);
 }
 
@@ -1186,8 +1223,9 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
         if (tid == 0) sh.g_qkv = mg_qkv(p, sh.layer[0]);
         __syncthreads();
         const GemvParams& gq = sh.g_qkv;
-        mg_gemv_prefill(gq, pipe, gw, nw, lane);
+        mg_gemv_prefill(gq, pipe, sh, gw, nw, lane);
         const GemvParams& glm = sh.g_lm;
+        const GemvParams& go = sh.g_o;
         for (int l = 0; l < p.n_layer; ++l) {
             const MegaLayer& L = sh.layer[l & 1];
             if (l + 1 < p.n_layer) load_layer(p, sh, l + 1, (l + 1) & 1);   // read long before it is used
@@ -1195,48 +1233,61 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             float* xout = (l & 1) ? p.xa : p.xb;
             // ---- P0: hidden state, attn_norm, Q8_K, QKV rows
             MG_MARK(0);
+            MG_WTRACE(0);
             ActSmem act;
             act.bind(act_base, p.T, p.H);
+            // the output projection's parameter block is written now (the barriers inside the norm phase publish
+            // it), so that every warp can ask for its first rows the moment it is done with its QKV rows
+            if (tid == 0) sh.g_o = mg_single(p, L.wo, L.wo_type, L.wo_rb, p.H, p.rpst_o, QD, DC_EPI_ACC, xout, p.H, nullptr);
             x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, l == 0 ? 0 : 1, xin, xout, L.attn_norm, act, nullptr, dn_r);
             if (p.dbg_x) mg_capture_x(p, xout, l);
             MG_MARK(2);
-            mg_gemv_consume<NT>(gq, pipe, act, gw, nw, lane);
+            MG_WTRACE(1);
+            mg_gemv_consume<NT>(gq, pipe, act, sh, gw, lane);
             MG_MARK(3);
-            if (tid == 0) sh.g_o = mg_single(p, L.wo, L.wo_type, L.wo_rb, p.H, p.rpst_o, QD, DC_EPI_ACC, xout, p.H, nullptr);
-            __syncthreads();
-            const GemvParams& go = sh.g_o;
-            mg_gemv_prefill(go, pipe, gw, nw, lane);   // output-projection rows stream in during attention
+            MG_WTRACE(2);
+            grid_arrive(p, epoch);
+            mg_gemv_prefill(go, pipe, sh, gw, nw, lane);   // output-projection rows stream in during attention
             prefetch_vec(L.ffn_norm, (size_t)p.H * 4);
             if ((int)blockIdx.x < p.E) prefetch_vec(L.router + (size_t)blockIdx.x * p.H, (size_t)p.H * 4);
-            grid_barrier(p, epoch);
+            grid_wait(p, epoch);
             MG_MARK(4);
+            MG_WTRACE(3);
             // ---- P1 / P2: attention
             attn_scores_phase(p, L, sh, item, s_sc, vbuf, vcap_blocks);
             MG_MARK(5);
+            MG_WTRACE(4);
             grid_barrier(p, epoch);
             MG_MARK(6);
+            MG_WTRACE(5);
             attn_pv_phase(p, L, sh, item, s_sc, vbuf, vcap_blocks);
             MG_MARK(7);
+            MG_WTRACE(6);
             grid_barrier(p, epoch);
             MG_MARK(8);
+            MG_WTRACE(7);
             // ---- P3: output projection, x += Wo . attn
             act.bind(act_base, p.T, QD);
             act.template fill<true>(p.q8_attn, p.T);
             __syncthreads();
             MG_MARK(9);
-            mg_gemv_consume<NT>(go, pipe, act, gw, nw, lane);
+            mg_gemv_consume<NT>(go, pipe, act, sh, gw, lane);
             MG_MARK(10);
+            MG_WTRACE(8);
             grid_barrier(p, epoch);
             MG_MARK(11);
+            MG_WTRACE(9);
             // ---- P4: ffn_norm, Q8_K, router logits
             act.bind(act_base, p.T, p.H);
             x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 2, xout, nullptr, L.ffn_norm, act, xs, nullptr);
             MG_MARK(12);
             router_logits_phase(p, L, sh, xs);
             MG_MARK(13);
+            MG_WTRACE(10);
             // parameter blocks of the two expert phases: they depend on the layer, not on the routing, so
             // they are built while this CTA would otherwise wait at the barrier
             float* dn_w = ep ? p.xdn[p.ep_rank] + (xe & 1u) * xhalf : p.dn;
+            grid_arrive(p, epoch);
             if (tid == 0) {
                 sh.m_gu = mg_experts(p, sh, L.gate, L.up, L.gate_type, L.gate_rb, p.F, p.H, p.rpst_gate, p.h);
                 sh.m_dn = mg_experts(p, sh, L.down, nullptr, L.down_type, L.down_rb, p.H, p.F, p.rpst_down, dn_w);
@@ -1247,17 +1298,21 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
                     sh.m_dn.n_peer = q;
                 }
             }
-            grid_barrier(p, epoch);
+            grid_wait(p, epoch);
             MG_MARK(14);
+            MG_WTRACE(11);
             // ---- P5: routing, gate/up + SwiGLU
             route_phase(p, sh);   // ends with a CTA barrier: the blocks above are visible too
             MG_MARK(15);
+            MG_WTRACE(12);
             const MoeMMParams& mgu = sh.m_gu;
-            mg_moe_prefill(mgu, sh.n_active, pipe, gw, nw, lane);
-            mg_moe_consume<NT>(mgu, sh.n_active, pipe, act, gw, nw, lane);
+            mg_moe_prefill(mgu, sh.n_active, pipe, sh, gw, nw, lane);
+            mg_moe_consume<NT>(mgu, pipe, act, sh, gw, lane);
             MG_MARK(16);
+            MG_WTRACE(13);
             const MoeMMParams& mdn = sh.m_dn;
-            mg_moe_prefill(mdn, sh.n_active, pipe, gw, nw, lane);  // down rows stream in across the barrier
+            grid_arrive(p, epoch);
+            mg_moe_prefill(mdn, sh.n_active, pipe, sh, gw, nw, lane);  // down rows stream in across the barrier
             if (l + 1 < p.n_layer) {
                 const MegaLayer& Ln = sh.layer[(l + 1) & 1];
                 prefetch_vec(Ln.attn_norm, (size_t)p.H * 4);
@@ -1266,32 +1321,36 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             } else {
                 prefetch_vec(p.out_norm, (size_t)p.H * 4);
             }
-            grid_barrier(p, epoch);
+            grid_wait(p, epoch);
             MG_MARK(17);
+            MG_WTRACE(14);
             // ---- P6: h -> Q8_K, down rows
             ActSmem acth;
             acth.bind(act_base, A, p.F);
+            // the parameter block of the stream that follows the down rows (next layer's QKV, or the lm_head) is
+            // written now: the barrier below publishes it, and no warp has to wait for the others before it asks
+            // for that stream's first rows
+            if (tid == 0) {
+                if (l + 1 < p.n_layer) sh.g_qkv = mg_qkv(p, sh.layer[(l + 1) & 1]);
+                else
+                    sh.g_lm = mg_single(p, p.out_w, p.out_type, p.out_rb, p.vocab, p.rpst_out, p.H, DC_EPI_STORE, p.logits,
+                                        p.vocab, p.argmax_keys);
+            }
             mg_h_quant(p, acth, A);
             __syncthreads();
             MG_MARK(18);
-            mg_moe_consume<NT>(mdn, sh.n_active, pipe, acth, gw, nw, lane);
+            MG_WTRACE(15);
+            mg_moe_consume<NT>(mdn, pipe, acth, sh, gw, lane);
             MG_MARK(19);
-            if (l + 1 < p.n_layer) {
-                if (tid == 0) sh.g_qkv = mg_qkv(p, sh.layer[(l + 1) & 1]);
-                __syncthreads();
-                mg_gemv_prefill(gq, pipe, gw, nw, lane);
-            } else {
-                if (tid == 0)
-                    sh.g_lm = mg_single(p, p.out_w, p.out_type, p.out_rb, p.vocab, p.rpst_out, p.H, DC_EPI_STORE, p.logits,
-                                        p.vocab, p.argmax_keys);
-                __syncthreads();
-                mg_gemv_prefill(glm, pipe, gw, nw, lane);
-            }
-            grid_barrier(p, epoch, ep);
+            MG_WTRACE(16);
+            grid_arrive(p, epoch, ep);
+            mg_gemv_prefill(l + 1 < p.n_layer ? gq : glm, pipe, sh, gw, nw, lane);
+            grid_wait(p, epoch);
             if (ep) ep_exchange(p, xe + 1);
             ++xe;
             dn_r = dn_w;
             MG_MARK(20);
+            MG_WTRACE(17);
         }
         // ---- final: last MoE output + residual, output norm, lm_head with arg-max keys
         ActSmem act;
@@ -1300,7 +1359,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
         x_norm_phase<(NT > 1 ? 2 : 1)>(p, sh, 1, (p.n_layer & 1) ? p.xb : p.xa,
                                        p.dbg_x ? p.dbg_x + (size_t)p.n_layer * DC_MAX_T * p.H : nullptr, p.out_norm, act,
                                        nullptr, dn_r);
-        mg_gemv_consume<NT>(glm, pipe, act, gw, nw, lane);
+        mg_gemv_consume<NT>(glm, pipe, act, sh, gw, lane);
         grid_barrier(p, epoch);
         MG_MARK(21);
         // greedy pick: first maximum wins (core/src/sampler/sampler.cpp:42-57)
@@ -1373,6 +1432,9 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
     p.n_hg = 1;
     while (p.n_hg < 4 && G / (T * c.n_kv_head * p.n_hg) > 20 && (g / (2 * p.n_hg)) % 2 == 0 && g / (2 * p.n_hg) >= 2) p.n_hg *= 2;
     p.nsplit = G / (T * c.n_kv_head * p.n_hg);
+    // at most 16 runs per group: the merging run then fetches all partials in one round of loads, and the merge is
+    // the tail of the phase (measured: the second round costs more than the 12 % longer runs)
+    if (p.nsplit > 16) p.nsplit = 16;
     if (p.nsplit < 1) NO("fewer SMs than (stream, kv head) pairs");
     const int max_blocks = m->kv.max_blocks_per_seq;
     if (p.nsplit > max_blocks) p.nsplit = max_blocks;

@@ -268,3 +268,15 @@ class Model:
         self._check(_lib.lib().dc_b200_model_phase_timing(self.handle, _vp(buf), buf.size))
         tr = buf[32:].reshape(14, 160)[:, :n_cta].astype(np.int64)
         return tr[:7], tr[7:]
+
+    WTRACE_POINTS = ["layer start", "norm+q8 done", "qkv rows done", "barrier", "scores done", "barrier", "pv+merge done",
+                     "barrier", "o-proj rows done", "barrier", "norm+router done", "barrier", "top-k done",
+                     "gate/up rows done", "barrier", "h q8 done", "down rows done", "barrier"]
+
+    def warp_trace(self, n_cta: int = 148):
+        """[18, n_cta, 16] globaltimer nanoseconds: when every warp of every CTA passed each point of the second
+        layer in the first step of the last launch (instrumented build with phase_timing on; zeros otherwise)."""
+        n = 32 + 14 * 160 + 18 * 2560
+        buf = np.zeros(n, dtype=np.uint64)
+        self._check(_lib.lib().dc_b200_model_phase_timing(self.handle, _vp(buf), buf.size))
+        return buf[32 + 14 * 160:].reshape(18, 160, 16)[:, :n_cta].astype(np.int64)
