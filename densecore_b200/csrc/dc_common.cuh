@@ -261,31 +261,30 @@ __device__ __forceinline__ void quantize_block_q8k_warp(const float* __restrict_
 }
 
 // ------------------------------------------------------- activations
-// Q8_K activations of the step's tokens, laid out in shared memory for the
-// dot kernels: qs[T][K] int8 (16-byte aligned rows), d[T][nb] f32,
-// bs[T][nb][16] int16.  Filled from the native 292-byte blocks in global memory.
+// Q8_K activations of the step's tokens in shared memory, laid out for the dot kernels, where one lane
+// works on one whole super-block: per (token, block) 256 int8 codes 272 bytes apart, the f32 scale, and
+// the 16 int16 sums 48 bytes apart.  The lanes of a quarter warp read the same offset of neighbouring
+// blocks with 128-bit loads: 272 bytes = 68 words and 48 bytes = 12 words put those eight accesses on
+// disjoint bank quads.  Filled from the native 292-byte blocks in global memory.
 struct ActSmem {
     uint32_t qs, d, bs;  // shared addresses
     int K, nb;
-    uint32_t rs;         // bytes between the int8 rows of two tokens
-    // The int8 codes are stored in 64-byte chunks 80 bytes apart: the lanes of a warp read
-    // chunks that are multiples of 64 values apart, and a stride of 80 bytes (20 banks) spreads
-    // those reads over all 32 banks instead of piling them onto two.
-    __host__ __device__ __forceinline__ static size_t row_stride(int K) { return (size_t)(K / 64) * 80; }
+    static constexpr uint32_t QS = 272, BS = 48;
     __host__ __device__ __forceinline__ static size_t bytes(int T, int K) {
-        const int nb = K / DC_QK_K;
-        return (size_t)T * row_stride(K) + (size_t)T * nb * 4 + (size_t)T * nb * 32;
+        const size_t n = (size_t)T * (K / DC_QK_K);
+        return n * QS + ((n * 4 + 15) & ~(size_t)15) + n * BS;
     }
     __device__ __forceinline__ void bind(uint8_t* base, int T, int K_) {
         K = K_;
         nb = K_ / DC_QK_K;
-        rs = (uint32_t)row_stride(K_);
+        const uint32_t n = (uint32_t)(T * nb);
         qs = smem_u32(base);
-        d = qs + T * rs;
-        bs = d + T * nb * 4;
+        d = qs + n * QS;
+        bs = d + ((n * 4 + 15) & ~15u);
     }
-    // shared address of code e (0 <= e < K) of token row t
-    __device__ __forceinline__ uint32_t q(int t, int e) const { return qs + t * rs + (e >> 6) * 80 + (e & 63); }
+    __device__ __forceinline__ uint32_t qblk(int t, int b) const { return qs + (uint32_t)(t * nb + b) * QS; }
+    __device__ __forceinline__ uint32_t dptr(int t, int b) const { return d + (uint32_t)(t * nb + b) * 4; }
+    __device__ __forceinline__ uint32_t bsptr(int t, int b) const { return bs + (uint32_t)(t * nb + b) * BS; }
     // Cooperative fill by the whole CTA from native Q8_K rows (row stride nb*292).
     // CG: read through L2 (the rows were written by other SMs during this kernel).
     template <bool CG = false>
@@ -300,9 +299,9 @@ struct ActSmem {
             const int b = w / 73, o = w - b * 73;
             const uint32_t v = CG ? __ldcg(src + i) : src[i];
             uint32_t dst;
-            if (o == 0) dst = d + (t * nb + b) * 4;
-            else if (o <= 64) dst = q(t, b * 256 + (o - 1) * 4);
-            else dst = bs + (t * nb + b) * 32 + (o - 65) * 4;
+            if (o == 0) dst = dptr(t, b);
+            else if (o <= 64) dst = qblk(t, b) + (o - 1) * 4;
+            else dst = bsptr(t, b) + (o - 65) * 4;
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(v));
         }
     }
@@ -314,141 +313,44 @@ __device__ __forceinline__ void quantize_block_q8k_to_act(const float (&v)[8], c
     uint32_t w0, w1, bw;
     float d;
     q8k_block_core(v, lane, w0, w1, bw, d);
-    const uint32_t qa = act.q(t, b * 256 + 8 * lane);
+    const uint32_t qa = act.qblk(t, b) + 8 * lane;
     asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(qa), "r"(w0), "r"(w1));
-    if ((lane & 3) == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(act.bs + (t * act.nb + b) * 32 + (lane >> 2) * 4), "r"(bw));
-    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(act.d + (t * act.nb + b) * 4), "f"(d));
+    if ((lane & 3) == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(act.bsptr(t, b) + (lane >> 2) * 4), "r"(bw));
+    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(act.dptr(t, b)), "f"(d));
 }
 
-// ------------------------------------------------------- Q4_K row dot
-// One "item" = (super-block b, chunk c): 32 bytes of qs = sub-blocks 2c (low
-// nibbles) and 2c+1 (high nibbles) (core/src/kernels/hwy/hwy_moe_quant.cc:202-211).
-// Returns the lane's exact integer partials: I = sc_lo*dot_lo + sc_hi*dot_hi,
-// M = m_lo*(bsums[4c]+bsums[4c+1]) + m_hi*(bsums[4c+2]+bsums[4c+3]).
+// ---------------------------------------------------------------- row dots
+// One lane works on one whole super-block (Q4_K) or one half of one (Q6_K), so a row of K values takes
+// G lanes and a warp runs 32 / G rows side by side: the reductions, the block-order float chain and the
+// loop overhead are paid once per pass of 32 / G rows.  (The earlier form, one 64-value chunk per lane
+// and one row per warp pass, took 418 warp instructions per Q4_K row of 2048 and 700 per Q6_K row,
+// measured, against a budget of about 200 at the HBM roofline.)
+__host__ __device__ inline int pow2_at_least(int n) {
+    int g = 1;
+    while (g < n) g <<= 1;
+    return g;
+}
+// Lanes that cooperate on one row.
+__host__ __device__ inline int lanes_per_row(int type, int K) {
+    const int g = pow2_at_least(K / DC_QK_K) * (type == DC_TYPE_Q6_K ? 2 : 1);
+    return g > 32 ? 32 : g;
+}
 // Four unsigned bytes of a times four signed bytes of b, added to c.
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     int d;
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-struct Q4Item {
-    uint32_t q[8];
-    int sc_lo, sc_hi, m_lo, m_hi;
-    float d, dmin;
-};
-__device__ __forceinline__ void q4k_load_item(uint32_t row, int b, int c, Q4Item& it) {
-    const uint32_t blk = row + b * DC_Q4K_BYTES;
-    const uint4 a = lds128(blk + 16 + 32 * c), e = lds128(blk + 32 + 32 * c);
-    it.q[0] = a.x; it.q[1] = a.y; it.q[2] = a.z; it.q[3] = a.w;
-    it.q[4] = e.x; it.q[5] = e.y; it.q[6] = e.z; it.q[7] = e.w;
-    const uint32_t dd = lds32(blk);
-    it.d = fp16_bits_to_float((uint16_t)(dd & 0xFFFF));
-    it.dmin = fp16_bits_to_float((uint16_t)(dd >> 16));
-    // 6-bit scale/min unpack, scalar form of hwy_moe_quant.cc:90-101
-    // (per sub-block j: j<4: sc=s[j]&63, m=s[j+4]&63; else sc=(s[j+4]&15)|((s[j-4]>>6)<<4),
-    //  m=(s[j+4]>>4)|((s[j]>>6)<<4)), for j = 2c and 2c+1.
-    const uint32_t s = blk + 4;
-    const int j = 2 * c;
-    if (c < 2) {
-        const uint32_t p = lds16(s + j), m = lds16(s + j + 4);
-        it.sc_lo = p & 63; it.sc_hi = (p >> 8) & 63;
-        it.m_lo = m & 63; it.m_hi = (m >> 8) & 63;
-    } else {
-        const uint32_t hi = lds16(s + j + 4), lo = lds16(s + j - 4), mid = lds16(s + j);
-        it.sc_lo = (hi & 15) | (((lo >> 6) & 3) << 4);
-        it.sc_hi = ((hi >> 8) & 15) | (((lo >> 14) & 3) << 4);
-        it.m_lo = ((hi >> 4) & 15) | (((mid >> 6) & 3) << 4);
-        it.m_hi = ((hi >> 12) & 15) | (((mid >> 14) & 3) << 4);
-    }
+// Two int16 of a times bytes (0,1) / (2,3) of b, added to c.
+__device__ __forceinline__ int dp2a_lo(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.lo.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
-__device__ __forceinline__ void q4k_item_ints(const Q4Item& it, uint32_t yq /*shared addr of 64 int8*/,
-                                              uint32_t ybs /*shared addr of 4 int16*/, int& I, int& M) {
-    // high nibbles stay in place (bytes 16*q, taken as unsigned): their dot is 16 times the wanted one,
-    // exactly, so one shift at the end replaces a shift per word
-    int lo = 0, hi16 = 0;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint4 y0 = lds128(yq + 16 * h), y1 = lds128(yq + 32 + 16 * h);
-        const uint32_t* w = &it.q[4 * h];
-        lo = __dp4a((int)(w[0] & 0x0F0F0F0F), (int)y0.x, lo);
-        lo = __dp4a((int)(w[1] & 0x0F0F0F0F), (int)y0.y, lo);
-        lo = __dp4a((int)(w[2] & 0x0F0F0F0F), (int)y0.z, lo);
-        lo = __dp4a((int)(w[3] & 0x0F0F0F0F), (int)y0.w, lo);
-        hi16 = dp4a_u8s8(w[0] & 0xF0F0F0F0u, y1.x, hi16);
-        hi16 = dp4a_u8s8(w[1] & 0xF0F0F0F0u, y1.y, hi16);
-        hi16 = dp4a_u8s8(w[2] & 0xF0F0F0F0u, y1.z, hi16);
-        hi16 = dp4a_u8s8(w[3] & 0xF0F0F0F0u, y1.w, hi16);
-    }
-    const int hi = hi16 >> 4;
-    const uint32_t b01 = lds32(ybs), b23 = lds32(ybs + 4);
-    const int s_lo = (int)(short)(b01 & 0xFFFF) + (int)(short)(b01 >> 16);
-    const int s_hi = (int)(short)(b23 & 0xFFFF) + (int)(short)(b23 >> 16);
-    I = it.sc_lo * lo + it.sc_hi * hi;
-    M = it.m_lo * s_lo + it.m_hi * s_hi;
-}
-
-// ------------------------------------------------------- Q6_K row dot
-// One "item" = (super-block b, half j, eighth t): 8 bytes of ql at 64j+8t, 8 at
-// 64j+32+8t, 8 of qh at 32j+8t -> 4 quadrants x 8 elements
-// (core/src/llm/matmul/q6_small_batch.h:52-74).  Block bytes are only 2-byte
-// aligned in shared memory.
-__device__ __forceinline__ uint32_t q6_signed(uint32_t q) { return ((q | 0x80808080u) - 0x20202020u) ^ 0x80808080u; }
-struct Q6Item {
-    uint32_t q[8];  // signed bytes (q-32), quadrant-major: q[2*quad + w]
-    int sc[4];
-    float d;
-};
-// Eight consecutive bytes from a 2-byte aligned shared address as two 32-bit words: two aligned
-// 64-bit loads and funnel shifts (instead of four 16-bit loads).  Reads up to a + 15.
-__device__ __forceinline__ uint2 lds64_a2(uint32_t a) {
-    const uint32_t a0 = a & ~7u, o = a & 7u;   // o in {0, 2, 4, 6}
-    const uint2 lo = lds64(a0), hi = lds64(a0 + 8);
-    const uint32_t sh = (o & 3u) * 8u;         // 0 or 16 bits
-    const bool up = o >= 4u;
-    const uint32_t w0 = up ? lo.y : lo.x, w1 = up ? hi.x : lo.y, w2 = up ? hi.y : hi.x;
-    return make_uint2(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh));
-}
-__device__ __forceinline__ void q6k_load_item(uint32_t row, int b, int j, int t, Q6Item& it) {
-    const uint32_t blk = row + b * DC_Q6K_BYTES;
-    const uint32_t ql0 = blk + 64 * j + 8 * t, ql1 = ql0 + 32, qh = blk + 128 + 32 * j + 8 * t;
-    // every range read below ends at most 15 bytes after its start, inside the 210-byte block
-    const uint2 A = lds64_a2(ql0), C = lds64_a2(ql1), H = lds64_a2(qh);
-#pragma unroll
-    for (int w = 0; w < 2; ++w) {
-        const uint32_t a = w ? A.y : A.x, c = w ? C.y : C.x, h = w ? H.y : H.x;
-        // per byte: q in 0..63 -> q - 32 as a signed byte.  With bit 7 set no byte borrows from its
-        // neighbour, so one 32-bit subtraction does all four: ((q | 0x80) - 0x20) ^ 0x80.
-        it.q[0 + w] = q6_signed((a & 0x0F0F0F0F) | ((h << 4) & 0x30303030));
-        it.q[2 + w] = q6_signed((c & 0x0F0F0F0F) | ((h << 2) & 0x30303030));
-        it.q[4 + w] = q6_signed(((a >> 4) & 0x0F0F0F0F) | (h & 0x30303030));
-        it.q[6 + w] = q6_signed(((c >> 4) & 0x0F0F0F0F) | ((h >> 2) & 0x30303030));
-    }
-    const uint32_t s = blk + 192 + 8 * j + (t >> 1);
-#pragma unroll
-    for (int qd = 0; qd < 4; ++qd) it.sc[qd] = lds_s8(s + 2 * qd);
-    it.d = fp16_bits_to_float((uint16_t)lds16(blk + 208));
-}
-// yq: shared address of the activation code at element 256b + 128j + 8t.  Quadrant qd
-// is 32*qd elements further on: same 64-value chunk for odd qd, next chunk (80 bytes on) for qd >= 2.
-// I0 takes bytes 8t..8t+3 of every quadrant, I1 bytes 8t+4..8t+7: they belong to the partials 2t and
-// 2t+1 of core/src/llm/matmul/q6_small_batch.h:62-83.
-__device__ __forceinline__ void q6k_item_ints(const Q6Item& it, uint32_t yq, int& I0, int& I1) {
-    I0 = I1 = 0;
-#pragma unroll
-    for (int qd = 0; qd < 4; ++qd) {
-        const uint32_t a = yq + (qd >> 1) * 80 + (qd & 1) * 32;
-        const uint2 y = lds64(a);
-        I0 += it.sc[qd] * __dp4a((int)it.q[2 * qd], (int)y.x, 0);
-        I1 += it.sc[qd] * __dp4a((int)it.q[2 * qd + 1], (int)y.y, 0);
-    }
-}
-
-// Sum over the G lanes of a power-of-two lane group (all 32 lanes call it).
-template <int G>
-__device__ __forceinline__ float group_sum(float v) {
-#pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+__device__ __forceinline__ int dp2a_hi(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.hi.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
 
 // Optional capture of the exact per-block integer sums a row dot forms (parity checks):
@@ -459,217 +361,325 @@ struct BlockSumDump {
     int N;   // rows of the whole matrix (stride of a token)
 };
 
-// Row dot for up to NT tokens, in the float order of the CPU kernels it stands in for, so that the
-// result is bit-identical to them:
-//   Q4_K (core/src/kernels/hwy/hwy_moe_quant.cc:218-253): per super-block the exact int32 sums
-//     I = sum_s scale_s * dot_s and M = sum_g bsums_g * min_(g/2), then in block order
-//     sumf += (d * yd) * float(I);  sumf -= (dmin * yd) * float(M).
-//   Q6_K (core/src/llm/matmul/q6_small_batch.h:62-103): per super-block eight int32 partials (partial L
-//     collects bytes 4L..4L+3 of every 32-value quadrant, times the group scales), then per partial
-//     acc[L] = fma(yd * d, float(partial L), acc[L]) in block order, and at the end
-//     ((a0 + a4) + (a2 + a6)) + ((a1 + a5) + (a3 + a7)).
-// Weights are decoded once per item and reused for every token.  G lanes cooperate on one row and ALL 32
-// lanes of the warp must call (the exchanges are full-warp shuffles); `active` = this lane's row exists.
-// On return lane row_dot_owner(type, s) of the group (among others) holds the row's result for token slot s.
-// tok[s] = row of the activation arrays in shared memory used by token slot s (slots >= nt are skipped).
-// Lane of a row's group that ends up with token t's result (see row_dot_exact).
-__device__ __forceinline__ int row_dot_owner(int type, int t) { return type == DC_TYPE_Q4_K ? (t & 3) : 4 * (t & 1); }
-
-// v[base + sub] for a lane-dependent sub < N (0 beyond the array): register arrays cannot be indexed by a
-// run-time value, so the pick is a chain of selects.
-template <int N, int LEN, typename T>
-__device__ __forceinline__ T pick_slot(const T (&v)[LEN], int base, int sub) {
-    T r = base < LEN ? v[base < LEN ? base : 0] : T(0);
+// Q4_K super-block at shared address blk (16-byte aligned) against block b of NT token rows: the exact
+// integers I = sum_s scale_s * (q . y)_s and M = sum_g bsums_g * min_(g/2)
+// (core/src/kernels/hwy/hwy_moe_quant.cc:202-246); low nibbles of 32 bytes are sub-block 2c, high
+// nibbles sub-block 2c+1 (:202-211); scales and mins from the 12 packed bytes as :90-101.
+template <int NT>
+__device__ __forceinline__ void q4k_block_ints(uint32_t blk, const ActSmem& act, int b, int nt, const int (&tok)[NT],
+                                               int (&I)[NT], int (&M)[NT], float& d, float& dmin) {
+    const uint32_t dd = lds32(blk);
+    d = fp16_bits_to_float((uint16_t)(dd & 0xFFFF));
+    dmin = fp16_bits_to_float((uint16_t)(dd >> 16));
+    const uint32_t u0 = lds32(blk + 4), u1 = lds32(blk + 8), u2 = lds32(blk + 12);
+    const uint32_t sc_a = u0 & 0x3f3f3f3fu, sc_b = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+    const uint32_t mn_a = u1 & 0x3f3f3f3fu, mn_b = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
 #pragma unroll
-    for (int j = 1; j < N; ++j)
-        if (base + j < LEN && sub == j) r = v[base + j < LEN ? base + j : 0];
-    return r;
+    for (int s = 0; s < NT; ++s) I[s] = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint4 w0 = lds128(blk + 16 + 32 * c), w1 = lds128(blk + 32 + 32 * c);
+        const uint32_t scw = c < 2 ? sc_a : sc_b;
+        const int sc_lo = (int)((scw >> (16 * (c & 1))) & 0xFFu), sc_hi = (int)((scw >> (16 * (c & 1) + 8)) & 0xFFu);
+#pragma unroll
+        for (int s = 0; s < NT; ++s) {
+            if (s < nt) {
+                const uint32_t yq = act.qblk(tok[s], b) + 64 * c;
+                const uint4 y0 = lds128(yq), y1 = lds128(yq + 16), y2 = lds128(yq + 32), y3 = lds128(yq + 48);
+                int lo = 0, hi16 = 0;
+                lo = __dp4a((int)(w0.x & 0x0F0F0F0Fu), (int)y0.x, lo);
+                lo = __dp4a((int)(w0.y & 0x0F0F0F0Fu), (int)y0.y, lo);
+                lo = __dp4a((int)(w0.z & 0x0F0F0F0Fu), (int)y0.z, lo);
+                lo = __dp4a((int)(w0.w & 0x0F0F0F0Fu), (int)y0.w, lo);
+                lo = __dp4a((int)(w1.x & 0x0F0F0F0Fu), (int)y1.x, lo);
+                lo = __dp4a((int)(w1.y & 0x0F0F0F0Fu), (int)y1.y, lo);
+                lo = __dp4a((int)(w1.z & 0x0F0F0F0Fu), (int)y1.z, lo);
+                lo = __dp4a((int)(w1.w & 0x0F0F0F0Fu), (int)y1.w, lo);
+                // high nibbles stay in place (bytes 16*q, taken as unsigned): their dot is 16 times the wanted
+                // one, exactly, so one shift at the end replaces a shift per word
+                hi16 = dp4a_u8s8(w0.x & 0xF0F0F0F0u, y2.x, hi16);
+                hi16 = dp4a_u8s8(w0.y & 0xF0F0F0F0u, y2.y, hi16);
+                hi16 = dp4a_u8s8(w0.z & 0xF0F0F0F0u, y2.z, hi16);
+                hi16 = dp4a_u8s8(w0.w & 0xF0F0F0F0u, y2.w, hi16);
+                hi16 = dp4a_u8s8(w1.x & 0xF0F0F0F0u, y3.x, hi16);
+                hi16 = dp4a_u8s8(w1.y & 0xF0F0F0F0u, y3.y, hi16);
+                hi16 = dp4a_u8s8(w1.z & 0xF0F0F0F0u, y3.z, hi16);
+                hi16 = dp4a_u8s8(w1.w & 0xF0F0F0F0u, y3.w, hi16);
+                I[s] += sc_lo * lo + sc_hi * (hi16 >> 4);
+            }
+        }
+    }
+    // mins: word k of the sums holds groups 2k and 2k+1, both of sub-block k
+    const uint32_t m01 = __byte_perm(mn_a, 0, 0x1100), m23 = __byte_perm(mn_a, 0, 0x3322);
+    const uint32_t m45 = __byte_perm(mn_b, 0, 0x1100), m67 = __byte_perm(mn_b, 0, 0x3322);
+#pragma unroll
+    for (int s = 0; s < NT; ++s) {
+        M[s] = 0;
+        if (s < nt) {
+            const uint32_t bp = act.bsptr(tok[s], b);
+            const uint4 b0 = lds128(bp), b1 = lds128(bp + 16);
+            int m = dp2a_lo(b0.x, m01, 0);
+            m = dp2a_hi(b0.y, m01, m);
+            m = dp2a_lo(b0.z, m23, m);
+            m = dp2a_hi(b0.w, m23, m);
+            m = dp2a_lo(b1.x, m45, m);
+            m = dp2a_hi(b1.y, m45, m);
+            m = dp2a_lo(b1.z, m67, m);
+            m = dp2a_hi(b1.w, m67, m);
+            M[s] = m;
+        }
+    }
 }
 
-template <int NT>
-__device__ DC_HOT void row_dot_exact(int type, uint32_t row, bool active, int lane, int G, const ActSmem& act, int nt,
-                                     const int (&tok)[NT], float (&out)[NT], const BlockSumDump* dump = nullptr,
-                                     int dump_row = 0) {
+// per byte: q in 0..63 -> q - 32 as a signed byte.  With bit 7 set no byte borrows from its
+// neighbour, so one 32-bit subtraction does all four: ((q | 0x80) - 0x20) ^ 0x80.
+__device__ __forceinline__ uint32_t q6_signed(uint32_t q) { return ((q | 0x80808080u) - 0x20202020u) ^ 0x80808080u; }
+
+// NW consecutive 32-bit words starting at a 2-byte aligned shared address: NW + 1 aligned loads and a
+// funnel shift each (the shift is 0 or 16 bits, the same for the whole block).
+template <int NW>
+__device__ __forceinline__ void lds_words_a2(uint32_t a, uint32_t (&out)[NW]) {
+    const uint32_t base = a & ~3u, sh = (a & 2u) * 8u;
+    uint32_t prev = lds32(base);
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        const uint32_t next = lds32(base + 4 * (i + 1));
+        out[i] = __funnelshift_r(prev, next, sh);
+        prev = next;
+    }
+}
+
+// Half j (128 values) of the Q6_K super-block at shared address blk (2-byte aligned) against block b of
+// TT token rows: P[s][L], the exact int32 partial that collects bytes 4L..4L+3 of each of the half's four
+// 32-value quadrants times the group scales (core/src/llm/matmul/q6_small_batch.h:52-83; element order
+// :52-74).  The block's partials are the sums of the two halves'.
+template <int TT>
+__device__ __forceinline__ void q6k_half_ints(uint32_t blk, int j, const ActSmem& act, int b, int nt, const int* tok,
+                                              int (&P)[TT][8], float& d) {
+    uint32_t ql[16], qh[8], scw[2];
+    lds_words_a2<16>(blk + 64 * j, ql);
+    lds_words_a2<8>(blk + 128 + 32 * j, qh);
+    lds_words_a2<2>(blk + 192 + 8 * j, scw);
+    d = fp16_bits_to_float((uint16_t)lds16(blk + 208));
+    int sc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sc[i] = (int)(int8_t)((scw[i >> 2] >> (8 * (i & 3))) & 0xFFu);
+#pragma unroll
+    for (int s = 0; s < TT; ++s)
+#pragma unroll
+        for (int L = 0; L < 8; ++L) P[s][L] = 0;
+#pragma unroll
+    for (int wq = 0; wq < 2; ++wq) {
+        uint32_t q[4][4];   // [quadrant][word]: signed bytes q - 32
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t a = ql[4 * wq + k], c = ql[8 + 4 * wq + k], h = qh[4 * wq + k];
+            q[0][k] = q6_signed((a & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u));
+            q[1][k] = q6_signed((c & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u));
+            q[2][k] = q6_signed(((a >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u));
+            q[3][k] = q6_signed(((c >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u));
+        }
+#pragma unroll
+        for (int s = 0; s < TT; ++s) {
+            if (s < nt) {
+                const uint32_t yh = act.qblk(tok[s], b) + 128 * j + 16 * wq;
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    const uint4 y = lds128(yh + 32 * qd);
+                    const int scale = sc[2 * qd + wq];
+                    P[s][4 * wq + 0] += scale * __dp4a((int)q[qd][0], (int)y.x, 0);
+                    P[s][4 * wq + 1] += scale * __dp4a((int)q[qd][1], (int)y.y, 0);
+                    P[s][4 * wq + 2] += scale * __dp4a((int)q[qd][2], (int)y.z, 0);
+                    P[s][4 * wq + 3] += scale * __dp4a((int)q[qd][3], (int)y.w, 0);
+                }
+            }
+        }
+    }
+}
+
+// Row dots for up to NT tokens in the float order of the CPU kernels they stand in for, so that the result
+// is bit-identical to them:
+//   Q4_K (core/src/kernels/hwy/hwy_moe_quant.cc:218-253): per super-block the exact int32 sums I and M,
+//     then in block order  sumf += (d * yd) * float(I);  sumf -= (dmin * yd) * float(M).
+//   Q6_K (core/src/llm/matmul/q6_small_batch.h:62-103): per super-block eight int32 partials, then per
+//     partial acc[L] = fma(yd * d, float(partial L), acc[L]) in block order, and at the end
+//     ((a0 + a4) + (a2 + a6)) + ((a1 + a5) + (a3 + a7)).
+// `row` is the shared address of THIS lane's row (the groups of a warp run different rows), G =
+// lanes_per_row; all 32 lanes of the warp must call (the exchanges are full-warp shuffles that stay inside a
+// group); `active` = this lane's row exists.  On return every lane of a group holds its row's results.
+// tok[s] = activation row of token slot s (slots >= nt are skipped).
+template <int NT, int TYPE>
+__device__ DC_HOT void rows_dot(uint32_t row, bool active, int lane, int G, const ActSmem& act, int nt,
+                                const int (&tok)[NT], float (&out)[NT], const BlockSumDump* dump = nullptr,
+                                int dump_row = 0) {
     const int nb = act.nb;
     const int lig = lane & (G - 1), gbase = lane & ~(G - 1);
-    if (type == DC_TYPE_Q4_K) {
-        // The four lanes of a block hold the same block sums after the integer exchange; lane `sub` of them
-        // carries the block-order chain of the tokens sub, sub + 4, ...: one pair of shuffles per block then
-        // serves four tokens.
-        constexpr int NG = (NT + 3) / 4;
-        const int sub = lig & 3;
-        float acc[NG];
+    if (TYPE == DC_TYPE_Q4_K) {
+        float acc[NT];
 #pragma unroll
-        for (int g = 0; g < NG; ++g) acc[g] = 0.0f;
-        const int n_items = nb * 4, bpp = G >> 2;   // blocks per pass
-        for (int i0 = 0; i0 < n_items; i0 += G) {
-            const int i = i0 + lig, b = i >> 2, c = i & 3;
-            const bool on = active && i < n_items;
-            Q4Item it;
-            if (on) q4k_load_item(row, b, c, it);
+        for (int s = 0; s < NT; ++s) acc[s] = 0.0f;
+#pragma unroll 1
+        for (int b0 = 0; b0 < nb; b0 += G) {
+            const int b = b0 + lig;
+            const bool on = active && b < nb;
             float tI[NT], tM[NT];
 #pragma unroll
-            for (int s = 0; s < NT; ++s) {
-                tI[s] = tM[s] = 0.0f;
-                if (s < nt) {
-                    const int t = tok[s];
-                    int I = 0, M = 0;
-                    float yd = 0.0f;
-                    if (on) {
-                        q4k_item_ints(it, act.q(t, b * 256 + 64 * c), act.bs + (t * nb + b) * 32 + 8 * c, I, M);
-                        yd = __int_as_float(lds32(act.d + (t * nb + b) * 4));
-                    }
-                    // the block's four chunks sit in four neighbouring lanes
-                    I += __shfl_xor_sync(0xffffffffu, I, 1);
-                    M += __shfl_xor_sync(0xffffffffu, M, 1);
-                    I += __shfl_xor_sync(0xffffffffu, I, 2);
-                    M += __shfl_xor_sync(0xffffffffu, M, 2);
-                    if (on) {
-                        tI[s] = __fmul_rn(__fmul_rn(it.d, yd), (float)I);
-                        tM[s] = __fmul_rn(__fmul_rn(it.dmin, yd), (float)M);
-                        if (dump && c == 0) {
-                            const size_t di = ((size_t)t * dump->N + dump_row) * nb + b;
-                            dump->I[di] = I;
-                            if (dump->M) dump->M[di] = M;
+            for (int s = 0; s < NT; ++s) tI[s] = tM[s] = 0.0f;
+            if (on) {
+                int I[NT], M[NT];
+                float d, dmin;
+                q4k_block_ints<NT>(row + b * DC_Q4K_BYTES, act, b, nt, tok, I, M, d, dmin);
+#pragma unroll
+                for (int s = 0; s < NT; ++s) {
+                    if (s < nt) {
+                        const float yd = __int_as_float(lds32(act.dptr(tok[s], b)));
+                        tI[s] = __fmul_rn(__fmul_rn(d, yd), (float)I[s]);
+                        tM[s] = __fmul_rn(__fmul_rn(dmin, yd), (float)M[s]);
+                        if (dump) {
+                            const size_t di = ((size_t)tok[s] * dump->N + dump_row) * nb + b;
+                            dump->I[di] = I[s];
+                            if (dump->M) dump->M[di] = M[s];
                         }
                     }
                 }
             }
-            float xi[NG], xm[NG];
-#pragma unroll
-            for (int g = 0; g < NG; ++g) {
-                xi[g] = pick_slot<4>(tI, 4 * g, sub);
-                xm[g] = pick_slot<4>(tM, 4 * g, sub);
-            }
-            // block order: the terms of the pass's blocks are fetched side by side, then added one by one
+            // block order: every lane of the group adds the pass's blocks one by one
+            const int nbb = min(G, nb - b0);
 #pragma unroll 1
-            for (int bb = 0; bb < bpp; ++bb) {
-                if ((i0 >> 2) + bb >= nb) break;
-                const int src = gbase + 4 * bb + sub;
+            for (int bb = 0; bb < nbb; ++bb) {
 #pragma unroll
-                for (int g = 0; g < NG; ++g) {
-                    const float a = __shfl_sync(0xffffffffu, xi[g], src);
-                    const float m = __shfl_sync(0xffffffffu, xm[g], src);
-                    acc[g] = __fsub_rn(__fadd_rn(acc[g], a), m);
+                for (int s = 0; s < NT; ++s) {
+                    if (s < nt) {
+                        const float a = __shfl_sync(0xffffffffu, tI[s], gbase + bb);
+                        const float m = __shfl_sync(0xffffffffu, tM[s], gbase + bb);
+                        acc[s] = __fsub_rn(__fadd_rn(acc[s], a), m);
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int s = 0; s < NT; ++s) out[s] = acc[s >> 2];   // valid on the lanes with sub == s % 4
+        for (int s = 0; s < NT; ++s) out[s] = acc[s];
     } else {
-        // lane -> (block, half j, eighth tq).  After the integer exchange both halves hold the block's partials
-        // 2tq and 2tq+1; half j then carries the chains of the tokens j, j + 2, ...
-        constexpr int NG = (NT + 1) / 2;
-        const int jj = (lig >> 2) & 1;
-        float a0[NG], a1[NG];
-#pragma unroll
-        for (int g = 0; g < NG; ++g) a0[g] = a1[g] = 0.0f;
-        const int n_items = nb * 8, bpp = G >> 3;
-        for (int i0 = 0; i0 < n_items; i0 += G) {
-            const int i = i0 + lig, b = i >> 3, j = (i >> 2) & 1, tq = i & 3;
-            const bool on = active && i < n_items;
-            Q6Item it;
-            if (on) q6k_load_item(row, b, j, tq, it);
-            int I0[NT], I1[NT];
-            float sc[NT];
-#pragma unroll
-            for (int s = 0; s < NT; ++s) {
-                I0[s] = I1[s] = 0;
-                sc[s] = 0.0f;
-                if (s < nt) {
-                    const int t = tok[s];
-                    if (on) {
-                        q6k_item_ints(it, act.q(t, b * 256 + 128 * j + 8 * tq), I0[s], I1[s]);
-                        sc[s] = __fmul_rn(__int_as_float(lds32(act.d + (t * nb + b) * 4)), it.d);
-                    }
-                    // the two halves of a block are four lanes apart
-                    I0[s] += __shfl_xor_sync(0xffffffffu, I0[s], 4);
-                    I1[s] += __shfl_xor_sync(0xffffffffu, I1[s], 4);
-                    if (dump) {
-                        int tot = I0[s] + I1[s];
-                        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
-                        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
-                        if (on && j == 0 && tq == 0) dump->I[((size_t)t * dump->N + dump_row) * nb + b] = tot;
-                    }
-                }
-            }
-            float xf[NG];
-            int x0[NG], x1[NG];
-#pragma unroll
-            for (int g = 0; g < NG; ++g) {
-                xf[g] = pick_slot<2>(sc, 2 * g, jj);
-                x0[g] = pick_slot<2>(I0, 2 * g, jj);
-                x1[g] = pick_slot<2>(I1, 2 * g, jj);
-            }
+        // lane -> (block lig / 2, half lig % 2).  After the integer exchange both lanes of a block hold its
+        // eight partials; the lane of half j then carries the block-order chains of partials 4j .. 4j+3.
+        constexpr int TT = NT < 4 ? NT : 4;   // tokens per decode of the weights (registers)
+        const int j = lig & 1, bpp = G >> 1;
 #pragma unroll 1
-            for (int bb = 0; bb < bpp; ++bb) {
-                if ((i0 >> 3) + bb >= nb) break;
-                const int src = gbase + 8 * bb + (lig & 7);
+        for (int s0 = 0; s0 < NT; s0 += TT) {
+            if (s0 >= nt) break;
+            float ac[TT][4];
 #pragma unroll
-                for (int g = 0; g < NG; ++g) {
-                    const float f = __shfl_sync(0xffffffffu, xf[g], src);
-                    const int v0 = __shfl_sync(0xffffffffu, x0[g], src);
-                    const int v1 = __shfl_sync(0xffffffffu, x1[g], src);
-                    a0[g] = __fmaf_rn(f, (float)v0, a0[g]);
-                    a1[g] = __fmaf_rn(f, (float)v1, a1[g]);
+            for (int s = 0; s < TT; ++s)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) ac[s][k] = 0.0f;
+#pragma unroll 1
+            for (int b0 = 0; b0 < nb; b0 += bpp) {
+                const int b = b0 + (lig >> 1);
+                const bool on = active && b < nb;
+                int P[TT][8];
+                float sf[TT];
+#pragma unroll
+                for (int s = 0; s < TT; ++s) {
+                    sf[s] = 0.0f;
+#pragma unroll
+                    for (int L = 0; L < 8; ++L) P[s][L] = 0;
+                }
+                if (on) {
+                    float d;
+                    q6k_half_ints<TT>(row + b * DC_Q6K_BYTES, j, act, b, nt - s0, &tok[s0], P, d);
+#pragma unroll
+                    for (int s = 0; s < TT; ++s)
+                        if (s0 + s < nt) sf[s] = __fmul_rn(__int_as_float(lds32(act.dptr(tok[s0 + s], b))), d);
+                }
+                int x[TT][4];
+#pragma unroll
+                for (int s = 0; s < TT; ++s) {
+                    if (s0 + s < nt) {
+#pragma unroll
+                        for (int L = 0; L < 8; ++L) P[s][L] += __shfl_xor_sync(0xffffffffu, P[s][L], 1);
+                        if (dump && on && j == 0) {
+                            int tot = 0;
+#pragma unroll
+                            for (int L = 0; L < 8; ++L) tot += P[s][L];
+                            dump->I[((size_t)tok[s0 + s] * dump->N + dump_row) * nb + b] = tot;
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) x[s][k] = j ? P[s][4 + k] : P[s][k];
+                }
+                const int nbb = min(bpp, nb - b0);
+#pragma unroll 1
+                for (int bb = 0; bb < nbb; ++bb) {
+                    const int src = gbase + 2 * bb + j;
+#pragma unroll
+                    for (int s = 0; s < TT; ++s) {
+                        if (s0 + s < nt) {
+                            const float f = __shfl_sync(0xffffffffu, sf[s], src);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const int v = __shfl_sync(0xffffffffu, x[s][k], src);
+                                ac[s][k] = __fmaf_rn(f, (float)v, ac[s][k]);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < TT; ++s) {
+                if (s0 + s < nt) {
+                    // the lane of half 0 holds a0..a3, its neighbour a4..a7
+                    float r[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) r[k] = __fadd_rn(ac[s][k], __shfl_xor_sync(0xffffffffu, ac[s][k], 1));
+                    const float res = __fadd_rn(__fadd_rn(r[0], r[2]), __fadd_rn(r[1], r[3]));
+#pragma unroll
+                    for (int q = 0; q < NT; ++q)
+                        if (q == s0 + s) out[q] = res;
                 }
             }
         }
-        float r[NG];
-#pragma unroll
-        for (int g = 0; g < NG; ++g) {
-            // lanes tq = 0..3 (of one half) hold (a0,a1), (a2,a3), (a4,a5), (a6,a7) of their token
-            const float x0s = __fadd_rn(a0[g], __shfl_xor_sync(0xffffffffu, a0[g], 2));   // a0+a4 | a2+a6
-            const float x1s = __fadd_rn(a1[g], __shfl_xor_sync(0xffffffffu, a1[g], 2));   // a1+a5 | a3+a7
-            const float y0 = __fadd_rn(x0s, __shfl_xor_sync(0xffffffffu, x0s, 1));        // (a0+a4)+(a2+a6)
-            const float y1 = __fadd_rn(x1s, __shfl_xor_sync(0xffffffffu, x1s, 1));        // (a1+a5)+(a3+a7)
-            r[g] = __fadd_rn(y0, y1);
-        }
-#pragma unroll
-        for (int s = 0; s < NT; ++s) out[s] = r[s >> 1];   // valid on the lanes of half s % 2
     }
 }
-// The single-token row dot as an out-of-line leaf with scalar arguments (everything travels in registers):
+
+// The single-token form as an out-of-line leaf with scalar arguments (everything travels in registers):
 // (qs_t, d_t, bs_t) are the shared-memory addresses of the token's codes, block scales and block sums.
 // Inside the persistent kernel the inlined form costs the surrounding phases their registers (the kernel and
 // its out-of-line phase functions share one register file along each call chain, and spill what does not
-// fit: measured 24 % of the step time), and a call per row of the 32-register leaf costs 3 %.
+// fit: measured 24 % of the step time); one call serves all the rows of a warp pass.
 template <int TYPE>
-__device__ __noinline__ float row_dot_exact1(uint32_t row, int active, int lane, int G, uint32_t qs_t, uint32_t d_t,
-                                             uint32_t bs_t, int nb) {
+__device__ __noinline__ float rows_dot1(uint32_t row, int active, int lane, int G, uint32_t qs_t, uint32_t d_t,
+                                        uint32_t bs_t, int nb) {
     ActSmem a;
     a.qs = qs_t;
     a.d = d_t;
     a.bs = bs_t;
     a.nb = nb;
     a.K = nb * DC_QK_K;
-    a.rs = 0;
     const int tok[1] = {0};
     float out[1];
-    row_dot_exact<1>(TYPE, row, active != 0, lane, G, a, 1, tok, out);
+    rows_dot<1, TYPE>(row, active != 0, lane, G, a, 1, tok, out);
     return out[0];
 }
 // Token row t of an activation layout, by either decoder.
-__device__ __forceinline__ float row_dot_exact1_typed(int type, uint32_t row, bool active, int lane, int G,
-                                                      const ActSmem& act, int t) {
-    const uint32_t qs_t = act.qs + t * act.rs, d_t = act.d + t * act.nb * 4, bs_t = act.bs + t * act.nb * 32;
-    return type == DC_TYPE_Q4_K ? row_dot_exact1<DC_TYPE_Q4_K>(row, active, lane, G, qs_t, d_t, bs_t, act.nb)
-                                : row_dot_exact1<DC_TYPE_Q6_K>(row, active, lane, G, qs_t, d_t, bs_t, act.nb);
+__device__ __forceinline__ float rows_dot1_typed(int type, uint32_t row, bool active, int lane, int G, const ActSmem& act,
+                                                 int t) {
+    const uint32_t qs_t = act.qblk(t, 0), d_t = act.dptr(t, 0), bs_t = act.bsptr(t, 0);
+    return type == DC_TYPE_Q4_K ? rows_dot1<DC_TYPE_Q4_K>(row, active, lane, G, qs_t, d_t, bs_t, act.nb)
+                                : rows_dot1<DC_TYPE_Q6_K>(row, active, lane, G, qs_t, d_t, bs_t, act.nb);
+}
+// Any token count, type decided at run time.
+template <int NT>
+__device__ __forceinline__ void rows_dot_typed(int type, uint32_t row, bool active, int lane, int G, const ActSmem& act,
+                                               int nt, const int (&tok)[NT], float (&out)[NT],
+                                               const BlockSumDump* dump = nullptr, int dump_row = 0) {
+    if (type == DC_TYPE_Q4_K) rows_dot<NT, DC_TYPE_Q4_K>(row, active, lane, G, act, nt, tok, out, dump, dump_row);
+    else rows_dot<NT, DC_TYPE_Q6_K>(row, active, lane, G, act, nt, tok, out, dump, dump_row);
 }
 
 // Generic-width lane-group sum (G a power of two <= 32, runtime value).
 __device__ __forceinline__ float group_sum_rt(float v, int G) {
     for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
-}
-
-// Lanes that cooperate on one row for a given type and K: one item per lane where the row
-// has that many items (measured: two items per lane and half-warp rows were ~30 % slower).
-__host__ __device__ inline int lanes_per_row(int type, int K) {
-    const int items = (K / DC_QK_K) * (type == DC_TYPE_Q4_K ? 4 : 8);
-    int g = 4;
-    while (g < items && g < 32) g <<= 1;
-    return g;
 }
 
 }  // namespace dc

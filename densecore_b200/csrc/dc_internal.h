@@ -11,7 +11,7 @@
 
 #define DC_NSTAGE 4
 #define DC_WARPS 8
-#define DC_STAGE_TARGET 2304  // bytes of weight rows one pipeline stage aims to hold
+#define DC_STAGE_TARGET 4608  // bytes of weight rows one pipeline stage aims to hold: one warp pass of Q4_K rows
 
 struct dc_weight {
     int type;        // ggml type id

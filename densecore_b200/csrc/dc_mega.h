@@ -5,8 +5,8 @@
 
 #define MG_THREADS 512
 #define MG_WARPS 16
-#define MG_NSTAGE 3
-#define MG_STAGE 2560   // bytes per pipeline stage of one warp
+#define MG_NSTAGE 2
+#define MG_STAGE 4864   // bytes per pipeline stage of one warp: one pass of four Q4_K rows of 2048, or two gate/up pairs
 #define MG_MAX_T 4
 #define MG_MAX_E 256
 #define MG_MAX_K 16
@@ -72,7 +72,7 @@ struct MegaParams {
     int* err;
     unsigned long long* phase_ns;  // optional [32] phase timing accumulators (CTA 0's view)
     // dynamic shared memory offsets
-    uint32_t off_pipe, off_act, off_xs, off_sc, smem_bytes;
+    uint32_t off_pipe, off_act, off_xs, off_sc, off_v, smem_bytes;
     // rows per pipeline stage
     int rpst_q, rpst_k, rpst_v, rpst_o, rpst_gate, rpst_down, rpst_out;
     uint32_t up_off;

@@ -131,7 +131,11 @@ struct GemvStream {
     }
     // SWIGLU = false leaves the paired gate/up path out of the generated code (callers that
     // never stream pairs).
-    // DUMP = true also stores the exact block sums (parity checks; never in the decoder's launches).
+    // SWIGLU = false leaves the paired gate/up path out of the generated code (callers that never stream
+    // pairs).  DUMP = true also stores the exact block sums (parity checks; never in the decoder's launches).
+    // A warp pass runs 32 / G rows side by side, one per lane group.  Gate/up pairs: the lower half of the
+    // groups takes gate rows, the upper half the up rows of the same outputs, and the two halves swap
+    // results 16 lanes across (one group per row, G = 32: gate row, then up row).
     template <int NT, bool SWIGLU = true, bool DUMP = false>
     __device__ DC_HOT void consume(const GemvParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
         int tok[NT];
@@ -140,39 +144,44 @@ struct GemvStream {
         unsigned long long best[NT];
 #pragma unroll
         for (int s = 0; s < NT; ++s) best[s] = 0ull;
+        const bool pair = SWIGLU && p.epi == DC_EPI_SWIGLU;
         int sg, lr, n;
         while (cons.next(p, sg, lr, n)) {
             const dc_gemv_seg& s = p.seg[sg];
             const uint32_t buf = pipe.wait();
             const int G = lanes_per_row(s.type, p.K);
-            const int rows_per_pass = 32 / G;
+            const int rpp = 32 / G;                       // rows per pass
             const int grp = lane / G, lig = lane % G;
+            const bool split = pair && rpp >= 2;          // gate and up rows in one pass
+            const int opp = split ? rpp / 2 : rpp;        // outputs per pass
+            const bool up_half = split && grp >= opp;
             const uint32_t skew = (uint32_t)(((uintptr_t)s.w + (size_t)lr * s.row_bytes) & 15);
-            const uint32_t skew_up =
-                (SWIGLU && p.epi == DC_EPI_SWIGLU) ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
+            const uint32_t skew_up = pair ? (uint32_t)(((uintptr_t)p.seg[1].w + (size_t)lr * s.row_bytes) & 15) : 0u;
+            const uint32_t base = up_half ? buf + p.up_off + skew_up : buf + skew;
             const BlockSumDump* dump = DUMP ? &p.dump : nullptr;
-            for (int r = 0; r < n; r += rows_per_pass) {
-                const int rr = r + grp;
+            for (int r = 0; r < n; r += opp) {
+                const int rr = r + (split ? grp % opp : grp);
                 const bool active = rr < n;
                 float acc[NT], acc2[NT];
-                // every lane takes part in the row dots (full-warp exchanges inside); all lanes of a row's
-                // group run together; the lane that owns token t's result stores it
-                if (NT == 1 && !DUMP) {
-                    acc[0] = row_dot_exact1_typed(s.type, buf + skew + rr * s.row_bytes, active, lane, G, act, 0);
-                    if ((SWIGLU && p.epi == DC_EPI_SWIGLU))
-                        acc2[0] = row_dot_exact1_typed(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, active, lane, G, act, 0);
-                } else {
-                    row_dot_exact<NT>(s.type, buf + skew + rr * s.row_bytes, active, lane, G, act, p.T, tok, acc, dump, lr + rr);
-                    if ((SWIGLU && p.epi == DC_EPI_SWIGLU))
-                        row_dot_exact<NT>(s.type, buf + p.up_off + skew_up + rr * s.row_bytes, active, lane, G, act, p.T, tok,
-                                          acc2);
+                if (NT == 1 && !DUMP) acc[0] = rows_dot1_typed(s.type, base + rr * s.row_bytes, active, lane, G, act, 0);
+                else rows_dot_typed<NT>(s.type, base + rr * s.row_bytes, active, lane, G, act, p.T, tok, acc, dump, lr + rr);
+                if (pair) {
+                    if (split) {
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) acc2[t] = __shfl_xor_sync(0xffffffffu, acc[t], 16);
+                    } else {
+                        const uint32_t urow = buf + p.up_off + skew_up + rr * s.row_bytes;
+                        if (NT == 1 && !DUMP) acc2[0] = rows_dot1_typed(s.type, urow, active, lane, G, act, 0);
+                        else rows_dot_typed<NT>(s.type, urow, active, lane, G, act, p.T, tok, acc2);
+                    }
                 }
+                // every lane of a row's group holds the row's results; lane (t mod G) of the group stores token t
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
                     if (t < p.T) {
                         float v = acc[t];
-                        if ((SWIGLU && p.epi == DC_EPI_SWIGLU)) v = __fmul_rn(silu_fast(v), acc2[t]);
-                        if (active && lig == row_dot_owner(s.type, t)) {
+                        if (pair) v = __fmul_rn(silu_fast(v), acc2[t]);
+                        if (active && !up_half && lig == (t & (G - 1))) {
                             const int row = lr + rr;
                             float* o = s.out + (size_t)t * s.ldo + row;
                             if (p.epi == DC_EPI_ACC) *o = __ldcg(o) + v;  // L2 read: another SM may have written it
@@ -316,37 +325,45 @@ struct MoeStream {
             for (int s = 0; s < NSTAGE; ++s) issue_next(p, pipe);
         }
     }
-    // The rows of one stage for the first NTT token slots of tok/asg.
+    // The rows of one stage for the first NTT token slots of tok/asg (see GemvStream::consume for the
+    // layout of a pass).
     template <int NTT>
     __device__ __forceinline__ static void stage_rows(const MoeMMParams& p, const ActSmem& act, uint32_t buf, uint32_t skew0,
-                                                      uint32_t skew1, int nhalf, int r, int n, int nt, const int* tok_in,
-                                                      const int* asg_in, int G, int grp, int lig, int lane) {
-        const int rows_per_pass = 32 / G;
+                                                      uint32_t skew1, bool pair, int r, int n, int nt, const int* tok_in,
+                                                      const int* asg_in, int G, int lane) {
+        const int rpp = 32 / G, grp = lane / G, lig = lane % G;
+        const bool split = pair && rpp >= 2;
+        const int opp = split ? rpp / 2 : rpp;
+        const bool up_half = split && grp >= opp;
+        const uint32_t base = buf + (up_half ? skew1 : skew0);
         int tok[NTT], asg[NTT];
 #pragma unroll
         for (int s = 0; s < NTT; ++s) {
             tok[s] = tok_in[s];
             asg[s] = asg_in[s];
         }
-        for (int rr0 = 0; rr0 < n; rr0 += rows_per_pass) {
-            const int rr = rr0 + grp;
+        for (int rr0 = 0; rr0 < n; rr0 += opp) {
+            const int rr = rr0 + (split ? grp % opp : grp);
             const bool active = rr < n;
-            float v[NTT];
+            float v[NTT], u[NTT];
+            if (NTT == 1) v[0] = rows_dot1_typed(p.type, base + rr * p.row_bytes, active, lane, G, act, tok[0]);
+            else rows_dot_typed<NTT>(p.type, base + rr * p.row_bytes, active, lane, G, act, nt, tok, v);
+            if (pair) {
+                if (split) {
 #pragma unroll
-            for (int s = 0; s < NTT; ++s) v[s] = 0.0f;
-            // gate row first, then (pairs) the up row of the same output through the same code
-#pragma unroll 1
-            for (int half = 0; half < nhalf; ++half) {
-                float acc[NTT];
-                if (NTT == 1) acc[0] = row_dot_exact1_typed(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, active, lane, G, act, tok[0]);
-                else row_dot_exact<NTT>(p.type, buf + (half ? skew1 : skew0) + rr * p.row_bytes, active, lane, G, act, nt, tok, acc);
+                    for (int s = 0; s < NTT; ++s) u[s] = __shfl_xor_sync(0xffffffffu, v[s], 16);
+                } else {
+                    const uint32_t urow = buf + skew1 + rr * p.row_bytes;
+                    if (NTT == 1) u[0] = rows_dot1_typed(p.type, urow, active, lane, G, act, tok[0]);
+                    else rows_dot_typed<NTT>(p.type, urow, active, lane, G, act, nt, tok, u);
+                }
 #pragma unroll
                 for (int s = 0; s < NTT; ++s)
-                    if (s < nt) v[s] = half ? __fmul_rn(silu_fast(v[s]), acc[s]) : acc[s];
+                    if (s < nt) v[s] = __fmul_rn(silu_fast(v[s]), u[s]);
             }
 #pragma unroll
             for (int s = 0; s < NTT; ++s)
-                if (s < nt && active && lig == row_dot_owner(p.type, s)) {
+                if (s < nt && active && !up_half && lig == (s & (G - 1))) {
                     const size_t oi = (size_t)asg[s] * p.N + r + rr;
                     p.out[oi] = v[s];
                     for (int q = 0; q < p.n_peer; ++q) p.peer_out[q][oi] = v[s];
@@ -358,8 +375,6 @@ struct MoeStream {
     __device__ DC_HOT void consume(const MoeMMParams& p, WarpPipe<NSTAGE>& pipe, const ActSmem& act, int lane) {
         const bool pair = is_pair(p);
         const int G = lanes_per_row(p.type, p.K);
-        const int grp = lane / G, lig = lane % G;
-        const int nhalf = pair ? 2 : 1;
         int u, r, n;
         while (cons.next(u, r, n)) {
             const uint32_t buf = pipe.wait();
@@ -374,8 +389,8 @@ struct MoeStream {
                 tok[s] = pair ? asg[s] / p.top_k : asg[s];
             }
             // most experts of a step serve a single token: that case runs the one-token body
-            if (NT > 1 && nt == 1) stage_rows<1>(p, act, buf, skew0, skew1, nhalf, r, n, nt, tok, asg, G, grp, lig, lane);
-            else stage_rows<NT>(p, act, buf, skew0, skew1, nhalf, r, n, nt, tok, asg, G, grp, lig, lane);
+            if (NT > 1 && nt == 1) stage_rows<1>(p, act, buf, skew0, skew1, pair, r, n, nt, tok, asg, G, lane);
+            else stage_rows<NT>(p, act, buf, skew0, skew1, pair, r, n, nt, tok, asg, G, lane);
             pipe.release();
             if (lane == 0) issue_next(p, pipe);
         }

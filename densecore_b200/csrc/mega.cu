@@ -1207,10 +1207,10 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
     unsigned epoch = 0;
     unsigned long long t_last = mg_now();
 
-    // V rows of an attention run are staged where the activations and the hidden state live
-    // in the other phases (both are idle during attention)
-    uint8_t* vbuf = act_base;
-    const int vcap_blocks = (int)((p.off_sc - p.off_act) / (DC_KV_BLOCK * 256));
+    // scores and the V rows of an attention run live where the activations and the hidden state live in the
+    // other phases (both are idle during attention)
+    uint8_t* vbuf = smem + p.off_v;
+    const int vcap_blocks = (int)((p.smem_bytes - p.off_v) / (DC_KV_BLOCK * 256));
     // expert parallel: rows of the down projection go to the exchange buffers, alternating halves by layer
     const bool ep = p.ep_size > 1;
     const size_t xhalf = (size_t)MG_MAX_T * MG_MAX_K * p.H;
@@ -1389,7 +1389,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
 static int mg_rows_per_stage(int type, int K, int row_bytes) {
     const int G = dc::lanes_per_row(type, K);
     const int per_pass = 32 / G;
-    int r = DC_STAGE_TARGET / row_bytes;
+    int r = (MG_STAGE - 32) / row_bytes;
     r = r / per_pass * per_pass;
     return r < per_pass ? per_pass : r;
 }
@@ -1463,42 +1463,50 @@ bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why) {
             NO("attention tensor types vary by layer");
     }
     if (!ok) NO("a weight row does not fit a pipeline stage");
-    // gate/up pairs: as many outputs per stage as two halves allow (the paired half-warp path takes
-    // one output per pass; otherwise a stage holds whole passes)
+    // gate/up pairs: a pass takes gate rows in the lower half of its lane groups and the up rows of the same
+    // outputs in the upper half, so a stage holds a multiple of (rows per pass) / 2 outputs in each of its halves
     {
         const int G = dc::lanes_per_row(L0.gate_exps->type, c.hidden);
-        const int step = G == 16 ? 1 : 32 / G;
-        int r = p.rpst_gate / step * step;
-        if (r < step) r = step;
-        uint32_t half = 0;
-        for (;;) {
-            half = ((uint32_t)r * (uint32_t)L0.gate_exps->row_bytes + 32 + 127) & ~127u;
-            if (2 * half <= MG_STAGE || r <= step) break;
-            r -= step;
-        }
+        const int rpp = 32 / G, step = rpp >= 2 ? rpp / 2 : 1;
+        int r = step;
+        uint32_t half = ((uint32_t)r * (uint32_t)L0.gate_exps->row_bytes + 32 + 127) & ~127u;
         if (2 * half > MG_STAGE) NO("a gate/up row pair does not fit a pipeline stage");
+        for (;;) {   // more passes per stage while they fit
+            const uint32_t h2 = ((uint32_t)(r + step) * (uint32_t)L0.gate_exps->row_bytes + 32 + 127) & ~127u;
+            if (2 * h2 > MG_STAGE) break;
+            r += step;
+            half = h2;
+        }
         p.rpst_gate = r;
         p.up_off = half;
     }
-    // shared memory plan
-    size_t act_bytes = ActSmem::bytes(T, QD);
-    const size_t a2 = ActSmem::bytes(T * c.n_expert_used, c.expert_ffn), a3 = ActSmem::bytes(T, c.hidden);
-    if (a2 > act_bytes) act_bytes = a2;
-    if (a3 > act_bytes) act_bytes = a3;
+    // Shared memory plan.  After the warps' pipelines comes one region that every phase lays out for itself:
+    // norm phases put the Q8_K hidden state first and (before the router) the normed f32 rows behind it; the
+    // output projection and the down projection put their Q8_K inputs there; attention puts its scores there
+    // and stages the run's V rows behind them.  The region is as large as its largest user, and is grown to
+    // hold a whole attention run's V rows if the SM has room left.
+    const size_t a_x = (ActSmem::bytes(T, c.hidden) + 127) & ~(size_t)127;
+    size_t region = a_x + (size_t)T * c.hidden * 4;
+    const size_t a_o = ActSmem::bytes(T, QD), a_h = ActSmem::bytes(T * c.n_expert_used, c.expert_ffn);
+    if (a_o > region) region = a_o;
+    if (a_h > region) region = a_h;
+    const uint32_t sc_bytes = mg_sc_bytes(p.s_keys);
+    const size_t v_run = (size_t)(p.s_keys / DC_KV_BLOCK) * DC_KV_BLOCK * 256;
     uint32_t off = 512;
     p.off_pipe = off;
     off += MG_WARPS * MG_NSTAGE * MG_STAGE;
     p.off_act = off;
-    off += (uint32_t)((act_bytes + 127) & ~(size_t)127);
-    p.off_xs = off;
-    off += (uint32_t)(T * c.hidden * 4);
-    {   // V rows of an attention run are staged over act+xs: pad so a whole run fits, if there is room
-        const uint32_t want = (uint32_t)(p.s_keys / DC_KV_BLOCK) * DC_KV_BLOCK * 256;
-        const uint32_t have = off - p.off_act, sc_bytes = mg_sc_bytes(p.s_keys);
-        if (want > have && off + (want - have) + sc_bytes <= MG_DYN_LIMIT) off += want - have;
-    }
+    p.off_xs = off + (uint32_t)a_x;
     p.off_sc = off;
-    off += mg_sc_bytes(p.s_keys);
+    p.off_v = off + sc_bytes;
+    if (region < sc_bytes + 4096) region = sc_bytes + 4096;
+    if (region < sc_bytes + v_run) {
+        const size_t room = off + region < MG_DYN_LIMIT ? MG_DYN_LIMIT - off - region : 0;
+        const size_t want = sc_bytes + v_run - region;
+        region += want < room ? want : (room & ~(size_t)4095);
+    }
+    region = (region + 127) & ~(size_t)127;
+    off += (uint32_t)region;
     p.smem_bytes = off;
     if (off > MG_DYN_LIMIT) NO("shared memory plan exceeds the 227 KB of an SM");
     if (p.s_keys / DC_KV_BLOCK > MG_MAX_RUN_BLOCKS) NO("attention run longer than 64 KV blocks");
