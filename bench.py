@@ -41,6 +41,9 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tok/s (1 & 4 streams), 35B-A3B-class Q4_K_M; % HBM roofline"
 UNIT = "tok/s"
 PROMPT = 2048
+WORKLOAD = ("moe35b_a3b_q4km decode: 48 layers, hidden 2048, 128 experts top-8, vocab 151936; "
+            "2048-token random prompt per stream, greedy, paged fp16 KV")
+CPU_CTX = PROMPT + 128     # context length of the CPU sample: the middle of a 256-token generation
 SAMPLE_LAYERS = 4          # layers of the model the CPU baseline times per sample
 SAMPLE_REPS = 12           # repeats of the sample (median taken)
 # DRAM bytes (read + write) of one launch of the persistent kernel divided by its algorithmic bytes,
@@ -160,14 +163,30 @@ def cpu_sample_run(o, S, n_streams: int, rng) -> float:
     return t_layers, t_head
 
 
-def cpu_tok_s(o, S, n_streams, reps, rng):
-    tl, th = [], []
+def cpu_reference(o, reps: int, warm: int = 2):
+    """The CPU restatement of DenseCore's ggml path, all host threads, on the bounded sample both CPU legs
+    use: SAMPLE_LAYERS of 48 layers (QKV/O matmuls, paged attention at ctx CPU_CTX, router, MoE FFN) plus
+    the lm_head per batch-1 decode step, scaled to 48 layers (norms, RoPE and residual adds are left out:
+    they are below 1 % of the step).  Returns (tok/s, seconds per step, threads, sample text)."""
+    threads = o.max_threads()
+    o.set_threads(threads)
+    rng = np.random.default_rng(0)
+    S = cpu_sample_setup(SAMPLE_LAYERS, CPU_CTX)
+    for _ in range(warm):
+        cpu_sample_run(o, S, 1, rng)
+    per = []
     for _ in range(reps):
-        a, b = cpu_sample_run(o, S, n_streams, rng)
-        tl.append(a)
-        th.append(b)
-    per_token_step = float(np.median(tl)) / len(S["layers"]) * 48 + float(np.median(th))
-    return n_streams / per_token_step, per_token_step
+        tl, th = cpu_sample_run(o, S, 1, rng)
+        per.append(tl / SAMPLE_LAYERS * 48 + th)
+    step_s = float(np.median(per))
+    sample = (f"{SAMPLE_LAYERS} of 48 layers (QKV/O matmuls, paged attention at ctx {CPU_CTX}, router, MoE FFN) + lm_head "
+              f"of one batch-1 decode step, median of {reps} repeats after {warm} warm-ups, scaled to 48 layers; norms, RoPE "
+              f"and residual adds left out; CPU restatement of DenseCore's ggml path")
+    return 1.0 / step_s, step_s, threads, sample
+
+
+def bench_config(streams: int = 1, layers: int = 48, prompt: int = PROMPT, world: int = 1) -> dict:
+    return {"workload": WORKLOAD, "streams": streams, "layers": layers, "prompt_tokens": prompt, "parallelism": f"ep{world}"}
 
 
 def reference_arm(args):
@@ -176,28 +195,16 @@ def reference_arm(args):
         return 0
     from oracle import oracle as o
     o.build()
-    threads = o.max_threads()
-    o.set_threads(threads)
-    rng = np.random.default_rng(0)
-    S = cpu_sample_setup(SAMPLE_LAYERS, PROMPT + 128)
-    for _ in range(max(1, min(args.warmup, 2))):
-        cpu_sample_run(o, S, 1, rng)
-    per = []
     t_all = time.perf_counter()
-    for _ in range(args.steps):
-        tl, th = cpu_sample_run(o, S, 1, rng)
-        per.append(tl / SAMPLE_LAYERS * 48 + th)
-    step_s = float(np.median(per))
-    value = 1.0 / step_s
+    value, step_s, threads, sample = cpu_reference(o, args.steps, max(1, min(args.warmup, 2)))
+    cfg = bench_config(1, 48, PROMPT, max(1, args.gpus))
+    cfg["parallelism"] = "cpu threads"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 x int4/int6 block dots, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "moe35b_a3b_q4km decode, batch 1, ctx 2176", "streams": 1, "prompt_tokens": PROMPT},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{SAMPLE_LAYERS} of 48 layers (QKV/O matmuls, paged attention at ctx 2176, router, "
-                                   f"MoE FFN) + lm_head per step, scaled to 48 layers; CPU restatement of DenseCore's "
-                                   f"ggml path"},
+        "config": cfg,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t_all,
     }
@@ -259,6 +266,120 @@ def op_gemv(ctx, ggml_type: int, N: int, K: int, M: int, ring: int, reps: int, p
             "floor_us": nbytes / peak_gbs / 1e3, "ring_copies": ring, "M": M}
 
 
+def op_moe_layer(ctx, T: int, reps: int, peak_gbs: float, weights=None) -> dict:
+    """One MoE FFN layer (hidden 2048, 128 experts top-8, FFN 768, gate/up Q4_K, down Q6_K, F32 router) on T
+    tokens, over a ring of different inputs so that successive calls route to different experts and read them
+    from HBM.  Bytes: router + 3 059 712 per distinct expert hit (counted from the returned ids) + 16 384 T."""
+    from densecore_b200 import blocks as B
+    H, F, E, k = 2048, 768, 128, 8
+    rng = np.random.default_rng(4242)
+    own = weights is None
+    if own:
+        router = (rng.normal(size=(E, H)) * 0.02).astype(np.float32)
+        weights = (ctx.upload_weight(B.GGML_TYPE_F32, router, H, E),
+                   ctx.upload_weight(B.GGML_TYPE_Q4_K, B.random_weight(rng, B.GGML_TYPE_Q4_K, E * F, H), H, F, E),
+                   ctx.upload_weight(B.GGML_TYPE_Q4_K, B.random_weight(rng, B.GGML_TYPE_Q4_K, E * F, H), H, F, E),
+                   ctx.upload_weight(B.GGML_TYPE_Q6_K, B.random_weight(rng, B.GGML_TYPE_Q6_K, E * H, F), F, H, E))
+    Wr, Wg, Wu, Wd = weights
+    ring = max(2, 48 // T)
+    xs = rng.normal(size=(ring, T, H)).astype(np.float32)
+    xd, yd, idd = ctx.alloc(xs.nbytes), ctx.alloc(T * H * 4), ctx.alloc(ring * T * k * 4)
+    ctx.to_device(xd, xs)
+
+    def enqueue():
+        for r in range(ring):
+            ctx.mul_mat_id_dev(Wr, Wg, Wu, Wd, xd + r * T * H * 4, T, k, yd, ids_dev=idd + r * T * k * 4)
+    us = _time_graph(ctx, enqueue, reps) / ring
+    ids = ctx.from_device(idd, np.zeros((ring, T * k), np.int32))
+    U = float(np.mean([len(set(r.tolist())) for r in ids]))
+    nbytes = E * H * 4 + U * 3059712 + T * 16384
+    for d in (xd, yd, idd):
+        ctx.free(d)
+    if own:
+        for w in weights:
+            w.free()
+    return {"T": T, "us": us, "distinct_experts": U, "bytes": nbytes, "gbs": nbytes / us / 1e3,
+            "frac": nbytes / us / 1e3 / peak_gbs, "floor_us": nbytes / peak_gbs / 1e3, "ring_inputs": ring}
+
+
+def moe_layer_sweep(ctx, reps, peak):
+    from densecore_b200 import blocks as B
+    H, F, E = 2048, 768, 128
+    rng = np.random.default_rng(4242)
+    router = (rng.normal(size=(E, H)) * 0.02).astype(np.float32)
+    weights = (ctx.upload_weight(B.GGML_TYPE_F32, router, H, E),
+               ctx.upload_weight(B.GGML_TYPE_Q4_K, B.random_weight(rng, B.GGML_TYPE_Q4_K, E * F, H), H, F, E),
+               ctx.upload_weight(B.GGML_TYPE_Q4_K, B.random_weight(rng, B.GGML_TYPE_Q4_K, E * F, H), H, F, E),
+               ctx.upload_weight(B.GGML_TYPE_Q6_K, B.random_weight(rng, B.GGML_TYPE_Q6_K, E * H, F), F, H, E))
+    out = [op_moe_layer(ctx, T, reps, peak, weights) for T in (1, 4, 8, 16)]
+    for w in weights:
+        w.free()
+    return out
+
+
+def bench_dense_0p8b(ctx, peak_gbs: float, n_decode: int = 256) -> dict:
+    """Config 2: dense 0.8B-class decoder, 512-token random prompt, greedy decode of 256 tokens at batch 1."""
+    import densecore_b200 as dc
+    cfg = dc.dense_0p8b(max_seqs=1, max_ctx=512 + n_decode + 64)
+    m = dc.Model(ctx, cfg)
+    m.init_synthetic(2, 0.02)
+    m.finalize()
+    rng = np.random.default_rng(2)
+    seq = m.seq_alloc()
+    t0 = time.perf_counter()
+    first = m.prefill(seq, rng.integers(0, cfg.vocab, size=512))
+    prefill_s = time.perf_counter() - t0
+    toks, _ = m.decode_run([seq], [first], 16)
+    toks, ms = m.decode_run([seq], toks[-1], n_decode - 16)
+    _, wbytes, kvb = m.step_stats()
+    ctx_mid = 512 + 16 + (n_decode - 16) // 2
+    step_bytes = wbytes + kvb * ctx_mid
+    tok_s = (n_decode - 16) / (ms * 1e-3)
+    m.close()
+    return {"tok_s": tok_s, "ms_per_step": ms / (n_decode - 16), "step_bytes": step_bytes,
+            "floor_tok_s": peak_gbs * 1e9 / step_bytes, "frac": tok_s * step_bytes / 1e9 / peak_gbs,
+            "prefill_512_ms": prefill_s * 1e3}
+
+
+def spec_sweep(ctx, model, cfg, rng, seqs_to_free) -> dict:
+    """Config 5: target = the benchmark model, draft = the dense 0.8B-class model, gamma 4, 1024-token prompt,
+    128 output tokens; greedy accept with synthetic drafts at forced 0 / 50 / 100 % acceptance, and the
+    stochastic rule at temperature 0.8 with the draft model's own sampled proposals."""
+    import densecore_b200 as dc
+    dcfg = dc.dense_0p8b(max_seqs=2, max_ctx=1024 + 512)
+    draft = dc.Model(ctx, dcfg)
+    draft.init_synthetic(4321, 0.02)
+    draft.finalize()
+    prompt = rng.integers(0, cfg.vocab, size=1024)
+    n_out, gamma = 128, 4
+    for s in seqs_to_free:
+        model.seq_free(s)   # the decode runs hold all four sequence slots
+    want, st0 = dc.speculative_decode(model, draft, prompt, n_out + gamma + 1, gamma=gamma)
+    out = {"gamma": gamma, "prompt_tokens": 1024, "output_tokens": n_out,
+           "draft_model_greedy": {"acceptance": st0.acceptance, "tokens_per_step": st0.tokens_per_step,
+                                  "tok_s": st0.emitted / st0.seconds, "ms_per_verify_step": st0.seconds / st0.steps * 1e3}}
+
+    def forced(rate):
+        def f(pos, g):
+            true = want[pos:pos + g].copy()
+            if rate == 0.0:
+                true[0] = (true[0] + 1) % cfg.vocab
+            elif rate == 0.5:
+                true[g // 2] = (true[g // 2] + 1) % cfg.vocab
+            return true
+        return f
+    for rate in (0.0, 0.5, 1.0):
+        got, st = dc.speculative_decode(model, draft, prompt, n_out, gamma=gamma, forced_drafts=forced(rate))
+        out[f"forced_{int(rate * 100)}"] = {"acceptance": st.acceptance, "tokens_per_step": st.tokens_per_step,
+                                            "tok_s": st.emitted / st.seconds, "ms_per_verify_step": st.seconds / st.steps * 1e3,
+                                            "equals_greedy_stream": bool(np.array_equal(got, want[:n_out]))}
+    got, st = dc.speculative_decode(model, draft, prompt, 64, gamma=gamma, mode=1, temperature=0.8, seed=99)
+    out["stochastic_T0.8"] = {"acceptance": st.acceptance, "tokens_per_step": st.tokens_per_step,
+                              "tok_s": st.emitted / st.seconds, "ms_per_verify_step": st.seconds / st.steps * 1e3}
+    draft.close()
+    return out
+
+
 def run_single_op(args) -> int:
     """--op: one operator alone (for profiling runs and for the per-config figures of the main line)."""
     import densecore_b200 as dc
@@ -271,6 +392,10 @@ def run_single_op(args) -> int:
         out = op_gemv(ctx, B.GGML_TYPE_Q4_K, 65536, 2048, 1, 4, args.steps, peak)
     elif args.op == "gemv-lm-head":
         out = op_gemv(ctx, B.GGML_TYPE_Q6_K, 151936, 2048, 1, 2, args.steps, peak)
+    elif args.op == "moe-layer":
+        out = {"T": moe_layer_sweep(ctx, args.steps, peak)}
+    elif args.op == "dense-0p8b":
+        out = bench_dense_0p8b(ctx, peak)
     else:
         raise SystemExit(f"unknown --op {args.op}")
     print(json.dumps({"op": args.op, **out}))
@@ -297,14 +422,11 @@ def main():
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: peer = the persistent kernel stores expert outputs into all GPUs' buffers over NVLink "
                          "(default); nccl = per-op kernels with one all-reduce per layer")
-    ap.add_argument("--spec-sweep", action="store_true",
-                    help="after the decode runs: speculative decoding (target = this model, draft = the dense 0.8B-class "
-                         "model, gamma 4, greedy accept), with the draft model's own proposals and with synthetic drafts "
-                         "at forced 0/50/100 %% acceptance; table to stderr")
     ap.add_argument("--streams", default="1,4", help="stream counts to time (the JSON line needs 1)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed 1-stream decode run with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--op", default=None, choices=["gemv-config1", "gemv-lm-head", "gemv-q4-big"],
+    ap.add_argument("--no-extras", action="store_true", help="skip the other workloads (single ops, dense model, speculative sweep)")
+    ap.add_argument("--op", default=None, choices=["gemv-config1", "gemv-lm-head", "gemv-q4-big", "moe-layer", "dense-0p8b"],
                     help="time one operator alone and print its own JSON line (not the benchmark line)")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -368,7 +490,12 @@ def main():
 
     rng = np.random.default_rng(0)
     seqs = [model.seq_alloc() for _ in range(4)]
-    first = [model.prefill(s, rng.integers(0, cfg.vocab, size=args.prompt)) for s in seqs]
+    prompts = [rng.integers(0, cfg.vocab, size=args.prompt) for _ in seqs]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    first = [model.prefill(seqs[0], prompts[0])]          # host prompt in, first token out: time to first token
+    ttft_ms = (time.perf_counter() - t0) * 1e3
+    first += [model.prefill(s, p) for s, p in zip(seqs[1:], prompts[1:])]
 
     def barrier():
         torch.cuda.synchronize()
@@ -469,35 +596,6 @@ def main():
                     print(f"    {name:20s} median-first {(np.median(a) - a.min()) / 1e3:6.2f}  last-median "
                           f"{(a.max() - np.median(a)) / 1e3:6.2f}  release-last {(np.median(r) - a.max()) / 1e3:6.2f}",
                           file=sys.stderr)
-    if args.spec_sweep and world == 1:
-        dcfg = dc.dense_0p8b(max_seqs=2, max_ctx=1024 + 512)
-        draft = dc.Model(ctx, dcfg)
-        draft.init_synthetic(4321, 0.02)
-        draft.finalize()
-        prompt = rng.integers(0, cfg.vocab, size=1024)
-        n_out, gamma = 128, 4
-        model.seq_free(seqs[3])   # the decode runs hold all four sequence slots
-        want, st0 = dc.speculative_decode(model, draft, prompt, n_out + gamma + 1, gamma=gamma)
-        print(f"speculative decoding, gamma {gamma}, greedy accept, 1024-token prompt, {n_out} output tokens:", file=sys.stderr)
-        print(f"  draft model's proposals: acceptance {st0.acceptance * 100:5.1f} %  {st0.tokens_per_step:4.2f} tokens/step  "
-              f"{st0.emitted / st0.seconds:7.1f} tok/s  {st0.seconds / st0.steps * 1e3:6.2f} ms/step", file=sys.stderr)
-
-        def forced(rate):
-            def f(pos, g):
-                true = want[pos:pos + g].copy()
-                if rate == 0.0:
-                    true[0] = (true[0] + 1) % cfg.vocab
-                elif rate == 0.5:
-                    true[g // 2] = (true[g // 2] + 1) % cfg.vocab
-                return true
-            return f
-        for rate in (0.0, 0.5, 1.0):
-            got, st = dc.speculative_decode(model, draft, prompt, n_out, gamma=gamma, forced_drafts=forced(rate))
-            ok = bool(np.array_equal(got, want[:n_out]))
-            print(f"  synthetic drafts {rate * 100:3.0f} %:  acceptance {st.acceptance * 100:5.1f} %  {st.tokens_per_step:4.2f} "
-                  f"tokens/step  {st.emitted / st.seconds:7.1f} tok/s  {st.seconds / st.steps * 1e3:6.2f} ms/verify step  "
-                  f"tokens equal the target's greedy stream: {ok}", file=sys.stderr)
-        draft.close()
     if args.profile_classes and rank == 0:
         for n_streams in stream_counts:
             last = results[n_streams]["last"][:n_streams]
@@ -509,15 +607,24 @@ def main():
                 print(f"  {k:22s} launches {n_:4d}  {ms_ * 1e3:9.1f} us  {ms_ / tot * 100:5.1f} %  "
                       f"{b_ / n_ / 1e6:8.2f} MB/launch  {b_ / (ms_ * 1e-3) / 1e9 if ms_ else 0:8.1f} GB/s", file=sys.stderr)
 
+    extras = {}
+    if world == 1 and not args.no_extras:
+        # the other workloads of the benchmark family, each on its own configuration (not the headline number)
+        extras["gemv_6144x2048_q4k"] = op_gemv(ctx, 12, 6144, 2048, 1, 32, 20, peak_gbs)
+        extras["lm_head_151936x2048_q6k"] = op_gemv(ctx, 14, 151936, 2048, 1, 2, 20, peak_gbs)
+        extras["moe_layer"] = moe_layer_sweep(ctx, 20, peak_gbs)
+        extras["dense_0p8b_decode"] = bench_dense_0p8b(ctx, peak_gbs)
+        extras["speculative"] = spec_sweep(ctx, model, cfg, rng, seqs[3:])
+        seqs = seqs[:3]
+
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 x int4/int6 block dots (dp4a), f32 accumulate", "data": "synthetic",
-        "config": {"workload": "moe35b_a3b_q4km decode: 48 layers, hidden 2048, 128 experts top-8, vocab 151936; "
-                               "2048-token random prompt per stream, greedy, paged fp16 KV",
-                   "streams": 1, "layers": args.layers, "prompt_tokens": args.prompt, "ctx_at_timing": r1["ctx"],
-                   "parallelism": f"ep{world}", "path": "persistent kernel" if persistent else "per-op CUDA graph",
-                   "l2": "each step reads ~1.9 GB of weights, far more than the 126 MB L2, so no flush is needed"},
+        "config": dict(bench_config(1, args.layers, args.prompt, world), ctx_at_timing=r1["ctx"],
+                       path="persistent kernel" if persistent else "per-op CUDA graph",
+                       l2="each step reads ~1.9 GB of weights, far more than the 126 MB L2, so no flush is needed"),
+        "ttft_ms": ttft_ms,
         "hbm_fraction_of_step": step_bytes / (ms_per_step * 1e-3) / 1e9 / (peak_gbs * world),
         "e2e": {"value": args.steps / r1["e2e_s"], "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4,
                 "api": "dc_b200_decode_step"},
@@ -527,21 +634,23 @@ def main():
     }
     if 4 in results:
         r4 = results[4]
+        # bytes of a 4-stream step: shared weights once, the distinct experts four tokens route to (expected
+        # 128 (1 - (1 - 8/128)^4) = 29.1 of 128 per layer under uniform routing), four K/V histories
+        n_moe = args.layers
+        expert_bytes = 3059712
+        shared = weight_bytes - n_moe * 8 * expert_bytes
+        b4 = shared + n_moe * 29.1 * expert_bytes + 4 * kv_bytes_per_tok * (r4["ctx"] - args.steps // 2)
         line["streams4"] = {"value": 4 * args.steps / (r4["ms"] * 1e-3), "ms_per_step": r4["ms"] / args.steps,
-                            "e2e": 4 * args.steps / r4["e2e_s"], "ctx_at_timing": r4["ctx"]}
+                            "e2e": 4 * args.steps / r4["e2e_s"], "ctx_at_timing": r4["ctx"],
+                            "step_bytes_expected": b4,
+                            "hbm_fraction_of_step": b4 / (r4["ms"] / args.steps * 1e-3) / 1e9 / (peak_gbs * world)}
+    if extras:
+        line["other_workloads"] = extras
     if rank == 0 and not args.no_cpu_baseline:
         from oracle import oracle as o
         o.build()
-        threads = o.max_threads()
-        o.set_threads(threads)
-        S = cpu_sample_setup(SAMPLE_LAYERS, r1["ctx"])
-        cpu_sample_run(o, S, 1, rng)
-        cpu_sample_run(o, S, 1, rng)
-        v, step_s = cpu_tok_s(o, S, 1, SAMPLE_REPS, rng)
-        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"{SAMPLE_LAYERS} of 48 layers + lm_head of one batch-1 decode step at ctx "
-                                          f"{r1['ctx']}, median of {SAMPLE_REPS} repeats, scaled to 48 layers; CPU restatement of DenseCore's "
-                                          f"ggml path"}
+        v, step_s, threads, sample = cpu_reference(o, SAMPLE_REPS)
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
     if rank == 0:
         print(json.dumps(line))
     model.close()

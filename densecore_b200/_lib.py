@@ -79,6 +79,7 @@ def _signatures() -> dict:
         "dc_b200_copy_to_device": (i32, [vp, vp, vp, sz]),
         "dc_b200_copy_from_device": (i32, [vp, vp, vp, sz]),
         "dc_b200_mul_mat_id": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
+        "dc_b200_mul_mat_id_dev": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
         "dc_b200_moe_route": (i32, [vp, vp, i32, i32, i32, f32, vp, vp]),
         "dc_b200_kv_create": (i32, [vp, i32, i32, i32, i32, i32, i32, pp]),
         "dc_b200_kv_destroy": (None, [vp]),
@@ -94,6 +95,7 @@ def _signatures() -> dict:
         "dc_b200_verify_uniforms": (i32, [vp, u64, u32, i32, vp]),
         "dc_b200_verify_accept_dev": (i32, [vp, vp, vp, vp, vp, u64, u32, i32, i32, i32, f32, pi, pi]),
         "dc_b200_softmax": (i32, [vp, vp, i32, i32, f32, vp]),
+        "dc_b200_sample_dev": (i32, [vp, vp, i32, f32, f32, vp, pi]),
         "dc_b200_model_create": (i32, [vp, C.POINTER(ModelConfig), pp]),
         "dc_b200_model_destroy": (None, [vp]),
         "dc_b200_model_set_tensor": (i32, [vp, cstr, i32, C.POINTER(i64), vp]),

@@ -131,3 +131,6 @@ int dc_launch_verify(dc_ctx* ctx, int mode, int gamma, int vocab, const float* t
                      int32_t* argmax_scratch, float* probs_scratch, int32_t* result);
 int dc_launch_verify_uniforms(dc_ctx* ctx, unsigned long long seed, uint32_t step, int n, float* u);
 int dc_launch_det_softmax(dc_ctx* ctx, const float* logits, int rows, int n, float temperature, float* probs);
+// probs = softmax(logits / temperature); *result = inverse-CDF draw with the uniform at u_dev
+int dc_launch_sample(dc_ctx* ctx, const float* logits, int n, float temperature, const float* u_dev, float* probs,
+                     int32_t* result);

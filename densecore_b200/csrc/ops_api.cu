@@ -97,51 +97,88 @@ int dc_b200_moe_route(dc_ctx* ctx, const float* logits_host, int T, int n_expert
     return dc_b200_synchronize(ctx);
 }
 
-int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
-                       const dc_weight* down, const float* x_host, int T, int top_k, float routed_scale,
-                       float* y_host, int32_t* ids_out, float* weights_out) {
-    if (!ctx) return DC_B200_INVALID_ARGUMENT;
-    if (!router || !gate || !up || !down || !x_host || !y_host || T < 1 || T > DC_MAX_T)
+static int mul_mat_id_check(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
+                            const dc_weight* down, int T, int top_k) {
+    if (!router || !gate || !up || !down || T < 1 || T > DC_MAX_T)
         return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: bad argument (T=%d)", T);
     const int H = (int)gate->K, F = (int)gate->N, E = (int)gate->E;
-    auto fail_closed = [&](int st) {
-        memset(y_host, 0, (size_t)T * H * sizeof(float));  // zero-fill on failure (moe/exec.cpp:397-414)
-        return st;
-    };
     if (router->K != H || router->N != E || up->K != H || up->N != F || up->E != E || down->K != F || down->N != H ||
         down->E != E)
-        return fail_closed(dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: tensor shapes do not agree"));
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: tensor shapes do not agree");
     if (E < 1 || E > 256 || top_k < 1 || top_k > 16 || top_k > E)
-        return fail_closed(dc_fail(ctx, DC_B200_UNSUPPORTED, "mul_mat_id: n_expert=%d top_k=%d out of range (1..256 experts, top_k <= min(16, n_expert))", E, top_k));
-    if (H % 256 || F % 256) return fail_closed(dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: hidden and ffn sizes must be multiples of 256"));
+        return dc_fail(ctx, DC_B200_UNSUPPORTED, "mul_mat_id: n_expert=%d top_k=%d out of range (1..256 experts, top_k <= min(16, n_expert))", E, top_k);
+    if (H % 256 || F % 256) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: hidden and ffn sizes must be multiples of 256");
+    return DC_B200_OK;
+}
+
+// Enqueues one MoE layer on device buffers: x_dev [T, H] -> y_dev [T, H]; ids_dev / w_dev (optional) receive the
+// routing.  Scratch comes from the context (grown on first use).
+int dc_b200_mul_mat_id_dev(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
+                           const dc_weight* down, const float* x_dev, int T, int top_k, float routed_scale,
+                           float* y_dev, int32_t* ids_dev, float* weights_dev) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!x_dev || !y_dev) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id_dev: null buffer");
+    DC_TRY(mul_mat_id_check(ctx, router, gate, up, down, T, top_k));
+    const int H = (int)gate->K, F = (int)gate->N, E = (int)gate->E;
     cudaSetDevice(ctx->device);
     const int A = T * top_k;
     dc_moe_route rt_size;
-    const size_t need = (size_t)T * H * 4 * 3 + (size_t)T * (H / 256) * 292 + (size_t)A * F * 4 +
-                        (size_t)A * (F / 256) * 292 + (size_t)A * H * 4 + dc_moe_route_bind(&rt_size, nullptr, T, E, top_k) + 4096;
+    const size_t need = (size_t)T * (H / 256) * 292 + (size_t)A * F * 4 + (size_t)A * (F / 256) * 292 + (size_t)A * H * 4 +
+                        dc_moe_route_bind(&rt_size, nullptr, T, E, top_k) + 4096;
     uint8_t* s = dc_scratch(ctx, need);
-    if (!s) return fail_closed(DC_B200_OUT_OF_MEMORY);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
     Bump b{s};
-    float* x = b.take<float>((size_t)T * H);
-    float* y = b.take<float>((size_t)T * H);
     uint8_t* xq = b.take<uint8_t>((size_t)T * (H / 256) * 292);
     float* h = b.take<float>((size_t)A * F);
     uint8_t* hq = b.take<uint8_t>((size_t)A * (F / 256) * 292);
     float* dn = b.take<float>((size_t)A * H);
     dc_moe_route rt;
     dc_moe_route_bind(&rt, s + b.off, T, E, top_k);
-    int st = dc_check_cuda(ctx, cudaMemsetAsync(rt.ticket, 0, sizeof(int), ctx->stream), "memset");
-    if (st == DC_B200_OK) st = h2d(ctx, x, x_host, (size_t)T * H * 4);
-    if (st == DC_B200_OK) st = dc_launch_router(ctx, router, x, E, T, top_k, routed_scale, 0, E, &rt, ctx->route_mode);
-    if (st == DC_B200_OK) st = dc_launch_quantize_q8k(ctx, x, T, H, xq);
-    if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, true, gate, up, xq, T, T, top_k, 0, &rt, h);
-    if (st == DC_B200_OK) st = dc_launch_quantize_q8k(ctx, h, A, F, hq);
-    if (st == DC_B200_OK) st = dc_launch_moe_mm(ctx, false, down, nullptr, hq, A, T, top_k, 0, &rt, dn);
-    if (st == DC_B200_OK) st = dc_launch_moe_combine(ctx, dn, rt.ids, rt.weights, T, top_k, H, 0, E, y);
-    if (st == DC_B200_OK) st = d2h(ctx, y_host, y, (size_t)T * H * 4);
-    if (st == DC_B200_OK && ids_out) st = d2h(ctx, ids_out, rt.ids, (size_t)A * 4);
-    if (st == DC_B200_OK && weights_out) st = d2h(ctx, weights_out, rt.weights, (size_t)A * 4);
+    DC_TRY(dc_check_cuda(ctx, cudaMemsetAsync(rt.ticket, 0, sizeof(int), ctx->stream), "memset"));
+    DC_TRY(dc_launch_router(ctx, router, x_dev, E, T, top_k, routed_scale, 0, E, &rt, ctx->route_mode));
+    DC_TRY(dc_launch_quantize_q8k(ctx, x_dev, T, H, xq));
+    DC_TRY(dc_launch_moe_mm(ctx, true, gate, up, xq, T, T, top_k, 0, &rt, h));
+    DC_TRY(dc_launch_quantize_q8k(ctx, h, A, F, hq));
+    DC_TRY(dc_launch_moe_mm(ctx, false, down, nullptr, hq, A, T, top_k, 0, &rt, dn));
+    DC_TRY(dc_launch_moe_combine(ctx, dn, rt.ids, rt.weights, T, top_k, H, 0, E, y_dev));
+    if (ids_dev) DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(ids_dev, rt.ids, (size_t)A * 4, cudaMemcpyDeviceToDevice, ctx->stream), "ids"));
+    if (weights_dev) DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(weights_dev, rt.weights, (size_t)A * 4, cudaMemcpyDeviceToDevice, ctx->stream), "weights"));
+    return DC_B200_OK;
+}
+
+int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
+                       const dc_weight* down, const float* x_host, int T, int top_k, float routed_scale,
+                       float* y_host, int32_t* ids_out, float* weights_out) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!gate || !x_host || !y_host || T < 1 || T > DC_MAX_T)
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: bad argument (T=%d)", T);
+    const int H = (int)gate->K;
+    auto fail_closed = [&](int st) {
+        memset(y_host, 0, (size_t)T * H * sizeof(float));  // zero-fill on failure (moe/exec.cpp:397-414)
+        return st;
+    };
+    int st = mul_mat_id_check(ctx, router, gate, up, down, T, top_k);
+    if (st != DC_B200_OK) return fail_closed(st);
+    cudaSetDevice(ctx->device);
+    const int A = T * top_k;
+    // staging buffers of this call live in pinned-size device allocations of their own (the context's scratch
+    // belongs to the device-level call)
+    float *x = nullptr, *y = nullptr, *w = nullptr;
+    int32_t* ids = nullptr;
+    const size_t xb = (size_t)T * H * 4;
+    cudaError_t e = cudaMalloc((void**)&x, 2 * xb + (size_t)A * 8 + 1024);
+    if (e != cudaSuccess) return fail_closed(dc_check_cuda(ctx, e, "mul_mat_id staging"));
+    y = (float*)((uint8_t*)x + xb);
+    ids = (int32_t*)((uint8_t*)y + xb);
+    w = (float*)(ids + A);
+    st = h2d(ctx, x, x_host, xb);
+    if (st == DC_B200_OK) st = dc_b200_mul_mat_id_dev(ctx, router, gate, up, down, x, T, top_k, routed_scale, y, ids, w);
+    if (st == DC_B200_OK) st = d2h(ctx, y_host, y, xb);
+    if (st == DC_B200_OK && ids_out) st = d2h(ctx, ids_out, ids, (size_t)A * 4);
+    if (st == DC_B200_OK && weights_out) st = d2h(ctx, weights_out, w, (size_t)A * 4);
     if (st == DC_B200_OK) st = dc_b200_synchronize(ctx);
+    else cudaStreamSynchronize(ctx->stream);
+    cudaFree(x);
     return st == DC_B200_OK ? st : fail_closed(st);
 }
 
@@ -245,6 +282,28 @@ int dc_b200_softmax(dc_ctx* ctx, const float* logits_host, int rows, int n, floa
     DC_TRY(dc_launch_det_softmax(ctx, l, rows, n, temperature, p));
     DC_TRY(d2h(ctx, probs_host, p, (size_t)rows * n * 4));
     return dc_b200_synchronize(ctx);
+}
+
+// Temperature sampling on device-resident logits: probs_dev [vocab] receives softmax(logits / temperature)
+// (the draft distribution q of a speculative step), *token_out one draw from it by inverse CDF with uniform u.
+int dc_b200_sample_dev(dc_ctx* ctx, const float* logits_dev, int vocab, float temperature, float u, float* probs_dev,
+                       int32_t* token_out) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!logits_dev || !probs_dev || !token_out || vocab < 2 || !(temperature > 0.0f) || !(u >= 0.0f && u < 1.0f))
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "sample_dev: bad argument");
+    cudaSetDevice(ctx->device);
+    uint8_t* s = dc_scratch(ctx, 1024);
+    if (!s) return DC_B200_OUT_OF_MEMORY;
+    float* ud = (float*)s;
+    int32_t* res = (int32_t*)(s + 256);
+    DC_TRY(h2d(ctx, ud, &u, 4));
+    DC_TRY(dc_check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "sync"));   // `u` is a stack value
+    DC_TRY(dc_launch_sample(ctx, logits_dev, vocab, temperature, ud, probs_dev, res));
+    int32_t out = -1;
+    DC_TRY(d2h(ctx, &out, res, 4));
+    DC_TRY(dc_b200_synchronize(ctx));
+    *token_out = out;
+    return DC_B200_OK;
 }
 
 int dc_b200_verify_accept(dc_ctx* ctx, const float* target_logits_host, const int32_t* draft_tokens,

@@ -233,6 +233,27 @@ int dc_launch_verify(dc_ctx* ctx, int mode, int gamma, int vocab, const float* t
     return dc_check_cuda(ctx, cudaGetLastError(), "k_verify_accept");
 }
 
+// One draw from probabilities p[n] (not necessarily normalised) by the same fixed-shape inverse CDF the
+// verify step uses for its resampling; *u is the uniform.
+__global__ void __launch_bounds__(1024) k_sample_cdf(const float* __restrict__ p, int n, const float* __restrict__ u,
+                                                     int32_t* __restrict__ result) {
+    __shared__ float runsum[CDF_MAX_RUNS];
+    __shared__ float chunksum[CDF_MAX_RUNS / 32];
+    const int tok = det_inverse_cdf_cta(p, nullptr, n, *u, runsum, chunksum);
+    if (threadIdx.x == 0) *result = tok;
+}
+
+int dc_launch_sample(dc_ctx* ctx, const float* logits, int n, float temperature, const float* u_dev, float* probs,
+                     int32_t* result) {
+    if (n > CDF_MAX_RUNS * 32) return dc_fail(ctx, DC_B200_UNSUPPORTED, "sample: vocab %d too large", n);
+    if (!(temperature > 0.0f)) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "sample: temperature must be > 0");
+    k_det_softmax<<<1, DET_LANES, 0, ctx->stream>>>(logits, n, 1.0f / temperature, probs);
+    int st = dc_check_cuda(ctx, cudaGetLastError(), "k_det_softmax");
+    if (st != DC_B200_OK) return st;
+    k_sample_cdf<<<1, 1024, 0, ctx->stream>>>(probs, n, u_dev, result);
+    return dc_check_cuda(ctx, cudaGetLastError(), "k_sample_cdf");
+}
+
 int dc_launch_verify_uniforms(dc_ctx* ctx, unsigned long long seed, uint32_t step, int n, float* u) {
     k_verify_uniforms<<<1, 32, 0, ctx->stream>>>(seed, step, n, u);
     return dc_check_cuda(ctx, cudaGetLastError(), "k_verify_uniforms");

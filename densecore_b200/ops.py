@@ -139,6 +139,14 @@ class Context:
         self._check(_lib.lib().dc_b200_copy_from_device(self.handle, _vp(out), C.c_void_p(dev), out.nbytes))
         return out
 
+    def mul_mat_id_dev(self, router: Weight, gate: Weight, up: Weight, down: Weight, x_dev: int, T: int, top_k: int,
+                       y_dev: int, ids_dev: int = 0, weights_dev: int = 0, routed_scale: float = 1.0):
+        """Device-pointer form of mul_mat_id (enqueue only)."""
+        self._check(_lib.lib().dc_b200_mul_mat_id_dev(self.handle, router.handle, gate.handle, up.handle, down.handle,
+                                                      C.c_void_p(x_dev), int(T), int(top_k), routed_scale, C.c_void_p(y_dev),
+                                                      C.c_void_p(ids_dev) if ids_dev else None,
+                                                      C.c_void_p(weights_dev) if weights_dev else None))
+
     # ---- MUL_MAT_ID
     def mul_mat_id(self, router: Weight, gate: Weight, up: Weight, down: Weight, x: np.ndarray, top_k: int,
                    routed_scale: float = 1.0):

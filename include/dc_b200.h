@@ -145,6 +145,12 @@ DC_B200_API int dc_b200_copy_from_device(dc_ctx* ctx, void* dst_host, const void
 DC_B200_API int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
                                    const dc_weight* down, const float* x_host, int T, int top_k, float routed_scale,
                                    float* y_host, int32_t* ids_out, float* weights_out);
+/* The same layer on device buffers (x_dev [T, hidden], y_dev [T, hidden], optional ids_dev / weights_dev
+ * [T, top_k]): what the body of cb_moe_forward calls when the graph's tensors already live on the GPU.  Only
+ * enqueues on the context's stream. */
+DC_B200_API int dc_b200_mul_mat_id_dev(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
+                                       const dc_weight* down, const float* x_dev, int T, int top_k,
+                                       float routed_scale, float* y_dev, int32_t* ids_dev, float* weights_dev);
 /* Routing alone from given logits [T, n_expert] (RouteMoESoftmaxTopK, core/src/llm/moe/exec.cpp:734);
  * which of the reference's two routers runs is the context option "route_mode".  1 <= n_expert <= 256,
  * 1 <= top_k <= min(16, n_expert), else DC_B200_UNSUPPORTED with nothing launched. */
@@ -205,6 +211,12 @@ DC_B200_API int dc_b200_verify_accept_dev(dc_ctx* ctx, const float* target_logit
                                           uint32_t step, int gamma, int vocab, int mode, float temperature,
                                           int32_t* n_accepted, int32_t* next_token);
 DC_B200_API int dc_b200_verify_uniforms(dc_ctx* ctx, uint64_t seed, uint32_t step, int n, float* out_host);
+/* Temperature sampling of one token from device-resident logits [vocab] (the sampler site,
+ * core/src/sampler/sampler.cpp:235-262: v * (1/T), minus max, exp, * 1/sum; here with the verify step's fully
+ * specified exp and sums, and an inverse-CDF draw in index order with the uniform u in [0, 1)).  probs_dev
+ * [vocab] keeps the distribution: it is the q a later dc_b200_verify_accept_dev (mode 1) needs for this token. */
+DC_B200_API int dc_b200_sample_dev(dc_ctx* ctx, const float* logits_dev, int vocab, float temperature, float u,
+                                   float* probs_dev, int32_t* token_out);
 DC_B200_API int dc_b200_softmax(dc_ctx* ctx, const float* logits_host, int rows, int n, float temperature,
                                 float* probs_host);
 

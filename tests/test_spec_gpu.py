@@ -60,3 +60,33 @@ def test_speculative_decode_emits_the_targets_greedy_tokens(ctx):
         assert abs(st.tokens_per_step - per_step) < 1e-9, (rate, st.tokens_per_step)
     target.close()
     draft.close()
+
+
+def test_stochastic_speculative_decode_replays_on_the_cpu(ctx, oracle):
+    """Config-5 style loop at temperature 0.8 with sampled drafts: every decision the device takes (the draft's
+    sampled tokens, how many are accepted, the resampled or bonus token) is replayed by the CPU restatement of
+    the rule from the very logits the device used and the same Philox uniforms, and must agree bit for bit."""
+    from densecore_b200.spec import DRAFT_STREAM
+    target, draft = models(ctx)
+    prompt = np.random.default_rng(3).integers(0, 1000, size=24)
+    gamma, T, seed = 4, 0.8, 777
+    trace = []
+    got, st = dc.speculative_decode(target, draft, prompt, 40, gamma=gamma, mode=1, temperature=T, seed=seed, trace=trace)
+    assert st.steps == len(trace) and st.emitted == st.accepted + st.steps
+    seen = set()
+    pos = 1
+    for rec in trace:
+        u_d = oracle.verify_uniforms(seed ^ DRAFT_STREAM, rec["step"], gamma)
+        q = np.stack([oracle.det_softmax(r, T) for r in rec["draft_logits"]])
+        drafts = [oracle.det_inverse_cdf(q[i], float(u_d[i])) for i in range(gamma)]
+        assert drafts == rec["drafts"].tolist(), rec["step"]
+        u = oracle.verify_uniforms(seed, rec["step"], gamma + 1)
+        n_acc, nxt = oracle.verify_accept(rec["target_logits"], drafts, q, u, 1, T)
+        assert (n_acc, nxt) == (rec["n_accepted"], rec["next_token"]), rec["step"]
+        emitted = drafts[:n_acc] + [nxt]
+        assert got[pos:pos + len(emitted)].tolist() == emitted[:max(0, len(got) - pos)]
+        pos += len(emitted)
+        seen.add(n_acc)
+    assert len(seen) > 1, "accepts and rejections should both occur"
+    target.close()
+    draft.close()
