@@ -9,6 +9,7 @@ from ._lib import DcError
 from .ops import Context, KVCache, Weight
 from .model import Config, Model, dense_0p8b, moe_35b_a3b, tensor_seed
 from .spec import speculative_decode
+from .sched import Scheduler
 
-__all__ = ["Context", "Weight", "KVCache", "Model", "Config", "dense_0p8b", "moe_35b_a3b", "tensor_seed", "speculative_decode", "DcError", "GGML_TYPE_F32", "GGML_TYPE_F16", "GGML_TYPE_Q4_K", "GGML_TYPE_Q6_K",
+__all__ = ["Context", "Weight", "KVCache", "Model", "Config", "dense_0p8b", "moe_35b_a3b", "tensor_seed", "speculative_decode", "Scheduler", "DcError", "GGML_TYPE_F32", "GGML_TYPE_F16", "GGML_TYPE_Q4_K", "GGML_TYPE_Q6_K",
            "QK_K", "row_bytes"]

@@ -80,6 +80,7 @@ def _signatures() -> dict:
         "dc_b200_copy_from_device": (i32, [vp, vp, vp, sz]),
         "dc_b200_mul_mat_id": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
         "dc_b200_mul_mat_id_dev": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
+        "dc_b200_moe_forward": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32, vp, vp, vp]),
         "dc_b200_moe_route": (i32, [vp, vp, i32, i32, i32, f32, vp, vp]),
         "dc_b200_kv_create": (i32, [vp, i32, i32, i32, i32, i32, i32, pp]),
         "dc_b200_kv_destroy": (None, [vp]),
@@ -88,6 +89,16 @@ def _signatures() -> dict:
         "dc_b200_kv_seq_reserve": (i32, [vp, i32, i32]),
         "dc_b200_kv_block_table": (i32, [vp, i32, vp, i32, pi]),
         "dc_b200_kv_free_blocks": (i32, [vp]),
+        "dc_b200_kv_prefix_attach": (i32, [vp, i32, vp, i32, pi]),
+        "dc_b200_kv_prefix_register": (i32, [vp, i32, vp, i32]),
+        "dc_b200_kv_prefix_stats": (i32, [vp, vp]),
+        "dc_b200_model_prefix_stats": (i32, [vp, vp]),
+        "dc_b200_sched_create": (i32, [vp, i32, i32, i32, pp]),
+        "dc_b200_sched_destroy": (None, [vp]),
+        "dc_b200_sched_add": (i32, [vp, vp, i32, i32, pi]),
+        "dc_b200_sched_step": (i32, [vp, vp, i32, pi]),
+        "dc_b200_sched_pending": (i32, [vp]),
+        "dc_b200_sched_stats": (i32, [vp, vp]),
         "dc_b200_flash_attn_decode": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, vp]),
         "dc_b200_kv_read_block": (i32, [vp, i32, i32, vp, vp]),
         "dc_b200_argmax": (i32, [vp, vp, i32, i32, vp]),

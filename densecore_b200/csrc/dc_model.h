@@ -75,6 +75,8 @@ struct dc_model {
     // bounded-wait test hooks: poll limits of the persistent kernel's waits (0 = the defaults)
     unsigned test_barrier_polls = 0;
     unsigned long long test_ep_wait_ns = 0;
+    bool prefix_cache = false;            // option "prefix_cache": prefill looks up and registers block prefixes
+    uint64_t prefill_tokens_run = 0;      // prompt tokens that went through the decoder (cached ones do not)
     // expert parallel
     bool ep_ready = false;
     void* ep_comm = nullptr;     // ncclComm_t
@@ -96,6 +98,9 @@ void dc_mega_release_xch(dc_model* m);
 struct MegaParams;
 bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why);
 int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback);
+// Appends tokens[0..n) to a sequence in chunks; if `final`, the last chunk also picks the next token (and leaves
+// its logits in the step buffer) and *next_token receives it after a synchronize.
+int dc_model_prefill_range(dc_model* m, int seq, const int32_t* tokens_host, int n, bool final, int32_t* next_token);
 int dc_mega_prepare(dc_model* m);
 // ---- ep.cu ----
 int dc_ep_allreduce(dc_model* m, float* buf, size_t n);

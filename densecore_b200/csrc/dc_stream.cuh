@@ -389,7 +389,9 @@ struct MoeStream {
                 tok[s] = pair ? asg[s] / p.top_k : asg[s];
             }
             // most experts of a step serve a single token: that case runs the one-token body
+            // and at 8 or 16 tokens per step few experts serve more than four
             if (NT > 1 && nt == 1) stage_rows<1>(p, act, buf, skew0, skew1, pair, r, n, nt, tok, asg, G, lane);
+            else if (NT > 4 && nt <= 4) stage_rows<4>(p, act, buf, skew0, skew1, pair, r, n, nt, tok, asg, G, lane);
             else stage_rows<NT>(p, act, buf, skew0, skew1, pair, r, n, nt, tok, asg, G, lane);
             pipe.release();
             if (lane == 0) issue_next(p, pipe);

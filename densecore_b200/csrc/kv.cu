@@ -33,7 +33,40 @@ int dc_kv_init(dc_ctx* ctx, dc_kv_cache* kv, int n_layer, int n_kv_head, int hea
     for (int b = max_blocks - 1; b >= 0; --b) kv->free_list.push_back(b);
     kv->ref.assign(max_blocks, 0);
     kv->seqs.assign(max_seqs, dc_kv_seq());
+    kv->prefix.clear();
+    kv->block_hash.assign(max_blocks, 0);
+    kv->block_tokens.assign(max_blocks, std::array<int32_t, 16>());
+    kv->block_used.assign(max_blocks, 0);
     return DC_B200_OK;
+}
+
+// Blocks an allocation can get: the free list plus cached blocks that only the prefix cache still holds.
+int dc_kv_available_blocks(const dc_kv_cache* kv) {
+    int n = (int)kv->free_list.size();
+    for (int b = 0; b < kv->max_blocks; ++b)
+        if (kv->block_hash[b] && kv->ref[b] == 1) ++n;
+    return n;
+}
+
+// A block for a new owner (reference count 1), evicting the least recently used cached block that no
+// sequence holds when the free list is empty; -1 if there is none.
+static int take_block(dc_kv_cache* kv) {
+    if (kv->free_list.empty()) {
+        int victim = -1;
+        for (int b = 0; b < kv->max_blocks; ++b)
+            if (kv->block_hash[b] && kv->ref[b] == 1 && (victim < 0 || kv->block_used[b] < kv->block_used[victim])) victim = b;
+        if (victim < 0) return -1;
+        auto it = kv->prefix.find(kv->block_hash[victim]);
+        if (it != kv->prefix.end() && it->second == victim) kv->prefix.erase(it);
+        kv->block_hash[victim] = 0;
+        kv->ref[victim] = 0;
+        ++kv->prefix_evictions;
+        kv->free_list.push_back(victim);
+    }
+    const int b = kv->free_list.back();
+    kv->free_list.pop_back();
+    kv->ref[b] = 1;
+    return b;
 }
 
 void dc_kv_release(dc_kv_cache* kv) {
@@ -132,10 +165,8 @@ int dc_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens) {
     for (int lb = s.len / DC_KV_BLOCK; lb < have && lb < need; ++lb) {
         const int old = s.blocks[lb];
         if (kv->ref[old] <= 1) continue;
-        if (kv->free_list.empty()) return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: out of blocks (copy-on-write)");
-        const int fresh = kv->free_list.back();
-        kv->free_list.pop_back();
-        kv->ref[fresh] = 1;
+        const int fresh = take_block(kv);
+        if (fresh < 0) return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: out of blocks (copy-on-write)");
         --kv->ref[old];
         const size_t be = (size_t)DC_KV_BLOCK * kv->n_kv * kv->head_dim;
         k_kv_copy_block<<<dim3(kv->n_layer, 2), 256, 0, kv->ctx->stream>>>(kv->k_arena, kv->v_arena, kv->layer_elems, be, old, fresh);
@@ -146,16 +177,84 @@ int dc_kv_seq_reserve(dc_kv_cache* kv, int seq, int n_tokens) {
         if (st != DC_B200_OK) return st;
     }
     if (need <= have) return DC_B200_OK;
-    if ((int)kv->free_list.size() < need - have)
+    if ((int)kv->free_list.size() < need - have && dc_kv_available_blocks(kv) < need - have)
         return dc_fail(kv->ctx, DC_B200_OUT_OF_MEMORY, "kv: out of blocks (%d free, %d needed)",
-                       (int)kv->free_list.size(), need - have);
-    for (int i = have; i < need; ++i) {
-        const int b = kv->free_list.back();
-        kv->free_list.pop_back();
-        kv->ref[b] = 1;
-        s.blocks.push_back(b);
-    }
+                       dc_kv_available_blocks(kv), need - have);
+    for (int i = have; i < need; ++i) s.blocks.push_back(take_block(kv));
     return upload_table(kv, seq, have, need - have);
+}
+
+// FNV-1a over the token ids, one 64-bit step per token, continued from h (start: 14695981039346656037);
+// BlockManager::ComputeTokenHash, core/src/runtime/memory/kv_cache_block_manager.cpp:515-522, without a salt.
+uint64_t dc_kv_token_hash(uint64_t h, const int32_t* tokens, int n) {
+    for (int i = 0; i < n; ++i) {
+        h ^= (uint64_t)(int64_t)tokens[i];
+        h *= 1099511628211ULL;
+    }
+    return h;
+}
+
+// Longest cached prefix of whole blocks for a sequence that holds nothing yet
+// (FindLongestCachedPrefixWithVerification, kv_cache_block_manager.cpp:364-416): block i is looked up under the
+// hash of tokens[0 .. 16 (i + 1)) and accepted only if its stored tokens equal tokens[16 i .. 16 (i + 1)).
+// At least one token is always left to run, so that the prompt's last logits are computed as usual.
+// The matched blocks join the sequence's table as shared blocks; *cached_tokens of its positions are then filled.
+int dc_kv_prefix_attach(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens, int* cached_tokens) {
+    *cached_tokens = 0;
+    if (seq < 0 || seq >= kv->max_seqs || !kv->seqs[seq].used)
+        return dc_fail(kv->ctx, DC_B200_INVALID_ARGUMENT, "kv: sequence %d is not allocated", seq);
+    dc_kv_seq& s = kv->seqs[seq];
+    if (s.len != 0 || !s.blocks.empty())
+        return dc_fail(kv->ctx, DC_B200_INVALID_ARGUMENT, "kv: prefix lookup needs an empty sequence (sequence %d holds %d tokens)", seq, s.len);
+    ++kv->prefix_lookups;
+    if (!tokens || n_tokens <= DC_KV_BLOCK) return DC_B200_OK;
+    int reusable = (n_tokens - 1) / DC_KV_BLOCK * DC_KV_BLOCK;
+    if (reusable > kv->max_blocks_per_seq * DC_KV_BLOCK) reusable = kv->max_blocks_per_seq * DC_KV_BLOCK;
+    uint64_t h = 14695981039346656037ULL;
+    ++kv->tick;
+    for (int off = 0; off < reusable; off += DC_KV_BLOCK) {
+        h = dc_kv_token_hash(h, tokens + off, DC_KV_BLOCK);
+        auto it = kv->prefix.find(h);
+        if (it == kv->prefix.end()) break;
+        const int b = it->second;
+        if (kv->block_hash[b] != h || memcmp(kv->block_tokens[b].data(), tokens + off, sizeof(int32_t) * DC_KV_BLOCK) != 0) break;
+        ++kv->ref[b];
+        kv->block_used[b] = kv->tick;
+        s.blocks.push_back(b);
+        ++kv->prefix_hit_blocks;
+    }
+    s.len = (int)s.blocks.size() * DC_KV_BLOCK;
+    *cached_tokens = s.len;
+    return upload_table(kv, seq, 0, (int)s.blocks.size());
+}
+
+// Registers every whole block of the sequence's first n_tokens positions (whose tokens are `tokens`) under
+// its cumulative-prefix hash (RegisterPrefixBlockWithTokens, kv_cache_block_manager.cpp:443-).  A prefix that
+// is cached already keeps its block.
+int dc_kv_prefix_register(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens) {
+    if (seq < 0 || seq >= kv->max_seqs || !kv->seqs[seq].used || !tokens)
+        return dc_fail(kv->ctx, DC_B200_INVALID_ARGUMENT, "kv: sequence %d is not allocated", seq);
+    dc_kv_seq& s = kv->seqs[seq];
+    if (n_tokens > s.len) n_tokens = s.len;
+    uint64_t h = 14695981039346656037ULL;
+    ++kv->tick;
+    for (int lb = 0; (lb + 1) * DC_KV_BLOCK <= n_tokens && lb < (int)s.blocks.size(); ++lb) {
+        h = dc_kv_token_hash(h, tokens + lb * DC_KV_BLOCK, DC_KV_BLOCK);
+        if (h == 0) continue;
+        const int b = s.blocks[lb];
+        auto it = kv->prefix.find(h);
+        if (it != kv->prefix.end()) {
+            kv->block_used[it->second] = kv->tick;
+            continue;
+        }
+        if (kv->block_hash[b]) continue;   // resident under another prefix already
+        kv->prefix[h] = b;
+        kv->block_hash[b] = h;
+        memcpy(kv->block_tokens[b].data(), tokens + lb * DC_KV_BLOCK, sizeof(int32_t) * DC_KV_BLOCK);
+        kv->block_used[b] = kv->tick;
+        ++kv->ref[b];                       // the cache's own reference
+    }
+    return DC_B200_OK;
 }
 
 extern "C" {
@@ -210,7 +309,23 @@ int dc_b200_kv_seq_fork(dc_kv_cache* kv, int src_seq, int* out_seq) {
 int dc_b200_kv_block_refcount(dc_kv_cache* kv, int block) {
     return (kv && block >= 0 && block < kv->max_blocks) ? kv->ref[block] : DC_B200_INVALID_ARGUMENT;
 }
-int dc_b200_kv_free_blocks(dc_kv_cache* kv) { return kv ? (int)kv->free_list.size() : DC_B200_INVALID_ARGUMENT; }
+int dc_b200_kv_free_blocks(dc_kv_cache* kv) { return kv ? dc_kv_available_blocks(kv) : DC_B200_INVALID_ARGUMENT; }
+int dc_b200_kv_prefix_attach(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens, int* cached_tokens) {
+    if (!kv || !cached_tokens) return DC_B200_INVALID_ARGUMENT;
+    cudaSetDevice(kv->ctx->device);
+    return dc_kv_prefix_attach(kv, seq, tokens, n_tokens, cached_tokens);
+}
+int dc_b200_kv_prefix_register(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens) {
+    return kv ? dc_kv_prefix_register(kv, seq, tokens, n_tokens) : DC_B200_INVALID_ARGUMENT;
+}
+int dc_b200_kv_prefix_stats(dc_kv_cache* kv, uint64_t out[4]) {
+    if (!kv || !out) return DC_B200_INVALID_ARGUMENT;
+    out[0] = kv->prefix_lookups;
+    out[1] = kv->prefix_hit_blocks;
+    out[2] = (uint64_t)kv->prefix.size();
+    out[3] = kv->prefix_evictions;
+    return DC_B200_OK;
+}
 
 int dc_b200_kv_read_block(dc_kv_cache* kv, int layer, int block, void* k_host, void* v_host) {
     if (!kv || layer < 0 || layer >= kv->n_layer || block < 0 || block >= kv->max_blocks) return DC_B200_INVALID_ARGUMENT;

@@ -580,7 +580,7 @@ int dc_b200_seq_fork(dc_model* m, int src_seq, int* out_seq) {
     cudaSetDevice(m->ctx->device);
     return dc_kv_seq_fork(&m->kv, src_seq, out_seq);
 }
-int dc_b200_model_free_blocks(dc_model* m) { return m ? (int)m->kv.free_list.size() : DC_B200_INVALID_ARGUMENT; }
+int dc_b200_model_free_blocks(dc_model* m) { return m ? dc_kv_available_blocks(&m->kv) : DC_B200_INVALID_ARGUMENT; }
 int dc_b200_seq_len(dc_model* m, int seq) {
     if (!m || seq < 0 || seq >= m->kv.max_seqs || !m->kv.seqs[seq].used) return DC_B200_INVALID_ARGUMENT;
     return m->kv.seqs[seq].len;
@@ -593,22 +593,52 @@ int dc_b200_seq_truncate(dc_model* m, int seq, int new_len) {
     return DC_B200_OK;
 }
 
+}  // extern "C"
+
+int dc_model_prefill_range(dc_model* m, int seq, const int32_t* tokens_host, int n, bool final, int32_t* next_token) {
+    for (int i0 = 0; i0 < n; i0 += DC_MAX_T) {
+        const int c = n - i0 < DC_MAX_T ? n - i0 : DC_MAX_T;
+        const bool last = final && i0 + c >= n;
+        DC_TRY(forward_chunk(m, seq, tokens_host + i0, c, last ? 1 : 0));
+    }
+    m->prefill_tokens_run += (uint64_t)n;
+    if (!final) return DC_B200_OK;
+    dc_ctx* ctx = m->ctx;
+    int32_t* pin = m->h_stage + 1000;
+    DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(pin, m->buf.out_tokens, 4, cudaMemcpyDeviceToHost, ctx->stream), "D2H token"));
+    DC_TRY(dc_b200_synchronize(ctx));
+    if (next_token) *next_token = pin[0];
+    return DC_B200_OK;
+}
+
+extern "C" {
+
 int dc_b200_prefill(dc_model* m, int seq, const int32_t* tokens_host, int n, float* logits_host, int32_t* next_token) {
     if (!m || !tokens_host || n < 1) return m ? dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "prefill: bad argument") : DC_B200_INVALID_ARGUMENT;
     if (!m->finalized) return dc_fail(m->ctx, DC_B200_MODEL_LOAD_FAILED, "prefill: model is not finalized");
     cudaSetDevice(m->ctx->device);
     DC_TRY(check_seq(m, seq));
-    for (int i0 = 0; i0 < n; i0 += DC_MAX_T) {
-        const int c = n - i0 < DC_MAX_T ? n - i0 : DC_MAX_T;
-        const bool last = i0 + c >= n;
-        DC_TRY(forward_chunk(m, seq, tokens_host + i0, c, last ? 1 : 0));
+    // with the prefix cache on, a sequence that holds nothing yet first takes over the cached blocks of the
+    // longest whole-block prefix of its prompt (at least one token is always left to run)
+    const bool fresh = m->kv.seqs[seq].len == 0 && m->kv.seqs[seq].blocks.empty();
+    int skip = 0;
+    if (m->prefix_cache && fresh) DC_TRY(dc_kv_prefix_attach(&m->kv, seq, tokens_host, n, &skip));
+    DC_TRY(dc_model_prefill_range(m, seq, tokens_host + skip, n - skip, true, next_token));
+    if (logits_host) {
+        DC_TRY(dc_check_cuda(m->ctx, cudaMemcpyAsync(logits_host, m->buf.logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->ctx->stream), "D2H logits"));
+        DC_TRY(dc_b200_synchronize(m->ctx));
     }
-    dc_ctx* ctx = m->ctx;
-    if (logits_host) DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(logits_host, m->buf.logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream), "D2H logits"));
-    int32_t* pin = m->h_stage + 1000;
-    DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(pin, m->buf.out_tokens, 4, cudaMemcpyDeviceToHost, ctx->stream), "D2H token"));
-    DC_TRY(dc_b200_synchronize(ctx));
-    if (next_token) *next_token = pin[0];
+    if (m->prefix_cache && fresh) DC_TRY(dc_kv_prefix_register(&m->kv, seq, tokens_host, n));
+    return DC_B200_OK;
+}
+
+int dc_b200_model_prefix_stats(dc_model* m, uint64_t out[5]) {
+    if (!m || !out) return DC_B200_INVALID_ARGUMENT;
+    out[0] = m->kv.prefix_lookups;
+    out[1] = m->kv.prefix_hit_blocks;
+    out[2] = (uint64_t)m->kv.prefix.size();
+    out[3] = m->kv.prefix_evictions;
+    out[4] = m->prefill_tokens_run;
     return DC_B200_OK;
 }
 
@@ -793,6 +823,10 @@ int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
     }
     // Test hooks for the bounded waits of the persistent kernel: a limit small enough to run out, so that
     // the error path (status code, usable context afterwards) can be exercised without any real failure.
+    if (!strcmp(name, "prefix_cache")) {
+        m->prefix_cache = value != 0;
+        return DC_B200_OK;
+    }
     if (!strcmp(name, "test_barrier_polls")) {
         m->test_barrier_polls = value < 0 ? 0u : (unsigned)value;
         return DC_B200_OK;

@@ -97,13 +97,14 @@ int dc_b200_moe_route(dc_ctx* ctx, const float* logits_host, int T, int n_expert
     return dc_b200_synchronize(ctx);
 }
 
+// router == nullptr: the caller supplies the router logits (cb_moe_forward's src1)
 static int mul_mat_id_check(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
-                            const dc_weight* down, int T, int top_k) {
-    if (!router || !gate || !up || !down || T < 1 || T > DC_MAX_T)
+                            const dc_weight* down, int T, int top_k, bool need_router = true) {
+    if ((need_router && !router) || !gate || !up || !down || T < 1 || T > DC_MAX_T)
         return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: bad argument (T=%d)", T);
     const int H = (int)gate->K, F = (int)gate->N, E = (int)gate->E;
-    if (router->K != H || router->N != E || up->K != H || up->N != F || up->E != E || down->K != F || down->N != H ||
-        down->E != E)
+    if ((router && (router->K != H || router->N != E)) || up->K != H || up->N != F || up->E != E || down->K != F ||
+        down->N != H || down->E != E)
         return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: tensor shapes do not agree");
     if (E < 1 || E > 256 || top_k < 1 || top_k > 16 || top_k > E)
         return dc_fail(ctx, DC_B200_UNSUPPORTED, "mul_mat_id: n_expert=%d top_k=%d out of range (1..256 experts, top_k <= min(16, n_expert))", E, top_k);
@@ -113,12 +114,12 @@ static int mul_mat_id_check(dc_ctx* ctx, const dc_weight* router, const dc_weigh
 
 // Enqueues one MoE layer on device buffers: x_dev [T, H] -> y_dev [T, H]; ids_dev / w_dev (optional) receive the
 // routing.  Scratch comes from the context (grown on first use).
-int dc_b200_mul_mat_id_dev(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
-                           const dc_weight* down, const float* x_dev, int T, int top_k, float routed_scale,
-                           float* y_dev, int32_t* ids_dev, float* weights_dev) {
+static int moe_layer_dev(dc_ctx* ctx, const dc_weight* router, const float* logits_dev, const dc_weight* gate,
+                         const dc_weight* up, const dc_weight* down, const float* x_dev, int T, int top_k,
+                         float routed_scale, float* y_dev, int32_t* ids_dev, float* weights_dev) {
     if (!ctx) return DC_B200_INVALID_ARGUMENT;
-    if (!x_dev || !y_dev) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id_dev: null buffer");
-    DC_TRY(mul_mat_id_check(ctx, router, gate, up, down, T, top_k));
+    if (!x_dev || !y_dev || (!router && !logits_dev)) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id_dev: null buffer");
+    DC_TRY(mul_mat_id_check(ctx, router, gate, up, down, T, top_k, router != nullptr));
     const int H = (int)gate->K, F = (int)gate->N, E = (int)gate->E;
     cudaSetDevice(ctx->device);
     const int A = T * top_k;
@@ -135,6 +136,8 @@ int dc_b200_mul_mat_id_dev(dc_ctx* ctx, const dc_weight* router, const dc_weight
     dc_moe_route rt;
     dc_moe_route_bind(&rt, s + b.off, T, E, top_k);
     DC_TRY(dc_check_cuda(ctx, cudaMemsetAsync(rt.ticket, 0, sizeof(int), ctx->stream), "memset"));
+    if (!router)
+        DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(rt.logits, logits_dev, (size_t)T * E * 4, cudaMemcpyDeviceToDevice, ctx->stream), "logits"));
     DC_TRY(dc_launch_router(ctx, router, x_dev, E, T, top_k, routed_scale, 0, E, &rt, ctx->route_mode));
     DC_TRY(dc_launch_quantize_q8k(ctx, x_dev, T, H, xq));
     DC_TRY(dc_launch_moe_mm(ctx, true, gate, up, xq, T, T, top_k, 0, &rt, h));
@@ -146,9 +149,41 @@ int dc_b200_mul_mat_id_dev(dc_ctx* ctx, const dc_weight* router, const dc_weight
     return DC_B200_OK;
 }
 
+int dc_b200_mul_mat_id_dev(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
+                           const dc_weight* down, const float* x_dev, int T, int top_k, float routed_scale,
+                           float* y_dev, int32_t* ids_dev, float* weights_dev) {
+    if (ctx && !router) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id_dev: null router");
+    return moe_layer_dev(ctx, router, nullptr, gate, up, down, x_dev, T, top_k, routed_scale, y_dev, ids_dev, weights_dev);
+}
+
+static int moe_layer_host(dc_ctx* ctx, const dc_weight* router, const float* logits_host, const dc_weight* gate,
+                          const dc_weight* up, const dc_weight* down, const float* x_host, int T, int top_k,
+                          float routed_scale, float* y_host, int32_t* ids_out, float* weights_out);
+
 int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
                        const dc_weight* down, const float* x_host, int T, int top_k, float routed_scale,
                        float* y_host, int32_t* ids_out, float* weights_out) {
+    if (ctx && !router) {
+        if (y_host && gate && T > 0 && T <= DC_MAX_T) memset(y_host, 0, (size_t)T * gate->K * sizeof(float));
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: null router");
+    }
+    return moe_layer_host(ctx, router, nullptr, gate, up, down, x_host, T, top_k, routed_scale, y_host, ids_out, weights_out);
+}
+
+int dc_b200_moe_forward(dc_ctx* ctx, const dc_weight* gate, const dc_weight* up, const dc_weight* down,
+                        const float* x_host, const float* gate_logits_host, int T, int top_k, float routed_scale,
+                        float* y_host, int32_t* ids_out, float* weights_out) {
+    if (ctx && !gate_logits_host) {
+        if (y_host && gate && T > 0 && T <= DC_MAX_T) memset(y_host, 0, (size_t)T * gate->K * sizeof(float));
+        return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "moe_forward: null gate logits");
+    }
+    return moe_layer_host(ctx, nullptr, gate_logits_host, gate, up, down, x_host, T, top_k, routed_scale, y_host, ids_out,
+                          weights_out);
+}
+
+static int moe_layer_host(dc_ctx* ctx, const dc_weight* router, const float* logits_host, const dc_weight* gate,
+                          const dc_weight* up, const dc_weight* down, const float* x_host, int T, int top_k,
+                          float routed_scale, float* y_host, int32_t* ids_out, float* weights_out) {
     if (!ctx) return DC_B200_INVALID_ARGUMENT;
     if (!gate || !x_host || !y_host || T < 1 || T > DC_MAX_T)
         return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "mul_mat_id: bad argument (T=%d)", T);
@@ -157,22 +192,25 @@ int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const dc_weight* ga
         memset(y_host, 0, (size_t)T * H * sizeof(float));  // zero-fill on failure (moe/exec.cpp:397-414)
         return st;
     };
-    int st = mul_mat_id_check(ctx, router, gate, up, down, T, top_k);
+    int st = mul_mat_id_check(ctx, router, gate, up, down, T, top_k, router != nullptr);
     if (st != DC_B200_OK) return fail_closed(st);
     cudaSetDevice(ctx->device);
     const int A = T * top_k;
+    const size_t lb = router ? 0 : (size_t)T * gate->E * 4;
     // staging buffers of this call live in pinned-size device allocations of their own (the context's scratch
     // belongs to the device-level call)
     float *x = nullptr, *y = nullptr, *w = nullptr;
     int32_t* ids = nullptr;
     const size_t xb = (size_t)T * H * 4;
-    cudaError_t e = cudaMalloc((void**)&x, 2 * xb + (size_t)A * 8 + 1024);
+    cudaError_t e = cudaMalloc((void**)&x, 2 * xb + (size_t)A * 8 + lb + 1024);
     if (e != cudaSuccess) return fail_closed(dc_check_cuda(ctx, e, "mul_mat_id staging"));
     y = (float*)((uint8_t*)x + xb);
     ids = (int32_t*)((uint8_t*)y + xb);
     w = (float*)(ids + A);
+    float* lg = router ? nullptr : w + A;
     st = h2d(ctx, x, x_host, xb);
-    if (st == DC_B200_OK) st = dc_b200_mul_mat_id_dev(ctx, router, gate, up, down, x, T, top_k, routed_scale, y, ids, w);
+    if (st == DC_B200_OK && lg) st = h2d(ctx, lg, logits_host, lb);
+    if (st == DC_B200_OK) st = moe_layer_dev(ctx, router, lg, gate, up, down, x, T, top_k, routed_scale, y, ids, w);
     if (st == DC_B200_OK) st = d2h(ctx, y_host, y, xb);
     if (st == DC_B200_OK && ids_out) st = d2h(ctx, ids_out, ids, (size_t)A * 4);
     if (st == DC_B200_OK && weights_out) st = d2h(ctx, weights_out, w, (size_t)A * 4);

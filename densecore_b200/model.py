@@ -208,6 +208,12 @@ class Model:
         self._check(_lib.lib().dc_b200_forward_chunk(self.handle, seq, _vp(tokens), tokens.size, _vp(logits)))
         return logits
 
+    def prefix_stats(self) -> dict:
+        """Prefix-cache counters: lookups, blocks hit, blocks resident, evictions, prompt tokens run."""
+        out = (C.c_uint64 * 5)()
+        self._check(_lib.lib().dc_b200_model_prefix_stats(self.handle, out))
+        return dict(zip(("lookups", "hit_blocks", "resident_blocks", "evictions", "prefill_tokens_run"), (int(v) for v in out)))
+
     def read_layer_input(self, layer: int, n_tokens: int = 1) -> np.ndarray:
         """Hidden state that entered `layer` in the last step (layer == n_layer: what entered the output norm).
         Needs set_option("capture_layer_inputs", 1) before the step."""

@@ -151,6 +151,12 @@ DC_B200_API int dc_b200_mul_mat_id(dc_ctx* ctx, const dc_weight* router, const d
 DC_B200_API int dc_b200_mul_mat_id_dev(dc_ctx* ctx, const dc_weight* router, const dc_weight* gate, const dc_weight* up,
                                        const dc_weight* down, const float* x_dev, int T, int top_k,
                                        float routed_scale, float* y_dev, int32_t* ids_dev, float* weights_dev);
+/* cb_moe_forward with its own arguments (core/src/llm/moe/exec.cpp:813: src0 = the routed input, src1 = the
+ * router logits the graph computed): routes from gate_logits [T, n_expert] as given, then runs the experts.
+ * Fails closed like the callback: y is zero-filled on any error. */
+DC_B200_API int dc_b200_moe_forward(dc_ctx* ctx, const dc_weight* gate, const dc_weight* up, const dc_weight* down,
+                                    const float* x_host, const float* gate_logits_host, int T, int top_k,
+                                    float routed_scale, float* y_host, int32_t* ids_out, float* weights_out);
 /* Routing alone from given logits [T, n_expert] (RouteMoESoftmaxTopK, core/src/llm/moe/exec.cpp:734);
  * which of the reference's two routers runs is the context option "route_mode".  1 <= n_expert <= 256,
  * 1 <= top_k <= min(16, n_expert), else DC_B200_UNSUPPORTED with nothing launched. */
@@ -180,6 +186,19 @@ DC_B200_API int dc_b200_kv_free_blocks(dc_kv_cache* kv);
  * to the free list when their last reference goes. */
 DC_B200_API int dc_b200_kv_seq_fork(dc_kv_cache* kv, int src_seq, int* out_seq);
 DC_B200_API int dc_b200_kv_block_refcount(dc_kv_cache* kv, int block);
+/* Prefix cache of the block manager (core/include/densecore/memory/kv_cache.h:176-213,
+ * core/src/runtime/memory/kv_cache_block_manager.cpp:364-416,515-522).  A whole block can be registered
+ * under the FNV-1a hash of the entire token prefix that ends with it; the cache keeps a reference of its
+ * own, so the block outlives its sequence until an allocation has to evict it (least recently used first;
+ * only blocks no sequence holds).
+ * kv_prefix_attach: for a sequence that holds nothing yet, finds the longest run of cached whole blocks
+ * of tokens[0..n_tokens) (each verified token by token, always leaving at least one token to run), makes
+ * them the sequence's first blocks (shared, copy-on-write) and sets its length; *cached_tokens = that
+ * length.  kv_prefix_register: registers the whole blocks of the sequence's first n_tokens positions,
+ * whose tokens the caller passes.  kv_prefix_stats: {lookups, blocks hit, blocks resident, evictions}. */
+DC_B200_API int dc_b200_kv_prefix_attach(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens, int* cached_tokens);
+DC_B200_API int dc_b200_kv_prefix_register(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens);
+DC_B200_API int dc_b200_kv_prefix_stats(dc_kv_cache* kv, uint64_t out[4]);
 /* cb_paged_attention_decode (core/src/llm/attention/paged_exec.cpp:343): writes
  * the T current tokens' K/V (f32 [T, n_kv, hd]) into the cache at positions[t]
  * of sequence seq_ids[t], then attends q [T, n_head, hd] over keys
@@ -339,6 +358,31 @@ DC_B200_API int dc_b200_model_read_kv(dc_model* m, int layer, int seq, int first
  * barriers between phases: 0 never, 1 for one stream (default: with more streams the per-op kernels are
  * faster), 2 for every stream count it supports (1-4). */
 DC_B200_API int dc_b200_model_set_option(dc_model* m, const char* name, int value);
+/* Prefix-cache counters of a model (option "prefix_cache" = 1 makes dc_b200_prefill and the scheduler use
+ * the cache): {lookups, blocks hit, blocks resident, evictions, prompt tokens run through the decoder}. */
+DC_B200_API int dc_b200_model_prefix_stats(dc_model* m, uint64_t out[5]);
+
+/* ---- step scheduler ---------------------------------------------------------- */
+/* Continuous batching over one model with DenseCore's CPU-path policy: at most max_num_seqs sequences
+ * (0: 4, KVCacheConfig::max_num_seqs, core/src/runtime/engine_internal.h:89), one prefill in flight at a
+ * time, prompts run in chunks of max_prefill_chunk tokens (0: 512) that alternate with batched decode
+ * steps of all running sequences; admission takes over cached prompt prefixes
+ * (core/src/runtime/scheduler.cpp:30-85).  Greedy sampling.  eos_token < 0: none. */
+typedef struct dc_sched dc_sched;
+typedef struct dc_sched_event {
+    int32_t request;  /* id from dc_b200_sched_add */
+    int32_t token;    /* the token this step produced for the request */
+    int32_t finished; /* 0: continues; 1: reached max_new_tokens; 2: end-of-sequence token; 3: failed */
+} dc_sched_event;
+DC_B200_API int dc_b200_sched_create(dc_model* m, int max_num_seqs, int max_prefill_chunk, int eos_token, dc_sched** out);
+DC_B200_API void dc_b200_sched_destroy(dc_sched* s);
+DC_B200_API int dc_b200_sched_add(dc_sched* s, const int32_t* prompt, int n_prompt, int max_new_tokens, int* request_id);
+/* One unit of GPU work (a prompt chunk or one batched decode step).  events receives at most capacity
+ * entries; *n_events is the number produced (0 with nothing pending: idle). */
+DC_B200_API int dc_b200_sched_step(dc_sched* s, dc_sched_event* events, int capacity, int* n_events);
+DC_B200_API int dc_b200_sched_pending(dc_sched* s);
+/* {steps, prompt chunks, decode steps, decoded tokens, largest decode batch, prompt tokens taken from the cache} */
+DC_B200_API int dc_b200_sched_stats(dc_sched* s, uint64_t out[6]);
 
 /* ---- expert parallelism over the GPUs of one node ---------------------------- */
 /* One process per GPU.  Experts are split into contiguous ranges (rank r owns

@@ -30,6 +30,30 @@ def test_library_exports_every_declared_symbol():
     assert sorted(_lib.exported_symbols()) == declared
 
 
+def test_library_exports_the_ggml_shaped_callbacks():
+    """Every entry of include/dc_ggml_compat.h is exported, and the C++ program that drives them builds."""
+    from densecore_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "dc_ggml_compat.h")).read()
+    names = sorted(set(re.findall(r"DC_B200_API[^;(]*?\b(\w+)\s*\(", text)))
+    assert names == ["cb_gemv_b200", "cb_moe_forward_b200", "cb_paged_attention_decode_b200", "dc_b200_shim_fail_closed_count"]
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), n
+    lib.dc_b200_shim_fail_closed_count.restype = ctypes.c_uint64
+    assert lib.dc_b200_shim_fail_closed_count() == 0
+    # a callback entered by a thread other than 0 returns at once, whatever it is given
+    lib.cb_gemv_b200(None, 1, 4, None)
+    lib.cb_moe_forward_b200(None, None, None, 3, 4, None)
+    lib.cb_paged_attention_decode_b200(None, 2, 4, None)
+    # thread 0 with no result tensor has nothing to fill and nothing to count
+    lib.cb_gemv_b200(None, 0, 4, None)
+    assert lib.dc_b200_shim_fail_closed_count() == 0
+    from oracle import oracle as o
+    o.build()
+    subprocess.check_call(["make", "-C", os.path.join(ROOT, "tests", "shims"), "ggml_shims_test"], stdout=subprocess.DEVNULL)
+    assert os.path.exists(os.path.join(ROOT, "tests", "shims", "ggml_shims_test"))
+
+
 def test_no_cpu_fallback_without_gpu():
     """On a machine without a GPU, init fails loudly instead of computing on the CPU."""
     import torch
