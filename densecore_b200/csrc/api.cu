@@ -177,6 +177,10 @@ int dc_b200_set_option(dc_ctx* ctx, const char* name, int value) {
         ctx->route_mode = value;
         return DC_B200_OK;
     }
+    if (!strcmp(name, "gemm_tc_min_rows")) {   // 0 or less: never (every MUL_MAT runs the row-streaming kernels)
+        ctx->gemm_tc_min_rows = value > 0 ? value : 0x7fffffff;
+        return DC_B200_OK;
+    }
     return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "unknown option '%s'", name);
 }
 
@@ -289,13 +293,28 @@ static int check_mul_mat_args(dc_ctx* ctx, const dc_weight* w, const void* x, in
     return DC_B200_OK;
 }
 
+// Bytes of the quantised-activation scratch of one MUL_MAT with M token rows.
+static size_t mul_mat_act_bytes(dc_ctx* ctx, const dc_weight* w, int M) {
+    if (M >= ctx->gemm_tc_min_rows && dc_gemm_tc_supports(w)) return dc_gemm_tc_act_bytes(M, (int)w->K);
+    return (size_t)DC_MAX_T * (w->K / DC_QK_K) * DC_Q8K_BYTES;
+}
+
+// Prompt-sized inputs take the tensor-core kernel (cb_gemv_batched_custom serves M up to 4096 on the CPU,
+// core/src/llm/matmul/dispatch.cpp:622,985-989); decode-sized ones the row-streaming kernels, 16 rows a pass.
+static int mul_mat_any(dc_ctx* ctx, const dc_weight* w, const float* x_dev, int M, float* y_dev, uint8_t* act) {
+    if (M >= ctx->gemm_tc_min_rows && dc_gemm_tc_supports(w) && ((uintptr_t)x_dev & 15) == 0) {
+        DC_TRY(dc_launch_quantize_q8k_tiled(ctx, x_dev, (int)w->K, M, (int)w->K, act, dc_gemm_tc_tiles(M), nullptr));
+        return dc_launch_gemm_tc(ctx, w, act, M, y_dev, (int)w->N, nullptr);
+    }
+    return mul_mat_chunks(ctx, w, x_dev, M, y_dev, act);
+}
+
 int dc_b200_mul_mat_dev(dc_ctx* ctx, const dc_weight* w, const float* x_dev, int M, float* y_dev) {
     DC_TRY(check_mul_mat_args(ctx, w, x_dev, M, y_dev));
     cudaSetDevice(ctx->device);
-    const size_t qb = (size_t)DC_MAX_T * (w->K / DC_QK_K) * DC_Q8K_BYTES;
-    uint8_t* s = dc_scratch(ctx, qb);
+    uint8_t* s = dc_scratch(ctx, mul_mat_act_bytes(ctx, w, M));
     if (!s) return DC_B200_OUT_OF_MEMORY;
-    return mul_mat_chunks(ctx, w, x_dev, M, y_dev, s);
+    return mul_mat_any(ctx, w, x_dev, M, y_dev, s);
 }
 
 int dc_b200_mul_mat(dc_ctx* ctx, const dc_weight* w, const float* x_host, int M, float* y_host) {
@@ -306,13 +325,13 @@ int dc_b200_mul_mat(dc_ctx* ctx, const dc_weight* w, const float* x_host, int M,
     }
     cudaSetDevice(ctx->device);
     const size_t xb = ((size_t)M * w->K * 4 + 255) & ~(size_t)255, yb = ((size_t)M * w->N * 4 + 255) & ~(size_t)255;
-    const size_t qb = (size_t)DC_MAX_T * (w->K / DC_QK_K) * DC_Q8K_BYTES;
+    const size_t qb = mul_mat_act_bytes(ctx, w, M);
     uint8_t* s = dc_scratch(ctx, xb + yb + qb);
     if (!s) return DC_B200_OUT_OF_MEMORY;
     float* xd = (float*)s;
     float* yd = (float*)(s + xb);
     st = dc_check_cuda(ctx, cudaMemcpyAsync(xd, x_host, (size_t)M * w->K * 4, cudaMemcpyHostToDevice, ctx->stream), "H2D x");
-    if (st == DC_B200_OK) st = mul_mat_chunks(ctx, w, xd, M, yd, s + xb + yb);
+    if (st == DC_B200_OK) st = mul_mat_any(ctx, w, xd, M, yd, s + xb + yb);
     if (st == DC_B200_OK)
         st = dc_check_cuda(ctx, cudaMemcpyAsync(y_host, yd, (size_t)M * w->N * 4, cudaMemcpyDeviceToHost, ctx->stream), "D2H y");
     if (st == DC_B200_OK) st = dc_b200_synchronize(ctx);

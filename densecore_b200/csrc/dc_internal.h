@@ -28,6 +28,7 @@ struct dc_ctx {
     int num_sms = 148;
     cudaStream_t stream = nullptr;
     int* d_err = nullptr;          // device error word (bounded waits report here)
+    int gemm_tc_min_rows = 32;     // option "gemm_tc_min_rows": token rows from which MUL_MAT runs on the tensor cores
     std::string last_error;
     std::mutex mu;
     std::vector<dc_weight*> weights;
@@ -71,6 +72,16 @@ int dc_launch_gemv(dc_ctx* ctx, const dc_gemv_seg* segs, int n_seg, int epi, con
                    unsigned long long* argmax, int32_t* dump_I = nullptr, int32_t* dump_M = nullptr);
 // rows x K f32 -> native Q8_K blocks (row stride K/256*292)
 int dc_launch_quantize_q8k(dc_ctx* ctx, const float* x, int rows, int K, uint8_t* out);
+// Tensor-core MUL_MAT for many token rows (gemm_tc.cu): activations quantised into 64-token tiles, then
+// out[slot * ldo + row] for every weight row; tile_expert (optional, device) picks an expert matrix per tile.
+size_t dc_gemm_tc_act_bytes(int n_slots, int K);
+int dc_gemm_tc_tiles(int n_slots);
+bool dc_gemm_tc_supports(const dc_weight* w);
+int dc_launch_quantize_q8k_tiled(dc_ctx* ctx, const float* x, int ldx, int n_rows, int K, uint8_t* act, int n_tt,
+                                 const int* slot_token);
+int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
+                      const int* tile_expert);
+
 
 // ---- misc.cu ----
 int dc_launch_embed(dc_ctx* ctx, const dc_weight* w, const int32_t* tokens, int T, float* x);

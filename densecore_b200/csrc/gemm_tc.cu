@@ -1,0 +1,436 @@
+// Batched MUL_MAT for prompt chunks (M >= 32 token rows): K-quant weights x Q8_K activations on the
+// 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in tensor memory), with the block sums
+// kept as exact integers so that the float steps per 256-value block are the CPU kernels' own
+// (core/src/llm/matmul/batched_exec.cpp:1040-1240 serves these shapes on the CPU; per block
+// sumf += (d*yd)*float(I); sumf -= (dmin*yd)*float(M), core/src/kernels/hwy/hwy_moe_quant.cc:248-253).
+//
+// One CTA owns 128 weight rows x 64 tokens over the whole reduction length.  Per 256-value block:
+//   1. the block's raw bytes of the 128 rows arrive by per-row bulk copies (mbarrier, no multicast);
+//   2. the threads expand them into 8-bit operand planes in shared memory, in the K-major core-matrix
+//      layout the tensor core reads (8 rows x 16 bytes per core matrix):
+//        Q4_K: q4 * (sc >> 3), q4 * (sc & 7) and the sub-block minimum m broadcast (3 planes, unsigned),
+//              so that I = 8 * acc0 + acc1 = sum sc_j * sum q4*q8 and M = acc2 = sum m_j * sum q8;
+//        Q6_K: sign(sc) * digit_i(|sc|) * (q6 - 32) for the four base-4 digits of |sc| (4 planes, signed),
+//              so that I = acc0 + 4 acc1 + 16 acc2 + 64 acc3;
+//      every plane entry fits 8 bits and the 32-bit accumulators are exact;
+//   3. one thread issues the UMMAs (128 x 64 x 32 each), two halves of 128 values per block;
+//   4. all threads read the accumulators back (tcgen05.ld) and add the block's float terms in block order.
+// The token side is prepared once per activation matrix by k_quantize_q8k_tiled: the Q8_K codes of every
+// (block, 64-token tile) stored as the B operand's core matrices, followed by the 64 block scales, so that
+// a tile is one contiguous bulk copy.
+//
+// Q4_K results are bit-equal to the GEMV path and the CPU oracle.  Q6_K adds one float term per block
+// instead of the CPU small-batch kernel's eight lane partials (q6_small_batch.h:62-103): equal integers,
+// a different float order, relative difference ~1e-7.
+#include "dc_common.cuh"
+#include "dc_internal.h"
+
+#define DC_TRY(expr)                       \
+    do {                                   \
+        int st_ = (expr);                  \
+        if (st_ != DC_B200_OK) return st_; \
+    } while (0)
+
+namespace dc {
+
+constexpr int TC_ROWS = 128;
+constexpr int TC_NTOK = 64;
+constexpr int TC_THREADS = 256;
+constexpr int TC_PLANE = 8 * TC_ROWS * 16;            // 8 K-chunks of 16 bytes for 128 rows: one half block
+constexpr int TC_B_Q = 16 * TC_NTOK * 16;             // codes of one (block, token tile): 16 K-chunks
+constexpr int TC_ACT_TILE = TC_B_Q + TC_NTOK * 4;     // + the tile's 64 block scales
+
+struct GemmTcParams {
+    const uint8_t* w;      // rows of the (first) matrix
+    int row_bytes, N, K;
+    const uint8_t* act;    // [K / 256][n_tt][TC_ACT_TILE]
+    int n_tt;
+    int n_slots;           // token slots that hold data (stores beyond are skipped)
+    float* out;            // out[slot * ldo + row]
+    int ldo;
+    const int* tile_expert;   // optional [n_tt]: weights of tile t start at w + tile_expert[t] * estride; < 0: tile unused
+    size_t estride;
+    int* err;
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[128 x N] (+)= A[128 x 32] * B[32 x N], 8-bit operands from shared memory, int32 accumulators in TMEM.
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Shared-memory operand descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes (128 contiguous
+// bytes); lbo = byte distance between the two 16-byte K-chunks of one instruction, sbo = between 8-row groups.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (((lbo >> 4) & 0x3FFFu) << 16);
+    const uint32_t hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14);   // descriptor version 1 (sm_100)
+    return ((uint64_t)hi << 32) | lo;
+}
+// Instruction descriptor: int32 accumulate, A unsigned or signed 8-bit, B signed 8-bit, both K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_i8(int a_signed, int M, int N) {
+    return (2u << 4) | ((uint32_t)a_signed << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
+// ---- activation side ---------------------------------------------------------------------------------
+// One warp per (token slot, 256-value block): Q8_K codes (bit-equal to the row quantiser) into the tile
+// layout [K-chunk c 0..15][slot % 64][16 bytes], block scale into the tile's tail.  slot_token (optional)
+// maps a slot to its source row, < 0 or beyond n_rows: the slot holds zeros.
+__global__ void __launch_bounds__(256) k_quantize_q8k_tiled(const float* __restrict__ x, int ldx, int n_rows, int K,
+                                                            uint8_t* __restrict__ act, int n_tt,
+                                                            const int* __restrict__ slot_token) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = K / DC_QK_K;
+    const long long total = (long long)n_tt * TC_NTOK * nb;
+    for (long long item = (long long)blockIdx.x * 8 + warp; item < total; item += (long long)gridDim.x * 8) {
+        const int b = (int)(item % nb);
+        const int slot = (int)(item / nb);
+        int row = slot_token ? slot_token[slot] : slot;
+        if (row >= n_rows) row = -1;
+        uint8_t* tile = act + ((size_t)b * n_tt + slot / TC_NTOK) * TC_ACT_TILE;
+        uint32_t w0 = 0, w1 = 0, bw = 0;
+        float d = 0.0f;
+        if (row >= 0) {
+            const float4* src = reinterpret_cast<const float4*>(x + (size_t)row * ldx + (size_t)b * DC_QK_K + 8 * lane);
+            const float4 a = src[0], c = src[1];
+            const float v[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+            q8k_block_core(v, lane, w0, w1, bw, d);
+        }
+        uint2* dst = reinterpret_cast<uint2*>(tile + (lane >> 1) * (TC_NTOK * 16) + (slot % TC_NTOK) * 16 + 8 * (lane & 1));
+        *dst = make_uint2(w0, w1);
+        if (lane == 0) reinterpret_cast<float*>(tile + TC_B_Q)[slot % TC_NTOK] = d;
+    }
+}
+
+// ---- weight side ---------------------------------------------------------------------------------------
+template <int TYPE>
+struct TcTraits;
+template <>
+struct TcTraits<DC_TYPE_Q4_K> {
+    static constexpr int NP = 3, BB = DC_Q4K_BYTES, RB = 144, NRAW = 2, A_SIGNED = 0;
+};
+template <>
+struct TcTraits<DC_TYPE_Q6_K> {
+    static constexpr int NP = 4, BB = DC_Q6K_BYTES, RB = 240, NRAW = 1, A_SIGNED = 1;
+};
+
+template <int TYPE>
+constexpr size_t tc_smem_bytes() {
+    using T = TcTraits<TYPE>;
+    return (size_t)T::NP * TC_PLANE + TC_ACT_TILE + (size_t)T::NRAW * TC_ROWS * T::RB + 64;
+}
+
+__device__ __forceinline__ void q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, uint32_t& sc, uint32_t& m) {
+    // 12 packed bytes -> the 6-bit scale and minimum of sub-block j (get_scale_min_k4 of ggml's K-quants)
+    const uint64_t lo = ((uint64_t)s1 << 32) | s0;
+    auto byte = [&](int i) -> uint32_t { return i < 8 ? (uint32_t)(lo >> (8 * i)) & 0xFFu : (s2 >> (8 * (i - 8))) & 0xFFu; };
+    if (j < 4) {
+        sc = byte(j) & 63u;
+        m = byte(j + 4) & 63u;
+    } else {
+        sc = (byte(j + 4) & 0xFu) | ((byte(j - 4) >> 6) << 4);
+        m = (byte(j + 4) >> 4) | ((byte(j) >> 6) << 4);
+    }
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
+    using T = TcTraits<TYPE>;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const uint32_t sA = smem_u32(smem_raw);
+    const uint32_t sB = sA + T::NP * TC_PLANE;
+    const uint32_t sRaw = sB + TC_ACT_TILE;
+    const uint32_t sBar = sRaw + T::NRAW * TC_ROWS * T::RB;     // raw[0], raw[1], b, mma (8 bytes each), tmem slot
+    const uint32_t bar_raw0 = sBar, bar_b = sBar + 16, bar_mma = sBar + 24, tmem_slot = sBar + 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tt = blockIdx.x, row0 = blockIdx.y * TC_ROWS;
+    const int expert = p.tile_expert ? p.tile_expert[tt] : 0;
+    if (expert < 0) return;                                      // the whole CTA: a tile no expert uses
+    const uint8_t* wbase = p.w + (size_t)expert * p.estride;
+    const int nb = p.K / DC_QK_K;
+    constexpr uint32_t NCOLS = 256;                              // NP x 64 accumulator columns, power of two
+
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, NCOLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        mbar_init(bar_raw0, 4);
+        mbar_init(bar_raw0 + 8, 4);
+        mbar_init(bar_b, 1);
+        mbar_init(bar_mma, 1);
+        mbar_fence_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = lds32(tmem_slot);
+
+    // this thread's weight row (threads 0..127 fetch; every thread expands row tid % 128)
+    const int r = tid & (TC_ROWS - 1), part = tid >> 7;
+    const int grow = min(row0 + r, p.N - 1);
+    const uint8_t* rp = wbase + (size_t)grow * p.row_bytes;
+
+    auto issue_raw = [&](int kb, int stage) {     // warps 0..3, all lanes
+        const uintptr_t a = (uintptr_t)(rp + (size_t)kb * T::BB);
+        const uint32_t skew = (uint32_t)(a & 15u);
+        const uint32_t bytes = (skew + T::BB + 15u) & ~15u;
+        const uint32_t sum = __reduce_add_sync(0xffffffffu, bytes);
+        const uint32_t bar = bar_raw0 + 8 * stage;
+        if (lane == 0) mbar_expect_tx(bar, sum);
+        __syncwarp();
+        bulk_g2s(sRaw + (stage * TC_ROWS + r) * T::RB, (const void*)(a - skew), bytes, bar);
+    };
+    auto issue_b = [&](int kb) {                  // one thread
+        mbar_expect_tx(bar_b, TC_ACT_TILE);
+        bulk_g2s(sB, p.act + ((size_t)kb * p.n_tt + tt) * TC_ACT_TILE, TC_ACT_TILE, bar_b);
+    };
+
+    if (warp < 4) issue_raw(0, 0);
+    if (tid == 128) issue_b(0);
+
+    constexpr uint32_t IDESC = umma_idesc_i8(T::A_SIGNED, TC_ROWS, TC_NTOK);
+    float sumf[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) sumf[i] = 0.0f;
+    uint32_t ph_raw[2] = {0, 0}, ph_b = 0, ph_mma = 0;
+    bool failed = false;
+    const int q = warp & 3, ch = warp >> 2;       // TMEM lane quarter of this warp, column half of the tile
+    const uint32_t t_lane = tmem + ((uint32_t)(32 * q) << 16) + 32 * ch;
+
+    for (int kb = 0; kb < nb && !failed; ++kb) {
+        const int stage = T::NRAW == 2 ? (kb & 1) : 0;
+        if (T::NRAW == 2 && kb + 1 < nb && warp < 4) issue_raw(kb + 1, (kb + 1) & 1);
+        if (!mbar_wait(bar_raw0 + 8 * stage, ph_raw[stage], p.err)) failed = true;
+        ph_raw[stage] ^= 1;
+        const uint32_t rr = sRaw + (stage * TC_ROWS + r) * T::RB +
+                            (uint32_t)(((uintptr_t)(rp + (size_t)kb * T::BB)) & 15u);
+        float d, dmin = 0.0f;
+        if (TYPE == DC_TYPE_Q4_K) {
+            const uint32_t dd = lds32(rr);
+            d = fp16_bits_to_float((uint16_t)(dd & 0xFFFF));
+            dmin = fp16_bits_to_float((uint16_t)(dd >> 16));
+        } else {
+            d = fp16_bits_to_float((uint16_t)lds16(rr + 208));
+        }
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+            // ---- expand this row's share of the half block into the operand planes
+            if (TYPE == DC_TYPE_Q4_K) {
+                const int g = 2 * h + part;      // 64 values: sub-blocks 2g (low nibbles) and 2g + 1 (high nibbles)
+                const uint32_t s0 = lds32(rr + 4), s1 = lds32(rr + 8), s2 = lds32(rr + 12);
+                uint32_t sc0, m0, sc1, m1;
+                q4k_scale_min(s0, s1, s2, 2 * g, sc0, m0);
+                q4k_scale_min(s0, s1, s2, 2 * g + 1, sc1, m1);
+                const uint32_t mm0 = m0 * 0x01010101u, mm1 = m1 * 0x01010101u;
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    const uint4 qv = lds128(rr + 16 + 32 * g + 16 * hf);
+                    const uint32_t in[4] = {qv.x, qv.y, qv.z, qv.w};
+                    uint32_t lo[4], hi[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        lo[k] = in[k] & 0x0F0F0F0Fu;
+                        hi[k] = (in[k] >> 4) & 0x0F0F0F0Fu;
+                    }
+                    const uint32_t c_lo = sA + (4 * part + hf) * (TC_ROWS * 16) + r * 16;        // chunk of sub-block 2g
+                    const uint32_t c_hi = c_lo + 2 * (TC_ROWS * 16);                             // chunk of sub-block 2g + 1
+                    const uint32_t a0 = sc0 >> 3, a1 = sc0 & 7u, b0 = sc1 >> 3, b1 = sc1 & 7u;
+                    sts128(c_lo, lo[0] * a0, lo[1] * a0, lo[2] * a0, lo[3] * a0);
+                    sts128(c_lo + TC_PLANE, lo[0] * a1, lo[1] * a1, lo[2] * a1, lo[3] * a1);
+                    sts128(c_lo + 2 * TC_PLANE, mm0, mm0, mm0, mm0);
+                    sts128(c_hi, hi[0] * b0, hi[1] * b0, hi[2] * b0, hi[3] * b0);
+                    sts128(c_hi + TC_PLANE, hi[0] * b1, hi[1] * b1, hi[2] * b1, hi[3] * b1);
+                    sts128(c_hi + 2 * TC_PLANE, mm1, mm1, mm1, mm1);
+                }
+            } else {
+                // half h: ql bytes 64h.., qh bytes 32h..; this thread's four chunks are quadrants 2 part, 2 part + 1
+                uint32_t ql[16], qh[8], scw[1];
+                lds_words_a2<16>(rr + 64 * h, ql);
+                lds_words_a2<8>(rr + 128 + 32 * h, qh);
+                lds_words_a2<1>(rr + 192 + 8 * h + 4 * part, scw);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int qd = 2 * part + (i >> 1), w0 = 4 * (i & 1);
+                    const int sc = (int)(int8_t)((scw[0] >> (8 * i)) & 0xFFu);
+                    const uint32_t mag = (uint32_t)(sc < 0 ? -sc : sc);
+                    uint32_t u[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        u[k] = ((ql[8 * (qd & 1) + w0 + k] >> (4 * part)) & 0x0F0F0F0Fu) |
+                               (((qh[w0 + k] >> (2 * qd)) & 0x03030303u) << 4);
+                    const uint32_t dst = sA + (4 * part + i) * (TC_ROWS * 16) + r * 16;
+#pragma unroll
+                    for (int di = 0; di < 4; ++di) {
+                        const uint32_t dg = (mag >> (2 * di)) & 3u;
+                        uint32_t v[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            v[k] = __vsub4(u[k] * dg, dg * 0x20202020u);      // dg * (q6 - 32), per byte
+                            if (sc < 0) v[k] = __vneg4(v[k]);
+                        }
+                        sts128(dst + di * TC_PLANE, v[0], v[1], v[2], v[3]);
+                    }
+                }
+            }
+            fence_async_smem();
+            if (h == 0) {
+                if (!mbar_wait(bar_b, ph_b, p.err)) failed = true;
+                ph_b ^= 1;
+            }
+            tc_fence_before();
+            failed = __syncthreads_or(failed);
+            if (failed) break;
+            if (T::NRAW == 1 && h == 1 && kb + 1 < nb && warp < 4) issue_raw(kb + 1, 0);   // the raw bytes are expanded
+            if (tid == 0) {
+                tc_fence_after();
+#pragma unroll
+                for (int pl = 0; pl < T::NP; ++pl)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_i8(tmem + pl * TC_NTOK,
+                                umma_desc(sA + pl * TC_PLANE + kk * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128),
+                                umma_desc(sB + (8 * h + 2 * kk) * (TC_NTOK * 16), TC_NTOK * 16, 128), IDESC,
+                                (h | kk) ? 1u : 0u);
+                umma_commit(bar_mma);
+            }
+            if (!mbar_wait(bar_mma, ph_mma, p.err)) failed = true;   // (acted on at the next block-wide vote)
+            ph_mma ^= 1;
+            tc_fence_after();
+        }
+        // ---- the block's float terms, in block order
+#pragma unroll
+        for (int piece = 0; piece < 2; ++piece) {
+            int a0[16], a1[16], a2[16], a3[16];
+            tmem_ld16(t_lane + 16 * piece, a0);
+            tmem_ld16(t_lane + TC_NTOK + 16 * piece, a1);
+            tmem_ld16(t_lane + 2 * TC_NTOK + 16 * piece, a2);
+            if (T::NP == 4) tmem_ld16(t_lane + 3 * TC_NTOK + 16 * piece, a3);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float yd = __uint_as_float(lds32(sB + TC_B_Q + 4 * (32 * ch + 16 * piece + i)));
+                float& s = sumf[16 * piece + i];
+                if (TYPE == DC_TYPE_Q4_K) {
+                    const int I = 8 * a0[i] + a1[i];
+                    const float tI = __fmul_rn(__fmul_rn(d, yd), (float)I);
+                    const float tM = __fmul_rn(__fmul_rn(dmin, yd), (float)a2[i]);
+                    s = __fsub_rn(__fadd_rn(s, tI), tM);
+                } else {
+                    const int I = a0[i] + 4 * a1[i] + 16 * a2[i] + 64 * a3[i];
+                    s = __fadd_rn(s, __fmul_rn(__fmul_rn(d, yd), (float)I));
+                }
+            }
+        }
+        tc_fence_before();
+        failed = __syncthreads_or(failed);         // accumulators and block scales are read: both may be overwritten
+        tc_fence_after();
+        if (failed) break;
+        if (kb + 1 < nb && tid == 128) issue_b(kb + 1);
+    }
+
+    if (!failed) {
+        const int row = row0 + 32 * q + lane;
+        if (row < p.N) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int slot = tt * TC_NTOK + 32 * ch + i;
+                if (slot < p.n_slots) p.out[(size_t)slot * p.ldo + row] = sumf[i];
+            }
+        }
+    } else {
+        // a wait ran out: give copies still in flight a bounded chance to land before the buffers go away
+        for (int s = 0; s < 2; ++s) mbar_wait(bar_raw0 + 8 * s, ph_raw[s], nullptr);
+        mbar_wait(bar_b, ph_b, nullptr);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, NCOLS);
+}
+
+}  // namespace dc
+
+using namespace dc;
+
+size_t dc_gemm_tc_act_bytes(int n_slots, int K) {
+    const int n_tt = (n_slots + TC_NTOK - 1) / TC_NTOK;
+    return (size_t)(K / DC_QK_K) * n_tt * TC_ACT_TILE;
+}
+
+int dc_gemm_tc_tiles(int n_slots) { return (n_slots + TC_NTOK - 1) / TC_NTOK; }
+
+// x [n_rows, K] f32 (row stride ldx) -> tiled Q8_K activations for n_tt token tiles; slot_token: optional
+// device array [n_tt * 64] mapping slots to rows of x.
+int dc_launch_quantize_q8k_tiled(dc_ctx* ctx, const float* x, int ldx, int n_rows, int K, uint8_t* act, int n_tt,
+                                 const int* slot_token) {
+    if (K % DC_QK_K || ldx % 4 || ((uintptr_t)x & 15)) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "quantize_q8k_tiled: K=%d ldx=%d", K, ldx);
+    const long long items = (long long)n_tt * TC_NTOK * (K / DC_QK_K);
+    long long blocks = (items + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    k_quantize_q8k_tiled<<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, ldx, n_rows, K, act, n_tt, slot_token);
+    return dc_check_cuda(ctx, cudaGetLastError(), "k_quantize_q8k_tiled");
+}
+
+bool dc_gemm_tc_supports(const dc_weight* w) {
+    if (w->type == DC_TYPE_Q4_K) return ((uintptr_t)w->dev & 15) == 0 && w->row_bytes % 16 == 0;
+    return w->type == DC_TYPE_Q6_K && ((uintptr_t)w->dev & 1) == 0;
+}
+
+// out[slot * ldo + row] = sum over K of w[row] . act[slot] for rows [0, N) and slots [0, n_slots); with tile_expert,
+// token tile t uses the matrix of expert tile_expert[t] (skipped when negative).
+int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
+                      const int* tile_expert) {
+    if (!dc_gemm_tc_supports(w)) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemm_tc: weight type %d or alignment", w->type);
+    GemmTcParams p = {};
+    p.w = w->dev;
+    p.row_bytes = (int)w->row_bytes;
+    p.N = (int)w->N;
+    p.K = (int)w->K;
+    p.act = act;
+    p.n_tt = dc_gemm_tc_tiles(n_slots);
+    p.n_slots = n_slots;
+    p.out = out;
+    p.ldo = ldo;
+    p.tile_expert = tile_expert;
+    p.estride = (size_t)w->N * w->row_bytes;
+    p.err = ctx->d_err;
+    const dim3 grid(p.n_tt, (p.N + TC_ROWS - 1) / TC_ROWS);
+    if (w->type == DC_TYPE_Q4_K) {
+        constexpr size_t smem = tc_smem_bytes<DC_TYPE_Q4_K>();
+        DC_TRY(dc_kernel_setup(ctx, (const void*)k_gemm_tc<DC_TYPE_Q4_K>, smem, "k_gemm_tc<Q4_K>"));
+        k_gemm_tc<DC_TYPE_Q4_K><<<grid, TC_THREADS, smem, ctx->stream>>>(p);
+    } else {
+        constexpr size_t smem = tc_smem_bytes<DC_TYPE_Q6_K>();
+        DC_TRY(dc_kernel_setup(ctx, (const void*)k_gemm_tc<DC_TYPE_Q6_K>, smem, "k_gemm_tc<Q6_K>"));
+        k_gemm_tc<DC_TYPE_Q6_K><<<grid, TC_THREADS, smem, ctx->stream>>>(p);
+    }
+    return dc_check_cuda(ctx, cudaGetLastError(), "k_gemm_tc");
+}

@@ -92,6 +92,38 @@ def test_mul_mat_shapes(ctx, oracle, t, N, K):
     W.free()
 
 
+@pytest.mark.parametrize("t,N,K", [(Q4, 4096, 2048), (Q6, 2048, 768), (Q4, 1000, 512), (Q6, 1000, 2048),
+                                   (Q4, 130, 4096), (Q6, 64, 256)])
+def test_mul_mat_prompt_sized_on_tensor_cores(ctx, oracle, t, N, K):
+    """M >= 32 token rows take the tcgen05 kernel (the CPU serves these shapes through cb_gemv_batched_custom,
+    core/src/llm/matmul/batched_exec.cpp:1040-1240).  Its block sums are exact integers (int8 UMMA into int32
+    accumulators) and the float terms are added block by block: Q4_K is bit-equal to the oracle (the order of
+    core/src/kernels/hwy/hwy_moe_quant.cc:248-253); Q6_K adds one term per block where the CPU small-batch
+    kernel keeps eight lane partials (q6_small_batch.h:84-103): same integers, tolerance 2e-6 of the largest
+    output.  Row counts off the 128-row tile and token counts off the 64-token tile are covered."""
+    rng = np.random.default_rng(77 + N + K)
+    w = B.random_weight(rng, t, N, K)
+    W = ctx.upload_weight(t, w, K, N)
+    for M in (32, 64, 100, 256, 512):
+        x = rng.normal(size=(M, K)).astype(np.float32)
+        x[3, :256] = 0.0                                 # an all-zero activation block
+        x[5] *= 1e-3
+        x[M - 1] *= 37.0
+        got = ctx.mul_mat(W, x)
+        want = oracle.mul_mat(t, w, N, K, x)
+        if t == Q4:
+            assert np.array_equal(got, want), M
+        else:
+            assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max(), (M, np.abs(got - want).max() / np.abs(want).max())
+        # the same rows through the row-streaming kernels (16 at a time): Q4_K identical, Q6_K at the same tolerance
+        if M == 100:
+            ctx.set_option("gemm_tc_min_rows", 0)
+            ref = ctx.mul_mat(W, x)
+            ctx.set_option("gemm_tc_min_rows", 32)
+            assert np.array_equal(ref, want)
+    W.free()
+
+
 def test_mul_mat_linearity_at_full_size(ctx, oracle):
     """Size-independent property at the lm_head size (151936 x 2048 Q6_K): scaling x by a power
     of two scales y by it exactly (Q8_K codes are unchanged, only d doubles)."""
