@@ -304,7 +304,7 @@ static size_t mul_mat_act_bytes(dc_ctx* ctx, const dc_weight* w, int M) {
 static int mul_mat_any(dc_ctx* ctx, const dc_weight* w, const float* x_dev, int M, float* y_dev, uint8_t* act) {
     if (M >= ctx->gemm_tc_min_rows && dc_gemm_tc_supports(w) && ((uintptr_t)x_dev & 15) == 0) {
         DC_TRY(dc_launch_quantize_q8k_tiled(ctx, x_dev, (int)w->K, M, (int)w->K, act, dc_gemm_tc_tiles(M), nullptr));
-        return dc_launch_gemm_tc(ctx, w, act, M, y_dev, (int)w->N, nullptr);
+        return dc_launch_gemm_tc(ctx, w, act, M, y_dev, (int)w->N);
     }
     return mul_mat_chunks(ctx, w, x_dev, M, y_dev, act);
 }

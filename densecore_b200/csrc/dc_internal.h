@@ -80,7 +80,7 @@ bool dc_gemm_tc_supports(const dc_weight* w);
 int dc_launch_quantize_q8k_tiled(dc_ctx* ctx, const float* x, int ldx, int n_rows, int K, uint8_t* act, int n_tt,
                                  const int* slot_token);
 int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
-                      const int* tile_expert);
+                      const int* tile_expert = nullptr, const int* slot_row = nullptr, bool accumulate = false);
 
 
 // ---- misc.cu ----

@@ -40,6 +40,8 @@ struct dc_graph {
     int launches = 0;
 };
 
+struct dc_prefill_buffers;
+
 struct dc_model {
     dc_ctx* ctx = nullptr;
     dc_model_config cfg = {};
@@ -75,6 +77,11 @@ struct dc_model {
     // bounded-wait test hooks: poll limits of the persistent kernel's waits (0 = the defaults)
     unsigned test_barrier_polls = 0;
     unsigned long long test_ep_wait_ns = 0;
+    // prompt chunks through the tensor-core matmuls (prefill.cu): option "tc_prefill" (default on), chunk
+    // length option "prefill_chunk" (default 512, fixed once the first chunk has run)
+    bool use_tc_prefill = true;
+    int prefill_chunk = 512;
+    dc_prefill_buffers* prefill = nullptr;
     bool prefix_cache = false;            // option "prefix_cache": prefill looks up and registers block prefixes
     uint64_t prefill_tokens_run = 0;      // prompt tokens that went through the decoder (cached ones do not)
     // expert parallel
@@ -102,6 +109,10 @@ int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback);
 // its logits in the step buffer) and *next_token receives it after a synchronize.
 int dc_model_prefill_range(dc_model* m, int seq, const int32_t* tokens_host, int n, bool final, int32_t* next_token);
 int dc_mega_prepare(dc_model* m);
+// ---- prefill.cu ----
+bool dc_prefill_tc_ok(dc_model* m, int n);
+int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool lm);
+void dc_prefill_release(dc_model* m);
 // ---- ep.cu ----
 int dc_ep_allreduce(dc_model* m, float* buf, size_t n);
 void dc_ep_destroy(dc_model* m);

@@ -50,6 +50,8 @@ struct GemmTcParams {
     int ldo;
     const int* tile_expert;   // optional [n_tt]: weights of tile t start at w + tile_expert[t] * estride; < 0: tile unused
     size_t estride;
+    const int* slot_row;      // optional [n_tt * 64]: output row of every slot instead of the slot itself; < 0: none
+    int accumulate;           // out += result (one float add) instead of out = result
     int* err;
 };
 
@@ -363,7 +365,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const int slot = tt * TC_NTOK + 32 * ch + i;
-                if (slot < p.n_slots) p.out[(size_t)slot * p.ldo + row] = sumf[i];
+                if (slot >= p.n_slots) continue;
+                const int orow = p.slot_row ? p.slot_row[slot] : slot;
+                if (orow < 0) continue;
+                float* o = p.out + (size_t)orow * p.ldo + row;
+                *o = p.accumulate ? __fadd_rn(*o, sumf[i]) : sumf[i];
             }
         }
     } else {
@@ -407,7 +413,7 @@ bool dc_gemm_tc_supports(const dc_weight* w) {
 // out[slot * ldo + row] = sum over K of w[row] . act[slot] for rows [0, N) and slots [0, n_slots); with tile_expert,
 // token tile t uses the matrix of expert tile_expert[t] (skipped when negative).
 int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
-                      const int* tile_expert) {
+                      const int* tile_expert, const int* slot_row, bool accumulate) {
     if (!dc_gemm_tc_supports(w)) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemm_tc: weight type %d or alignment", w->type);
     GemmTcParams p = {};
     p.w = w->dev;
@@ -420,6 +426,8 @@ int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n
     p.out = out;
     p.ldo = ldo;
     p.tile_expert = tile_expert;
+    p.slot_row = slot_row;
+    p.accumulate = accumulate ? 1 : 0;
     p.estride = (size_t)w->N * w->row_bytes;
     p.err = ctx->d_err;
     const dim3 grid(p.n_tt, (p.N + TC_ROWS - 1) / TC_ROWS);

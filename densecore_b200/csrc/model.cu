@@ -458,6 +458,7 @@ void dc_b200_model_destroy(dc_model* m) {
     for (void* p : ptrs)
         if (p) cudaFree(p);
     if (m->dbg_x) cudaFree(m->dbg_x);
+    dc_prefill_release(m);
     if (m->mega_layers) cudaFree(m->mega_layers);
     if (m->mega_counter) cudaFree(m->mega_counter);
     dc_mega_release_xch(m);
@@ -596,10 +597,18 @@ int dc_b200_seq_truncate(dc_model* m, int seq, int new_len) {
 }  // extern "C"
 
 int dc_model_prefill_range(dc_model* m, int seq, const int32_t* tokens_host, int n, bool final, int32_t* next_token) {
-    for (int i0 = 0; i0 < n; i0 += DC_MAX_T) {
-        const int c = n - i0 < DC_MAX_T ? n - i0 : DC_MAX_T;
-        const bool last = final && i0 + c >= n;
-        DC_TRY(forward_chunk(m, seq, tokens_host + i0, c, last ? 1 : 0));
+    for (int i0 = 0; i0 < n;) {
+        const int left = n - i0;
+        if (dc_prefill_tc_ok(m, left)) {
+            // enough tokens for the tensor-core matmuls: one chunk of up to prefill_chunk tokens
+            const int c = left < m->prefill_chunk ? left : m->prefill_chunk;
+            DC_TRY(dc_prefill_chunk_tc(m, seq, tokens_host + i0, c, final && i0 + c >= n));
+            i0 += c;
+        } else {
+            const int c = left < DC_MAX_T ? left : DC_MAX_T;
+            DC_TRY(forward_chunk(m, seq, tokens_host + i0, c, (final && i0 + c >= n) ? 1 : 0));
+            i0 += c;
+        }
     }
     m->prefill_tokens_run += (uint64_t)n;
     if (!final) return DC_B200_OK;
@@ -823,6 +832,16 @@ int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
     }
     // Test hooks for the bounded waits of the persistent kernel: a limit small enough to run out, so that
     // the error path (status code, usable context afterwards) can be exercised without any real failure.
+    if (!strcmp(name, "tc_prefill")) {
+        m->use_tc_prefill = value != 0;
+        return DC_B200_OK;
+    }
+    if (!strcmp(name, "prefill_chunk")) {
+        if (value < 32 || value > 4096) return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "prefill_chunk must be 32..4096");
+        if (m->prefill) return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "prefill_chunk is fixed once a chunk has run");
+        m->prefill_chunk = value;
+        return DC_B200_OK;
+    }
     if (!strcmp(name, "prefix_cache")) {
         m->prefix_cache = value != 0;
         return DC_B200_OK;

@@ -1,0 +1,297 @@
+// Prompt processing in chunks of up to 512 tokens: every matmul of the decoder runs as one tensor-core
+// MUL_MAT over the whole chunk (gemm_tc.cu) instead of sixteen tokens at a time through the row-streaming
+// kernels, which re-read every weight for each sixteen tokens.  The CPU side of this is DenseCore's batched
+// matmul path for prefill chunks (core/src/llm/matmul/batched_exec.cpp:1040-1240, chunks up to M = 4096,
+// core/src/llm/matmul/dispatch.cpp:622,985-989) and ggml_flash_attn_ext (core/src/llm/attention/exec.cpp:255-275).
+//
+// Per layer: RMSNorm (the decode kernel, one CTA per token) -> tiled Q8_K -> Q, K, V GEMMs -> per-head norm,
+// RoPE and cache write (the decode kernel) -> causal attention of every chunk token over the paged cache
+// (the decode kernels, one grid for the chunk) -> output projection accumulated into the residual ->
+// RMSNorm -> router (sixteen tokens per launch) -> assignments grouped by expert into 64-slot tiles ->
+// gate and up GEMMs with an expert per tile -> SwiGLU + tiled Q8_K -> down GEMM scattered back to
+// assignment order -> weighted combine (the decode kernel).  The last chunk ends with the decode path's
+// output norm, lm_head row-streaming kernel and greedy pick for its last token.
+#include <algorithm>
+
+#include "dc_common.cuh"
+#include "dc_model.h"
+
+#define DC_TRY(expr)                       \
+    do {                                   \
+        int st_ = (expr);                  \
+        if (st_ != DC_B200_OK) return st_; \
+    } while (0)
+
+using namespace dc;
+
+struct dc_prefill_buffers {
+    int cap = 0;               // tokens per chunk
+    int max_tiles = 0;         // 64-slot tiles of the grouped expert matmuls
+    int32_t *tokens = nullptr, *seq_ids = nullptr, *positions = nullptr;
+    float *x = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *g = nullptr, *u = nullptr,
+          *dn = nullptr, *moe_out = nullptr, *logits = nullptr, *weights = nullptr;
+    int32_t* ids = nullptr;
+    int32_t *slot_assign = nullptr, *slot_token = nullptr, *tile_expert = nullptr;
+    uint8_t *act_x = nullptr, *act_att = nullptr, *act_moe = nullptr, *act_h = nullptr, *attn_mem = nullptr;
+    dc_attn_scratch attn = {};
+    int32_t* h_stage = nullptr;   // pinned: ring of (tokens, seq ids, positions) triples
+    int stage_slot = 0;
+    std::vector<void*> owned;
+};
+
+static constexpr int PF_STAGE_SLOTS = 4;
+
+void dc_prefill_release(dc_model* m) {
+    dc_prefill_buffers* P = m->prefill;
+    if (!P) return;
+    for (void* p : P->owned) cudaFree(p);
+    if (P->h_stage) cudaFreeHost(P->h_stage);
+    delete P;
+    m->prefill = nullptr;
+}
+
+template <typename T>
+static int pf_alloc(dc_model* m, T** p, size_t n) {
+    DC_TRY(dc_check_cuda(m->ctx, cudaMalloc((void**)p, n * sizeof(T) + 256), "cudaMalloc(prefill buffer)"));
+    m->prefill->owned.push_back((void*)*p);
+    return DC_B200_OK;
+}
+
+static int prefill_prepare(dc_model* m) {
+    if (m->prefill) return DC_B200_OK;
+    const dc_model_config& c = m->cfg;
+    dc_prefill_buffers* P = m->prefill = new dc_prefill_buffers();
+    const size_t C = (size_t)m->prefill_chunk, H = c.hidden, QD = (size_t)c.n_head * 128, KD = (size_t)c.n_kv_head * 128;
+    const bool moe = c.n_expert > 0;
+    const size_t F = moe ? c.expert_ffn : c.ffn;
+    const size_t A = moe ? C * c.n_expert_used : C;
+    // every expert's assignments are padded to whole tiles: at most one partly filled tile per expert
+    P->max_tiles = moe ? (int)(A / 64 + c.n_expert) : (int)((C + 63) / 64);
+    const size_t slots = (size_t)P->max_tiles * 64;
+    P->cap = (int)C;
+    int st = DC_B200_OK;
+    auto A_ = [&](int s) { if (st == DC_B200_OK) st = s; };
+    A_(pf_alloc(m, &P->tokens, C));
+    A_(pf_alloc(m, &P->seq_ids, C));
+    A_(pf_alloc(m, &P->positions, C));
+    A_(pf_alloc(m, &P->x, C * H));
+    A_(pf_alloc(m, &P->xn, C * H));
+    A_(pf_alloc(m, &P->qkv, C * (QD + 2 * KD)));
+    A_(pf_alloc(m, &P->q, C * QD));
+    A_(pf_alloc(m, &P->att, C * QD));
+    A_(pf_alloc(m, &P->g, slots * F));
+    A_(pf_alloc(m, &P->u, slots * F));
+    A_(pf_alloc(m, &P->act_x, dc_gemm_tc_act_bytes((int)C, (int)H)));
+    A_(pf_alloc(m, &P->act_att, dc_gemm_tc_act_bytes((int)C, (int)QD)));
+    A_(pf_alloc(m, &P->act_h, dc_gemm_tc_act_bytes((int)slots, (int)F)));
+    if (moe) {
+        A_(pf_alloc(m, &P->dn, A * H));
+        A_(pf_alloc(m, &P->moe_out, C * H));
+        A_(pf_alloc(m, &P->logits, C * c.n_expert));
+        A_(pf_alloc(m, &P->weights, A));
+        A_(pf_alloc(m, &P->ids, A));
+        A_(pf_alloc(m, &P->slot_assign, slots));
+        A_(pf_alloc(m, &P->slot_token, slots));
+        A_(pf_alloc(m, &P->tile_expert, (size_t)P->max_tiles));
+        A_(pf_alloc(m, &P->act_moe, dc_gemm_tc_act_bytes((int)slots, (int)H)));
+    }
+    const size_t att_bytes = dc_attention_scratch_bytes((int)C, c.n_head, c.n_kv_head, m->kv.max_blocks_per_seq, m->nsplit);
+    A_(pf_alloc(m, &P->attn_mem, att_bytes));
+    if (st == DC_B200_OK) {
+        dc_attn_scratch_bind(&P->attn, P->attn_mem, (int)C, c.n_head, c.n_kv_head, m->kv.max_blocks_per_seq, m->nsplit);
+        st = dc_check_cuda(m->ctx, cudaMemsetAsync(P->attn.tickets, 0, C * c.n_head * 4, m->ctx->stream), "memset");
+    }
+    if (st == DC_B200_OK) st = dc_check_cuda(m->ctx, cudaMallocHost((void**)&P->h_stage, PF_STAGE_SLOTS * 3 * C * 4), "cudaMallocHost");
+    if (st != DC_B200_OK) dc_prefill_release(m);
+    return st;
+}
+
+// ---- grouping of the chunk's expert assignments ----------------------------------------------------------
+// ids [C][top_k] -> for every expert (ascending) its assignments in assignment order, padded to whole 64-slot
+// tiles: slot_assign[slot] = t * top_k + k or -1, slot_token[slot] = t or -1, tile_expert[tile] = expert or -1.
+// One CTA; thread e owns expert e.
+__global__ void __launch_bounds__(256) k_moe_group(const int32_t* __restrict__ ids, int A, int top_k, int E, int max_tiles,
+                                                   int32_t* __restrict__ slot_assign, int32_t* __restrict__ slot_token,
+                                                   int32_t* __restrict__ tile_expert) {
+    extern __shared__ int32_t s_ids[];
+    __shared__ int s_scan[256];
+    for (int i = threadIdx.x; i < A; i += blockDim.x) s_ids[i] = ids[i];
+    __syncthreads();
+    const int e = threadIdx.x;
+    int cnt = 0;
+    if (e < E)
+        for (int i = 0; i < A; ++i) cnt += (s_ids[i] == e);
+    const int tiles = (cnt + 63) / 64;
+    s_scan[e] = tiles;
+    __syncthreads();
+    // exclusive prefix over the 256 threads (tiny: serial per thread)
+    int off = 0;
+    for (int i = 0; i < e; ++i) off += s_scan[i];
+    int total = 0;
+    for (int i = 0; i < 256; ++i) total += s_scan[i];
+    if (e < E && tiles > 0) {
+        for (int t = 0; t < tiles; ++t) tile_expert[off + t] = e;
+        int slot = off * 64;
+        for (int i = 0; i < A; ++i)
+            if (s_ids[i] == e) {
+                slot_assign[slot] = i;
+                slot_token[slot] = i / top_k;
+                ++slot;
+            }
+        for (; slot < (off + tiles) * 64; ++slot) {
+            slot_assign[slot] = -1;
+            slot_token[slot] = -1;
+        }
+    }
+    for (int t = total + threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+    for (int s = total * 64 + threadIdx.x; s < max_tiles * 64; s += blockDim.x) {
+        slot_assign[s] = -1;
+        slot_token[s] = -1;
+    }
+}
+
+// h = silu(g) * u per slot (the production SwiGLU of the CPU kernels, see silu_fast), quantised to the
+// tiled Q8_K layout of the down projection's activations.  One warp per (slot, 256-value block);
+// slot_valid (optional): slots whose entry is negative hold zeros.
+__global__ void __launch_bounds__(256) k_swiglu_q8k_tiled(const float* __restrict__ g, const float* __restrict__ u, int F,
+                                                          int n_slots_data, uint8_t* __restrict__ act, int n_tt,
+                                                          const int32_t* __restrict__ slot_valid) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = F / DC_QK_K;
+    const long long total = (long long)n_tt * 64 * nb;
+    for (long long item = (long long)blockIdx.x * 8 + warp; item < total; item += (long long)gridDim.x * 8) {
+        const int b = (int)(item % nb), slot = (int)(item / nb);
+        const bool live = slot < n_slots_data && (!slot_valid || slot_valid[slot] >= 0);
+        uint8_t* tile = act + ((size_t)b * n_tt + slot / 64) * (16 * 64 * 16 + 64 * 4);
+        uint32_t w0 = 0, w1 = 0, bw = 0;
+        float d = 0.0f;
+        if (live) {
+            const size_t base = (size_t)slot * F + (size_t)b * DC_QK_K + 8 * lane;
+            const float4 g0 = *reinterpret_cast<const float4*>(g + base), g1 = *reinterpret_cast<const float4*>(g + base + 4);
+            const float4 u0 = *reinterpret_cast<const float4*>(u + base), u1 = *reinterpret_cast<const float4*>(u + base + 4);
+            const float v[8] = {__fmul_rn(silu_fast(g0.x), u0.x), __fmul_rn(silu_fast(g0.y), u0.y),
+                                __fmul_rn(silu_fast(g0.z), u0.z), __fmul_rn(silu_fast(g0.w), u0.w),
+                                __fmul_rn(silu_fast(g1.x), u1.x), __fmul_rn(silu_fast(g1.y), u1.y),
+                                __fmul_rn(silu_fast(g1.z), u1.z), __fmul_rn(silu_fast(g1.w), u1.w)};
+            q8k_block_core(v, lane, w0, w1, bw, d);
+        }
+        *reinterpret_cast<uint2*>(tile + (lane >> 1) * (64 * 16) + (slot % 64) * 16 + 8 * (lane & 1)) = make_uint2(w0, w1);
+        if (lane == 0) reinterpret_cast<float*>(tile + 16 * 64 * 16)[slot % 64] = d;
+    }
+}
+
+static int launch_swiglu(dc_ctx* ctx, const float* g, const float* u, int F, int n_slots_data, uint8_t* act, int n_tt,
+                         const int32_t* slot_valid) {
+    const long long items = (long long)n_tt * 64 * (F / DC_QK_K);
+    long long blocks = (items + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    k_swiglu_q8k_tiled<<<(unsigned)blocks, 256, 0, ctx->stream>>>(g, u, F, n_slots_data, act, n_tt, slot_valid);
+    return dc_check_cuda(ctx, cudaGetLastError(), "k_swiglu_q8k_tiled");
+}
+
+// ---- one chunk ---------------------------------------------------------------------------------------------
+bool dc_prefill_tc_ok(dc_model* m, int n) {
+    const dc_model_config& c = m->cfg;
+    if (!m->use_tc_prefill || n < m->ctx->gemm_tc_min_rows || c.ep_size > 1 || m->dbg_x || m->prof) return false;
+    for (const dc_layer& L : m->layers) {
+        const dc_weight* ws[] = {L.wq, L.wk, L.wv, L.wo, L.gate_exps, L.up_exps, L.down_exps, L.ffn_gate, L.ffn_up, L.ffn_down};
+        for (const dc_weight* w : ws)
+            if (w && !dc_gemm_tc_supports(w)) return false;
+    }
+    return true;
+}
+
+// Appends n <= prefill_chunk tokens to the sequence; lm: also the logits and greedy pick of the last token
+// (left in the step buffers of the decode path).
+int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool lm) {
+    DC_TRY(prefill_prepare(m));
+    dc_prefill_buffers& P = *m->prefill;
+    const dc_model_config& c = m->cfg;
+    dc_ctx* ctx = m->ctx;
+    dc_kv_seq& s = m->kv.seqs[seq];
+    if (n > P.cap) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "prefill chunk of %d tokens exceeds %d", n, P.cap);
+    if (s.len + n > c.max_ctx) return dc_fail(ctx, DC_B200_OUT_OF_MEMORY, "sequence %d would exceed max_ctx %d", seq, c.max_ctx);
+    for (int i = 0; i < n; ++i)
+        if (tokens[i] < 0 || tokens[i] >= c.vocab) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "token id %d out of range", tokens[i]);
+    DC_TRY(dc_kv_seq_reserve(&m->kv, seq, s.len + n));
+    // inputs through a pinned ring
+    if (P.stage_slot == 0) cudaStreamSynchronize(ctx->stream);
+    int32_t* st = P.h_stage + (size_t)P.stage_slot * 3 * P.cap;
+    P.stage_slot = (P.stage_slot + 1) % PF_STAGE_SLOTS;
+    for (int i = 0; i < n; ++i) {
+        st[i] = tokens[i];
+        st[P.cap + i] = seq;
+        st[2 * P.cap + i] = s.len + i;
+    }
+    DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(P.tokens, st, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream), "H2D tokens"));
+    DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(P.seq_ids, st + P.cap, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream), "H2D seqs"));
+    DC_TRY(dc_check_cuda(ctx, cudaMemcpyAsync(P.positions, st + 2 * P.cap, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream), "H2D positions"));
+
+    const int H = c.hidden, QD = c.n_head * 128, KD = c.n_kv_head * 128, QKV = QD + 2 * KD;
+    const float scale = 1.0f / sqrtf((float)c.head_dim);
+    const int E = c.n_expert, top_k = c.n_expert_used;
+    const int n_tt = dc_gemm_tc_tiles(n);
+    DC_TRY(dc_launch_embed(ctx, m->tok_embd, P.tokens, n, P.x));
+    const float* pending = nullptr;   // MoE output of the previous layer, added in the next norm
+    for (int il = 0; il < c.n_layer; ++il) {
+        dc_layer& Ly = m->layers[il];
+        DC_TRY(dc_launch_rmsnorm_q8k(ctx, P.x, pending, (const float*)Ly.attn_norm->dev, n, H, c.rms_eps, P.xn, nullptr));
+        pending = nullptr;
+        DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_x, n_tt, nullptr));
+        DC_TRY(dc_launch_gemm_tc(ctx, Ly.wq, P.act_x, n, P.qkv, QKV));
+        DC_TRY(dc_launch_gemm_tc(ctx, Ly.wk, P.act_x, n, P.qkv + QD, QKV));
+        DC_TRY(dc_launch_gemm_tc(ctx, Ly.wv, P.act_x, n, P.qkv + QD + KD, QKV));
+        __half* ka = m->kv.k_arena + m->kv.layer_elems * il;
+        __half* va = m->kv.v_arena + m->kv.layer_elems * il;
+        DC_TRY(dc_launch_qknorm_rope_kv(ctx, P.qkv, Ly.q_norm ? (const float*)Ly.q_norm->dev : nullptr,
+                                        Ly.k_norm ? (const float*)Ly.k_norm->dev : nullptr, m->buf.cos_sin, c.max_ctx, P.positions,
+                                        P.seq_ids, m->kv.d_tables, m->kv.max_blocks_per_seq, ka, va, c.n_head, c.n_kv_head,
+                                        c.rms_eps, n, P.q));
+        DC_TRY(dc_launch_attention(ctx, P.q, ka, va, m->kv.d_tables, m->kv.max_blocks_per_seq, P.seq_ids, P.positions, n,
+                                   c.n_head, c.n_kv_head, scale, m->nsplit, &P.attn, P.att, nullptr));
+        DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.att, QD, n, QD, P.act_att, n_tt, nullptr));
+        DC_TRY(dc_launch_gemm_tc(ctx, Ly.wo, P.act_att, n, P.x, H, nullptr, nullptr, true));
+        DC_TRY(dc_launch_rmsnorm_q8k(ctx, P.x, nullptr, (const float*)Ly.ffn_norm->dev, n, H, c.rms_eps, P.xn, nullptr));
+        if (E > 0) {
+            const int A = n * top_k, F = c.expert_ffn;
+            for (int t0 = 0; t0 < n; t0 += DC_MAX_T) {
+                const int tn = std::min(DC_MAX_T, n - t0);
+                dc_moe_route rt = m->buf.route;     // unit lists of the decode path: written, not used here
+                rt.logits = P.logits + (size_t)t0 * E;
+                rt.ids = P.ids + (size_t)t0 * top_k;
+                rt.weights = P.weights + (size_t)t0 * top_k;
+                DC_TRY(dc_launch_router(ctx, Ly.router, P.xn + (size_t)t0 * H, E, tn, top_k, c.routed_scale, 0, E, &rt, m->route_mode));
+            }
+            k_moe_group<<<1, 256, (size_t)A * 4, ctx->stream>>>(P.ids, A, top_k, E, P.max_tiles, P.slot_assign, P.slot_token, P.tile_expert);
+            DC_TRY(dc_check_cuda(ctx, cudaGetLastError(), "k_moe_group"));
+            const int slots = P.max_tiles * 64;
+            DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_moe, P.max_tiles, P.slot_token));
+            DC_TRY(dc_launch_gemm_tc(ctx, Ly.gate_exps, P.act_moe, slots, P.g, F, P.tile_expert));
+            DC_TRY(dc_launch_gemm_tc(ctx, Ly.up_exps, P.act_moe, slots, P.u, F, P.tile_expert));
+            DC_TRY(launch_swiglu(ctx, P.g, P.u, F, slots, P.act_h, P.max_tiles, P.slot_assign));
+            DC_TRY(dc_launch_gemm_tc(ctx, Ly.down_exps, P.act_h, slots, P.dn, H, P.tile_expert, P.slot_assign));
+            DC_TRY(dc_launch_moe_combine(ctx, P.dn, P.ids, P.weights, n, top_k, H, 0, E, P.moe_out));
+            pending = P.moe_out;
+        } else {
+            const int F = c.ffn;
+            DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_x, n_tt, nullptr));
+            DC_TRY(dc_launch_gemm_tc(ctx, Ly.ffn_gate, P.act_x, n, P.g, F));
+            DC_TRY(dc_launch_gemm_tc(ctx, Ly.ffn_up, P.act_x, n, P.u, F));
+            DC_TRY(launch_swiglu(ctx, P.g, P.u, F, n, P.act_h, n_tt, nullptr));
+            DC_TRY(dc_launch_gemm_tc(ctx, Ly.ffn_down, P.act_h, n, P.x, H, nullptr, nullptr, true));
+        }
+    }
+    if (lm) {
+        // the last token through the decode path's output norm, lm_head and greedy pick
+        dc_step_buffers& b = m->buf;
+        const size_t off = (size_t)(n - 1) * H;
+        DC_TRY(dc_launch_rmsnorm_q8k(ctx, P.x + off, pending ? pending + off : nullptr, (const float*)m->out_norm->dev, 1, H,
+                                     c.rms_eps, nullptr, b.q8_x));
+        const dc_weight* out_w = c.tie_embeddings ? m->tok_embd : m->output;
+        dc_gemv_seg lmh = {out_w->dev, out_w->type, c.vocab, (int)out_w->row_bytes, b.logits, c.vocab};
+        DC_TRY(dc_launch_gemv(ctx, &lmh, 1, DC_EPI_STORE, b.q8_x, 1, H, b.argmax_keys));
+        DC_TRY(dc_launch_argmax_finish(ctx, b.argmax_keys, 1, b.out_tokens, nullptr, nullptr, nullptr, nullptr, DC_HISTORY_CAP));
+    }
+    s.len += n;
+    return DC_B200_OK;
+}

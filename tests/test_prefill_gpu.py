@@ -1,0 +1,127 @@
+"""Prompt chunks through the tensor-core matmuls (the CPU serves prefill through its batched matmul path,
+core/src/llm/matmul/batched_exec.cpp:1040-1240, and ggml_flash_attn_ext, core/src/llm/attention/exec.cpp:255-275)
+against the sixteen-token path that the oracle tests pin, and against the CPU decoder itself."""
+import time
+
+import numpy as np
+import pytest
+
+import densecore_b200 as dc
+from oracle.decoder_ref import RefModel
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    return float(np.abs(a - b).max() / (np.abs(b).max() + 1e-30))
+
+
+def names_of(cfg):
+    names = ["token_embd.weight", "output_norm.weight"] + ([] if cfg.tie_embeddings else ["output.weight"])
+    per = ["attn_norm.weight", "attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight", "ffn_norm.weight",
+           "attn_q_norm.weight", "attn_k_norm.weight"]
+    per += (["ffn_gate_inp.weight", "ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"] if cfg.n_expert
+            else ["ffn_gate.weight", "ffn_up.weight", "ffn_down.weight"])
+    for il in range(cfg.n_layer):
+        names += [f"blk.{il}.{n}" for n in per]
+    return names
+
+
+CONFIGS = {
+    "moe_small": dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, vocab=1000, n_expert=8, n_expert_used=2, expert_ffn=256),
+    "dense_small": dict(n_layer=2, hidden=512, n_head=4, n_kv_head=2, vocab=1000, ffn=768, tie_embeddings=True),
+    # one layer pair at the benchmark model's width: 128 experts, top-8, 32 query / 4 KV heads
+    "moe_full_width": dict(n_layer=2, hidden=2048, n_head=32, n_kv_head=4, vocab=8192, n_expert=128, n_expert_used=8,
+                           expert_ffn=768),
+}
+
+
+def build_model(ctx, cfg, all_q4k: bool):
+    """Synthetic weights; all_q4k: every Q6_K matrix replaced by a Q4_K one of the same shape, so that every
+    matmul of both prefill paths is bit-equal and the two paths must agree bit for bit."""
+    m = dc.Model(ctx, cfg)
+    m.init_synthetic(21, 0.05)
+    if all_q4k:
+        from densecore_b200 import blocks as B
+        src = m
+        tensors = {n: src.get_tensor(n) for n in names_of(cfg)}
+        m = dc.Model(ctx, cfg)
+        rng = np.random.default_rng(99)
+        for n, (t, (K, N, E), data) in tensors.items():
+            if t == dc.GGML_TYPE_Q6_K:
+                t, data = dc.GGML_TYPE_Q4_K, B.random_q4k(rng, N * E, K, 0.02)
+            m.set_tensor(n, t, data, K, N, E)
+        src.close()
+    m.finalize()
+    return m
+
+
+@pytest.mark.parametrize("name,n_prompt,all_q4k", [("moe_small", 200, True), ("dense_small", 333, True), ("moe_small", 200, False),
+                                                   ("dense_small", 333, False), ("moe_full_width", 700, False)])
+def test_chunked_prefill_on_tensor_cores_matches_the_sixteen_token_path(ctx, name, n_prompt, all_q4k):
+    cfg = dc.Config(max_seqs=2, max_ctx=1024, **CONFIGS[name])
+    m = build_model(ctx, cfg, all_q4k)
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, cfg.vocab, size=n_prompt)
+    res = {}
+    for tc in (0, 1):
+        m.set_option("tc_prefill", tc)
+        s = m.seq_alloc()
+        t0 = time.perf_counter()
+        first, lg = m.prefill(s, prompt, want_logits=True)
+        dt = time.perf_counter() - t0
+        run, _ = m.decode_run([s], [first], 6)
+        k0, v0 = m.read_kv(0, s, 0, n_prompt)
+        k1, v1 = m.read_kv(cfg.n_layer - 1, s, 0, n_prompt)
+        res[tc] = (first, lg.copy(), run[:, 0].copy(), k0, v0, k1, v1, dt)
+        m.seq_free(s)
+    a, b = res[0], res[1]
+    if all_q4k:
+        # every product is bit-equal in both paths, and norms, RoPE, attention, routing and combine are the same
+        # kernels: the chunked path must reproduce the sixteen-token path exactly
+        assert a[0] == b[0] and np.array_equal(a[1], b[1]) and np.array_equal(a[2], b[2])
+        for i in range(3, 7):
+            assert np.array_equal(a[i], b[i])
+        m.close()
+        return
+    print(f"{name}: prefill of {n_prompt} tokens {a[7] * 1e3:.1f} ms (sixteen-token path) -> {b[7] * 1e3:.1f} ms; "
+          f"logits rel {rel(b[1], a[1]):.2e}")
+    # layer 0's K and V rows come from bit-equal Q4_K products and norms: identical fp16 bytes wherever the
+    # projection is Q4_K; a Q6_K projection (different float order of equal integers) may move a value by one
+    # fp16 step
+    for x, y in ((a[3], b[3]), (a[4], b[4])):
+        d = np.abs(x.view(np.float16).astype(np.float32) - y.view(np.float16).astype(np.float32))
+        assert d.max() <= 2e-3 * np.abs(x.view(np.float16).astype(np.float32)).max()
+    # with Q6_K matrices the two paths differ by the float order of equal integer sums (~1e-7 per product); each
+    # Q8_K re-quantisation and fp16 cache write can turn that into a one-step flip, so whole-model logits of two
+    # correct paths drift apart like those of the GPU and the CPU do (see the layer-reset tests): reported, and
+    # gated at the loose end-to-end figure
+    assert rel(b[1], a[1]) < 5e-2
+    margin = np.sort(a[1])[-1] - np.sort(a[1])[-2]
+    if margin > 1e-2 * np.abs(a[1]).max():
+        assert a[0] == b[0]
+    m.close()
+
+
+def test_chunked_prefill_against_the_cpu_decoder(ctx):
+    """A 100-token prompt (one 64-token tile and a ragged one) against oracle/decoder_ref.py token by token."""
+    cfg = dc.Config(max_seqs=2, max_ctx=256, **CONFIGS["moe_small"])
+    m = dc.Model(ctx, cfg)
+    m.init_synthetic(42, 0.05)
+    m.finalize()
+    ref = RefModel(cfg, {n: m.get_tensor(n) for n in names_of(cfg)})
+    rng = np.random.default_rng(17)
+    prompt = rng.integers(0, cfg.vocab, size=100)
+    s = m.seq_alloc()
+    first, lg = m.prefill(s, prompt, want_logits=True)
+    for t in prompt:
+        lr = ref.step(s, int(t))
+    r = rel(lg, lr)
+    print(f"tensor-core prefill vs the CPU decoder after 100 tokens: logits rel {r:.2e}")
+    assert r < 5e-2
+    # the first layer's cache rows depend on no attention history: they match the CPU's fp16 rows to one step
+    k0, v0 = m.read_kv(0, s, 0, 100)
+    kr = ref.k[0][s * ref.bps * 16: s * ref.bps * 16 + 100]
+    d = np.abs(k0.view(np.float16).astype(np.float32) - kr.view(np.float16).astype(np.float32))
+    assert d.max() <= 2e-3 * np.abs(kr.view(np.float16).astype(np.float32)).max()
+    m.close()
