@@ -100,6 +100,7 @@ def _signatures() -> dict:
         "dc_b200_sched_pending": (i32, [vp]),
         "dc_b200_sched_stats": (i32, [vp, vp]),
         "dc_b200_flash_attn_decode": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, vp]),
+        "dc_b200_flash_attn_prefill": (i32, [vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, f32, vp]),
         "dc_b200_kv_read_block": (i32, [vp, i32, i32, vp, vp]),
         "dc_b200_argmax": (i32, [vp, vp, i32, i32, vp]),
         "dc_b200_verify_accept": (i32, [vp, vp, vp, vp, vp, u64, u32, i32, i32, i32, f32, pi, pi]),

@@ -112,6 +112,10 @@ int dc_launch_attention(dc_ctx* ctx, const float* q, const void* k_arena, const 
                         uint8_t* q8_out);
 
 // ---- moe.cu ----
+// causal attention of a prompt chunk (positions pos0 .. pos0 + n - 1 of one sequence) on the tensor cores
+int dc_launch_attention_prefill(dc_ctx* ctx, const float* q, const void* k_arena, const void* v_arena, const int32_t* table,
+                                int pos0, int n, int n_head, int n_kv, float scale, float* out);
+
 struct dc_moe_route {
     float* logits;     // [T][E]
     int32_t* ids;      // [T][top_k]
@@ -128,6 +132,9 @@ struct dc_moe_route {
 enum { DC_ROUTE_STABLE = 0, DC_ROUTE_SOFTMAX = 1 };
 int dc_launch_router(dc_ctx* ctx, const dc_weight* wr, const float* xn, int n_expert, int T, int top_k, float scale,
                      int ep_lo, int ep_hi, const dc_moe_route* rt, int mode = DC_ROUTE_STABLE);
+// the same routing for any number of tokens (prompt chunks): logits [T][E], ids and weights [T][top_k]
+int dc_launch_router_batched(dc_ctx* ctx, const dc_weight* wr, const float* xn, int T, int top_k, float scale, float* logits,
+                             int32_t* ids, float* weights, int mode);
 // carves a dc_moe_route for (T, E, top_k) out of a byte buffer; returns bytes used
 size_t dc_moe_route_bind(dc_moe_route* rt, uint8_t* base, int T, int E, int top_k);
 int dc_launch_moe_mm(dc_ctx* ctx, bool pair, const dc_weight* w0, const dc_weight* w1, const uint8_t* act_q8,

@@ -81,6 +81,7 @@ struct dc_model {
     // length option "prefill_chunk" (default 512, fixed once the first chunk has run)
     bool use_tc_prefill = true;
     int prefill_chunk = 512;
+    bool prefill_flash = true;            // option "prefill_attention": 1 tensor-core flash attention, 0 the decode kernels' exact chain
     dc_prefill_buffers* prefill = nullptr;
     bool prefix_cache = false;            // option "prefix_cache": prefill looks up and registers block prefixes
     uint64_t prefill_tokens_run = 0;      // prompt tokens that went through the decoder (cached ones do not)

@@ -836,6 +836,10 @@ int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
         m->use_tc_prefill = value != 0;
         return DC_B200_OK;
     }
+    if (!strcmp(name, "prefill_attention")) {
+        m->prefill_flash = value != 0;
+        return DC_B200_OK;
+    }
     if (!strcmp(name, "prefill_chunk")) {
         if (value < 32 || value > 4096) return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "prefill_chunk must be 32..4096");
         if (m->prefill) return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "prefill_chunk is fixed once a chunk has run");

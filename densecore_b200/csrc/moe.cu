@@ -54,6 +54,107 @@ __device__ __forceinline__ unsigned long long route_key(float v, int id) {
 // exponentials must be the CPU's bit for bit.
 __device__ __forceinline__ float expf_cr(float x) { return (float)exp((double)x); }
 
+// Routing of token t by one warp: stable top-k on the logits (native router) or on the softmax probabilities
+// (generic router), then the routing weights.  s_prob: MOE_MAX_E floats of shared memory owned by this warp;
+// s_ids (optional): shared copy of the ids for the bucketing that follows in k_router.
+__device__ __forceinline__ void route_token(const RouterParams& p, int t, int lane, float* s_prob, int32_t* s_ids) {
+    float lv[MOE_MAX_E / 32];
+    bool taken[MOE_MAX_E / 32];
+#pragma unroll
+    for (int j = 0; j < MOE_MAX_E / 32; ++j) {
+        const int id = j * 32 + lane;
+        lv[j] = id < p.E ? __ldcg(p.logits + (size_t)t * p.E + id) : 0.0f;
+        taken[j] = id >= p.E;
+    }
+    if (p.mode == DC_ROUTE_SOFTMAX) {
+        // softmax over all experts: expf(x - max), sum in index order, times 1/sum
+        // (core/include/densecore/simd/simd_ops.h:1171-1195); selection then runs on the probabilities
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < MOE_MAX_E / 32; ++j)
+            if (!taken[j]) mx = fmaxf(mx, lv[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+#pragma unroll
+        for (int j = 0; j < MOE_MAX_E / 32; ++j) {
+            if (!taken[j]) {
+                lv[j] = expf_cr(__fsub_rn(lv[j], mx));
+                s_prob[j * 32 + lane] = lv[j];
+            }
+        }
+        __syncwarp();
+        float sum = 0.0f;
+        if (lane == 0)
+            for (int e = 0; e < p.E; ++e) sum = __fadd_rn(sum, s_prob[e]);
+        sum = __shfl_sync(0xffffffffu, sum, 0);
+        const float inv = __fdiv_rn(1.0f, sum);
+#pragma unroll
+        for (int j = 0; j < MOE_MAX_E / 32; ++j)
+            if (!taken[j]) lv[j] = __fmul_rn(lv[j], inv);
+        __syncwarp();
+    }
+    float sel_l[MOE_MAX_K];
+    for (int k = 0; k < p.top_k; ++k) {
+        unsigned long long best = 0ull;
+#pragma unroll
+        for (int j = 0; j < MOE_MAX_E / 32; ++j) {
+            if (!taken[j]) {
+                const unsigned long long key = route_key(lv[j], j * 32 + lane);
+                best = key > best ? key : best;
+            }
+        }
+        // a real candidate's key is never 0 (its low word is 0xFFFFFFFF - id), so 0 means "none"
+        unsigned long long win = best;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long ok = __shfl_xor_sync(0xffffffffu, win, o);
+            win = ok > win ? ok : win;
+        }
+        const int wid = (int)(0xFFFFFFFFu - (uint32_t)(win & 0xFFFFFFFFull));
+#pragma unroll
+        for (int j = 0; j < MOE_MAX_E / 32; ++j)
+            if (j * 32 + lane == wid) taken[j] = true;
+        // the winner's value back out of its key (NaN stays NaN; -0 was made +0, which exp treats alike):
+        // no load per round
+        const uint32_t ku = (uint32_t)(win >> 32);
+        const float wl = __uint_as_float((ku & 0x80000000u) ? (ku & 0x7FFFFFFFu) : ~ku);
+        if (k < MOE_MAX_K) sel_l[k] = wl;
+        if (lane == 0) {
+            p.ids[t * p.top_k + k] = wid;
+            if (s_ids) s_ids[t * p.top_k + k] = wid;
+        }
+    }
+    if (lane == 0 && p.mode == DC_ROUTE_SOFTMAX) {
+        // renormalise over the picks in pick order: w * (1 / sum) (core/src/moe/moe_routing.cpp:90-101),
+        // then the routed scaling factor (core/src/llm/moe/exec.cpp:764-768)
+        float sum = 0.0f;
+        for (int k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, sel_l[k]);
+        const float is = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 1.0f;
+        for (int k = 0; k < p.top_k; ++k)
+            p.weights[t * p.top_k + k] = __fmul_rn(sum > 0.0f ? __fmul_rn(sel_l[k], is) : sel_l[k], p.scale);
+    } else if (lane == 0) {
+        // weights over the selected experts only (native.cpp:649-674)
+        float mx = -INFINITY;
+        bool finite = true;
+        for (int k = 0; k < p.top_k; ++k) {
+            finite = finite && isfinite(sel_l[k]);
+            if (isfinite(sel_l[k]) && sel_l[k] > mx) mx = sel_l[k];
+        }
+        float den = 0.0f, wv[MOE_MAX_K];
+        if (finite && isfinite(mx)) {
+            for (int k = 0; k < p.top_k; ++k) {
+                wv[k] = expf(sel_l[k] - mx);
+                den += wv[k];
+            }
+        }
+        const bool ok = den > 0.0f && isfinite(den);
+        for (int k = 0; k < p.top_k; ++k) {
+            const float w = ok ? __fdiv_rn(wv[k], den) : __fdiv_rn(1.0f, (float)p.top_k);
+            p.weights[t * p.top_k + k] = __fmul_rn(w, p.scale);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
     __shared__ int s_last;
     __shared__ float s_prob[8][MOE_MAX_E];
@@ -137,103 +238,7 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
     if (threadIdx.x == 0) *p.ticket = 0;
 
     // ---- stable top-k per token, one warp per token
-    for (int t = warp; t < p.T; t += 8) {
-        float lv[MOE_MAX_E / 32];
-        bool taken[MOE_MAX_E / 32];
-#pragma unroll
-        for (int j = 0; j < MOE_MAX_E / 32; ++j) {
-            const int id = j * 32 + lane;
-            lv[j] = id < p.E ? __ldcg(p.logits + (size_t)t * p.E + id) : 0.0f;
-            taken[j] = id >= p.E;
-        }
-        if (p.mode == DC_ROUTE_SOFTMAX) {
-            // softmax over all experts: expf(x - max), sum in index order, times 1/sum
-            // (core/include/densecore/simd/simd_ops.h:1171-1195); selection then runs on the probabilities
-            float mx = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < MOE_MAX_E / 32; ++j)
-                if (!taken[j]) mx = fmaxf(mx, lv[j]);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-#pragma unroll
-            for (int j = 0; j < MOE_MAX_E / 32; ++j) {
-                if (!taken[j]) {
-                    lv[j] = expf_cr(__fsub_rn(lv[j], mx));
-                    s_prob[warp][j * 32 + lane] = lv[j];
-                }
-            }
-            __syncwarp();
-            float sum = 0.0f;
-            if (lane == 0)
-                for (int e = 0; e < p.E; ++e) sum = __fadd_rn(sum, s_prob[warp][e]);
-            sum = __shfl_sync(0xffffffffu, sum, 0);
-            const float inv = __fdiv_rn(1.0f, sum);
-#pragma unroll
-            for (int j = 0; j < MOE_MAX_E / 32; ++j)
-                if (!taken[j]) lv[j] = __fmul_rn(lv[j], inv);
-            __syncwarp();
-        }
-        float sel_l[MOE_MAX_K];
-        for (int k = 0; k < p.top_k; ++k) {
-            unsigned long long best = 0ull;
-#pragma unroll
-            for (int j = 0; j < MOE_MAX_E / 32; ++j) {
-                if (!taken[j]) {
-                    const unsigned long long key = route_key(lv[j], j * 32 + lane);
-                    best = key > best ? key : best;
-                }
-            }
-            // a real candidate's key is never 0 (its low word is 0xFFFFFFFF - id), so 0 means "none"
-            unsigned long long win = best;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const unsigned long long ok = __shfl_xor_sync(0xffffffffu, win, o);
-                win = ok > win ? ok : win;
-            }
-            const int wid = (int)(0xFFFFFFFFu - (uint32_t)(win & 0xFFFFFFFFull));
-#pragma unroll
-            for (int j = 0; j < MOE_MAX_E / 32; ++j)
-                if (j * 32 + lane == wid) taken[j] = true;
-            // the winner's value back out of its key (NaN stays NaN; -0 was made +0, which exp treats alike):
-            // no load per round
-            const uint32_t ku = (uint32_t)(win >> 32);
-            const float wl = __uint_as_float((ku & 0x80000000u) ? (ku & 0x7FFFFFFFu) : ~ku);
-            if (k < MOE_MAX_K) sel_l[k] = wl;
-            if (lane == 0) {
-                p.ids[t * p.top_k + k] = wid;
-                s_ids[t * p.top_k + k] = wid;
-            }
-        }
-        if (lane == 0 && p.mode == DC_ROUTE_SOFTMAX) {
-            // renormalise over the picks in pick order: w * (1 / sum) (core/src/moe/moe_routing.cpp:90-101),
-            // then the routed scaling factor (core/src/llm/moe/exec.cpp:764-768)
-            float sum = 0.0f;
-            for (int k = 0; k < p.top_k; ++k) sum = __fadd_rn(sum, sel_l[k]);
-            const float is = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 1.0f;
-            for (int k = 0; k < p.top_k; ++k)
-                p.weights[t * p.top_k + k] = __fmul_rn(sum > 0.0f ? __fmul_rn(sel_l[k], is) : sel_l[k], p.scale);
-        } else if (lane == 0) {
-            // weights over the selected experts only (native.cpp:649-674)
-            float mx = -INFINITY;
-            bool finite = true;
-            for (int k = 0; k < p.top_k; ++k) {
-                finite = finite && isfinite(sel_l[k]);
-                if (isfinite(sel_l[k]) && sel_l[k] > mx) mx = sel_l[k];
-            }
-            float den = 0.0f, wv[MOE_MAX_K];
-            if (finite && isfinite(mx)) {
-                for (int k = 0; k < p.top_k; ++k) {
-                    wv[k] = expf(sel_l[k] - mx);
-                    den += wv[k];
-                }
-            }
-            const bool ok = den > 0.0f && isfinite(den);
-            for (int k = 0; k < p.top_k; ++k) {
-                const float w = ok ? __fdiv_rn(wv[k], den) : __fdiv_rn(1.0f, (float)p.top_k);
-                p.weights[t * p.top_k + k] = __fmul_rn(w, p.scale);
-            }
-        }
-    }
+    for (int t = warp; t < p.T; t += 8) route_token(p, t, lane, s_prob[warp], s_ids);
     __syncthreads();
     // ---- bucketing: thread e owns expert e
     const int A = p.T * p.top_k;
@@ -279,6 +284,102 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
         *p.n_active = tot_a;
         p.uoff[tot_a] = tot_c;
     }
+}
+
+// ------------------------------------------- router over a prompt chunk
+// The same arithmetic as k_router for any number of tokens: logits by CTAs of two experts x sixteen tokens
+// (four warps per expert, a quarter of the row each, lane partials chained by fma in the same element order,
+// butterfly sum, quarters added pairwise), then one warp per token for the selection.  No bucketing: the
+// chunk's assignments are grouped by k_moe_group.
+__global__ void __launch_bounds__(256) k_router_logits_batched(const RouterParams p) {
+    __shared__ float s_part[8][DC_MAX_T];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 2 + (warp >> 2), quarter = warp & 3, seg = p.H / 4;
+    const int t0 = blockIdx.y * DC_MAX_T, tn = min(DC_MAX_T, p.T - t0);
+    float acc[DC_MAX_T];
+#pragma unroll
+    for (int t = 0; t < DC_MAX_T; ++t) acc[t] = 0.0f;
+    if (e < p.E) {
+        const float4* w4 = reinterpret_cast<const float4*>(p.wr + (size_t)e * p.H + quarter * seg);
+        for (int i0 = 0; i0 < seg / 4; i0 += 128) {
+            float4 wv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * 32 + lane;
+                wv[j] = i < seg / 4 ? w4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int t = 0; t < DC_MAX_T; ++t) {
+                if (t < tn) {
+                    const float4* x4 = reinterpret_cast<const float4*>(p.xn + (size_t)(t0 + t) * p.H + quarter * seg);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int i = i0 + j * 32 + lane;
+                        if (i < seg / 4) {
+                            const float4 xv = x4[i];
+                            acc[t] = fmaf(wv[j].x, xv.x, acc[t]);
+                            acc[t] = fmaf(wv[j].y, xv.y, acc[t]);
+                            acc[t] = fmaf(wv[j].z, xv.z, acc[t]);
+                            acc[t] = fmaf(wv[j].w, xv.w, acc[t]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < DC_MAX_T; ++t) {
+        if (t < tn) {
+            float v = acc[t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) s_part[warp][t] = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * tn) {
+        const int which = threadIdx.x / tn, t = threadIdx.x % tn, ee = blockIdx.x * 2 + which;
+        if (ee < p.E)
+            p.logits[(size_t)(t0 + t) * p.E + ee] = (s_part[which * 4][t] + s_part[which * 4 + 1][t]) +
+                                                    (s_part[which * 4 + 2][t] + s_part[which * 4 + 3][t]);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_router_select_batched(const RouterParams p) {
+    __shared__ float s_prob[8][MOE_MAX_E];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    if (t < p.T) route_token(p, t, lane, s_prob[warp], nullptr);
+}
+
+// Router of a prompt chunk: logits [T][E], ids and weights [T][top_k] for any T.
+int dc_launch_router_batched(dc_ctx* ctx, const dc_weight* wr, const float* xn, int T, int top_k, float scale, float* logits,
+                             int32_t* ids, float* weights, int mode) {
+    if (!wr || wr->type != DC_TYPE_F32) return dc_fail(ctx, DC_B200_UNSUPPORTED, "router weight must be F32");
+    const int E = (int)wr->N;
+    if (E < 1 || E > MOE_MAX_E || top_k < 1 || top_k > MOE_MAX_K || top_k > E || T < 1)
+        return dc_fail(ctx, DC_B200_UNSUPPORTED, "router: E=%d top_k=%d T=%d out of range", E, top_k, T);
+    RouterParams p = {};
+    p.wr = (const float*)wr->dev;
+    p.xn = xn;
+    p.E = E;
+    p.H = (int)wr->K;
+    p.T = T;
+    p.top_k = top_k;
+    p.scale = scale;
+    p.mode = mode;
+    p.ep_lo = 0;
+    p.ep_hi = E;
+    p.logits = logits;
+    p.ids = ids;
+    p.weights = weights;
+    k_router_logits_batched<<<dim3((E + 1) / 2, (T + DC_MAX_T - 1) / DC_MAX_T), 256, 0, ctx->stream>>>(p);
+    {
+        const int st = dc_check_cuda(ctx, cudaGetLastError(), "k_router_logits_batched");
+        if (st != DC_B200_OK) return st;
+    }
+    k_router_select_batched<<<(T + 7) / 8, 256, 0, ctx->stream>>>(p);
+    return dc_check_cuda(ctx, cudaGetLastError(), "k_router_select_batched");
 }
 
 // --------------------------------------------------- expert matmul kernel

@@ -283,6 +283,61 @@ int dc_b200_flash_attn_decode(dc_ctx* ctx, dc_kv_cache* kv, int layer, const flo
     return st == DC_B200_OK ? st : fail_closed(st);
 }
 
+// Prompt-chunk form of the attention op: n tokens of ONE sequence at positions pos0 .. pos0 + n - 1 (their K/V
+// rows are written first), causal attention on the tensor cores (ggml_flash_attn_ext on the CPU,
+// core/src/llm/attention/exec.cpp:255-275).
+int dc_b200_flash_attn_prefill(dc_ctx* ctx, dc_kv_cache* kv, int layer, const float* q_host, const float* k_host,
+                               const float* v_host, int seq, int pos0, int n, int n_head, float scale, float* out_host) {
+    if (!ctx) return DC_B200_INVALID_ARGUMENT;
+    if (!out_host || n < 1 || n_head < 1) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "flash_attn_prefill: bad argument");
+    const size_t out_n = (size_t)n * n_head * 128;
+    auto fail_closed = [&](int st) {
+        memset(out_host, 0, out_n * sizeof(float));
+        return st;
+    };
+    if (!kv || !q_host || !k_host || !v_host || n > 4096 || layer < 0 || layer >= kv->n_layer || seq < 0 ||
+        seq >= kv->max_seqs || !kv->seqs[seq].used || pos0 < 0 || n_head % kv->n_kv)
+        return fail_closed(dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "flash_attn_prefill: bad argument (n=%d layer=%d seq=%d)", n, layer, seq));
+    cudaSetDevice(ctx->device);
+    int st = dc_kv_seq_reserve(kv, seq, pos0 + n);
+    if (st != DC_B200_OK) return fail_closed(st);
+    if (kv->seqs[seq].len < pos0 + n) kv->seqs[seq].len = pos0 + n;
+    const int n_kv = kv->n_kv, heads = n_head + 2 * n_kv;
+    uint8_t* s = dc_scratch(ctx, (size_t)n * heads * 128 * 4 * 3 + (size_t)n * 8 + (1 << 16));
+    if (!s) return fail_closed(DC_B200_OUT_OF_MEMORY);
+    Bump b{s};
+    float* qkv = b.take<float>((size_t)n * heads * 128);
+    float* q = b.take<float>((size_t)n * n_head * 128);
+    float* out = b.take<float>(out_n);
+    int32_t* d_seq = b.take<int32_t>(n);
+    int32_t* d_pos = b.take<int32_t>(n);
+    std::vector<float> packed((size_t)n * heads * 128);
+    std::vector<int32_t> meta(2 * (size_t)n);
+    for (int t = 0; t < n; ++t) {
+        float* row = packed.data() + (size_t)t * heads * 128;
+        memcpy(row, q_host + (size_t)t * n_head * 128, (size_t)n_head * 128 * 4);
+        memcpy(row + (size_t)n_head * 128, k_host + (size_t)t * n_kv * 128, (size_t)n_kv * 128 * 4);
+        memcpy(row + (size_t)(n_head + n_kv) * 128, v_host + (size_t)t * n_kv * 128, (size_t)n_kv * 128 * 4);
+        meta[t] = seq;
+        meta[n + t] = pos0 + t;
+    }
+    st = dc_check_cuda(ctx, cudaMemcpyAsync(qkv, packed.data(), packed.size() * 4, cudaMemcpyHostToDevice, ctx->stream), "H2D qkv");
+    if (st == DC_B200_OK) st = h2d(ctx, d_seq, meta.data(), (size_t)n * 4);
+    if (st == DC_B200_OK) st = h2d(ctx, d_pos, meta.data() + n, (size_t)n * 4);
+    if (st == DC_B200_OK) st = dc_check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "sync");
+    __half* ka = kv->k_arena + kv->layer_elems * layer;
+    __half* va = kv->v_arena + kv->layer_elems * layer;
+    if (st == DC_B200_OK)
+        st = dc_launch_qknorm_rope_kv(ctx, qkv, nullptr, nullptr, nullptr, 0, d_pos, d_seq, kv->d_tables,
+                                      kv->max_blocks_per_seq, ka, va, n_head, n_kv, 0.0f, n, q);
+    if (st == DC_B200_OK)
+        st = dc_launch_attention_prefill(ctx, q, ka, va, kv->d_tables + (size_t)seq * kv->max_blocks_per_seq, pos0, n, n_head,
+                                         n_kv, scale, out);
+    if (st == DC_B200_OK) st = d2h(ctx, out_host, out, out_n * 4);
+    if (st == DC_B200_OK) st = dc_b200_synchronize(ctx);
+    return st == DC_B200_OK ? st : fail_closed(st);
+}
+
 int dc_b200_argmax(dc_ctx* ctx, const float* logits_host, int rows, int n, int32_t* out_ids) {
     if (!ctx || !logits_host || !out_ids || rows < 1 || n < 1) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "argmax: bad argument");
     cudaSetDevice(ctx->device);

@@ -6,8 +6,8 @@
 //
 // Per layer: RMSNorm (the decode kernel, one CTA per token) -> tiled Q8_K -> Q, K, V GEMMs -> per-head norm,
 // RoPE and cache write (the decode kernel) -> causal attention of every chunk token over the paged cache
-// (the decode kernels, one grid for the chunk) -> output projection accumulated into the residual ->
-// RMSNorm -> router (sixteen tokens per launch) -> assignments grouped by expert into 64-slot tiles ->
+// (attn_prefill.cu on the tensor cores; or the decode kernels' exact chain, one grid for the chunk) -> output projection accumulated into the residual ->
+// RMSNorm -> router (logits, then one warp per token) -> assignments grouped by expert into 64-slot tiles ->
 // gate and up GEMMs with an expert per tile -> SwiGLU + tiled Q8_K -> down GEMM scattered back to
 // assignment order -> weighted combine (the decode kernel).  The last chunk ends with the decode path's
 // output norm, lm_head row-streaming kernel and greedy pick for its last token.
@@ -107,46 +107,38 @@ static int prefill_prepare(dc_model* m) {
 }
 
 // ---- grouping of the chunk's expert assignments ----------------------------------------------------------
-// ids [C][top_k] -> for every expert (ascending) its assignments in assignment order, padded to whole 64-slot
-// tiles: slot_assign[slot] = t * top_k + k or -1, slot_token[slot] = t or -1, tile_expert[tile] = expert or -1.
-// One CTA; thread e owns expert e.
-__global__ void __launch_bounds__(256) k_moe_group(const int32_t* __restrict__ ids, int A, int top_k, int E, int max_tiles,
-                                                   int32_t* __restrict__ slot_assign, int32_t* __restrict__ slot_token,
-                                                   int32_t* __restrict__ tile_expert) {
-    extern __shared__ int32_t s_ids[];
-    __shared__ int s_scan[256];
-    for (int i = threadIdx.x; i < A; i += blockDim.x) s_ids[i] = ids[i];
+// ids [C][top_k] -> the assignments of every expert (ascending experts) in runs padded to whole 64-slot tiles:
+// slot_assign[slot] = t * top_k + k or -1, slot_token[slot] = t or -1, tile_expert[tile] = expert or -1.
+// Slots of one expert are filled in arrival order (the rows of a tile are independent, and results return to
+// assignment order through slot_assign).  One CTA.
+__global__ void __launch_bounds__(1024) k_moe_group(const int32_t* __restrict__ ids, int A, int top_k, int E, int max_tiles,
+                                                    int32_t* __restrict__ slot_assign, int32_t* __restrict__ slot_token,
+                                                    int32_t* __restrict__ tile_expert) {
+    __shared__ int s_cnt[256], s_off[256], s_fill[256], s_total;
+    const int tid = threadIdx.x;
+    if (tid < 256) s_cnt[tid] = s_fill[tid] = 0;
     __syncthreads();
-    const int e = threadIdx.x;
-    int cnt = 0;
-    if (e < E)
-        for (int i = 0; i < A; ++i) cnt += (s_ids[i] == e);
-    const int tiles = (cnt + 63) / 64;
-    s_scan[e] = tiles;
+    for (int i = tid; i < A; i += blockDim.x) atomicAdd(&s_cnt[ids[i]], 1);
     __syncthreads();
-    // exclusive prefix over the 256 threads (tiny: serial per thread)
-    int off = 0;
-    for (int i = 0; i < e; ++i) off += s_scan[i];
-    int total = 0;
-    for (int i = 0; i < 256; ++i) total += s_scan[i];
-    if (e < E && tiles > 0) {
-        for (int t = 0; t < tiles; ++t) tile_expert[off + t] = e;
-        int slot = off * 64;
-        for (int i = 0; i < A; ++i)
-            if (s_ids[i] == e) {
-                slot_assign[slot] = i;
-                slot_token[slot] = i / top_k;
-                ++slot;
-            }
-        for (; slot < (off + tiles) * 64; ++slot) {
-            slot_assign[slot] = -1;
-            slot_token[slot] = -1;
-        }
+    if (tid < 256) {
+        int off = 0;
+        for (int i = 0; i < tid; ++i) off += (s_cnt[i] + 63) / 64;
+        s_off[tid] = off;
+        const int tiles = tid < E ? (s_cnt[tid] + 63) / 64 : 0;
+        for (int t = 0; t < tiles; ++t) tile_expert[off + t] = tid;
+        if (tid == 255) s_total = off + tiles;
     }
-    for (int t = total + threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
-    for (int s = total * 64 + threadIdx.x; s < max_tiles * 64; s += blockDim.x) {
-        slot_assign[s] = -1;
-        slot_token[s] = -1;
+    for (int sl = tid; sl < max_tiles * 64; sl += blockDim.x) {
+        slot_assign[sl] = -1;
+        slot_token[sl] = -1;
+    }
+    __syncthreads();
+    for (int t = s_total + tid; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+    for (int i = tid; i < A; i += blockDim.x) {
+        const int e = ids[i];
+        const int slot = s_off[e] * 64 + atomicAdd(&s_fill[e], 1);
+        slot_assign[slot] = i;
+        slot_token[slot] = i / top_k;
     }
 }
 
@@ -247,22 +239,19 @@ int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool
                                         Ly.k_norm ? (const float*)Ly.k_norm->dev : nullptr, m->buf.cos_sin, c.max_ctx, P.positions,
                                         P.seq_ids, m->kv.d_tables, m->kv.max_blocks_per_seq, ka, va, c.n_head, c.n_kv_head,
                                         c.rms_eps, n, P.q));
-        DC_TRY(dc_launch_attention(ctx, P.q, ka, va, m->kv.d_tables, m->kv.max_blocks_per_seq, P.seq_ids, P.positions, n,
-                                   c.n_head, c.n_kv_head, scale, m->nsplit, &P.attn, P.att, nullptr));
+        if (m->prefill_flash)
+            DC_TRY(dc_launch_attention_prefill(ctx, P.q, ka, va, m->kv.d_tables + (size_t)seq * m->kv.max_blocks_per_seq, s.len, n,
+                                               c.n_head, c.n_kv_head, scale, P.att));
+        else
+            DC_TRY(dc_launch_attention(ctx, P.q, ka, va, m->kv.d_tables, m->kv.max_blocks_per_seq, P.seq_ids, P.positions, n,
+                                       c.n_head, c.n_kv_head, scale, m->nsplit, &P.attn, P.att, nullptr));
         DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.att, QD, n, QD, P.act_att, n_tt, nullptr));
         DC_TRY(dc_launch_gemm_tc(ctx, Ly.wo, P.act_att, n, P.x, H, nullptr, nullptr, true));
         DC_TRY(dc_launch_rmsnorm_q8k(ctx, P.x, nullptr, (const float*)Ly.ffn_norm->dev, n, H, c.rms_eps, P.xn, nullptr));
         if (E > 0) {
             const int A = n * top_k, F = c.expert_ffn;
-            for (int t0 = 0; t0 < n; t0 += DC_MAX_T) {
-                const int tn = std::min(DC_MAX_T, n - t0);
-                dc_moe_route rt = m->buf.route;     // unit lists of the decode path: written, not used here
-                rt.logits = P.logits + (size_t)t0 * E;
-                rt.ids = P.ids + (size_t)t0 * top_k;
-                rt.weights = P.weights + (size_t)t0 * top_k;
-                DC_TRY(dc_launch_router(ctx, Ly.router, P.xn + (size_t)t0 * H, E, tn, top_k, c.routed_scale, 0, E, &rt, m->route_mode));
-            }
-            k_moe_group<<<1, 256, (size_t)A * 4, ctx->stream>>>(P.ids, A, top_k, E, P.max_tiles, P.slot_assign, P.slot_token, P.tile_expert);
+            DC_TRY(dc_launch_router_batched(ctx, Ly.router, P.xn, n, top_k, c.routed_scale, P.logits, P.ids, P.weights, m->route_mode));
+            k_moe_group<<<1, 1024, 0, ctx->stream>>>(P.ids, A, top_k, E, P.max_tiles, P.slot_assign, P.slot_token, P.tile_expert);
             DC_TRY(dc_check_cuda(ctx, cudaGetLastError(), "k_moe_group"));
             const int slots = P.max_tiles * 64;
             DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_moe, P.max_tiles, P.slot_token));

@@ -261,3 +261,14 @@ class KVCache:
         self.ctx._check(_lib.lib().dc_b200_flash_attn_decode(self.ctx.handle, self.handle, layer, _vp(q), _vp(k), _vp(v),
                                                              _vp(seq_ids), _vp(positions), T, n_head, scale, _vp(out)))
         return out
+
+    def flash_attn_prefill(self, layer: int, q, k, v, seq: int, pos0: int, scale: float) -> np.ndarray:
+        """Prompt chunk of one sequence: writes K/V at positions pos0.., then causal attention on the tensor cores."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        k = np.ascontiguousarray(k, dtype=np.float32)
+        v = np.ascontiguousarray(v, dtype=np.float32)
+        n, n_head = q.shape[0], q.shape[1]
+        out = np.empty((n, n_head, self.head_dim), dtype=np.float32)
+        self.ctx._check(_lib.lib().dc_b200_flash_attn_prefill(self.ctx.handle, self.handle, layer, _vp(q), _vp(k), _vp(v), seq,
+                                                              pos0, n, n_head, scale, _vp(out)))
+        return out

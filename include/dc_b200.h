@@ -206,6 +206,13 @@ DC_B200_API int dc_b200_kv_prefix_stats(dc_kv_cache* kv, uint64_t out[4]);
 DC_B200_API int dc_b200_flash_attn_decode(dc_ctx* ctx, dc_kv_cache* kv, int layer, const float* q_host,
                                           const float* k_host, const float* v_host, const int32_t* seq_ids,
                                           const int32_t* positions, int T, int n_head, float scale, float* out_host);
+/* The same op for a prompt chunk: n <= 4096 tokens of one sequence at positions pos0 .. pos0 + n - 1, causal.
+ * What the CPU runs for chunks is ggml_flash_attn_ext over the fp16 cache with the query converted to fp16
+ * (core/src/llm/attention/exec.cpp:255-275); here scores and P.V run on the tensor cores with fp16
+ * operands (the query as a sum of two fp16 terms) and fp32 accumulation. */
+DC_B200_API int dc_b200_flash_attn_prefill(dc_ctx* ctx, dc_kv_cache* kv, int layer, const float* q_host,
+                                           const float* k_host, const float* v_host, int seq, int pos0, int n,
+                                           int n_head, float scale, float* out_host);
 /* Raw fp16 contents of one block of one layer (K then V planes), for tests. */
 DC_B200_API int dc_b200_kv_read_block(dc_kv_cache* kv, int layer, int block, void* k_host, void* v_host);
 

@@ -61,6 +61,9 @@ def build_model(ctx, cfg, all_q4k: bool):
 def test_chunked_prefill_on_tensor_cores_matches_the_sixteen_token_path(ctx, name, n_prompt, all_q4k):
     cfg = dc.Config(max_seqs=2, max_ctx=1024, **CONFIGS[name])
     m = build_model(ctx, cfg, all_q4k)
+    # all_q4k: the decode kernels' exact attention chain, so that the whole chunked path is bit-comparable;
+    # otherwise the default (fp16 flash attention on the tensor cores, as ggml_flash_attn_ext is on the CPU)
+    m.set_option("prefill_attention", 0 if all_q4k else 1)
     rng = np.random.default_rng(3)
     prompt = rng.integers(0, cfg.vocab, size=n_prompt)
     res = {}
@@ -124,4 +127,65 @@ def test_chunked_prefill_against_the_cpu_decoder(ctx):
     kr = ref.k[0][s * ref.bps * 16: s * ref.bps * 16 + 100]
     d = np.abs(k0.view(np.float16).astype(np.float32) - kr.view(np.float16).astype(np.float32))
     assert d.max() <= 2e-3 * np.abs(kr.view(np.float16).astype(np.float32)).max()
+    m.close()
+
+
+@pytest.mark.parametrize("n_head,n_kv", [(32, 4), (16, 8)])
+def test_flash_attn_prefill_op_against_the_oracle(ctx, oracle, n_head, n_kv):
+    """The chunk attention op alone: two chunks of one sequence (200 tokens from position 0, then 333 more), both
+    head layouts of the benchmark models.  Against the oracle's scalar attention (exact exponential, what
+    ggml_flash_attn_ext computes) and its blockwise one (the decode kernels' polynomial exponential): the
+    kernel rounds probabilities to fp16 before P.V, so the gate is 1e-3 of the largest output; the oracle's own
+    two variants differ by up to 5e-4."""
+    rng = np.random.default_rng(11)
+    kv = ctx.kv_cache(1, n_kv, 128, 64, 2, 40)
+    s = kv.seq_alloc()
+    scale = float(1.0 / np.sqrt(128.0))
+    ref_k = np.zeros((64 * 16, n_kv, 128), np.uint16)
+    ref_v = np.zeros_like(ref_k)
+    pos0, worst_s, worst_b = 0, 0.0, 0.0
+    for n in (200, 333):
+        q = rng.normal(size=(n, n_head, 128)).astype(np.float32)
+        k = rng.normal(size=(n, n_kv, 128)).astype(np.float32)
+        v = rng.normal(size=(n, n_kv, 128)).astype(np.float32)
+        out = kv.flash_attn_prefill(0, q, k, v, s, pos0, scale)
+        tb = kv.block_table(s)
+        for i in range(n):
+            oracle.kv_write(ref_k, ref_v, tb, pos0 + i, n_kv, 128, k[i], v[i])
+        for i in sorted({0, 1, 15, 16, 63, 64, 65, 127, 128, n - 2, n - 1}):
+            a = oracle.paged_attention(q[i], ref_k, ref_v, tb, pos0 + i, n_head, n_kv, 128, scale, "scalar")
+            b = oracle.paged_attention(q[i], ref_k, ref_v, tb, pos0 + i, n_head, n_kv, 128, scale, "blockwise")
+            worst_s, worst_b = max(worst_s, rel(out[i], a)), max(worst_b, rel(out[i], b))
+        pos0 += n
+    print(f"chunk attention {n_head}/{n_kv} heads: rel {worst_s:.2e} vs exact-exponential oracle, {worst_b:.2e} vs blockwise")
+    assert worst_s < 1e-3 and worst_b < 1.5e-3
+    # the cache rows are the same fp16 bytes the decode op writes
+    for blk in kv.block_table(s)[:4]:
+        kb, vb = kv.read_block(0, int(blk))
+        assert np.array_equal(kb.view(np.uint16), ref_k[blk * 16:(blk + 1) * 16])
+    kv.close()
+
+
+@pytest.mark.parametrize("pos0", [0, 530])
+def test_flash_attention_of_a_chunk_against_the_exact_chain(ctx, pos0):
+    """One decoder layer: everything but attention is the same code in both runs, so the logits differ only by
+    the attention kernel: fp16 query and probabilities with fp32 accumulation against the fp32 running-max chain
+    that the oracle tests pin (1e-5).  Chunk of 300 tokens appended after pos0 cached ones."""
+    cfg = dc.Config(max_seqs=2, max_ctx=1024, n_layer=1, hidden=2048, n_head=32, n_kv_head=4, vocab=4096, ffn=1024,
+                    tie_embeddings=True)
+    m = build_model(ctx, cfg, True)
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, cfg.vocab, size=pos0 + 300)
+    out = {}
+    for flash in (0, 1):
+        m.set_option("prefill_attention", flash)
+        s = m.seq_alloc()
+        if pos0:
+            m.prefill(s, prompt[:pos0])
+        first, lg = m.prefill(s, prompt[pos0:], want_logits=True)
+        out[flash] = lg.copy()
+        m.seq_free(s)
+    r = rel(out[1], out[0])
+    print(f"flash vs exact attention, one layer, {pos0} cached + 300 chunk tokens: logits rel {r:.2e}")
+    assert r < 2e-2        # (an attention difference of a few 1e-4 after three Q8_K re-quantisations)
     m.close()
