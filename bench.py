@@ -380,6 +380,22 @@ def spec_sweep(ctx, model, cfg, rng, seqs_to_free) -> dict:
     return out
 
 
+def op_gemm(ctx, ggml_type: int, N: int, K: int, M: int, reps: int) -> dict:
+    """Prompt-sized MUL_MAT (M token rows) through the tensor-core kernel: activation tiling + GEMM, as
+    dc_b200_mul_mat_dev enqueues them.  Reported in int8 multiply-accumulate operations (2 N K M per call)."""
+    from densecore_b200 import blocks as B
+    rng = np.random.default_rng(7)
+    w = ctx.upload_weight(ggml_type, B.random_weight(rng, ggml_type, N, K), K, N)
+    x = rng.normal(size=(M, K)).astype(np.float32)
+    xd, yd = ctx.alloc(x.nbytes), ctx.alloc(M * N * 4)
+    ctx.to_device(xd, x)
+    us = _time_graph(ctx, lambda: ctx.mul_mat_dev(w, xd, M, yd), reps)
+    ctx.free(xd)
+    ctx.free(yd)
+    w.free()
+    return {"N": N, "K": K, "M": M, "type": ggml_type, "us": us, "tops": 2.0 * N * K * M / us / 1e6}
+
+
 def run_single_op(args) -> int:
     """--op: one operator alone (for profiling runs and for the per-config figures of the main line)."""
     import densecore_b200 as dc
@@ -392,6 +408,10 @@ def run_single_op(args) -> int:
         out = op_gemv(ctx, B.GGML_TYPE_Q4_K, 65536, 2048, 1, 4, args.steps, peak)
     elif args.op == "gemv-lm-head":
         out = op_gemv(ctx, B.GGML_TYPE_Q6_K, 151936, 2048, 1, 2, args.steps, peak)
+    elif args.op == "gemm-q4":
+        out = op_gemm(ctx, B.GGML_TYPE_Q4_K, 4096, 2048, 2048, args.steps)
+    elif args.op == "gemm-q6":
+        out = op_gemm(ctx, B.GGML_TYPE_Q6_K, 2048, 768, 4096, args.steps)
     elif args.op == "moe-layer":
         out = {"T": moe_layer_sweep(ctx, args.steps, peak)}
     elif args.op == "dense-0p8b":
@@ -426,7 +446,7 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed 1-stream decode run with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads (single ops, dense model, speculative sweep)")
-    ap.add_argument("--op", default=None, choices=["gemv-config1", "gemv-lm-head", "gemv-q4-big", "moe-layer", "dense-0p8b"],
+    ap.add_argument("--op", default=None, choices=["gemv-config1", "gemv-lm-head", "gemv-q4-big", "gemm-q4", "gemm-q6", "moe-layer", "dense-0p8b"],
                     help="time one operator alone and print its own JSON line (not the benchmark line)")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -81,6 +81,10 @@ int dc_launch_quantize_q8k_tiled(dc_ctx* ctx, const float* x, int ldx, int n_row
                                  const int* slot_token);
 int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
                       const int* tile_expert = nullptr, const int* slot_row = nullptr, bool accumulate = false);
+// up to three matrices of one type, K and row length in one launch (Q | K | V, gate | up)
+int dc_launch_gemm_tc_multi(dc_ctx* ctx, const dc_weight* const* ws, const int* out_off, int nseg, const uint8_t* act,
+                            int n_slots, float* out, int ldo, const int* tile_expert = nullptr, const int* slot_row = nullptr,
+                            bool accumulate = false);
 
 
 // ---- misc.cu ----

@@ -22,6 +22,9 @@
 // Q4_K results are bit-equal to the GEMV path and the CPU oracle.  Q6_K adds one float term per block
 // instead of the CPU small-batch kernel's eight lane partials (q6_small_batch.h:62-103): equal integers,
 // a different float order, relative difference ~1e-7.
+#include <cstdio>
+#include <cstdlib>
+
 #include "dc_common.cuh"
 #include "dc_internal.h"
 
@@ -40,9 +43,16 @@ constexpr int TC_PLANE = 8 * TC_ROWS * 16;            // 8 K-chunks of 16 bytes 
 constexpr int TC_B_Q = 16 * TC_NTOK * 16;             // codes of one (block, token tile): 16 K-chunks
 constexpr int TC_ACT_TILE = TC_B_Q + TC_NTOK * 4;     // + the tile's 64 block scales
 
+struct GemmTcSeg {
+    const uint8_t* w;      // rows of the matrix (expert 0)
+    int N;                 // its rows
+    int out_off;           // column offset of its outputs in a row of out
+};
+
 struct GemmTcParams {
-    const uint8_t* w;      // rows of the (first) matrix
-    int row_bytes, N, K;
+    GemmTcSeg seg[3];      // matrices of one shape family (same K, row bytes, type) run in one launch: Q | K | V, gate | up
+    int nseg;
+    int row_bytes, K;
     const uint8_t* act;    // [K / 256][n_tt][TC_ACT_TILE]
     int n_tt;
     int n_slots;           // token slots that hold data (stores beyond are skipped)
@@ -53,6 +63,7 @@ struct GemmTcParams {
     const int* slot_row;      // optional [n_tt * 64]: output row of every slot instead of the slot itself; < 0: none
     int accumulate;           // out += result (one float add) instead of out = result
     int* err;
+    unsigned long long* timing;   // instrumented build only: per-CTA cycles of the loop's phases
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------------
@@ -137,17 +148,21 @@ template <int TYPE>
 struct TcTraits;
 template <>
 struct TcTraits<DC_TYPE_Q4_K> {
-    static constexpr int NP = 3, BB = DC_Q4K_BYTES, RB = 144, NRAW = 2, A_SIGNED = 0;
+    // rows are 16-byte aligned: every thread fetches its share of a block straight from global memory into
+    // registers one half block ahead; the token tile is double-buffered
+    static constexpr int NP = 3, BB = DC_Q4K_BYTES, RB = 0, NB = 2, A_SIGNED = 0;
 };
 template <>
 struct TcTraits<DC_TYPE_Q6_K> {
-    static constexpr int NP = 4, BB = DC_Q6K_BYTES, RB = 240, NRAW = 1, A_SIGNED = 1;
+    // 210-byte blocks are only 2-byte aligned: a block of the 128 rows is staged by per-row bulk copies
+    // (rounded out to 16-byte boundaries); one token-tile buffer, refilled as soon as the block's UMMAs are done
+    static constexpr int NP = 4, BB = DC_Q6K_BYTES, RB = 240, NB = 1, A_SIGNED = 1;
 };
 
 template <int TYPE>
 constexpr size_t tc_smem_bytes() {
     using T = TcTraits<TYPE>;
-    return (size_t)T::NP * TC_PLANE + TC_ACT_TILE + (size_t)T::NRAW * TC_ROWS * T::RB + 64;
+    return (size_t)T::NP * TC_PLANE + (size_t)T::NB * TC_B_Q + 2 * TC_NTOK * 4 + (size_t)TC_ROWS * T::RB + 64;
 }
 
 __device__ __forceinline__ void q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, uint32_t& sc, uint32_t& m) {
@@ -168,15 +183,23 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
     using T = TcTraits<TYPE>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t sA = smem_u32(smem_raw);
-    const uint32_t sB = sA + T::NP * TC_PLANE;
-    const uint32_t sRaw = sB + TC_ACT_TILE;
-    const uint32_t sBar = sRaw + T::NRAW * TC_ROWS * T::RB;     // raw[0], raw[1], b, mma (8 bytes each), tmem slot
-    const uint32_t bar_raw0 = sBar, bar_b = sBar + 16, bar_mma = sBar + 24, tmem_slot = sBar + 32;
+    const uint32_t sBq = sA + T::NP * TC_PLANE;                  // NB buffers of token codes
+    const uint32_t sBd = sBq + T::NB * TC_B_Q;                   // two buffers of the tile's 64 block scales
+    const uint32_t sRaw = sBd + 2 * TC_NTOK * 4;
+    const uint32_t sBar = sRaw + TC_ROWS * T::RB;                // b[0], b[1], raw, mma (8 bytes each), tmem slot
+    const uint32_t bar_b0 = sBar, bar_raw = sBar + 16, bar_mma = sBar + 24, tmem_slot = sBar + 32;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tt = blockIdx.x, row0 = blockIdx.y * TC_ROWS;
+    const int tt = blockIdx.x;
     const int expert = p.tile_expert ? p.tile_expert[tt] : 0;
     if (expert < 0) return;                                      // the whole CTA: a tile no expert uses
-    const uint8_t* wbase = p.w + (size_t)expert * p.estride;
+    // the matrix (segment) and row tile of this CTA
+    int seg = 0, rt = blockIdx.y;
+    while (seg + 1 < p.nseg && rt >= (p.seg[seg].N + TC_ROWS - 1) / TC_ROWS) {
+        rt -= (p.seg[seg].N + TC_ROWS - 1) / TC_ROWS;
+        ++seg;
+    }
+    const int N = p.seg[seg].N, row0 = rt * TC_ROWS;
+    const uint8_t* wbase = p.seg[seg].w + (size_t)expert * p.estride;
     const int nb = p.K / DC_QK_K;
     constexpr uint32_t NCOLS = 256;                              // NP x 64 accumulator columns, power of two
 
@@ -185,9 +208,9 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
         tmem_relinquish();
     }
     if (tid == 0) {
-        mbar_init(bar_raw0, 4);
-        mbar_init(bar_raw0 + 8, 4);
-        mbar_init(bar_b, 1);
+        mbar_init(bar_b0, 1);
+        mbar_init(bar_b0 + 8, 1);
+        mbar_init(bar_raw, 4);
         mbar_init(bar_mma, 1);
         mbar_fence_init();
     }
@@ -196,66 +219,91 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
     tc_fence_after();
     const uint32_t tmem = lds32(tmem_slot);
 
-    // this thread's weight row (threads 0..127 fetch; every thread expands row tid % 128)
+    // every thread expands row tid % 128 (threads 0..127 also fetch it where blocks are staged)
     const int r = tid & (TC_ROWS - 1), part = tid >> 7;
-    const int grow = min(row0 + r, p.N - 1);
+    const int grow = min(row0 + r, N - 1);
     const uint8_t* rp = wbase + (size_t)grow * p.row_bytes;
 
-    auto issue_raw = [&](int kb, int stage) {     // warps 0..3, all lanes
+    auto issue_raw = [&](int kb) {                // Q6_K: warps 0..3, all lanes
         const uintptr_t a = (uintptr_t)(rp + (size_t)kb * T::BB);
         const uint32_t skew = (uint32_t)(a & 15u);
         const uint32_t bytes = (skew + T::BB + 15u) & ~15u;
         const uint32_t sum = __reduce_add_sync(0xffffffffu, bytes);
-        const uint32_t bar = bar_raw0 + 8 * stage;
-        if (lane == 0) mbar_expect_tx(bar, sum);
+        if (lane == 0) mbar_expect_tx(bar_raw, sum);
         __syncwarp();
-        bulk_g2s(sRaw + (stage * TC_ROWS + r) * T::RB, (const void*)(a - skew), bytes, bar);
+        bulk_g2s(sRaw + r * T::RB, (const void*)(a - skew), bytes, bar_raw);
     };
-    auto issue_b = [&](int kb) {                  // one thread
-        mbar_expect_tx(bar_b, TC_ACT_TILE);
-        bulk_g2s(sB, p.act + ((size_t)kb * p.n_tt + tt) * TC_ACT_TILE, TC_ACT_TILE, bar_b);
+    auto issue_b = [&](int kb) {                  // one thread: codes and scales of token tile (kb, tt)
+        const uint8_t* src = p.act + ((size_t)kb * p.n_tt + tt) * TC_ACT_TILE;
+        const uint32_t bar = bar_b0 + 8 * (kb & 1);
+        mbar_expect_tx(bar, TC_ACT_TILE);
+        bulk_g2s(sBq + (T::NB == 2 ? (kb & 1) : 0) * TC_B_Q, src, TC_B_Q, bar);
+        bulk_g2s(sBd + (kb & 1) * (TC_NTOK * 4), src + TC_B_Q, TC_NTOK * 4, bar);
+    };
+    // Q4_K: this thread's share of half block (kb, h): the 16-byte header (d, dmin, packed scales) and the 32
+    // bytes of quants of sub-block pair g = 2 h + part
+    uint4 nx_hdr = make_uint4(0, 0, 0, 0), nx_q0 = nx_hdr, nx_q1 = nx_hdr;
+    auto fetch_q4 = [&](int kb, int h) {
+        const uint4* b = reinterpret_cast<const uint4*>(rp + (size_t)kb * T::BB);
+        const int g = 2 * h + part;
+        nx_hdr = __ldg(b);
+        nx_q0 = __ldg(b + 1 + 2 * g);
+        nx_q1 = __ldg(b + 2 + 2 * g);
     };
 
-    if (warp < 4) issue_raw(0, 0);
+    if (TYPE == DC_TYPE_Q4_K) fetch_q4(0, 0);
+    else if (warp < 4) issue_raw(0);
     if (tid == 128) issue_b(0);
 
     constexpr uint32_t IDESC = umma_idesc_i8(T::A_SIGNED, TC_ROWS, TC_NTOK);
     float sumf[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) sumf[i] = 0.0f;
-    uint32_t ph_raw[2] = {0, 0}, ph_b = 0, ph_mma = 0;
+    uint32_t ph_raw = 0, ph_b[2] = {0, 0}, ph_mma = 0;
     bool failed = false;
     const int q = warp & 3, ch = warp >> 2;       // TMEM lane quarter of this warp, column half of the tile
     const uint32_t t_lane = tmem + ((uint32_t)(32 * q) << 16) + 32 * ch;
 
+#ifdef DC_TC_TIMING
+    long long tc_t[6] = {0, 0, 0, 0, 0, 0}, tc_last = clock64();
+#define TC_MARK(i)                       \
+    do {                                 \
+        const long long now_ = clock64(); \
+        tc_t[i] += now_ - tc_last;       \
+        tc_last = now_;                  \
+    } while (0)
+#else
+#define TC_MARK(i)
+#endif
     for (int kb = 0; kb < nb && !failed; ++kb) {
-        const int stage = T::NRAW == 2 ? (kb & 1) : 0;
-        if (T::NRAW == 2 && kb + 1 < nb && warp < 4) issue_raw(kb + 1, (kb + 1) & 1);
-        if (!mbar_wait(bar_raw0 + 8 * stage, ph_raw[stage], p.err)) failed = true;
-        ph_raw[stage] ^= 1;
-        const uint32_t rr = sRaw + (stage * TC_ROWS + r) * T::RB +
-                            (uint32_t)(((uintptr_t)(rp + (size_t)kb * T::BB)) & 15u);
-        float d, dmin = 0.0f;
-        if (TYPE == DC_TYPE_Q4_K) {
-            const uint32_t dd = lds32(rr);
-            d = fp16_bits_to_float((uint16_t)(dd & 0xFFFF));
-            dmin = fp16_bits_to_float((uint16_t)(dd >> 16));
-        } else {
+        if (T::NB == 2 && kb + 1 < nb && tid == 128) issue_b(kb + 1);   // the other buffer is free since the last vote
+        const uint32_t sBcur = sBq + (T::NB == 2 ? (kb & 1) : 0) * TC_B_Q;
+        uint32_t rr = 0;
+        float d = 0.0f, dmin = 0.0f;
+        if (TYPE == DC_TYPE_Q6_K) {
+            if (!mbar_wait(bar_raw, ph_raw, p.err)) failed = true;
+            ph_raw ^= 1;
+            rr = sRaw + r * T::RB + (uint32_t)(((uintptr_t)(rp + (size_t)kb * T::BB)) & 15u);
             d = fp16_bits_to_float((uint16_t)lds16(rr + 208));
         }
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
             // ---- expand this row's share of the half block into the operand planes
             if (TYPE == DC_TYPE_Q4_K) {
+                const uint4 hdr = nx_hdr, qv0 = nx_q0, qv1 = nx_q1;
+                if (h == 0) fetch_q4(kb, 1);
+                else if (kb + 1 < nb) fetch_q4(kb + 1, 0);
+                d = fp16_bits_to_float((uint16_t)(hdr.x & 0xFFFF));
+                dmin = fp16_bits_to_float((uint16_t)(hdr.x >> 16));
                 const int g = 2 * h + part;      // 64 values: sub-blocks 2g (low nibbles) and 2g + 1 (high nibbles)
-                const uint32_t s0 = lds32(rr + 4), s1 = lds32(rr + 8), s2 = lds32(rr + 12);
                 uint32_t sc0, m0, sc1, m1;
-                q4k_scale_min(s0, s1, s2, 2 * g, sc0, m0);
-                q4k_scale_min(s0, s1, s2, 2 * g + 1, sc1, m1);
+                q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * g, sc0, m0);
+                q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * g + 1, sc1, m1);
                 const uint32_t mm0 = m0 * 0x01010101u, mm1 = m1 * 0x01010101u;
+                const uint32_t a0 = sc0 >> 3, a1 = sc0 & 7u, b0 = sc1 >> 3, b1 = sc1 & 7u;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
-                    const uint4 qv = lds128(rr + 16 + 32 * g + 16 * hf);
+                    const uint4 qv = hf ? qv1 : qv0;
                     const uint32_t in[4] = {qv.x, qv.y, qv.z, qv.w};
                     uint32_t lo[4], hi[4];
 #pragma unroll
@@ -265,7 +313,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
                     }
                     const uint32_t c_lo = sA + (4 * part + hf) * (TC_ROWS * 16) + r * 16;        // chunk of sub-block 2g
                     const uint32_t c_hi = c_lo + 2 * (TC_ROWS * 16);                             // chunk of sub-block 2g + 1
-                    const uint32_t a0 = sc0 >> 3, a1 = sc0 & 7u, b0 = sc1 >> 3, b1 = sc1 & 7u;
                     sts128(c_lo, lo[0] * a0, lo[1] * a0, lo[2] * a0, lo[3] * a0);
                     sts128(c_lo + TC_PLANE, lo[0] * a1, lo[1] * a1, lo[2] * a1, lo[3] * a1);
                     sts128(c_lo + 2 * TC_PLANE, mm0, mm0, mm0, mm0);
@@ -304,14 +351,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
                 }
             }
             fence_async_smem();
+            TC_MARK(0);      // expand
             if (h == 0) {
-                if (!mbar_wait(bar_b, ph_b, p.err)) failed = true;
-                ph_b ^= 1;
+                if (!mbar_wait(bar_b0 + 8 * (kb & 1), ph_b[kb & 1], p.err)) failed = true;
+                ph_b[kb & 1] ^= 1;
             }
+            TC_MARK(1);      // wait for the token tile
             tc_fence_before();
             failed = __syncthreads_or(failed);
             if (failed) break;
-            if (T::NRAW == 1 && h == 1 && kb + 1 < nb && warp < 4) issue_raw(kb + 1, 0);   // the raw bytes are expanded
+            TC_MARK(2);      // block-wide vote
+            if (TYPE == DC_TYPE_Q6_K && h == 1 && kb + 1 < nb && warp < 4) issue_raw(kb + 1);   // the raw bytes are expanded
             if (tid == 0) {
                 tc_fence_after();
 #pragma unroll
@@ -320,15 +370,20 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
                     for (int kk = 0; kk < 4; ++kk)
                         umma_i8(tmem + pl * TC_NTOK,
                                 umma_desc(sA + pl * TC_PLANE + kk * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128),
-                                umma_desc(sB + (8 * h + 2 * kk) * (TC_NTOK * 16), TC_NTOK * 16, 128), IDESC,
+                                umma_desc(sBcur + (8 * h + 2 * kk) * (TC_NTOK * 16), TC_NTOK * 16, 128), IDESC,
                                 (h | kk) ? 1u : 0u);
                 umma_commit(bar_mma);
             }
             if (!mbar_wait(bar_mma, ph_mma, p.err)) failed = true;   // (acted on at the next block-wide vote)
             ph_mma ^= 1;
             tc_fence_after();
+            TC_MARK(3);      // UMMA issue to completion
         }
+        if (failed) break;
+        // single code buffer: it is free now that the block's UMMAs are done; the scales have their own buffers
+        if (T::NB == 1 && kb + 1 < nb && tid == 128) issue_b(kb + 1);
         // ---- the block's float terms, in block order
+        const uint32_t yd_base = sBd + (kb & 1) * (TC_NTOK * 4) + 4 * (32 * ch);
 #pragma unroll
         for (int piece = 0; piece < 2; ++piece) {
             int a0[16], a1[16], a2[16], a3[16];
@@ -339,7 +394,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float yd = __uint_as_float(lds32(sB + TC_B_Q + 4 * (32 * ch + 16 * piece + i)));
+                const float yd = __uint_as_float(lds32(yd_base + 4 * (16 * piece + i)));
                 float& s = sumf[16 * piece + i];
                 if (TYPE == DC_TYPE_Q4_K) {
                     const int I = 8 * a0[i] + a1[i];
@@ -352,30 +407,35 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
                 }
             }
         }
+        TC_MARK(4);          // accumulator read-out and float terms
         tc_fence_before();
         failed = __syncthreads_or(failed);         // accumulators and block scales are read: both may be overwritten
         tc_fence_after();
-        if (failed) break;
-        if (kb + 1 < nb && tid == 128) issue_b(kb + 1);
+        TC_MARK(5);
     }
+#ifdef DC_TC_TIMING
+    if (p.timing && tid == 0)
+        for (int i = 0; i < 6; ++i) atomicAdd(p.timing + i, (unsigned long long)tc_t[i]);
+#endif
 
     if (!failed) {
         const int row = row0 + 32 * q + lane;
-        if (row < p.N) {
+        if (row < N) {
+            float* out = p.out + p.seg[seg].out_off;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const int slot = tt * TC_NTOK + 32 * ch + i;
                 if (slot >= p.n_slots) continue;
                 const int orow = p.slot_row ? p.slot_row[slot] : slot;
                 if (orow < 0) continue;
-                float* o = p.out + (size_t)orow * p.ldo + row;
+                float* o = out + (size_t)orow * p.ldo + row;
                 *o = p.accumulate ? __fadd_rn(*o, sumf[i]) : sumf[i];
             }
         }
     } else {
         // a wait ran out: give copies still in flight a bounded chance to land before the buffers go away
-        for (int s = 0; s < 2; ++s) mbar_wait(bar_raw0 + 8 * s, ph_raw[s], nullptr);
-        mbar_wait(bar_b, ph_b, nullptr);
+        if (TYPE == DC_TYPE_Q6_K) mbar_wait(bar_raw, ph_raw, nullptr);
+        for (int s = 0; s < 2; ++s) mbar_wait(bar_b0 + 8 * s, ph_b[s], nullptr);
     }
     tc_fence_before();
     __syncthreads();
@@ -412,13 +472,23 @@ bool dc_gemm_tc_supports(const dc_weight* w) {
 
 // out[slot * ldo + row] = sum over K of w[row] . act[slot] for rows [0, N) and slots [0, n_slots); with tile_expert,
 // token tile t uses the matrix of expert tile_expert[t] (skipped when negative).
-int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
-                      const int* tile_expert, const int* slot_row, bool accumulate) {
-    if (!dc_gemm_tc_supports(w)) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemm_tc: weight type %d or alignment", w->type);
+// Up to three matrices of one shape family (same type, K and row bytes: Q | K | V, or gate | up) in one launch;
+// matrix i writes its rows to columns out_off[i].. of out.
+int dc_launch_gemm_tc_multi(dc_ctx* ctx, const dc_weight* const* ws, const int* out_off, int nseg, const uint8_t* act,
+                            int n_slots, float* out, int ldo, const int* tile_expert, const int* slot_row, bool accumulate) {
+    if (nseg < 1 || nseg > 3) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemm_tc: %d matrices", nseg);
+    const dc_weight* w = ws[0];
     GemmTcParams p = {};
-    p.w = w->dev;
+    int row_tiles = 0;
+    for (int i = 0; i < nseg; ++i) {
+        if (!dc_gemm_tc_supports(ws[i])) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gemm_tc: weight type %d or alignment", ws[i]->type);
+        if (ws[i]->type != w->type || ws[i]->K != w->K || ws[i]->row_bytes != w->row_bytes || (tile_expert && ws[i]->N != w->N))
+            return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemm_tc: matrices of one launch must share type, K and row bytes");
+        p.seg[i] = {ws[i]->dev, (int)ws[i]->N, out_off ? out_off[i] : 0};
+        row_tiles += ((int)ws[i]->N + TC_ROWS - 1) / TC_ROWS;
+    }
+    p.nseg = nseg;
     p.row_bytes = (int)w->row_bytes;
-    p.N = (int)w->N;
     p.K = (int)w->K;
     p.act = act;
     p.n_tt = dc_gemm_tc_tiles(n_slots);
@@ -430,7 +500,22 @@ int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n
     p.accumulate = accumulate ? 1 : 0;
     p.estride = (size_t)w->N * w->row_bytes;
     p.err = ctx->d_err;
-    const dim3 grid(p.n_tt, (p.N + TC_ROWS - 1) / TC_ROWS);
+#ifdef DC_TC_TIMING
+    {
+        static unsigned long long* t = nullptr;
+        if (!t) {
+            cudaMalloc((void**)&t, 64);
+            cudaMemset(t, 0, 64);
+        }
+        p.timing = t;
+        if (getenv("DC_TC_TIMING_DUMP")) {
+            unsigned long long h[6];
+            cudaMemcpy(h, t, 48, cudaMemcpyDeviceToHost);
+            fprintf(stderr, "gemm_tc cycles so far: expand %llu wait_b %llu vote %llu umma %llu readout %llu vote2 %llu\n", h[0], h[1], h[2], h[3], h[4], h[5]);
+        }
+    }
+#endif
+    const dim3 grid(p.n_tt, row_tiles);
     if (w->type == DC_TYPE_Q4_K) {
         constexpr size_t smem = tc_smem_bytes<DC_TYPE_Q4_K>();
         DC_TRY(dc_kernel_setup(ctx, (const void*)k_gemm_tc<DC_TYPE_Q4_K>, smem, "k_gemm_tc<Q4_K>"));
@@ -441,4 +526,9 @@ int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n
         k_gemm_tc<DC_TYPE_Q6_K><<<grid, TC_THREADS, smem, ctx->stream>>>(p);
     }
     return dc_check_cuda(ctx, cudaGetLastError(), "k_gemm_tc");
+}
+
+int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
+                      const int* tile_expert, const int* slot_row, bool accumulate) {
+    return dc_launch_gemm_tc_multi(ctx, &w, nullptr, 1, act, n_slots, out, ldo, tile_expert, slot_row, accumulate);
 }

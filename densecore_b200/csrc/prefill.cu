@@ -28,7 +28,7 @@ struct dc_prefill_buffers {
     int cap = 0;               // tokens per chunk
     int max_tiles = 0;         // 64-slot tiles of the grouped expert matmuls
     int32_t *tokens = nullptr, *seq_ids = nullptr, *positions = nullptr;
-    float *x = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *g = nullptr, *u = nullptr,
+    float *x = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *g = nullptr,
           *dn = nullptr, *moe_out = nullptr, *logits = nullptr, *weights = nullptr;
     int32_t* ids = nullptr;
     int32_t *slot_assign = nullptr, *slot_token = nullptr, *tile_expert = nullptr;
@@ -79,8 +79,7 @@ static int prefill_prepare(dc_model* m) {
     A_(pf_alloc(m, &P->qkv, C * (QD + 2 * KD)));
     A_(pf_alloc(m, &P->q, C * QD));
     A_(pf_alloc(m, &P->att, C * QD));
-    A_(pf_alloc(m, &P->g, slots * F));
-    A_(pf_alloc(m, &P->u, slots * F));
+    A_(pf_alloc(m, &P->g, slots * 2 * F));      // gate | up, 2 F columns per slot
     A_(pf_alloc(m, &P->act_x, dc_gemm_tc_act_bytes((int)C, (int)H)));
     A_(pf_alloc(m, &P->act_att, dc_gemm_tc_act_bytes((int)C, (int)QD)));
     A_(pf_alloc(m, &P->act_h, dc_gemm_tc_act_bytes((int)slots, (int)F)));
@@ -145,7 +144,7 @@ __global__ void __launch_bounds__(1024) k_moe_group(const int32_t* __restrict__ 
 // h = silu(g) * u per slot (the production SwiGLU of the CPU kernels, see silu_fast), quantised to the
 // tiled Q8_K layout of the down projection's activations.  One warp per (slot, 256-value block);
 // slot_valid (optional): slots whose entry is negative hold zeros.
-__global__ void __launch_bounds__(256) k_swiglu_q8k_tiled(const float* __restrict__ g, const float* __restrict__ u, int F,
+__global__ void __launch_bounds__(256) k_swiglu_q8k_tiled(const float* __restrict__ g, const float* __restrict__ u, int ld, int F,
                                                           int n_slots_data, uint8_t* __restrict__ act, int n_tt,
                                                           const int32_t* __restrict__ slot_valid) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -158,7 +157,7 @@ __global__ void __launch_bounds__(256) k_swiglu_q8k_tiled(const float* __restric
         uint32_t w0 = 0, w1 = 0, bw = 0;
         float d = 0.0f;
         if (live) {
-            const size_t base = (size_t)slot * F + (size_t)b * DC_QK_K + 8 * lane;
+            const size_t base = (size_t)slot * ld + (size_t)b * DC_QK_K + 8 * lane;
             const float4 g0 = *reinterpret_cast<const float4*>(g + base), g1 = *reinterpret_cast<const float4*>(g + base + 4);
             const float4 u0 = *reinterpret_cast<const float4*>(u + base), u1 = *reinterpret_cast<const float4*>(u + base + 4);
             const float v[8] = {__fmul_rn(silu_fast(g0.x), u0.x), __fmul_rn(silu_fast(g0.y), u0.y),
@@ -172,12 +171,13 @@ __global__ void __launch_bounds__(256) k_swiglu_q8k_tiled(const float* __restric
     }
 }
 
-static int launch_swiglu(dc_ctx* ctx, const float* g, const float* u, int F, int n_slots_data, uint8_t* act, int n_tt,
+// g, u: rows of ld floats per slot
+static int launch_swiglu(dc_ctx* ctx, const float* g, const float* u, int ld, int F, int n_slots_data, uint8_t* act, int n_tt,
                          const int32_t* slot_valid) {
     const long long items = (long long)n_tt * 64 * (F / DC_QK_K);
     long long blocks = (items + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    k_swiglu_q8k_tiled<<<(unsigned)blocks, 256, 0, ctx->stream>>>(g, u, F, n_slots_data, act, n_tt, slot_valid);
+    k_swiglu_q8k_tiled<<<(unsigned)blocks, 256, 0, ctx->stream>>>(g, u, ld, F, n_slots_data, act, n_tt, slot_valid);
     return dc_check_cuda(ctx, cudaGetLastError(), "k_swiglu_q8k_tiled");
 }
 
@@ -230,9 +230,17 @@ int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool
         DC_TRY(dc_launch_rmsnorm_q8k(ctx, P.x, pending, (const float*)Ly.attn_norm->dev, n, H, c.rms_eps, P.xn, nullptr));
         pending = nullptr;
         DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_x, n_tt, nullptr));
-        DC_TRY(dc_launch_gemm_tc(ctx, Ly.wq, P.act_x, n, P.qkv, QKV));
-        DC_TRY(dc_launch_gemm_tc(ctx, Ly.wk, P.act_x, n, P.qkv + QD, QKV));
-        DC_TRY(dc_launch_gemm_tc(ctx, Ly.wv, P.act_x, n, P.qkv + QD + KD, QKV));
+        {
+            // Q | K | V in as few launches as their types allow (V is often Q6_K beside Q4_K Q and K)
+            const dc_weight* ws[3] = {Ly.wq, Ly.wk, Ly.wv};
+            const int offs[3] = {0, QD, QD + KD};
+            for (int i = 0; i < 3;) {
+                int j = i + 1;
+                while (j < 3 && ws[j]->type == ws[i]->type && ws[j]->row_bytes == ws[i]->row_bytes) ++j;
+                DC_TRY(dc_launch_gemm_tc_multi(ctx, ws + i, offs + i, j - i, P.act_x, n, P.qkv, QKV));
+                i = j;
+            }
+        }
         __half* ka = m->kv.k_arena + m->kv.layer_elems * il;
         __half* va = m->kv.v_arena + m->kv.layer_elems * il;
         DC_TRY(dc_launch_qknorm_rope_kv(ctx, P.qkv, Ly.q_norm ? (const float*)Ly.q_norm->dev : nullptr,
@@ -255,18 +263,31 @@ int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool
             DC_TRY(dc_check_cuda(ctx, cudaGetLastError(), "k_moe_group"));
             const int slots = P.max_tiles * 64;
             DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_moe, P.max_tiles, P.slot_token));
-            DC_TRY(dc_launch_gemm_tc(ctx, Ly.gate_exps, P.act_moe, slots, P.g, F, P.tile_expert));
-            DC_TRY(dc_launch_gemm_tc(ctx, Ly.up_exps, P.act_moe, slots, P.u, F, P.tile_expert));
-            DC_TRY(launch_swiglu(ctx, P.g, P.u, F, slots, P.act_h, P.max_tiles, P.slot_assign));
+            if (Ly.gate_exps->type == Ly.up_exps->type) {
+                // gate | up in one launch: g and u are one buffer of 2 F columns per slot (gate first)
+                const dc_weight* ws[2] = {Ly.gate_exps, Ly.up_exps};
+                const int offs[2] = {0, F};
+                DC_TRY(dc_launch_gemm_tc_multi(ctx, ws, offs, 2, P.act_moe, slots, P.g, 2 * F, P.tile_expert));
+            } else {
+                DC_TRY(dc_launch_gemm_tc(ctx, Ly.gate_exps, P.act_moe, slots, P.g, 2 * F, P.tile_expert));
+                DC_TRY(dc_launch_gemm_tc(ctx, Ly.up_exps, P.act_moe, slots, P.g + F, 2 * F, P.tile_expert));
+            }
+            DC_TRY(launch_swiglu(ctx, P.g, P.g + F, 2 * F, F, slots, P.act_h, P.max_tiles, P.slot_assign));
             DC_TRY(dc_launch_gemm_tc(ctx, Ly.down_exps, P.act_h, slots, P.dn, H, P.tile_expert, P.slot_assign));
             DC_TRY(dc_launch_moe_combine(ctx, P.dn, P.ids, P.weights, n, top_k, H, 0, E, P.moe_out));
             pending = P.moe_out;
         } else {
             const int F = c.ffn;
             DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_x, n_tt, nullptr));
-            DC_TRY(dc_launch_gemm_tc(ctx, Ly.ffn_gate, P.act_x, n, P.g, F));
-            DC_TRY(dc_launch_gemm_tc(ctx, Ly.ffn_up, P.act_x, n, P.u, F));
-            DC_TRY(launch_swiglu(ctx, P.g, P.u, F, n, P.act_h, n_tt, nullptr));
+            if (Ly.ffn_gate->type == Ly.ffn_up->type) {
+                const dc_weight* ws[2] = {Ly.ffn_gate, Ly.ffn_up};
+                const int offs[2] = {0, F};
+                DC_TRY(dc_launch_gemm_tc_multi(ctx, ws, offs, 2, P.act_x, n, P.g, 2 * F));
+            } else {
+                DC_TRY(dc_launch_gemm_tc(ctx, Ly.ffn_gate, P.act_x, n, P.g, 2 * F));
+                DC_TRY(dc_launch_gemm_tc(ctx, Ly.ffn_up, P.act_x, n, P.g + F, 2 * F));
+            }
+            DC_TRY(launch_swiglu(ctx, P.g, P.g + F, 2 * F, F, n, P.act_h, n_tt, nullptr));
             DC_TRY(dc_launch_gemm_tc(ctx, Ly.ffn_down, P.act_h, n, P.x, H, nullptr, nullptr, true));
         }
     }

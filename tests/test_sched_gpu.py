@@ -140,6 +140,9 @@ def test_prefix_cache_at_the_block_manager(ctx):
 
 def test_scheduler_batches_four_sequences_with_one_prefill_at_a_time(ctx):
     m, cfg = small_model(ctx, max_seqs=4, max_ctx=512)
+    # token-for-token comparison of differently chunked prompts: the sixteen-token prefill path, whose results do
+    # not depend on where a prompt is cut (the tensor-core path's flash attention and Q6_K float order do, at 1e-4)
+    m.set_option("tc_prefill", 0)
     rng = np.random.default_rng(8)
     prompts = [rng.integers(0, cfg.vocab, size=n) for n in (70, 33, 150, 20, 95, 64)]
     n_new = [12, 5, 9, 14, 7, 10]
@@ -190,6 +193,7 @@ def test_scheduler_batches_four_sequences_with_one_prefill_at_a_time(ctx):
 
 def test_scheduler_end_of_sequence_and_argument_checks(ctx):
     m, cfg = small_model(ctx, max_seqs=2, max_ctx=256)
+    m.set_option("tc_prefill", 0)
     rng = np.random.default_rng(9)
     p = rng.integers(0, cfg.vocab, size=30)
     s = m.seq_alloc()
