@@ -60,8 +60,8 @@ struct MegaParams {
     // meet once per layer through flags in each other's memory; the combine then reads local memory only.
     int ep_rank, ep_size, e_lo, e_hi;
     float* xdn[MG_MAX_RANKS];        // rank r's exchange rows: two halves of [MG_MAX_T * MG_MAX_K][H] floats
-    unsigned* xflag[MG_MAX_RANKS];   // in rank r's memory: the flag this rank raises there
-    unsigned* my_flags;              // this rank's flags, one per peer
+    unsigned* xcnt[MG_MAX_RANKS];    // in rank r's memory: the counter this rank's CTAs add their arrivals to
+    unsigned* my_xcnt;               // this rank's counter: arrivals of all CTAs of all peers
     unsigned xepoch0;                // exchanges completed before this launch
     int route_mode;                  // DC_ROUTE_STABLE / DC_ROUTE_SOFTMAX
     float* dbg_x;                    // optional capture of every layer's input [n_layer + 1][DC_MAX_T][H]

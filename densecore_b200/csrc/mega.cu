@@ -43,6 +43,7 @@ __device__ __forceinline__ unsigned long long mg_now();
 // Split in two so that work that does not depend on the other CTAs (asking for the next phase's weight rows,
 // prefetches) runs between a CTA's arrival and its release instead of in front of the arrival: issuing those
 // copies takes a warp longer than the barrier's own release latency.
+__device__ __forceinline__ void ep_arrive(const MegaParams& p);
 __device__ __noinline__ void grid_arrive(const MegaParams& p, unsigned& epoch, bool sys_scope = false) {
     __syncthreads();
     ++epoch;
@@ -51,9 +52,9 @@ __device__ __noinline__ void grid_arrive(const MegaParams& p, unsigned& epoch, b
     const bool trace = threadIdx.x == 0 && p.phase_ns && epoch > 7 && epoch <= 14;
     if (trace) p.phase_ns[32 + (epoch - 8) * 160 + blockIdx.x] = mg_now();
 #endif
+    if (sys_scope) ep_arrive(p);                 // this CTA's stores to other GPUs are performed first
     if (threadIdx.x == 0) {
-        if (sys_scope) __threadfence_system();   // this CTA's stores to other GPUs are performed first
-        else __threadfence();
+        __threadfence();
         atomicAdd(p.bar_counter, 1u);
     }
 }
@@ -80,39 +81,44 @@ __device__ __forceinline__ void grid_barrier(const MegaParams& p, unsigned& epoc
     grid_wait(p, epoch);
 }
 
-// Expert-parallel meeting point, once per layer, after a grid barrier with system-scope fences: CTA 0
-// raises this rank's flag in every peer's memory; every CTA then waits until all peers have raised theirs
-// here (their rows for this layer are then in this GPU's exchange buffer).  The wait gives up after two
-// seconds, or at once if an error is already recorded, and records DC_ERR_EP_WAIT.
+// Expert-parallel meeting point, once per layer, folded into the grid barrier that ends the down projection:
+// a CTA that arrives (its rows are stored in every GPU's exchange buffer) also adds one to an arrival counter
+// in every peer's memory (red.release.sys after a system-scope fence; lane r of warp 0 talks to rank r, so the
+// peers are signalled side by side), and after the local barrier every CTA waits until all CTAs of all peers
+// have arrived here.  The remote arrivals travel while the local barrier and the next phase's prefetch run.
+// The wait gives up after two seconds, or at once if an error is already recorded, and records DC_ERR_EP_WAIT.
 #define DC_ERR_EP_WAIT 3
 #define MG_EP_WAIT_NS 2000000000ull
-__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+#define MG_XCNT_WORD 32          // word index of the arrival counter in an exchange buffer's flag area
+__device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __noinline__ void ep_exchange(const MegaParams& p, unsigned value) {
+// after the CTA's __syncthreads (grid_arrive): tell the peers
+__device__ __forceinline__ void ep_arrive(const MegaParams& p) {
+    const int r = threadIdx.x;
+    if (r < p.ep_size && r != p.ep_rank) {
+        __threadfence_system();
+        red_release_sys_add(p.xcnt[r], 1u);
+    }
+}
+// exchanges: how many have completed once this one has (all ranks count alike)
+__device__ __noinline__ void ep_wait(const MegaParams& p, unsigned exchanges) {
     if (threadIdx.x == 0) {
-        if (blockIdx.x == 0) {
-            __threadfence_system();
-            for (int r = 0; r < p.ep_size; ++r)
-                if (r != p.ep_rank) st_release_sys_u32(p.xflag[r], value);
-        }
+        const unsigned target = exchanges * (unsigned)(p.ep_size - 1) * gridDim.x;
         const unsigned long long t0 = mg_now();
-        for (int r = 0; r < p.ep_size; ++r) {
-            if (r == p.ep_rank) continue;
-            // flags only grow; the difference is taken modulo 2^32
-            while ((int)(ld_acquire_sys_u32(p.my_flags + r) - value) < 0) {
-                if (*reinterpret_cast<volatile int*>(p.err) != 0) break;
-                if (mg_now() - t0 > p.ep_wait_ns) {
-                    atomicExch(p.err, DC_ERR_EP_WAIT);
-                    break;
-                }
-                __nanosleep(64);
+        // the counter only grows; the difference is taken modulo 2^32
+        while ((int)(ld_acquire_sys_u32(p.my_xcnt) - target) < 0) {
+            if (*reinterpret_cast<volatile int*>(p.err) != 0) break;
+            if (mg_now() - t0 > p.ep_wait_ns) {
+                atomicExch(p.err, DC_ERR_EP_WAIT);
+                break;
             }
+            __nanosleep(32);
         }
     }
     __syncthreads();
@@ -1346,7 +1352,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             grid_arrive(p, epoch, ep);
             mg_gemv_prefill(l + 1 < p.n_layer ? gq : glm, pipe, sh, gw, nw, lane);
             grid_wait(p, epoch);
-            if (ep) ep_exchange(p, xe + 1);
+            if (ep) ep_wait(p, xe + 1);
             ++xe;
             dn_r = dn_w;
             MG_MARK(20);
@@ -1365,7 +1371,9 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
         // greedy pick: first maximum wins (core/src/sampler/sampler.cpp:42-57)
         if (blockIdx.x == 0 && tid < p.T) {
             const unsigned long long k = __ldcg(p.argmax_keys + tid);
-            const int32_t tok = (int32_t)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull));
+            int32_t tok = (int32_t)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull));
+            // (a step cut short by a wait that ran out may leave no key behind: the id must stay a valid row index)
+            if ((uint32_t)tok >= (uint32_t)p.vocab) tok = 0;
             p.out_tokens[tid] = tok;
             if (p.feedback) {
                 p.tokens[tid] = tok;
@@ -1566,9 +1574,9 @@ int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback) {
     if (p.ep_size > 1) {
         for (int r = 0; r < p.ep_size; ++r) {
             p.xdn[r] = (float*)(m->xch_peer[r] + MG_XCH_FLAG_BYTES);
-            p.xflag[r] = (unsigned*)m->xch_peer[r] + p.ep_rank;
+            p.xcnt[r] = (unsigned*)m->xch_peer[r] + MG_XCNT_WORD;
         }
-        p.my_flags = (unsigned*)m->xch;
+        p.my_xcnt = (unsigned*)m->xch + MG_XCNT_WORD;
         p.xepoch0 = m->xepoch;
         m->xepoch += (unsigned)(m->cfg.n_layer * n_steps);
     }

@@ -108,11 +108,11 @@ static int prefill_prepare(dc_model* m) {
 // ---- grouping of the chunk's expert assignments ----------------------------------------------------------
 // ids [C][top_k] -> the assignments of every expert (ascending experts) in runs padded to whole 64-slot tiles:
 // slot_assign[slot] = t * top_k + k or -1, slot_token[slot] = t or -1, tile_expert[tile] = expert or -1.
-// Slots of one expert are filled in arrival order (the rows of a tile are independent, and results return to
+// tile_expert holds the expert's slab index on this GPU.  Slots of one expert are filled in arrival order (the rows of a tile are independent, and results return to
 // assignment order through slot_assign).  One CTA.
 __global__ void __launch_bounds__(1024) k_moe_group(const int32_t* __restrict__ ids, int A, int top_k, int E, int max_tiles,
-                                                    int32_t* __restrict__ slot_assign, int32_t* __restrict__ slot_token,
-                                                    int32_t* __restrict__ tile_expert) {
+                                                    int ep_lo, int ep_hi, int32_t* __restrict__ slot_assign,
+                                                    int32_t* __restrict__ slot_token, int32_t* __restrict__ tile_expert) {
     __shared__ int s_cnt[256], s_off[256], s_fill[256], s_total;
     const int tid = threadIdx.x;
     if (tid < 256) s_cnt[tid] = s_fill[tid] = 0;
@@ -124,7 +124,10 @@ __global__ void __launch_bounds__(1024) k_moe_group(const int32_t* __restrict__ 
         for (int i = 0; i < tid; ++i) off += (s_cnt[i] + 63) / 64;
         s_off[tid] = off;
         const int tiles = tid < E ? (s_cnt[tid] + 63) / 64 : 0;
-        for (int t = 0; t < tiles; ++t) tile_expert[off + t] = tid;
+        // expert parallel: this GPU stores experts [ep_lo, ep_hi) only, as slabs 0 .. ep_hi - ep_lo - 1; tiles of the
+        // others are skipped here and their share of the layer arrives by all-reduce
+        const int local = (tid >= ep_lo && tid < ep_hi) ? tid - ep_lo : -1;
+        for (int t = 0; t < tiles; ++t) tile_expert[off + t] = local;
         if (tid == 255) s_total = off + tiles;
     }
     for (int sl = tid; sl < max_tiles * 64; sl += blockDim.x) {
@@ -184,7 +187,7 @@ static int launch_swiglu(dc_ctx* ctx, const float* g, const float* u, int ld, in
 // ---- one chunk ---------------------------------------------------------------------------------------------
 bool dc_prefill_tc_ok(dc_model* m, int n) {
     const dc_model_config& c = m->cfg;
-    if (!m->use_tc_prefill || n < m->ctx->gemm_tc_min_rows || c.ep_size > 1 || m->dbg_x || m->prof) return false;
+    if (!m->use_tc_prefill || n < m->ctx->gemm_tc_min_rows || (c.ep_size > 1 && !m->ep_ready) || m->dbg_x || m->prof) return false;
     for (const dc_layer& L : m->layers) {
         const dc_weight* ws[] = {L.wq, L.wk, L.wv, L.wo, L.gate_exps, L.up_exps, L.down_exps, L.ffn_gate, L.ffn_up, L.ffn_down};
         for (const dc_weight* w : ws)
@@ -259,7 +262,8 @@ int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool
         if (E > 0) {
             const int A = n * top_k, F = c.expert_ffn;
             DC_TRY(dc_launch_router_batched(ctx, Ly.router, P.xn, n, top_k, c.routed_scale, P.logits, P.ids, P.weights, m->route_mode));
-            k_moe_group<<<1, 1024, 0, ctx->stream>>>(P.ids, A, top_k, E, P.max_tiles, P.slot_assign, P.slot_token, P.tile_expert);
+            k_moe_group<<<1, 1024, 0, ctx->stream>>>(P.ids, A, top_k, E, P.max_tiles, m->ep_lo, m->ep_hi, P.slot_assign, P.slot_token,
+                                                     P.tile_expert);
             DC_TRY(dc_check_cuda(ctx, cudaGetLastError(), "k_moe_group"));
             const int slots = P.max_tiles * 64;
             DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_moe, P.max_tiles, P.slot_token));
@@ -274,7 +278,8 @@ int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool
             }
             DC_TRY(launch_swiglu(ctx, P.g, P.g + F, 2 * F, F, slots, P.act_h, P.max_tiles, P.slot_assign));
             DC_TRY(dc_launch_gemm_tc(ctx, Ly.down_exps, P.act_h, slots, P.dn, H, P.tile_expert, P.slot_assign));
-            DC_TRY(dc_launch_moe_combine(ctx, P.dn, P.ids, P.weights, n, top_k, H, 0, E, P.moe_out));
+            DC_TRY(dc_launch_moe_combine(ctx, P.dn, P.ids, P.weights, n, top_k, H, m->ep_lo, m->ep_hi, P.moe_out));
+            if (c.ep_size > 1) DC_TRY(dc_ep_allreduce(m, P.moe_out, (size_t)n * H));
             pending = P.moe_out;
         } else {
             const int F = c.ffn;
