@@ -152,6 +152,12 @@ struct WarpPipe {
         ++consumed;
         __syncwarp();
     }
+    // Leaving early: lane 0 (the only lane that counts issues) waits, bounded, for the copies still in flight.
+    __device__ __forceinline__ void drain() {
+        if ((threadIdx.x & 31) == 0)
+            for (; consumed < issued; ++consumed) mbar_wait(bar0 + 8 * (consumed % NSTAGE), (consumed / NSTAGE) & 1, nullptr);
+        __syncwarp();
+    }
 };
 
 // ------------------------------------------------------- shared loads

@@ -94,6 +94,7 @@ struct dc_model {
     uint8_t* xch = nullptr;
     uint8_t* xch_peer[8] = {};
     int xch_connected = 0;       // peers mapped so far
+    bool xch_loopback = false;   // test hook: the peer buffer is a local allocation (dc_mega_test_loopback)
     unsigned xepoch = 0;         // exchanges completed by earlier launches
 };
 
@@ -103,6 +104,7 @@ int dc_launch_synth_quantized(dc_ctx* ctx, int type, uint64_t seed, int64_t firs
 int dc_launch_synth_f32(dc_ctx* ctx, uint64_t seed, int64_t n, float sigma, float offset, float* out);
 // ---- mega.cu ----
 void dc_mega_release_xch(dc_model* m);
+int dc_mega_test_loopback(dc_model* m);
 struct MegaParams;
 bool dc_mega_plan(dc_model* m, int T, MegaParams* out, const char** why);
 int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback);

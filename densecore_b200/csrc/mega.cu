@@ -58,27 +58,35 @@ __device__ __noinline__ void grid_arrive(const MegaParams& p, unsigned& epoch, b
         atomicAdd(p.bar_counter, 1u);
     }
 }
-__device__ __noinline__ void grid_wait(const MegaParams& p, unsigned epoch) {
+// Returns true if this CTA's wait ran out: the caller then leaves the kernel (drains its copies in flight and
+// returns) instead of computing on data that other CTAs may not have written yet.  The CTAs that did arrive
+// run out at their next barrier, since this one never arrives there.
+__device__ __noinline__ bool grid_wait(const MegaParams& p, unsigned epoch) {
+    __shared__ int s_gave_up;
     if (threadIdx.x == 0) {
         const unsigned target = epoch * gridDim.x;
         unsigned polls = 0;
+        int gave_up = 0;
         while (ld_acquire_u32(p.bar_counter) < target) {
             if (++polls > p.bar_polls) {
                 atomicExch(p.err, DC_ERR_GRID_BARRIER);
+                gave_up = 1;
                 break;
             }
             if (MG_BAR_SLEEP) __nanosleep(MG_BAR_SLEEP);
         }
+        s_gave_up = gave_up;
         __threadfence();
     }
 #ifdef DC_MEGA_SUBMARKS
     if (threadIdx.x == 0 && p.phase_ns && epoch > 7 && epoch <= 14) p.phase_ns[32 + (7 + epoch - 8) * 160 + blockIdx.x] = mg_now();
 #endif
     __syncthreads();
+    return s_gave_up != 0;
 }
-__device__ __forceinline__ void grid_barrier(const MegaParams& p, unsigned& epoch, bool sys_scope = false) {
+__device__ __forceinline__ bool grid_barrier(const MegaParams& p, unsigned& epoch, bool sys_scope = false) {
     grid_arrive(p, epoch, sys_scope);
-    grid_wait(p, epoch);
+    return grid_wait(p, epoch);
 }
 
 // Expert-parallel meeting point, once per layer, folded into the grid barrier that ends the down projection:
@@ -107,21 +115,25 @@ __device__ __forceinline__ void ep_arrive(const MegaParams& p) {
     }
 }
 // exchanges: how many have completed once this one has (all ranks count alike)
-__device__ __noinline__ void ep_wait(const MegaParams& p, unsigned exchanges) {
+__device__ __noinline__ bool ep_wait(const MegaParams& p, unsigned exchanges) {
+    __shared__ int s_gave_up;
     if (threadIdx.x == 0) {
         const unsigned target = exchanges * (unsigned)(p.ep_size - 1) * gridDim.x;
         const unsigned long long t0 = mg_now();
+        int gave_up = 0;
         // the counter only grows; the difference is taken modulo 2^32
         while ((int)(ld_acquire_sys_u32(p.my_xcnt) - target) < 0) {
-            if (*reinterpret_cast<volatile int*>(p.err) != 0) break;
-            if (mg_now() - t0 > p.ep_wait_ns) {
+            if (*reinterpret_cast<volatile int*>(p.err) != 0 || mg_now() - t0 > p.ep_wait_ns) {
                 atomicExch(p.err, DC_ERR_EP_WAIT);
+                gave_up = 1;
                 break;
             }
             __nanosleep(32);
         }
+        s_gave_up = gave_up;
     }
     __syncthreads();
+    return s_gave_up != 0;
 }
 
 // Every CTA reads the same small arrays (hidden state, expert outputs, attention
@@ -1256,20 +1268,20 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             mg_gemv_prefill(go, pipe, sh, gw, nw, lane);   // output-projection rows stream in during attention
             prefetch_vec(L.ffn_norm, (size_t)p.H * 4);
             if ((int)blockIdx.x < p.E) prefetch_vec(L.router + (size_t)blockIdx.x * p.H, (size_t)p.H * 4);
-            grid_wait(p, epoch);
+            if (grid_wait(p, epoch)) goto gave_up;
             MG_MARK(4);
             MG_WTRACE(3);
             // ---- P1 / P2: attention
             attn_scores_phase(p, L, sh, item, s_sc, vbuf, vcap_blocks);
             MG_MARK(5);
             MG_WTRACE(4);
-            grid_barrier(p, epoch);
+            if (grid_barrier(p, epoch)) goto gave_up;
             MG_MARK(6);
             MG_WTRACE(5);
             attn_pv_phase(p, L, sh, item, s_sc, vbuf, vcap_blocks);
             MG_MARK(7);
             MG_WTRACE(6);
-            grid_barrier(p, epoch);
+            if (grid_barrier(p, epoch)) goto gave_up;
             MG_MARK(8);
             MG_WTRACE(7);
             // ---- P3: output projection, x += Wo . attn
@@ -1280,7 +1292,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             mg_gemv_consume<NT>(go, pipe, act, sh, gw, lane);
             MG_MARK(10);
             MG_WTRACE(8);
-            grid_barrier(p, epoch);
+            if (grid_barrier(p, epoch)) goto gave_up;
             MG_MARK(11);
             MG_WTRACE(9);
             // ---- P4: ffn_norm, Q8_K, router logits
@@ -1304,7 +1316,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
                     sh.m_dn.n_peer = q;
                 }
             }
-            grid_wait(p, epoch);
+            if (grid_wait(p, epoch)) goto gave_up;
             MG_MARK(14);
             MG_WTRACE(11);
             // ---- P5: routing, gate/up + SwiGLU
@@ -1327,7 +1339,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             } else {
                 prefetch_vec(p.out_norm, (size_t)p.H * 4);
             }
-            grid_wait(p, epoch);
+            if (grid_wait(p, epoch)) goto gave_up;
             MG_MARK(17);
             MG_WTRACE(14);
             // ---- P6: h -> Q8_K, down rows
@@ -1351,8 +1363,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             MG_WTRACE(16);
             grid_arrive(p, epoch, ep);
             mg_gemv_prefill(l + 1 < p.n_layer ? gq : glm, pipe, sh, gw, nw, lane);
-            grid_wait(p, epoch);
-            if (ep) ep_wait(p, xe + 1);
+            if (grid_wait(p, epoch)) goto gave_up;
+            if (ep && ep_wait(p, xe + 1)) goto gave_up;
             ++xe;
             dn_r = dn_w;
             MG_MARK(20);
@@ -1366,7 +1378,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
                                        p.dbg_x ? p.dbg_x + (size_t)p.n_layer * DC_MAX_T * p.H : nullptr, p.out_norm, act,
                                        nullptr, dn_r);
         mg_gemv_consume<NT>(glm, pipe, act, sh, gw, lane);
-        grid_barrier(p, epoch);
+        if (grid_barrier(p, epoch)) goto gave_up;
         MG_MARK(21);
         // greedy pick: first maximum wins (core/src/sampler/sampler.cpp:42-57)
         if (blockIdx.x == 0 && tid < p.T) {
@@ -1389,8 +1401,13 @@ __global__ void __launch_bounds__(MG_THREADS, 1) k_decode_mega(const __grid_cons
             __syncthreads();
             if (tid == 0 && p.feedback && p.history) *p.history_len += 1;
         }
-        if (step + 1 < p.n_steps) grid_barrier(p, epoch);
+        if (step + 1 < p.n_steps && grid_barrier(p, epoch)) goto gave_up;
     }
+    return;
+gave_up:
+    // a bounded wait ran out (the error word is set): wait, again with a limit, for this warp's weight copies
+    // still in flight, then leave; nothing is computed on data that may not be there
+    pipe.drain();
 }
 
 // ------------------------------------------------------------------ host
@@ -1589,6 +1606,9 @@ int dc_mega_run(dc_model* m, int T, int n_steps, bool feedback) {
     p.phase_ns = m->mega_timing ? (unsigned long long*)((uint8_t*)m->mega_counter + 64) : nullptr;
     int st = dc_check_cuda(m->ctx, cudaMemsetAsync(m->mega_counter, 0, sizeof(unsigned), m->ctx->stream), "memset");
     if (st != DC_B200_OK) return st;
+    // the merge tickets reset themselves when a merge completes; a launch that gave up may have left some behind
+    st = dc_check_cuda(m->ctx, cudaMemsetAsync(b.attn.tickets, 0, (size_t)DC_MAX_T * m->cfg.n_head * sizeof(int), m->ctx->stream), "memset");
+    if (st != DC_B200_OK) return st;
     m->last_launches = 1;
     return (T == 1 && m->cfg.hidden <= 4096) ? mg_launch<1>(m, p) : mg_launch<MG_MAX_T>(m, p);
 }
@@ -1663,9 +1683,34 @@ int dc_b200_model_ep_import(dc_model* m, int rank, const void* handle_64) {
 
 }  // extern "C"
 
+// Test hook for the exchange's bounded wait on ONE GPU: a rank of a two-rank model whose "peer" is a second
+// local buffer that nothing ever signals.  The persistent kernel then stores its rows into that buffer, adds its
+// arrivals to a counter nobody reads, and its own wait for the peer's arrivals runs out.  No communicator exists:
+// only decode steps through the persistent kernel may run on such a model.
+int dc_mega_test_loopback(dc_model* m) {
+    if (m->cfg.ep_size != 2 || m->xch || m->ep_ready)
+        return dc_fail(m->ctx, DC_B200_INVALID_ARGUMENT, "test_ep_loopback needs a fresh two-rank model");
+    cudaSetDevice(m->ctx->device);
+    uint8_t* fake = nullptr;
+    cudaError_t e = cudaMalloc((void**)&m->xch, dc_mega_xch_bytes(m));
+    if (e == cudaSuccess) e = cudaMemset(m->xch, 0, dc_mega_xch_bytes(m));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&fake, dc_mega_xch_bytes(m));
+    if (e == cudaSuccess) e = cudaMemset(fake, 0, dc_mega_xch_bytes(m));
+    if (e != cudaSuccess) return dc_check_cuda(m->ctx, e, "loopback exchange buffers");
+    m->xch_peer[m->cfg.ep_rank] = m->xch;
+    m->xch_peer[1 - m->cfg.ep_rank] = fake;
+    m->xch_connected = 1;
+    m->xch_loopback = true;
+    m->ep_ready = true;
+    return DC_B200_OK;
+}
+
 void dc_mega_release_xch(dc_model* m) {
     for (int r = 0; r < 8; ++r) {
-        if (m->xch_peer[r] && m->xch_peer[r] != m->xch) cudaIpcCloseMemHandle(m->xch_peer[r]);
+        if (m->xch_peer[r] && m->xch_peer[r] != m->xch) {
+            if (m->xch_loopback) cudaFree(m->xch_peer[r]);
+            else cudaIpcCloseMemHandle(m->xch_peer[r]);
+        }
         m->xch_peer[r] = nullptr;
     }
     if (m->xch) cudaFree(m->xch);

@@ -850,6 +850,7 @@ int dc_b200_model_set_option(dc_model* m, const char* name, int value) {
         m->prefix_cache = value != 0;
         return DC_B200_OK;
     }
+    if (!strcmp(name, "test_ep_loopback")) return value ? dc_mega_test_loopback(m) : DC_B200_OK;
     if (!strcmp(name, "test_barrier_polls")) {
         m->test_barrier_polls = value < 0 ? 0u : (unsigned)value;
         return DC_B200_OK;

@@ -360,7 +360,13 @@ DC_B200_API int dc_b200_model_read_kv(dc_model* m, int layer, int seq, int first
  * "capture_layer_inputs" 0/1: see dc_b200_model_read_layer_input (steps then run without graphs).
  * "test_barrier_polls" n, "test_ep_wait_us" n: shorten the poll limit of the persistent kernel's grid
  * barrier / the time limit of its expert-parallel meeting (0 restores the defaults), so that a test can
- * make a bounded wait run out and check the status that comes back.
+ * make a bounded wait run out and check the status that comes back (DC_B200_BACKEND_ERROR; the kernel drains
+ * its copies in flight and returns, the context stays usable).  "test_ep_loopback" 1, before finalize, on
+ * a fresh model of ep_size 2: the peer's exchange buffer is a second local buffer that nothing signals, so
+ * that the expert-parallel wait can be exercised on one GPU (such a model may only run decode steps).
+ * "tc_prefill" 0/1 (default 1): prompts of 32 tokens or more run in chunks through the tensor-core matmuls;
+ * "prefill_chunk" 32..4096 (default 512, fixed once a chunk has run); "prefill_attention" 1 (default) chunk
+ * attention on the tensor cores, 0 the decode kernels' exact running-maximum chain; "prefix_cache" 0/1.
  * "persistent" 0/1/2: decode steps of MoE models run in one persistent cooperative kernel with grid
  * barriers between phases: 0 never, 1 for one stream (default: with more streams the per-op kernels are
  * faster), 2 for every stream count it supports (1-4). */
