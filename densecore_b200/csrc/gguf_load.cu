@@ -200,8 +200,32 @@ extern "C" int dc_b200_model_from_gguf(dc_ctx* ctx, const char* path, int max_se
     cfg.n_expert_used = (int)num("expert_used_count", 0);
     cfg.expert_ffn = (int)num("expert_feed_forward_length", 0);
     cfg.ffn = cfg.n_expert > 0 ? 0 : (int)num("feed_forward_length", 0);
-    cfg.routed_scale = (float)num("expert_weights_scale", 1.0);
+    {
+        // either name of the routing weights' scale (core/src/models/model_loader.cpp:2849)
+        bool have_scale = false;
+        cfg.routed_scale = (float)num("expert_weights_scale", 1.0, &have_scale);
+        if (!have_scale) cfg.routed_scale = (float)num("routed_scaling_factor", 1.0);
+    }
     if (cfg.routed_scale == 0.0f) cfg.routed_scale = 1.0f;
+    if (cfg.n_expert > 0) {
+        // MoE variants that the reference's loader reads (model_loader.cpp:2833-2850) and this decoder does not
+        // compute: refusing them beats decoding wrong tokens silently
+        const char* why = nullptr;
+        if (num("norm_topk_prob", 1.0) == 0.0) why = "norm_topk_prob = false (routing weights are always renormalised over the top-k here)";
+        else if (num("n_shared_experts", 0) > 0 || num("expert_shared_count", 0) > 0) why = "shared experts";
+        else if (num("n_group", 0) > 1 || num("topk_group", 0) > 1 || num("expert_group_count", 0) > 1 ||
+                 num("expert_group_used_count", 0) > 1)
+            why = "grouped routing";
+        else if (num("first_k_dense_replace", 0) > 0 || num("leading_dense_block_count", 0) > 0) why = "leading dense layers";
+        else {
+            for (const auto& kv : tensors)
+                if (kv.first.find("_shexp") != std::string::npos) {
+                    why = "shared-expert tensors (ffn_*_shexp)";
+                    break;
+                }
+        }
+        if (why) return dc_fail(ctx, DC_B200_UNSUPPORTED, "gguf: '%s' uses %s", path, why);
+    }
     auto emb = tensors.find("token_embd.weight");
     if (emb == tensors.end()) return dc_fail(ctx, DC_B200_MODEL_LOAD_FAILED, "gguf: token_embd.weight is missing");
     cfg.vocab = (int)emb->second.ne[1];

@@ -13,7 +13,7 @@ gguf = pytest.importorskip("gguf")
 pytestmark = pytest.mark.gpu
 
 
-def write_gguf(path, m: dc.Model, arch: str, drop=(), extra_meta=True):
+def write_gguf(path, m: dc.Model, arch: str, drop=(), extra_meta=True, moe_meta=None):
     cfg = m.cfg
     w = gguf.GGUFWriter(path, arch)
     w.add_block_count(cfg.n_layer)
@@ -30,6 +30,13 @@ def write_gguf(path, m: dc.Model, arch: str, drop=(), extra_meta=True):
         w.add_expert_feed_forward_length(cfg.expert_ffn)
     else:
         w.add_feed_forward_length(cfg.ffn)
+    for key, val in (moe_meta or {}).items():   # <arch>.<key>, the MoE switches the reference's loader reads
+        if isinstance(val, bool):
+            w.add_bool(f"{arch}.{key}", val)
+        elif isinstance(val, float):
+            w.add_float32(f"{arch}.{key}", val)
+        else:
+            w.add_uint32(f"{arch}.{key}", val)
     if extra_meta:   # values the loader must step over
         w.add_array("tokenizer.ggml.tokens", [f"tok{i}" for i in range(50)])
         w.add_array("tokenizer.ggml.scores", [float(i) for i in range(50)])
@@ -110,4 +117,28 @@ def test_gguf_errors(ctx, tmp_path):
     assert e.value.status == -2
     with pytest.raises(dc.DcError):
         dc.Model.from_gguf(ctx, str(tmp_path / "absent.gguf"))
+    src.close()
+
+
+def test_gguf_moe_variants_the_decoder_does_not_compute_are_refused(ctx, tmp_path):
+    """The reference's loader reads norm_topk_prob, shared experts, grouped routing and leading dense layers
+    (core/src/models/model_loader.cpp:2833-2850); this decoder computes none of them, so such files fail with
+    UNSUPPORTED instead of decoding wrong tokens.  routed_scaling_factor is accepted as the scale's other name."""
+    cfg = dc.Config(n_layer=1, hidden=512, n_head=4, n_kv_head=2, vocab=300, n_expert=8, n_expert_used=2, expert_ffn=256,
+                    max_seqs=1, max_ctx=32)
+    src = dc.Model(ctx, cfg)
+    src.init_synthetic(3, 0.05)
+    src.finalize()
+    for i, meta in enumerate(({"norm_topk_prob": False}, {"n_shared_experts": 1}, {"expert_shared_count": 2},
+                              {"n_group": 4, "topk_group": 2}, {"first_k_dense_replace": 1}, {"leading_dense_block_count": 1})):
+        path = str(tmp_path / f"variant{i}.gguf")
+        write_gguf(path, src, "qwen3moe", extra_meta=False, moe_meta=meta)
+        with pytest.raises(dc.DcError) as e:
+            dc.Model.from_gguf(ctx, path)
+        assert e.value.status == -7, (meta, e.value.status)
+    ok = str(tmp_path / "scaled.gguf")
+    write_gguf(ok, src, "qwen3moe", extra_meta=False, moe_meta={"routed_scaling_factor": 2.5, "norm_topk_prob": True})
+    m = dc.Model.from_gguf(ctx, ok, max_seqs=1, max_ctx=32)
+    assert abs(m.cfg.routed_scale - 2.5) < 1e-6
+    m.close()
     src.close()
