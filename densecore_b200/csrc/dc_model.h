@@ -78,9 +78,9 @@ struct dc_model {
     unsigned test_barrier_polls = 0;
     unsigned long long test_ep_wait_ns = 0;
     // prompt chunks through the tensor-core matmuls (prefill.cu): option "tc_prefill" (default on), chunk
-    // length option "prefill_chunk" (default 512, fixed once the first chunk has run)
+    // length option "prefill_chunk" (default 2048, fixed once the first chunk has run)
     bool use_tc_prefill = true;
-    int prefill_chunk = 512;
+    int prefill_chunk = 2048;
     bool prefill_flash = true;            // option "prefill_attention": 1 tensor-core flash attention, 0 the decode kernels' exact chain
     dc_prefill_buffers* prefill = nullptr;
     bool prefix_cache = false;            // option "prefix_cache": prefill looks up and registers block prefixes

@@ -1,4 +1,4 @@
-// Prompt processing in chunks of up to 512 tokens: every matmul of the decoder runs as one tensor-core
+// Prompt processing in chunks of up to 2048 tokens: every matmul of the decoder runs as one tensor-core
 // MUL_MAT over the whole chunk (gemm_tc.cu) instead of sixteen tokens at a time through the row-streaming
 // kernels, which re-read every weight for each sixteen tokens.  The CPU side of this is DenseCore's batched
 // matmul path for prefill chunks (core/src/llm/matmul/batched_exec.cpp:1040-1240, chunks up to M = 4096,
@@ -94,12 +94,6 @@ static int prefill_prepare(dc_model* m) {
         A_(pf_alloc(m, &P->tile_expert, (size_t)P->max_tiles));
         A_(pf_alloc(m, &P->act_moe, dc_gemm_tc_act_bytes((int)slots, (int)H)));
     }
-    const size_t att_bytes = dc_attention_scratch_bytes((int)C, c.n_head, c.n_kv_head, m->kv.max_blocks_per_seq, m->nsplit);
-    A_(pf_alloc(m, &P->attn_mem, att_bytes));
-    if (st == DC_B200_OK) {
-        dc_attn_scratch_bind(&P->attn, P->attn_mem, (int)C, c.n_head, c.n_kv_head, m->kv.max_blocks_per_seq, m->nsplit);
-        st = dc_check_cuda(m->ctx, cudaMemsetAsync(P->attn.tickets, 0, C * c.n_head * 4, m->ctx->stream), "memset");
-    }
     if (st == DC_B200_OK) st = dc_check_cuda(m->ctx, cudaMallocHost((void**)&P->h_stage, PF_STAGE_SLOTS * 3 * C * 4), "cudaMallocHost");
     if (st != DC_B200_OK) dc_prefill_release(m);
     return st;
@@ -184,6 +178,18 @@ static int launch_swiglu(dc_ctx* ctx, const float* g, const float* u, int ld, in
     return dc_check_cuda(ctx, cudaGetLastError(), "k_swiglu_q8k_tiled");
 }
 
+// Scratch of the decode kernels' exact attention chain for a whole chunk (scores of every token over the whole
+// context): only allocated when that attention is asked for.
+static int prefill_exact_attention_scratch(dc_model* m) {
+    dc_prefill_buffers* P = m->prefill;
+    if (P->attn_mem) return DC_B200_OK;
+    const dc_model_config& c = m->cfg;
+    const size_t att_bytes = dc_attention_scratch_bytes(P->cap, c.n_head, c.n_kv_head, m->kv.max_blocks_per_seq, m->nsplit);
+    DC_TRY(pf_alloc(m, &P->attn_mem, att_bytes));
+    dc_attn_scratch_bind(&P->attn, P->attn_mem, P->cap, c.n_head, c.n_kv_head, m->kv.max_blocks_per_seq, m->nsplit);
+    return dc_check_cuda(m->ctx, cudaMemsetAsync(P->attn.tickets, 0, (size_t)P->cap * c.n_head * 4, m->ctx->stream), "memset");
+}
+
 // ---- one chunk ---------------------------------------------------------------------------------------------
 bool dc_prefill_tc_ok(dc_model* m, int n) {
     const dc_model_config& c = m->cfg;
@@ -200,6 +206,7 @@ bool dc_prefill_tc_ok(dc_model* m, int n) {
 // (left in the step buffers of the decode path).
 int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool lm) {
     DC_TRY(prefill_prepare(m));
+    if (!m->prefill_flash) DC_TRY(prefill_exact_attention_scratch(m));
     dc_prefill_buffers& P = *m->prefill;
     const dc_model_config& c = m->cfg;
     dc_ctx* ctx = m->ctx;

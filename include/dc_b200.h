@@ -365,7 +365,7 @@ DC_B200_API int dc_b200_model_read_kv(dc_model* m, int layer, int seq, int first
  * a fresh model of ep_size 2: the peer's exchange buffer is a second local buffer that nothing signals, so
  * that the expert-parallel wait can be exercised on one GPU (such a model may only run decode steps).
  * "tc_prefill" 0/1 (default 1): prompts of 32 tokens or more run in chunks through the tensor-core matmuls;
- * "prefill_chunk" 32..4096 (default 512, fixed once a chunk has run); "prefill_attention" 1 (default) chunk
+ * "prefill_chunk" 32..4096 (default 2048, fixed once a chunk has run); "prefill_attention" 1 (default) chunk
  * attention on the tensor cores, 0 the decode kernels' exact running-maximum chain; "prefix_cache" 0/1.
  * "persistent" 0/1/2: decode steps of MoE models run in one persistent cooperative kernel with grid
  * barriers between phases: 0 never, 1 for one stream (default: with more streams the per-op kernels are

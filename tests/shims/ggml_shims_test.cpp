@@ -95,7 +95,7 @@ static bool all_equal(const std::vector<float>& a, float v) {
 
 static void test_gemv(dc_ctx* ctx) {
     for (int type : {(int)GGML_TYPE_Q4_K, (int)GGML_TYPE_Q6_K}) {
-        for (int M : {1, 5, 19}) {
+        for (int M : {1, 5, 19, 70}) {       // 70 rows: the tensor-core kernel (a whole 64-token tile and a ragged one)
             const int64_t n_in = 2048, k_out = 1024;
             std::vector<uint8_t> w((size_t)(k_out * dco_row_bytes(type, n_in)));
             dco_synth_quantized(type, 77 + type, k_out, n_in, 0.02f, w.data());
@@ -114,14 +114,18 @@ static void test_gemv(dc_ctx* ctx) {
             check(all_equal(y, 7.0f), "gemv: threads with ith != 0 write nothing");
             run_threads(4, [&](int ith, int nth) { cb_gemv_b200(&ty, ith, nth, &ud); });
             dco_mul_mat(type, w.data(), k_out, n_in, x.data(), M, want.data(), nullptr);
-            check(memcmp(y.data(), want.data(), y.size() * 4) == 0,
-                  "gemv type " + std::to_string(type) + " M=" + std::to_string(M) + ": bit-equal to the CPU kernel");
+            // the tensor-core kernel adds one float term per Q6_K block where the CPU kernel keeps eight lane partials:
+            // equal integers, a different float order
+            const bool exact = !(M >= 32 && type == (int)GGML_TYPE_Q6_K);
+            check(exact ? memcmp(y.data(), want.data(), y.size() * 4) == 0 : max_rel(y, want) < 2e-6f,
+                  "gemv type " + std::to_string(type) + " M=" + std::to_string(M) + (exact ? ": bit-equal to the CPU kernel" : ": 2e-6 of the CPU kernel"));
             check(ud.weight != nullptr, "gemv: the weight was uploaded once and kept in the userdata");
             // second call reuses the handle
             dc_weight* kept = ud.weight;
             std::fill(y.begin(), y.end(), 3.0f);
             run_threads(4, [&](int ith, int nth) { cb_gemv_b200(&ty, ith, nth, &ud); });
-            check(ud.weight == kept && memcmp(y.data(), want.data(), y.size() * 4) == 0, "gemv: second call, same handle, same result");
+            check(ud.weight == kept && (exact ? memcmp(y.data(), want.data(), y.size() * 4) == 0 : max_rel(y, want) < 2e-6f),
+                  "gemv: second call, same handle, same result");
             // wrong output size: zero-fill, one CRITICAL line, one count
             ggml_tensor bad = ty;
             bad.ne[0] = k_out - 256;

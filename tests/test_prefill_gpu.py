@@ -64,6 +64,12 @@ def test_chunked_prefill_on_tensor_cores_matches_the_sixteen_token_path(ctx, nam
     # all_q4k: the decode kernels' exact attention chain, so that the whole chunked path is bit-comparable;
     # otherwise the default (fp16 flash attention on the tensor cores, as ggml_flash_attn_ext is on the CPU)
     m.set_option("prefill_attention", 0 if all_q4k else 1)
+    # several chunks per prompt: 64-token chunks for the bit-identity cases, 256 for the full-width model, one
+    # chunk (the default length, 2048) otherwise
+    if all_q4k:
+        m.set_option("prefill_chunk", 64)
+    elif name == "moe_full_width":
+        m.set_option("prefill_chunk", 256)
     rng = np.random.default_rng(3)
     prompt = rng.integers(0, cfg.vocab, size=n_prompt)
     res = {}
