@@ -61,6 +61,8 @@ struct GemmTcParams {
     const int* tile_expert;   // optional [n_tt]: weights of tile t start at w + tile_expert[t] * estride; < 0: tile unused
     size_t estride;
     const int* slot_row;      // optional [n_tt * 64]: output row of every slot instead of the slot itself; < 0: none
+    const int* pair_tile0;    // second kernel form, optional [grid.x]: first tile of the CTA's tile pair (< 0: none) ...
+    const int* pair_nset;     // ... and how many tiles of the pair exist (1 or 2)
     int accumulate;           // out += result (one float add) instead of out = result
     int* err;
     unsigned long long* timing;   // instrumented build only: per-CTA cycles of the loop's phases
@@ -442,6 +444,378 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
     if (warp == 0) tmem_dealloc(tmem, NCOLS);
 }
 
+
+// =====================================================================================================
+// Second form of the kernel: the three jobs of a block (expanding operand planes, issuing UMMAs, reading
+// the accumulators out) run on different warps of one CTA per SM and overlap; a CTA owns 128 rows x two
+// 64-token tiles, so that a block's planes are expanded once for 128 tokens.
+//   warps 0-3   expanders: thread r turns its row's half block into the planes of stage h (two stages)
+//   warp 4      one thread issues the UMMAs: stage h x token set th -> accumulator set th (TMEM), commits
+//               "stage free", "token codes free" and "accumulators full"
+//   warp 5      one thread loads the token tiles (codes double-buffered, block scales in a ring of four)
+//   warps 6-13  read-out: warp e owns TMEM lane quarter e % 4 of accumulator set e / 4, adds the block's float
+//               terms for its row and 64 tokens, then frees the set
+// Every wait is bounded and watches a CTA-wide give-up flag.
+constexpr int TC2_THREADS = 448;
+constexpr int TC2_EXPAND = 128;
+constexpr int TC2_SET = 64;                 // tokens per accumulator set
+
+struct Tc2Bars {       // shared addresses of the mbarriers
+    uint32_t a_full[2], a_free[2], b_full[2], b_free[2], s_full[4], d_full[4], acc_full[2], acc_free[2];
+};
+
+__device__ __forceinline__ bool tc2_wait_raw(uint32_t bar, uint32_t parity, volatile int* give_up, int* err) {
+    for (uint32_t i = 0; i < DC_WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && *give_up) return false;
+    }
+    *give_up = 1;
+    if (err) atomicExch(err, DC_ERR_MBAR_TIMEOUT);
+    return false;
+}
+#ifdef DC_TC_TIMING
+// instrumented build: cycles spent in each kind of wait, summed over one thread of every role
+__device__ unsigned long long g_tc2_wait[8];
+#define tc2_wait(bar, parity, give_up, err) tc2_wait_timed(bar, parity, give_up, err, __LINE__)
+__device__ __forceinline__ bool tc2_wait_timed(uint32_t bar, uint32_t parity, volatile int* give_up, int* err, int line) {
+    const long long t0 = clock64();
+    const bool ok = tc2_wait_raw(bar, parity, give_up, err);
+    if ((threadIdx.x & 31) == 0) atomicAdd(&g_tc2_wait[line & 7], (unsigned long long)(clock64() - t0));
+    return ok;
+}
+#else
+#define tc2_wait tc2_wait_raw
+#endif
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int TYPE>
+constexpr size_t tc2_smem_bytes() {
+    using T = TcTraits<TYPE>;
+    // planes: 2 stages; token codes: 2 buffers x 2 sets; block scales: 4 x 128 floats; row scales: 4 x 128 x 2 floats
+    return (size_t)2 * T::NP * TC_PLANE + (size_t)4 * TC_B_Q + 4 * 128 * 4 + 4 * 128 * 8 + 256;
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
+    using T = TcTraits<TYPE>;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ int s_give_up;
+    const uint32_t sA = smem_u32(smem_raw);                      // [2 stages][NP planes][16 KB]
+    const uint32_t sBq = sA + 2 * T::NP * TC_PLANE;              // [2 buffers][2 sets][16 KB]
+    const uint32_t sS = sBq + 4 * TC_B_Q;                        // [4][128] block scales of the tokens
+    const uint32_t sD = sS + 4 * 128 * 4;                        // [4][128][2] d, dmin of the rows
+    const uint32_t sBar = sD + 4 * 128 * 8;
+    Tc2Bars B;
+    {
+        uint32_t a = sBar;
+        for (int i = 0; i < 2; ++i) B.a_full[i] = a, a += 8;
+        for (int i = 0; i < 2; ++i) B.a_free[i] = a, a += 8;
+        for (int i = 0; i < 2; ++i) B.b_full[i] = a, a += 8;
+        for (int i = 0; i < 2; ++i) B.b_free[i] = a, a += 8;
+        for (int i = 0; i < 4; ++i) B.s_full[i] = a, a += 8;
+        for (int i = 0; i < 4; ++i) B.d_full[i] = a, a += 8;
+        for (int i = 0; i < 2; ++i) B.acc_full[i] = a, a += 8;
+        for (int i = 0; i < 2; ++i) B.acc_free[i] = a, a += 8;
+    }
+    const uint32_t tmem_slot = sBar + 22 * 8;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // work item: a pair of neighbouring 64-token tiles of one expert
+    int tt0, nset;
+    if (p.pair_tile0) {
+        tt0 = p.pair_tile0[blockIdx.x];
+        if (tt0 < 0) return;
+        nset = p.pair_nset[blockIdx.x];
+    } else {
+        tt0 = 2 * blockIdx.x;
+        nset = min(2, p.n_tt - tt0);
+    }
+    const int expert = p.tile_expert ? p.tile_expert[tt0] : 0;
+    if (expert < 0) return;
+    int seg = 0, rt = blockIdx.y;
+    while (seg + 1 < p.nseg && rt >= (p.seg[seg].N + TC_ROWS - 1) / TC_ROWS) {
+        rt -= (p.seg[seg].N + TC_ROWS - 1) / TC_ROWS;
+        ++seg;
+    }
+    const int N = p.seg[seg].N, row0 = rt * TC_ROWS;
+    const uint8_t* wbase = p.seg[seg].w + (size_t)expert * p.estride;
+    const int nb = p.K / DC_QK_K;
+    constexpr uint32_t NCOLS = 512;
+
+    if (warp == 4) {
+        tmem_alloc(tmem_slot, NCOLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        s_give_up = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(B.a_full[i], TC2_EXPAND);
+            mbar_init(B.a_free[i], 1);
+            mbar_init(B.b_full[i], 1);
+            mbar_init(B.b_free[i], 1);
+            mbar_init(B.acc_full[i], 1);
+            mbar_init(B.acc_free[i], 128);
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(B.s_full[i], 1);
+            mbar_init(B.d_full[i], TC2_EXPAND);
+        }
+        mbar_fence_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = lds32(tmem_slot);
+    volatile int* give_up = &s_give_up;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ expanders
+        const int r = tid;
+        const int grow = min(row0 + r, N - 1);
+        const uint8_t* rp = wbase + (size_t)grow * p.row_bytes;
+        if (TYPE == DC_TYPE_Q4_K) {
+            uint4 hdr = make_uint4(0, 0, 0, 0), q[4];
+            auto fetch = [&](int kb, int h) {
+                const uint4* b = reinterpret_cast<const uint4*>(rp + (size_t)kb * T::BB);
+                hdr = __ldg(b);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) q[i] = __ldg(b + 1 + 4 * h + i);
+            };
+            fetch(0, 0);
+            for (int kb = 0; kb < nb; ++kb) {
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 H = hdr;
+                    uint4 Q[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) Q[i] = q[i];
+                    if (h == 0) fetch(kb, 1);
+                    else if (kb + 1 < nb) fetch(kb + 1, 0);
+                    if (kb > 0 && !tc2_wait(B.a_free[h], (kb - 1) & 1, give_up, p.err)) goto done;
+                    if (h == 0) {
+                        // this row's scales for the read-out warps
+                        const uint32_t da = sD + ((kb & 3) * 128 + r) * 8;
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(da), "f"(fp16_bits_to_float((uint16_t)(H.x & 0xFFFF))),
+                                     "f"(fp16_bits_to_float((uint16_t)(H.x >> 16)))
+                                     : "memory");
+                        mbar_arrive(B.d_full[kb & 3]);
+                    }
+                    const uint32_t stage = sA + h * (T::NP * TC_PLANE) + r * 16;
+#pragma unroll
+                    for (int gl = 0; gl < 2; ++gl) {          // sub-block pairs 2h + gl of the block
+                        const int g = 2 * h + gl;
+                        uint32_t sc0, m0, sc1, m1;
+                        q4k_scale_min(H.y, H.z, H.w, 2 * g, sc0, m0);
+                        q4k_scale_min(H.y, H.z, H.w, 2 * g + 1, sc1, m1);
+                        const uint32_t mm0 = m0 * 0x01010101u, mm1 = m1 * 0x01010101u;
+                        const uint32_t a0 = sc0 >> 3, a1 = sc0 & 7u, b0 = sc1 >> 3, b1 = sc1 & 7u;
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            const uint4 qv = Q[2 * gl + hf];
+                            const uint32_t in[4] = {qv.x, qv.y, qv.z, qv.w};
+                            uint32_t lo[4], hi[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                lo[k] = in[k] & 0x0F0F0F0Fu;
+                                hi[k] = (in[k] >> 4) & 0x0F0F0F0Fu;
+                            }
+                            const uint32_t c_lo = stage + (4 * gl + hf) * (TC_ROWS * 16);
+                            const uint32_t c_hi = c_lo + 2 * (TC_ROWS * 16);
+                            sts128(c_lo, lo[0] * a0, lo[1] * a0, lo[2] * a0, lo[3] * a0);
+                            sts128(c_lo + TC_PLANE, lo[0] * a1, lo[1] * a1, lo[2] * a1, lo[3] * a1);
+                            sts128(c_lo + 2 * TC_PLANE, mm0, mm0, mm0, mm0);
+                            sts128(c_hi, hi[0] * b0, hi[1] * b0, hi[2] * b0, hi[3] * b0);
+                            sts128(c_hi + TC_PLANE, hi[0] * b1, hi[1] * b1, hi[2] * b1, hi[3] * b1);
+                            sts128(c_hi + 2 * TC_PLANE, mm1, mm1, mm1, mm1);
+                        }
+                    }
+                    fence_async_smem();
+                    mbar_arrive(B.a_full[h]);
+                }
+            }
+        } else {
+            // Q6_K: 210-byte blocks at 2-byte aligned addresses: aligned 32-bit loads and a funnel shift
+            uint32_t wl[17], wh[9], ws[3], wd = 0;
+            auto fetch = [&](int kb, int h) {
+                const uintptr_t a = (uintptr_t)(rp + (size_t)kb * T::BB);
+                const uint32_t* bl = reinterpret_cast<const uint32_t*>((a + 64 * h) & ~(uintptr_t)3);
+                const uint32_t* bh = reinterpret_cast<const uint32_t*>((a + 128 + 32 * h) & ~(uintptr_t)3);
+                const uint32_t* bs = reinterpret_cast<const uint32_t*>((a + 192 + 8 * h) & ~(uintptr_t)3);
+#pragma unroll
+                for (int i = 0; i < 17; ++i) wl[i] = __ldg(bl + i);
+#pragma unroll
+                for (int i = 0; i < 9; ++i) wh[i] = __ldg(bh + i);
+#pragma unroll
+                for (int i = 0; i < 3; ++i) ws[i] = __ldg(bs + i);
+                wd = __ldg(reinterpret_cast<const uint32_t*>((a + 208) & ~(uintptr_t)3));
+            };
+            fetch(0, 0);
+            for (int kb = 0; kb < nb; ++kb) {
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h) {
+                    const uintptr_t a = (uintptr_t)(rp + (size_t)kb * T::BB);
+                    const uint32_t sh = (uint32_t)(a & 2u) * 8u;       // every field of the block shares the 2-byte phase
+                    uint32_t ql[16], qh[8], scw[2];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) ql[i] = __funnelshift_r(wl[i], wl[i + 1], sh);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) qh[i] = __funnelshift_r(wh[i], wh[i + 1], sh);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) scw[i] = __funnelshift_r(ws[i], ws[i + 1], sh);
+                    const float d = fp16_bits_to_float((uint16_t)((wd >> sh) & 0xFFFFu));
+                    if (h == 0) fetch(kb, 1);
+                    else if (kb + 1 < nb) fetch(kb + 1, 0);
+                    if (kb > 0 && !tc2_wait(B.a_free[h], (kb - 1) & 1, give_up, p.err)) goto done;
+                    if (h == 0) {
+                        const uint32_t da = sD + ((kb & 3) * 128 + r) * 8;
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(da), "f"(d), "f"(0.0f) : "memory");
+                        mbar_arrive(B.d_full[kb & 3]);
+                    }
+                    const uint32_t stage = sA + h * (T::NP * TC_PLANE) + r * 16;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {                       // chunk i of the half: quadrant i / 2, words 4 (i & 1)..
+                        const int qd = i >> 1, w0 = 4 * (i & 1);
+                        const int sc = (int)(int8_t)((scw[i >> 2] >> (8 * (i & 3))) & 0xFFu);
+                        const uint32_t mag = (uint32_t)(sc < 0 ? -sc : sc);
+                        uint32_t u[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            u[k] = ((ql[8 * (qd & 1) + w0 + k] >> (4 * (qd >> 1))) & 0x0F0F0F0Fu) |
+                                   (((qh[w0 + k] >> (2 * qd)) & 0x03030303u) << 4);
+#pragma unroll
+                        for (int di = 0; di < 4; ++di) {
+                            const uint32_t dg = (mag >> (2 * di)) & 3u;
+                            uint32_t v[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                v[k] = __vsub4(u[k] * dg, dg * 0x20202020u);
+                                if (sc < 0) v[k] = __vneg4(v[k]);
+                            }
+                            sts128(stage + i * (TC_ROWS * 16) + di * TC_PLANE, v[0], v[1], v[2], v[3]);
+                        }
+                    }
+                    fence_async_smem();
+                    mbar_arrive(B.a_full[h]);
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ------------------------------------------------------------------ UMMA issue
+        if (lane == 0) {
+            constexpr uint32_t IDESC = umma_idesc_i8(T::A_SIGNED, TC_ROWS, TC2_SET);
+            for (int kb = 0; kb < nb; ++kb) {
+                if (!tc2_wait(B.b_full[kb & 1], (kb >> 1) & 1, give_up, p.err)) break;
+                const uint32_t sBcur = sBq + (kb & 1) * (2 * TC_B_Q);
+                bool ok = true;
+                for (int h = 0; h < 2 && ok; ++h) {
+                    if (!tc2_wait(B.a_full[h], kb & 1, give_up, p.err)) { ok = false; break; }
+                    tc_fence_after();
+                    for (int th = 0; th < nset; ++th) {
+                        // the read-out of the previous block must have drained this accumulator set
+                        if (h == 0 && kb > 0 && !tc2_wait(B.acc_free[th], (kb - 1) & 1, give_up, p.err)) { ok = false; break; }
+                        tc_fence_after();
+#pragma unroll
+                        for (int pl = 0; pl < T::NP; ++pl)
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk)
+                                umma_i8(tmem + (th * T::NP + pl) * TC2_SET,
+                                        umma_desc(sA + h * (T::NP * TC_PLANE) + pl * TC_PLANE + kk * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128),
+                                        umma_desc(sBcur + th * TC_B_Q + (8 * h + 2 * kk) * (TC2_SET * 16), TC2_SET * 16, 128), IDESC,
+                                        (h | kk) ? 1u : 0u);
+                        if (h == 1) umma_commit(B.acc_full[th]);
+                    }
+                    umma_commit(B.a_free[h]);
+                }
+                if (!ok) break;
+                umma_commit(B.b_free[kb & 1]);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ token tiles
+        if (lane == 0) {
+            for (int kb = 0; kb < nb; ++kb) {
+                if (kb >= 2 && !tc2_wait(B.b_free[kb & 1], ((kb - 2) >> 1) & 1, give_up, p.err)) break;
+                const uint8_t* src = p.act + ((size_t)kb * p.n_tt + tt0) * TC_ACT_TILE;
+                mbar_expect_tx(B.b_full[kb & 1], (uint32_t)nset * TC_B_Q);
+                mbar_expect_tx(B.s_full[kb & 3], (uint32_t)nset * TC2_SET * 4);
+                for (int th = 0; th < nset; ++th) {
+                    bulk_g2s(sBq + ((kb & 1) * 2 + th) * TC_B_Q, src + (size_t)th * TC_ACT_TILE, TC_B_Q, B.b_full[kb & 1]);
+                    bulk_g2s(sS + ((kb & 3) * 128 + th * TC2_SET) * 4, src + (size_t)th * TC_ACT_TILE + TC_B_Q, TC2_SET * 4, B.s_full[kb & 3]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ read-out
+        // a warp reaches the TMEM lanes 32 (warp index % 4) .. + 31: warps 6..9 read set 0, warps 10..13 set 1
+        const int q = warp & 3, th = (warp - 6) >> 2;
+        if (th < nset) {
+            float sumf[TC2_SET];
+#pragma unroll
+            for (int i = 0; i < TC2_SET; ++i) sumf[i] = 0.0f;
+            const uint32_t t_lane = tmem + ((uint32_t)(32 * q) << 16) + th * T::NP * TC2_SET;
+            const int r = 32 * q + lane;
+            bool ok = true;
+            for (int kb = 0; kb < nb && ok; ++kb) {
+                if (!tc2_wait(B.d_full[kb & 3], (kb >> 2) & 1, give_up, p.err) ||
+                    !tc2_wait(B.s_full[kb & 3], (kb >> 2) & 1, give_up, p.err) ||
+                    !tc2_wait(B.acc_full[th], kb & 1, give_up, p.err)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint2 dd = lds64(sD + ((kb & 3) * 128 + r) * 8);
+                const float d = __uint_as_float(dd.x), dmin = __uint_as_float(dd.y);
+                const uint32_t yd_base = sS + ((kb & 3) * 128 + th * TC2_SET) * 4;
+#pragma unroll
+                for (int piece = 0; piece < TC2_SET / 16; ++piece) {
+                    int a0[16], a1[16], a2[16], a3[16];
+                    tmem_ld16(t_lane + 16 * piece, a0);
+                    tmem_ld16(t_lane + TC2_SET + 16 * piece, a1);
+                    tmem_ld16(t_lane + 2 * TC2_SET + 16 * piece, a2);
+                    if (T::NP == 4) tmem_ld16(t_lane + 3 * TC2_SET + 16 * piece, a3);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float yd = __uint_as_float(lds32(yd_base + 4 * (16 * piece + i)));
+                        float& s = sumf[16 * piece + i];
+                        if (TYPE == DC_TYPE_Q4_K) {
+                            const int I = 8 * a0[i] + a1[i];
+                            const float tI = __fmul_rn(__fmul_rn(d, yd), (float)I);
+                            const float tM = __fmul_rn(__fmul_rn(dmin, yd), (float)a2[i]);
+                            s = __fsub_rn(__fadd_rn(s, tI), tM);
+                        } else {
+                            const int I = a0[i] + 4 * a1[i] + 16 * a2[i] + 64 * a3[i];
+                            s = __fadd_rn(s, __fmul_rn(__fmul_rn(d, yd), (float)I));
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(B.acc_free[th]);
+            }
+            if (ok) {
+                const int row = row0 + r;
+                if (row < N) {
+                    float* out = p.out + p.seg[seg].out_off;
+#pragma unroll
+                    for (int i = 0; i < TC2_SET; ++i) {
+                        const int slot = (tt0 + th) * TC_NTOK + i;
+                        if (slot >= p.n_slots) continue;
+                        const int orow = p.slot_row ? p.slot_row[slot] : slot;
+                        if (orow < 0) continue;
+                        float* o = out + (size_t)orow * p.ldo + row;
+                        *o = p.accumulate ? __fadd_rn(*o, sumf[i]) : sumf[i];
+                    }
+                }
+            }
+        }
+    }
+done:
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem, NCOLS);
+}
+
 }  // namespace dc
 
 using namespace dc;
@@ -475,7 +849,8 @@ bool dc_gemm_tc_supports(const dc_weight* w) {
 // Up to three matrices of one shape family (same type, K and row bytes: Q | K | V, or gate | up) in one launch;
 // matrix i writes its rows to columns out_off[i].. of out.
 int dc_launch_gemm_tc_multi(dc_ctx* ctx, const dc_weight* const* ws, const int* out_off, int nseg, const uint8_t* act,
-                            int n_slots, float* out, int ldo, const int* tile_expert, const int* slot_row, bool accumulate) {
+                            int n_slots, float* out, int ldo, const int* tile_expert, const int* slot_row, bool accumulate,
+                            const int* pair_tile0, const int* pair_nset, int n_pairs) {
     if (nseg < 1 || nseg > 3) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemm_tc: %d matrices", nseg);
     const dc_weight* w = ws[0];
     GemmTcParams p = {};
@@ -515,6 +890,22 @@ int dc_launch_gemm_tc_multi(dc_ctx* ctx, const dc_weight* const* ws, const int* 
         }
     }
 #endif
+    if (ctx->gemm_tc_form == 2 && (!tile_expert || pair_tile0)) {
+        // one CTA per SM with separate warps for expansion, issue and read-out, two token tiles per CTA
+        p.pair_tile0 = pair_tile0;
+        p.pair_nset = pair_nset;
+        const dim3 grid2(pair_tile0 ? n_pairs : (p.n_tt + 1) / 2, row_tiles);
+        if (w->type == DC_TYPE_Q4_K) {
+            constexpr size_t smem = tc2_smem_bytes<DC_TYPE_Q4_K>();
+            DC_TRY(dc_kernel_setup(ctx, (const void*)k_gemm_tc2<DC_TYPE_Q4_K>, smem, "k_gemm_tc2<Q4_K>"));
+            k_gemm_tc2<DC_TYPE_Q4_K><<<grid2, TC2_THREADS, smem, ctx->stream>>>(p);
+        } else {
+            constexpr size_t smem = tc2_smem_bytes<DC_TYPE_Q6_K>();
+            DC_TRY(dc_kernel_setup(ctx, (const void*)k_gemm_tc2<DC_TYPE_Q6_K>, smem, "k_gemm_tc2<Q6_K>"));
+            k_gemm_tc2<DC_TYPE_Q6_K><<<grid2, TC2_THREADS, smem, ctx->stream>>>(p);
+        }
+        return dc_check_cuda(ctx, cudaGetLastError(), "k_gemm_tc2");
+    }
     const dim3 grid(p.n_tt, row_tiles);
     if (w->type == DC_TYPE_Q4_K) {
         constexpr size_t smem = tc_smem_bytes<DC_TYPE_Q4_K>();
@@ -529,6 +920,10 @@ int dc_launch_gemm_tc_multi(dc_ctx* ctx, const dc_weight* const* ws, const int* 
 }
 
 int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
-                      const int* tile_expert, const int* slot_row, bool accumulate) {
-    return dc_launch_gemm_tc_multi(ctx, &w, nullptr, 1, act, n_slots, out, ldo, tile_expert, slot_row, accumulate);
+                      const int* tile_expert, const int* slot_row, bool accumulate, const int* pair_tile0, const int* pair_nset,
+                      int n_pairs) {
+    if (pair_tile0)
+        return dc_launch_gemm_tc_multi(ctx, &w, nullptr, 1, act, n_slots, out, ldo, tile_expert, slot_row, accumulate, pair_tile0,
+                                       pair_nset, n_pairs);
+    return dc_launch_gemm_tc_multi(ctx, &w, nullptr, 1, act, n_slots, out, ldo, tile_expert, slot_row, accumulate, nullptr, nullptr, 0);
 }

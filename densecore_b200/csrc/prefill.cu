@@ -31,7 +31,7 @@ struct dc_prefill_buffers {
     float *x = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *g = nullptr,
           *dn = nullptr, *moe_out = nullptr, *logits = nullptr, *weights = nullptr;
     int32_t* ids = nullptr;
-    int32_t *slot_assign = nullptr, *slot_token = nullptr, *tile_expert = nullptr;
+    int32_t *slot_assign = nullptr, *slot_token = nullptr, *tile_expert = nullptr, *pair_tile0 = nullptr, *pair_nset = nullptr;
     uint8_t *act_x = nullptr, *act_att = nullptr, *act_moe = nullptr, *act_h = nullptr, *attn_mem = nullptr;
     dc_attn_scratch attn = {};
     int32_t* h_stage = nullptr;   // pinned: ring of (tokens, seq ids, positions) triples
@@ -92,6 +92,8 @@ static int prefill_prepare(dc_model* m) {
         A_(pf_alloc(m, &P->slot_assign, slots));
         A_(pf_alloc(m, &P->slot_token, slots));
         A_(pf_alloc(m, &P->tile_expert, (size_t)P->max_tiles));
+        A_(pf_alloc(m, &P->pair_tile0, (size_t)P->max_tiles));
+        A_(pf_alloc(m, &P->pair_nset, (size_t)P->max_tiles));
         A_(pf_alloc(m, &P->act_moe, dc_gemm_tc_act_bytes((int)slots, (int)H)));
     }
     if (st == DC_B200_OK) st = dc_check_cuda(m->ctx, cudaMallocHost((void**)&P->h_stage, PF_STAGE_SLOTS * 3 * C * 4), "cudaMallocHost");
@@ -106,8 +108,9 @@ static int prefill_prepare(dc_model* m) {
 // assignment order through slot_assign).  One CTA.
 __global__ void __launch_bounds__(1024) k_moe_group(const int32_t* __restrict__ ids, int A, int top_k, int E, int max_tiles,
                                                     int ep_lo, int ep_hi, int32_t* __restrict__ slot_assign,
-                                                    int32_t* __restrict__ slot_token, int32_t* __restrict__ tile_expert) {
-    __shared__ int s_cnt[256], s_off[256], s_fill[256], s_total;
+                                                    int32_t* __restrict__ slot_token, int32_t* __restrict__ tile_expert,
+                                                    int32_t* __restrict__ pair_tile0, int32_t* __restrict__ pair_nset) {
+    __shared__ int s_cnt[256], s_off[256], s_fill[256], s_total, s_pairs;
     const int tid = threadIdx.x;
     if (tid < 256) s_cnt[tid] = s_fill[tid] = 0;
     __syncthreads();
@@ -123,6 +126,15 @@ __global__ void __launch_bounds__(1024) k_moe_group(const int32_t* __restrict__ 
         const int local = (tid >= ep_lo && tid < ep_hi) ? tid - ep_lo : -1;
         for (int t = 0; t < tiles; ++t) tile_expert[off + t] = local;
         if (tid == 255) s_total = off + tiles;
+        // pairs of neighbouring tiles of one expert (the work items of the matmul kernel's second form)
+        int poff = 0;
+        for (int i = 0; i < tid; ++i) poff += ((s_cnt[i] + 63) / 64 + 1) / 2;
+        const int pairs = (tiles + 1) / 2;
+        for (int j = 0; j < pairs; ++j) {
+            pair_tile0[poff + j] = local >= 0 ? off + 2 * j : -1;
+            pair_nset[poff + j] = min(2, tiles - 2 * j);
+        }
+        if (tid == 255) s_pairs = poff + pairs;
     }
     for (int sl = tid; sl < max_tiles * 64; sl += blockDim.x) {
         slot_assign[sl] = -1;
@@ -130,6 +142,7 @@ __global__ void __launch_bounds__(1024) k_moe_group(const int32_t* __restrict__ 
     }
     __syncthreads();
     for (int t = s_total + tid; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+    for (int t = s_pairs + tid; t < max_tiles; t += blockDim.x) pair_tile0[t] = -1;
     for (int i = tid; i < A; i += blockDim.x) {
         const int e = ids[i];
         const int slot = s_off[e] * 64 + atomicAdd(&s_fill[e], 1);
@@ -270,7 +283,7 @@ int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool
             const int A = n * top_k, F = c.expert_ffn;
             DC_TRY(dc_launch_router_batched(ctx, Ly.router, P.xn, n, top_k, c.routed_scale, P.logits, P.ids, P.weights, m->route_mode));
             k_moe_group<<<1, 1024, 0, ctx->stream>>>(P.ids, A, top_k, E, P.max_tiles, m->ep_lo, m->ep_hi, P.slot_assign, P.slot_token,
-                                                     P.tile_expert);
+                                                     P.tile_expert, P.pair_tile0, P.pair_nset);
             DC_TRY(dc_check_cuda(ctx, cudaGetLastError(), "k_moe_group"));
             const int slots = P.max_tiles * 64;
             DC_TRY(dc_launch_quantize_q8k_tiled(ctx, P.xn, H, n, H, P.act_moe, P.max_tiles, P.slot_token));
@@ -278,13 +291,17 @@ int dc_prefill_chunk_tc(dc_model* m, int seq, const int32_t* tokens, int n, bool
                 // gate | up in one launch: g and u are one buffer of 2 F columns per slot (gate first)
                 const dc_weight* ws[2] = {Ly.gate_exps, Ly.up_exps};
                 const int offs[2] = {0, F};
-                DC_TRY(dc_launch_gemm_tc_multi(ctx, ws, offs, 2, P.act_moe, slots, P.g, 2 * F, P.tile_expert));
+                DC_TRY(dc_launch_gemm_tc_multi(ctx, ws, offs, 2, P.act_moe, slots, P.g, 2 * F, P.tile_expert, nullptr, false, P.pair_tile0,
+                                               P.pair_nset, P.max_tiles));
             } else {
-                DC_TRY(dc_launch_gemm_tc(ctx, Ly.gate_exps, P.act_moe, slots, P.g, 2 * F, P.tile_expert));
-                DC_TRY(dc_launch_gemm_tc(ctx, Ly.up_exps, P.act_moe, slots, P.g + F, 2 * F, P.tile_expert));
+                DC_TRY(dc_launch_gemm_tc(ctx, Ly.gate_exps, P.act_moe, slots, P.g, 2 * F, P.tile_expert, nullptr, false, P.pair_tile0,
+                                         P.pair_nset, P.max_tiles));
+                DC_TRY(dc_launch_gemm_tc(ctx, Ly.up_exps, P.act_moe, slots, P.g + F, 2 * F, P.tile_expert, nullptr, false, P.pair_tile0,
+                                         P.pair_nset, P.max_tiles));
             }
             DC_TRY(launch_swiglu(ctx, P.g, P.g + F, 2 * F, F, slots, P.act_h, P.max_tiles, P.slot_assign));
-            DC_TRY(dc_launch_gemm_tc(ctx, Ly.down_exps, P.act_h, slots, P.dn, H, P.tile_expert, P.slot_assign));
+            DC_TRY(dc_launch_gemm_tc(ctx, Ly.down_exps, P.act_h, slots, P.dn, H, P.tile_expert, P.slot_assign, false, P.pair_tile0,
+                                     P.pair_nset, P.max_tiles));
             DC_TRY(dc_launch_moe_combine(ctx, P.dn, P.ids, P.weights, n, top_k, H, m->ep_lo, m->ep_hi, P.moe_out));
             if (c.ep_size > 1) DC_TRY(dc_ep_allreduce(m, P.moe_out, (size_t)n * H));
             pending = P.moe_out;
