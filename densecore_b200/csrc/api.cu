@@ -177,11 +177,6 @@ int dc_b200_set_option(dc_ctx* ctx, const char* name, int value) {
         ctx->route_mode = value;
         return DC_B200_OK;
     }
-    if (!strcmp(name, "gemm_tc_form")) {
-        if (value != 1 && value != 2) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemm_tc_form must be 1 or 2");
-        ctx->gemm_tc_form = value;
-        return DC_B200_OK;
-    }
     if (!strcmp(name, "gemm_tc_min_rows")) {   // 0 or less: never (every MUL_MAT runs the row-streaming kernels)
         ctx->gemm_tc_min_rows = value > 0 ? value : 0x7fffffff;
         return DC_B200_OK;

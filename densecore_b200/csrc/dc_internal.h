@@ -28,7 +28,6 @@ struct dc_ctx {
     int num_sms = 148;
     cudaStream_t stream = nullptr;
     int* d_err = nullptr;          // device error word (bounded waits report here)
-    int gemm_tc_form = 2;          // option "gemm_tc_form": 1 two small CTAs per SM, 2 one CTA with specialised warps
     int gemm_tc_min_rows = 32;     // option "gemm_tc_min_rows": token rows from which MUL_MAT runs on the tensor cores
     std::string last_error;
     std::mutex mu;
@@ -80,8 +79,8 @@ int dc_gemm_tc_tiles(int n_slots);
 bool dc_gemm_tc_supports(const dc_weight* w);
 int dc_launch_quantize_q8k_tiled(dc_ctx* ctx, const float* x, int ldx, int n_rows, int K, uint8_t* act, int n_tt,
                                  const int* slot_token);
-// pair_tile0 / pair_nset (device, n_pairs entries; grouped expert matmuls of the second kernel form): the tile
-// pairs of one expert that a CTA works on
+// pair_tile0 / pair_nset (device, n_pairs entries; needed with tile_expert): the pairs of neighbouring tiles of
+// one expert that a CTA works on
 int dc_launch_gemm_tc(dc_ctx* ctx, const dc_weight* w, const uint8_t* act, int n_slots, float* out, int ldo,
                       const int* tile_expert = nullptr, const int* slot_row = nullptr, bool accumulate = false,
                       const int* pair_tile0 = nullptr, const int* pair_nset = nullptr, int n_pairs = 0);

@@ -4,20 +4,21 @@
 // (core/src/llm/matmul/batched_exec.cpp:1040-1240 serves these shapes on the CPU; per block
 // sumf += (d*yd)*float(I); sumf -= (dmin*yd)*float(M), core/src/kernels/hwy/hwy_moe_quant.cc:248-253).
 //
-// One CTA owns 128 weight rows x 64 tokens over the whole reduction length.  Per 256-value block:
-//   1. the block's raw bytes of the 128 rows arrive by per-row bulk copies (mbarrier, no multicast);
-//   2. the threads expand them into 8-bit operand planes in shared memory, in the K-major core-matrix
-//      layout the tensor core reads (8 rows x 16 bytes per core matrix):
+// One CTA per SM owns 128 weight rows x two 64-token tiles over the whole reduction length; its warps split
+// the three jobs of a 256-value block and overlap them (see k_gemm_tc below):
+//   1. expanders turn the raw quants of the 128 rows into 8-bit operand planes in shared memory, K-major rows
+//      of 128 bytes with the 128-byte swizzle the tensor core reads at full rate (a half block is exactly one
+//      such row):
 //        Q4_K: q4 * (sc >> 3), q4 * (sc & 7) and the sub-block minimum m broadcast (3 planes, unsigned),
 //              so that I = 8 * acc0 + acc1 = sum sc_j * sum q4*q8 and M = acc2 = sum m_j * sum q8;
 //        Q6_K: sign(sc) * digit_i(|sc|) * (q6 - 32) for the four base-4 digits of |sc| (4 planes, signed),
 //              so that I = acc0 + 4 acc1 + 16 acc2 + 64 acc3;
 //      every plane entry fits 8 bits and the 32-bit accumulators are exact;
-//   3. one thread issues the UMMAs (128 x 64 x 32 each), two halves of 128 values per block;
-//   4. all threads read the accumulators back (tcgen05.ld) and add the block's float terms in block order.
+//   2. one thread issues the UMMAs (128 rows x 128 tokens x 32 values each), two halves of 128 values per block;
+//   3. read-out warps fetch the accumulators (tcgen05.ld) and add the block's float terms in block order.
 // The token side is prepared once per activation matrix by k_quantize_q8k_tiled: the Q8_K codes of every
-// (block, 64-token tile) stored as the B operand's core matrices, followed by the 64 block scales, so that
-// a tile is one contiguous bulk copy.
+// (block, 64-token tile) stored as the B operand (two halves of 64 swizzled 128-byte rows), followed by the
+// 64 block scales, so that a tile half is one contiguous bulk copy.  No multicast load anywhere.
 //
 // Q4_K results are bit-equal to the GEMV path and the CPU oracle.  Q6_K adds one float term per block
 // instead of the CPU small-batch kernel's eight lane partials (q6_small_batch.h:62-103): equal integers,
@@ -26,6 +27,7 @@
 #include <cstdlib>
 
 #include "dc_common.cuh"
+#include "dc_gemm_tc.h"
 #include "dc_internal.h"
 
 #define DC_TRY(expr)                       \
@@ -37,11 +39,7 @@
 namespace dc {
 
 constexpr int TC_ROWS = 128;
-constexpr int TC_NTOK = 64;
-constexpr int TC_THREADS = 256;
-constexpr int TC_PLANE = 8 * TC_ROWS * 16;            // 8 K-chunks of 16 bytes for 128 rows: one half block
-constexpr int TC_B_Q = 16 * TC_NTOK * 16;             // codes of one (block, token tile): 16 K-chunks
-constexpr int TC_ACT_TILE = TC_B_Q + TC_NTOK * 4;     // + the tile's 64 block scales
+constexpr int TC_PLANE = TC_ROWS * 128;               // one operand plane of a half block: 128 rows of 128 bytes
 
 struct GemmTcSeg {
     const uint8_t* w;      // rows of the matrix (expert 0)
@@ -61,11 +59,10 @@ struct GemmTcParams {
     const int* tile_expert;   // optional [n_tt]: weights of tile t start at w + tile_expert[t] * estride; < 0: tile unused
     size_t estride;
     const int* slot_row;      // optional [n_tt * 64]: output row of every slot instead of the slot itself; < 0: none
-    const int* pair_tile0;    // second kernel form, optional [grid.x]: first tile of the CTA's tile pair (< 0: none) ...
-    const int* pair_nset;     // ... and how many tiles of the pair exist (1 or 2)
+    const int* pair_tile0;    // optional [grid.x]: first tile of the CTA's pair of neighbouring tiles (< 0: none) ...
+    const int* pair_nset;     // ... and how many tiles of the pair exist (1 or 2); without it CTA i owns tiles 2i, 2i + 1
     int accumulate;           // out += result (one float add) instead of out = result
     int* err;
-    unsigned long long* timing;   // instrumented build only: per-CTA cycles of the loop's phases
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------------
@@ -90,11 +87,12 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// Shared-memory operand descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes (128 contiguous
-// bytes); lbo = byte distance between the two 16-byte K-chunks of one instruction, sbo = between 8-row groups.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (((lbo >> 4) & 0x3FFFu) << 16);
-    const uint32_t hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14);   // descriptor version 1 (sm_100)
+// Shared-memory operand descriptor, K-major rows of 128 bytes with the 128-byte swizzle (8-row groups of 1024
+// bytes, 1024-byte aligned; chunk c of row r at chunk position c ^ (r % 8)).  saddr = the tile's base plus the
+// K offset of the instruction in bytes (32 per K-step); sbo = byte distance between 8-row groups.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr, uint32_t sbo) {
+    const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (1u << 16);                 // leading byte offset: unused with a swizzle
+    const uint32_t hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);      // version 1 (sm_100), SWIZZLE_128B
     return ((uint64_t)hi << 32) | lo;
 }
 // Instruction descriptor: int32 accumulate, A unsigned or signed 8-bit, B signed 8-bit, both K-major.
@@ -117,8 +115,8 @@ __device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint3
 
 // ---- activation side ---------------------------------------------------------------------------------
 // One warp per (token slot, 256-value block): Q8_K codes (bit-equal to the row quantiser) into the tile
-// layout [K-chunk c 0..15][slot % 64][16 bytes], block scale into the tile's tail.  slot_token (optional)
-// maps a slot to its source row, < 0 or beyond n_rows: the slot holds zeros.
+// layout of dc_gemm_tc.h, block scale into the tile's tail.  slot_token (optional) maps a slot to its source
+// row, < 0 or beyond n_rows: the slot holds zeros.
 __global__ void __launch_bounds__(256) k_quantize_q8k_tiled(const float* __restrict__ x, int ldx, int n_rows, int K,
                                                             uint8_t* __restrict__ act, int n_tt,
                                                             const int* __restrict__ slot_token) {
@@ -139,8 +137,7 @@ __global__ void __launch_bounds__(256) k_quantize_q8k_tiled(const float* __restr
             const float v[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
             q8k_block_core(v, lane, w0, w1, bw, d);
         }
-        uint2* dst = reinterpret_cast<uint2*>(tile + (lane >> 1) * (TC_NTOK * 16) + (slot % TC_NTOK) * 16 + 8 * (lane & 1));
-        *dst = make_uint2(w0, w1);
+        *reinterpret_cast<uint2*>(tile + tc_act_code_offset(slot % TC_NTOK, lane)) = make_uint2(w0, w1);
         if (lane == 0) reinterpret_cast<float*>(tile + TC_B_Q)[slot % TC_NTOK] = d;
     }
 }
@@ -150,22 +147,12 @@ template <int TYPE>
 struct TcTraits;
 template <>
 struct TcTraits<DC_TYPE_Q4_K> {
-    // rows are 16-byte aligned: every thread fetches its share of a block straight from global memory into
-    // registers one half block ahead; the token tile is double-buffered
-    static constexpr int NP = 3, BB = DC_Q4K_BYTES, RB = 0, NB = 2, A_SIGNED = 0;
+    static constexpr int NP = 3, BB = DC_Q4K_BYTES, A_SIGNED = 0;
 };
 template <>
 struct TcTraits<DC_TYPE_Q6_K> {
-    // 210-byte blocks are only 2-byte aligned: a block of the 128 rows is staged by per-row bulk copies
-    // (rounded out to 16-byte boundaries); one token-tile buffer, refilled as soon as the block's UMMAs are done
-    static constexpr int NP = 4, BB = DC_Q6K_BYTES, RB = 240, NB = 1, A_SIGNED = 1;
+    static constexpr int NP = 4, BB = DC_Q6K_BYTES, A_SIGNED = 1;
 };
-
-template <int TYPE>
-constexpr size_t tc_smem_bytes() {
-    using T = TcTraits<TYPE>;
-    return (size_t)T::NP * TC_PLANE + (size_t)T::NB * TC_B_Q + 2 * TC_NTOK * 4 + (size_t)TC_ROWS * T::RB + 64;
-}
 
 __device__ __forceinline__ void q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, uint32_t& sc, uint32_t& m) {
     // 12 packed bytes -> the 6-bit scale and minimum of sub-block j (get_scale_min_k4 of ggml's K-quants)
@@ -180,291 +167,28 @@ __device__ __forceinline__ void q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t
     }
 }
 
-template <int TYPE>
-__global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(GemmTcParams p) {
-    using T = TcTraits<TYPE>;
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    const uint32_t sA = smem_u32(smem_raw);
-    const uint32_t sBq = sA + T::NP * TC_PLANE;                  // NB buffers of token codes
-    const uint32_t sBd = sBq + T::NB * TC_B_Q;                   // two buffers of the tile's 64 block scales
-    const uint32_t sRaw = sBd + 2 * TC_NTOK * 4;
-    const uint32_t sBar = sRaw + TC_ROWS * T::RB;                // b[0], b[1], raw, mma (8 bytes each), tmem slot
-    const uint32_t bar_b0 = sBar, bar_raw = sBar + 16, bar_mma = sBar + 24, tmem_slot = sBar + 32;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tt = blockIdx.x;
-    const int expert = p.tile_expert ? p.tile_expert[tt] : 0;
-    if (expert < 0) return;                                      // the whole CTA: a tile no expert uses
-    // the matrix (segment) and row tile of this CTA
-    int seg = 0, rt = blockIdx.y;
-    while (seg + 1 < p.nseg && rt >= (p.seg[seg].N + TC_ROWS - 1) / TC_ROWS) {
-        rt -= (p.seg[seg].N + TC_ROWS - 1) / TC_ROWS;
-        ++seg;
-    }
-    const int N = p.seg[seg].N, row0 = rt * TC_ROWS;
-    const uint8_t* wbase = p.seg[seg].w + (size_t)expert * p.estride;
-    const int nb = p.K / DC_QK_K;
-    constexpr uint32_t NCOLS = 256;                              // NP x 64 accumulator columns, power of two
-
-    if (warp == 0) {
-        tmem_alloc(tmem_slot, NCOLS);
-        tmem_relinquish();
-    }
-    if (tid == 0) {
-        mbar_init(bar_b0, 1);
-        mbar_init(bar_b0 + 8, 1);
-        mbar_init(bar_raw, 4);
-        mbar_init(bar_mma, 1);
-        mbar_fence_init();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = lds32(tmem_slot);
-
-    // every thread expands row tid % 128 (threads 0..127 also fetch it where blocks are staged)
-    const int r = tid & (TC_ROWS - 1), part = tid >> 7;
-    const int grow = min(row0 + r, N - 1);
-    const uint8_t* rp = wbase + (size_t)grow * p.row_bytes;
-
-    auto issue_raw = [&](int kb) {                // Q6_K: warps 0..3, all lanes
-        const uintptr_t a = (uintptr_t)(rp + (size_t)kb * T::BB);
-        const uint32_t skew = (uint32_t)(a & 15u);
-        const uint32_t bytes = (skew + T::BB + 15u) & ~15u;
-        const uint32_t sum = __reduce_add_sync(0xffffffffu, bytes);
-        if (lane == 0) mbar_expect_tx(bar_raw, sum);
-        __syncwarp();
-        bulk_g2s(sRaw + r * T::RB, (const void*)(a - skew), bytes, bar_raw);
-    };
-    auto issue_b = [&](int kb) {                  // one thread: codes and scales of token tile (kb, tt)
-        const uint8_t* src = p.act + ((size_t)kb * p.n_tt + tt) * TC_ACT_TILE;
-        const uint32_t bar = bar_b0 + 8 * (kb & 1);
-        mbar_expect_tx(bar, TC_ACT_TILE);
-        bulk_g2s(sBq + (T::NB == 2 ? (kb & 1) : 0) * TC_B_Q, src, TC_B_Q, bar);
-        bulk_g2s(sBd + (kb & 1) * (TC_NTOK * 4), src + TC_B_Q, TC_NTOK * 4, bar);
-    };
-    // Q4_K: this thread's share of half block (kb, h): the 16-byte header (d, dmin, packed scales) and the 32
-    // bytes of quants of sub-block pair g = 2 h + part
-    uint4 nx_hdr = make_uint4(0, 0, 0, 0), nx_q0 = nx_hdr, nx_q1 = nx_hdr;
-    auto fetch_q4 = [&](int kb, int h) {
-        const uint4* b = reinterpret_cast<const uint4*>(rp + (size_t)kb * T::BB);
-        const int g = 2 * h + part;
-        nx_hdr = __ldg(b);
-        nx_q0 = __ldg(b + 1 + 2 * g);
-        nx_q1 = __ldg(b + 2 + 2 * g);
-    };
-
-    if (TYPE == DC_TYPE_Q4_K) fetch_q4(0, 0);
-    else if (warp < 4) issue_raw(0);
-    if (tid == 128) issue_b(0);
-
-    constexpr uint32_t IDESC = umma_idesc_i8(T::A_SIGNED, TC_ROWS, TC_NTOK);
-    float sumf[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) sumf[i] = 0.0f;
-    uint32_t ph_raw = 0, ph_b[2] = {0, 0}, ph_mma = 0;
-    bool failed = false;
-    const int q = warp & 3, ch = warp >> 2;       // TMEM lane quarter of this warp, column half of the tile
-    const uint32_t t_lane = tmem + ((uint32_t)(32 * q) << 16) + 32 * ch;
-
-#ifdef DC_TC_TIMING
-    long long tc_t[6] = {0, 0, 0, 0, 0, 0}, tc_last = clock64();
-#define TC_MARK(i)                       \
-    do {                                 \
-        const long long now_ = clock64(); \
-        tc_t[i] += now_ - tc_last;       \
-        tc_last = now_;                  \
-    } while (0)
-#else
-#define TC_MARK(i)
-#endif
-    for (int kb = 0; kb < nb && !failed; ++kb) {
-        if (T::NB == 2 && kb + 1 < nb && tid == 128) issue_b(kb + 1);   // the other buffer is free since the last vote
-        const uint32_t sBcur = sBq + (T::NB == 2 ? (kb & 1) : 0) * TC_B_Q;
-        uint32_t rr = 0;
-        float d = 0.0f, dmin = 0.0f;
-        if (TYPE == DC_TYPE_Q6_K) {
-            if (!mbar_wait(bar_raw, ph_raw, p.err)) failed = true;
-            ph_raw ^= 1;
-            rr = sRaw + r * T::RB + (uint32_t)(((uintptr_t)(rp + (size_t)kb * T::BB)) & 15u);
-            d = fp16_bits_to_float((uint16_t)lds16(rr + 208));
-        }
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-            // ---- expand this row's share of the half block into the operand planes
-            if (TYPE == DC_TYPE_Q4_K) {
-                const uint4 hdr = nx_hdr, qv0 = nx_q0, qv1 = nx_q1;
-                if (h == 0) fetch_q4(kb, 1);
-                else if (kb + 1 < nb) fetch_q4(kb + 1, 0);
-                d = fp16_bits_to_float((uint16_t)(hdr.x & 0xFFFF));
-                dmin = fp16_bits_to_float((uint16_t)(hdr.x >> 16));
-                const int g = 2 * h + part;      // 64 values: sub-blocks 2g (low nibbles) and 2g + 1 (high nibbles)
-                uint32_t sc0, m0, sc1, m1;
-                q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * g, sc0, m0);
-                q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * g + 1, sc1, m1);
-                const uint32_t mm0 = m0 * 0x01010101u, mm1 = m1 * 0x01010101u;
-                const uint32_t a0 = sc0 >> 3, a1 = sc0 & 7u, b0 = sc1 >> 3, b1 = sc1 & 7u;
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const uint4 qv = hf ? qv1 : qv0;
-                    const uint32_t in[4] = {qv.x, qv.y, qv.z, qv.w};
-                    uint32_t lo[4], hi[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        lo[k] = in[k] & 0x0F0F0F0Fu;
-                        hi[k] = (in[k] >> 4) & 0x0F0F0F0Fu;
-                    }
-                    const uint32_t c_lo = sA + (4 * part + hf) * (TC_ROWS * 16) + r * 16;        // chunk of sub-block 2g
-                    const uint32_t c_hi = c_lo + 2 * (TC_ROWS * 16);                             // chunk of sub-block 2g + 1
-                    sts128(c_lo, lo[0] * a0, lo[1] * a0, lo[2] * a0, lo[3] * a0);
-                    sts128(c_lo + TC_PLANE, lo[0] * a1, lo[1] * a1, lo[2] * a1, lo[3] * a1);
-                    sts128(c_lo + 2 * TC_PLANE, mm0, mm0, mm0, mm0);
-                    sts128(c_hi, hi[0] * b0, hi[1] * b0, hi[2] * b0, hi[3] * b0);
-                    sts128(c_hi + TC_PLANE, hi[0] * b1, hi[1] * b1, hi[2] * b1, hi[3] * b1);
-                    sts128(c_hi + 2 * TC_PLANE, mm1, mm1, mm1, mm1);
-                }
-            } else {
-                // half h: ql bytes 64h.., qh bytes 32h..; this thread's four chunks are quadrants 2 part, 2 part + 1
-                uint32_t ql[16], qh[8], scw[1];
-                lds_words_a2<16>(rr + 64 * h, ql);
-                lds_words_a2<8>(rr + 128 + 32 * h, qh);
-                lds_words_a2<1>(rr + 192 + 8 * h + 4 * part, scw);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int qd = 2 * part + (i >> 1), w0 = 4 * (i & 1);
-                    const int sc = (int)(int8_t)((scw[0] >> (8 * i)) & 0xFFu);
-                    const uint32_t mag = (uint32_t)(sc < 0 ? -sc : sc);
-                    uint32_t u[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        u[k] = ((ql[8 * (qd & 1) + w0 + k] >> (4 * part)) & 0x0F0F0F0Fu) |
-                               (((qh[w0 + k] >> (2 * qd)) & 0x03030303u) << 4);
-                    const uint32_t dst = sA + (4 * part + i) * (TC_ROWS * 16) + r * 16;
-#pragma unroll
-                    for (int di = 0; di < 4; ++di) {
-                        const uint32_t dg = (mag >> (2 * di)) & 3u;
-                        uint32_t v[4];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            v[k] = __vsub4(u[k] * dg, dg * 0x20202020u);      // dg * (q6 - 32), per byte
-                            if (sc < 0) v[k] = __vneg4(v[k]);
-                        }
-                        sts128(dst + di * TC_PLANE, v[0], v[1], v[2], v[3]);
-                    }
-                }
-            }
-            fence_async_smem();
-            TC_MARK(0);      // expand
-            if (h == 0) {
-                if (!mbar_wait(bar_b0 + 8 * (kb & 1), ph_b[kb & 1], p.err)) failed = true;
-                ph_b[kb & 1] ^= 1;
-            }
-            TC_MARK(1);      // wait for the token tile
-            tc_fence_before();
-            failed = __syncthreads_or(failed);
-            if (failed) break;
-            TC_MARK(2);      // block-wide vote
-            if (TYPE == DC_TYPE_Q6_K && h == 1 && kb + 1 < nb && warp < 4) issue_raw(kb + 1);   // the raw bytes are expanded
-            if (tid == 0) {
-                tc_fence_after();
-#pragma unroll
-                for (int pl = 0; pl < T::NP; ++pl)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_i8(tmem + pl * TC_NTOK,
-                                umma_desc(sA + pl * TC_PLANE + kk * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128),
-                                umma_desc(sBcur + (8 * h + 2 * kk) * (TC_NTOK * 16), TC_NTOK * 16, 128), IDESC,
-                                (h | kk) ? 1u : 0u);
-                umma_commit(bar_mma);
-            }
-            if (!mbar_wait(bar_mma, ph_mma, p.err)) failed = true;   // (acted on at the next block-wide vote)
-            ph_mma ^= 1;
-            tc_fence_after();
-            TC_MARK(3);      // UMMA issue to completion
-        }
-        if (failed) break;
-        // single code buffer: it is free now that the block's UMMAs are done; the scales have their own buffers
-        if (T::NB == 1 && kb + 1 < nb && tid == 128) issue_b(kb + 1);
-        // ---- the block's float terms, in block order
-        const uint32_t yd_base = sBd + (kb & 1) * (TC_NTOK * 4) + 4 * (32 * ch);
-#pragma unroll
-        for (int piece = 0; piece < 2; ++piece) {
-            int a0[16], a1[16], a2[16], a3[16];
-            tmem_ld16(t_lane + 16 * piece, a0);
-            tmem_ld16(t_lane + TC_NTOK + 16 * piece, a1);
-            tmem_ld16(t_lane + 2 * TC_NTOK + 16 * piece, a2);
-            if (T::NP == 4) tmem_ld16(t_lane + 3 * TC_NTOK + 16 * piece, a3);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float yd = __uint_as_float(lds32(yd_base + 4 * (16 * piece + i)));
-                float& s = sumf[16 * piece + i];
-                if (TYPE == DC_TYPE_Q4_K) {
-                    const int I = 8 * a0[i] + a1[i];
-                    const float tI = __fmul_rn(__fmul_rn(d, yd), (float)I);
-                    const float tM = __fmul_rn(__fmul_rn(dmin, yd), (float)a2[i]);
-                    s = __fsub_rn(__fadd_rn(s, tI), tM);
-                } else {
-                    const int I = a0[i] + 4 * a1[i] + 16 * a2[i] + 64 * a3[i];
-                    s = __fadd_rn(s, __fmul_rn(__fmul_rn(d, yd), (float)I));
-                }
-            }
-        }
-        TC_MARK(4);          // accumulator read-out and float terms
-        tc_fence_before();
-        failed = __syncthreads_or(failed);         // accumulators and block scales are read: both may be overwritten
-        tc_fence_after();
-        TC_MARK(5);
-    }
-#ifdef DC_TC_TIMING
-    if (p.timing && tid == 0)
-        for (int i = 0; i < 6; ++i) atomicAdd(p.timing + i, (unsigned long long)tc_t[i]);
-#endif
-
-    if (!failed) {
-        const int row = row0 + 32 * q + lane;
-        if (row < N) {
-            float* out = p.out + p.seg[seg].out_off;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int slot = tt * TC_NTOK + 32 * ch + i;
-                if (slot >= p.n_slots) continue;
-                const int orow = p.slot_row ? p.slot_row[slot] : slot;
-                if (orow < 0) continue;
-                float* o = out + (size_t)orow * p.ldo + row;
-                *o = p.accumulate ? __fadd_rn(*o, sumf[i]) : sumf[i];
-            }
-        }
-    } else {
-        // a wait ran out: give copies still in flight a bounded chance to land before the buffers go away
-        if (TYPE == DC_TYPE_Q6_K) mbar_wait(bar_raw, ph_raw, nullptr);
-        for (int s = 0; s < 2; ++s) mbar_wait(bar_b0 + 8 * s, ph_b[s], nullptr);
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, NCOLS);
-}
-
-
-// =====================================================================================================
-// Second form of the kernel: the three jobs of a block (expanding operand planes, issuing UMMAs, reading
+// ---- the kernel: the three jobs of a block (expanding operand planes, issuing UMMAs, reading
 // the accumulators out) run on different warps of one CTA per SM and overlap; a CTA owns 128 rows x two
-// 64-token tiles, so that a block's planes are expanded once for 128 tokens.
+// 64-token tiles, so that a block's planes are expanded once for 128 tokens and every UMMA is 128 tokens wide
+// (the instruction takes about as long at N = 64 as at N = 128: measured 144 cycles each at N = 64).
 //   warps 0-3   expanders: thread r turns its row's half block into the planes of stage h (two stages)
-//   warp 4      one thread issues the UMMAs: stage h x token set th -> accumulator set th (TMEM), commits
+//   warp 4      one thread issues the UMMAs (stage h x 128 tokens -> accumulators in TMEM), commits
 //               "stage free", "token codes free" and "accumulators full"
-//   warp 5      one thread loads the token tiles (codes double-buffered, block scales in a ring of four)
-//   warps 6-13  read-out: warp e owns TMEM lane quarter e % 4 of accumulator set e / 4, adds the block's float
-//               terms for its row and 64 tokens, then frees the set
-// Every wait is bounded and watches a CTA-wide give-up flag.
-constexpr int TC2_THREADS = 448;
-constexpr int TC2_EXPAND = 128;
-constexpr int TC2_SET = 64;                 // tokens per accumulator set
+//   warp 5      one thread loads the token tiles (codes double-buffered, interleaved so that the two tiles
+//               form one 128-row operand; block scales in a ring of four)
+//   warps 6-13  read-out: warp w owns TMEM lane quarter w % 4 and tokens 64 ((w - 6) / 4) .. + 63: adds the
+//               block's float terms for its row, then frees the accumulators
+// The accumulators are single-buffered (3 or 4 planes x 128 columns of the 512): the UMMAs of the next block
+// wait for the read-out, the expansion does not.  Every wait is bounded and watches a CTA-wide give-up flag.
+constexpr int TC_THREADS = 448;
+constexpr int TC_EXPAND = 128;
+constexpr int TC_N = 128;                  // tokens per CTA
 
-struct Tc2Bars {       // shared addresses of the mbarriers
-    uint32_t a_full[2], a_free[2], b_full[2], b_free[2], s_full[4], d_full[4], acc_full[2], acc_free[2];
+struct TcBars {       // shared addresses of the mbarriers
+    uint32_t a_full[2], a_free[2], b_full[2], b_free[2], s_full[4], d_full[4], acc_full, acc_free;
 };
 
-__device__ __forceinline__ bool tc2_wait_raw(uint32_t bar, uint32_t parity, volatile int* give_up, int* err) {
+__device__ __forceinline__ bool tc_wait_raw(uint32_t bar, uint32_t parity, volatile int* give_up, int* err) {
     for (uint32_t i = 0; i < DC_WAIT_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 63u && *give_up) return false;
@@ -474,40 +198,42 @@ __device__ __forceinline__ bool tc2_wait_raw(uint32_t bar, uint32_t parity, vola
     return false;
 }
 #ifdef DC_TC_TIMING
-// instrumented build: cycles spent in each kind of wait, summed over one thread of every role
-__device__ unsigned long long g_tc2_wait[8];
-#define tc2_wait(bar, parity, give_up, err) tc2_wait_timed(bar, parity, give_up, err, __LINE__)
-__device__ __forceinline__ bool tc2_wait_timed(uint32_t bar, uint32_t parity, volatile int* give_up, int* err, int line) {
+// instrumented build: cycles one thread of every role spends in each kind of wait, summed over CTAs
+// 0 a_free (expander)  1 b_full  2 a_full  3 acc_free (issuer)  4 b_free (loader)  5 d/s_full  6 acc_full (read-out)
+// 7 whole kernel (thread 0)
+__device__ unsigned long long g_tc_wait[8];
+__device__ __forceinline__ bool tc_wait_k(int kind, uint32_t bar, uint32_t parity, volatile int* give_up, int* err) {
     const long long t0 = clock64();
-    const bool ok = tc2_wait_raw(bar, parity, give_up, err);
-    if ((threadIdx.x & 31) == 0) atomicAdd(&g_tc2_wait[line & 7], (unsigned long long)(clock64() - t0));
+    const bool ok = tc_wait_raw(bar, parity, give_up, err);
+    if ((threadIdx.x & 31) == 0) atomicAdd(&g_tc_wait[kind], (unsigned long long)(clock64() - t0));
     return ok;
 }
 #else
-#define tc2_wait tc2_wait_raw
+#define tc_wait_k(kind, bar, parity, give_up, err) tc_wait_raw(bar, parity, give_up, err)
 #endif
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 template <int TYPE>
-constexpr size_t tc2_smem_bytes() {
+constexpr size_t tc_smem_bytes() {
     using T = TcTraits<TYPE>;
-    // planes: 2 stages; token codes: 2 buffers x 2 sets; block scales: 4 x 128 floats; row scales: 4 x 128 x 2 floats
-    return (size_t)2 * T::NP * TC_PLANE + (size_t)4 * TC_B_Q + 4 * 128 * 4 + 4 * 128 * 8 + 256;
+    // planes: 2 stages; token codes: 2 buffers x 2 tiles; block scales: 4 x 128 floats; row scales: 4 x 128 x 2 floats;
+    // 1024 bytes of slack to start the swizzled tiles on a 1024-byte boundary
+    return (size_t)2 * T::NP * TC_PLANE + (size_t)4 * TC_B_Q + 4 * 128 * 4 + 4 * 128 * 8 + 256 + 1024;
 }
 
 template <int TYPE>
-__global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(GemmTcParams p) {
     using T = TcTraits<TYPE>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ int s_give_up;
-    const uint32_t sA = smem_u32(smem_raw);                      // [2 stages][NP planes][16 KB]
+    const uint32_t sA = (smem_u32(smem_raw) + 1023u) & ~1023u;   // [2 stages][NP planes][16 KB], swizzle-aligned
     const uint32_t sBq = sA + 2 * T::NP * TC_PLANE;              // [2 buffers][2 sets][16 KB]
     const uint32_t sS = sBq + 4 * TC_B_Q;                        // [4][128] block scales of the tokens
     const uint32_t sD = sS + 4 * 128 * 4;                        // [4][128][2] d, dmin of the rows
     const uint32_t sBar = sD + 4 * 128 * 8;
-    Tc2Bars B;
+    TcBars B;
     {
         uint32_t a = sBar;
         for (int i = 0; i < 2; ++i) B.a_full[i] = a, a += 8;
@@ -516,8 +242,8 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
         for (int i = 0; i < 2; ++i) B.b_free[i] = a, a += 8;
         for (int i = 0; i < 4; ++i) B.s_full[i] = a, a += 8;
         for (int i = 0; i < 4; ++i) B.d_full[i] = a, a += 8;
-        for (int i = 0; i < 2; ++i) B.acc_full[i] = a, a += 8;
-        for (int i = 0; i < 2; ++i) B.acc_free[i] = a, a += 8;
+        B.acc_full = a, a += 8;
+        B.acc_free = a, a += 8;
     }
     const uint32_t tmem_slot = sBar + 22 * 8;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -550,16 +276,16 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
     if (tid == 0) {
         s_give_up = 0;
         for (int i = 0; i < 2; ++i) {
-            mbar_init(B.a_full[i], TC2_EXPAND);
+            mbar_init(B.a_full[i], TC_EXPAND);
             mbar_init(B.a_free[i], 1);
             mbar_init(B.b_full[i], 1);
             mbar_init(B.b_free[i], 1);
-            mbar_init(B.acc_full[i], 1);
-            mbar_init(B.acc_free[i], 128);
         }
+        mbar_init(B.acc_full, 1);
+        mbar_init(B.acc_free, 128 * nset);
         for (int i = 0; i < 4; ++i) {
             mbar_init(B.s_full[i], 1);
-            mbar_init(B.d_full[i], TC2_EXPAND);
+            mbar_init(B.d_full[i], TC_EXPAND);
         }
         mbar_fence_init();
     }
@@ -568,6 +294,9 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
     tc_fence_after();
     const uint32_t tmem = lds32(tmem_slot);
     volatile int* give_up = &s_give_up;
+#ifdef DC_TC_TIMING
+    const long long t_kernel0 = clock64();
+#endif
 
     if (warp < 4) {
         // ------------------------------------------------------------------ expanders
@@ -592,7 +321,7 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
                     for (int i = 0; i < 4; ++i) Q[i] = q[i];
                     if (h == 0) fetch(kb, 1);
                     else if (kb + 1 < nb) fetch(kb + 1, 0);
-                    if (kb > 0 && !tc2_wait(B.a_free[h], (kb - 1) & 1, give_up, p.err)) goto done;
+                    if (kb > 0 && !tc_wait_k(0, B.a_free[h], (kb - 1) & 1, give_up, p.err)) goto done;
                     if (h == 0) {
                         // this row's scales for the read-out warps
                         const uint32_t da = sD + ((kb & 3) * 128 + r) * 8;
@@ -601,7 +330,9 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
                                      : "memory");
                         mbar_arrive(B.d_full[kb & 3]);
                     }
-                    const uint32_t stage = sA + h * (T::NP * TC_PLANE) + r * 16;
+                    // row r of the stage's planes; chunk c of the row goes to chunk position c ^ (r % 8)
+                    const uint32_t stage = sA + h * (T::NP * TC_PLANE) + (r >> 3) * 1024 + (r & 7) * 128;
+                    const uint32_t rx = (uint32_t)(r & 7);
 #pragma unroll
                     for (int gl = 0; gl < 2; ++gl) {          // sub-block pairs 2h + gl of the block
                         const int g = 2 * h + gl;
@@ -620,8 +351,8 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
                                 lo[k] = in[k] & 0x0F0F0F0Fu;
                                 hi[k] = (in[k] >> 4) & 0x0F0F0F0Fu;
                             }
-                            const uint32_t c_lo = stage + (4 * gl + hf) * (TC_ROWS * 16);
-                            const uint32_t c_hi = c_lo + 2 * (TC_ROWS * 16);
+                            const uint32_t c_lo = stage + (((uint32_t)(4 * gl + hf) ^ rx) << 4);
+                            const uint32_t c_hi = stage + (((uint32_t)(4 * gl + hf + 2) ^ rx) << 4);
                             sts128(c_lo, lo[0] * a0, lo[1] * a0, lo[2] * a0, lo[3] * a0);
                             sts128(c_lo + TC_PLANE, lo[0] * a1, lo[1] * a1, lo[2] * a1, lo[3] * a1);
                             sts128(c_lo + 2 * TC_PLANE, mm0, mm0, mm0, mm0);
@@ -666,13 +397,14 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
                     const float d = fp16_bits_to_float((uint16_t)((wd >> sh) & 0xFFFFu));
                     if (h == 0) fetch(kb, 1);
                     else if (kb + 1 < nb) fetch(kb + 1, 0);
-                    if (kb > 0 && !tc2_wait(B.a_free[h], (kb - 1) & 1, give_up, p.err)) goto done;
+                    if (kb > 0 && !tc_wait_k(0, B.a_free[h], (kb - 1) & 1, give_up, p.err)) goto done;
                     if (h == 0) {
                         const uint32_t da = sD + ((kb & 3) * 128 + r) * 8;
                         asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(da), "f"(d), "f"(0.0f) : "memory");
                         mbar_arrive(B.d_full[kb & 3]);
                     }
-                    const uint32_t stage = sA + h * (T::NP * TC_PLANE) + r * 16;
+                    const uint32_t stage = sA + h * (T::NP * TC_PLANE) + (r >> 3) * 1024 + (r & 7) * 128;
+                    const uint32_t rx = (uint32_t)(r & 7);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {                       // chunk i of the half: quadrant i / 2, words 4 (i & 1)..
                         const int qd = i >> 1, w0 = 4 * (i & 1);
@@ -685,14 +417,15 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
                                    (((qh[w0 + k] >> (2 * qd)) & 0x03030303u) << 4);
 #pragma unroll
                         for (int di = 0; di < 4; ++di) {
-                            const uint32_t dg = (mag >> (2 * di)) & 3u;
-                            uint32_t v[4];
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                v[k] = __vsub4(u[k] * dg, dg * 0x20202020u);
-                                if (sc < 0) v[k] = __vneg4(v[k]);
-                            }
-                            sts128(stage + i * (TC_ROWS * 16) + di * TC_PLANE, v[0], v[1], v[2], v[3]);
+                            // signed digit m in -3..3; per byte m * (u - 32) + 128 = m * u + (128 - 32 m) lies in 32..224, so
+                            // one 32-bit multiply-add does the four bytes without carries between them, and flipping
+                            // each byte's top bit turns the biased value into the two's-complement byte m * (u - 32)
+                            const int dg = (int)((mag >> (2 * di)) & 3u);
+                            const int m = sc < 0 ? -dg : dg;
+                            const uint32_t K = (uint32_t)(128 - 32 * m) * 0x01010101u;
+                            sts128(stage + (((uint32_t)i ^ rx) << 4) + di * TC_PLANE, (u[0] * (uint32_t)m + K) ^ 0x80808080u,
+                                   (u[1] * (uint32_t)m + K) ^ 0x80808080u, (u[2] * (uint32_t)m + K) ^ 0x80808080u,
+                                   (u[3] * (uint32_t)m + K) ^ 0x80808080u);
                         }
                     }
                     fence_async_smem();
@@ -703,28 +436,23 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
     } else if (warp == 4) {
         // ------------------------------------------------------------------ UMMA issue
         if (lane == 0) {
-            constexpr uint32_t IDESC = umma_idesc_i8(T::A_SIGNED, TC_ROWS, TC2_SET);
+            const uint32_t idesc = umma_idesc_i8(T::A_SIGNED, TC_ROWS, TC_NTOK * nset);
             for (int kb = 0; kb < nb; ++kb) {
-                if (!tc2_wait(B.b_full[kb & 1], (kb >> 1) & 1, give_up, p.err)) break;
+                if (!tc_wait_k(1, B.b_full[kb & 1], (kb >> 1) & 1, give_up, p.err)) break;
                 const uint32_t sBcur = sBq + (kb & 1) * (2 * TC_B_Q);
                 bool ok = true;
                 for (int h = 0; h < 2 && ok; ++h) {
-                    if (!tc2_wait(B.a_full[h], kb & 1, give_up, p.err)) { ok = false; break; }
+                    if (!tc_wait_k(2, B.a_full[h], kb & 1, give_up, p.err)) { ok = false; break; }
+                    // the read-out of the previous block must have drained the accumulators
+                    if (h == 0 && kb > 0 && !tc_wait_k(3, B.acc_free, (kb - 1) & 1, give_up, p.err)) { ok = false; break; }
                     tc_fence_after();
-                    for (int th = 0; th < nset; ++th) {
-                        // the read-out of the previous block must have drained this accumulator set
-                        if (h == 0 && kb > 0 && !tc2_wait(B.acc_free[th], (kb - 1) & 1, give_up, p.err)) { ok = false; break; }
-                        tc_fence_after();
 #pragma unroll
-                        for (int pl = 0; pl < T::NP; ++pl)
+                    for (int pl = 0; pl < T::NP; ++pl)
 #pragma unroll
-                            for (int kk = 0; kk < 4; ++kk)
-                                umma_i8(tmem + (th * T::NP + pl) * TC2_SET,
-                                        umma_desc(sA + h * (T::NP * TC_PLANE) + pl * TC_PLANE + kk * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128),
-                                        umma_desc(sBcur + th * TC_B_Q + (8 * h + 2 * kk) * (TC2_SET * 16), TC2_SET * 16, 128), IDESC,
-                                        (h | kk) ? 1u : 0u);
-                        if (h == 1) umma_commit(B.acc_full[th]);
-                    }
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma_i8(tmem + pl * TC_N, umma_desc_sw128(sA + h * (T::NP * TC_PLANE) + pl * TC_PLANE + 32 * kk, 1024),
+                                    umma_desc_sw128(sBcur + h * (2 * TC_B_HALF) + 32 * kk, 1024), idesc, (h | kk) ? 1u : 0u);
+                    if (h == 1) umma_commit(B.acc_full);
                     umma_commit(B.a_free[h]);
                 }
                 if (!ok) break;
@@ -735,13 +463,18 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
         // ------------------------------------------------------------------ token tiles
         if (lane == 0) {
             for (int kb = 0; kb < nb; ++kb) {
-                if (kb >= 2 && !tc2_wait(B.b_free[kb & 1], ((kb - 2) >> 1) & 1, give_up, p.err)) break;
+                if (kb >= 2 && !tc_wait_k(4, B.b_free[kb & 1], ((kb - 2) >> 1) & 1, give_up, p.err)) break;
                 const uint8_t* src = p.act + ((size_t)kb * p.n_tt + tt0) * TC_ACT_TILE;
                 mbar_expect_tx(B.b_full[kb & 1], (uint32_t)nset * TC_B_Q);
-                mbar_expect_tx(B.s_full[kb & 3], (uint32_t)nset * TC2_SET * 4);
+                mbar_expect_tx(B.s_full[kb & 3], (uint32_t)nset * TC_NTOK * 4);
+                // operand rows 0..63 come from the first tile, 64..127 from the second: per half block, the two tiles'
+                // 8 KB of swizzled rows back to back
+                const uint32_t dst = sBq + (kb & 1) * (2 * TC_B_Q);
                 for (int th = 0; th < nset; ++th) {
-                    bulk_g2s(sBq + ((kb & 1) * 2 + th) * TC_B_Q, src + (size_t)th * TC_ACT_TILE, TC_B_Q, B.b_full[kb & 1]);
-                    bulk_g2s(sS + ((kb & 3) * 128 + th * TC2_SET) * 4, src + (size_t)th * TC_ACT_TILE + TC_B_Q, TC2_SET * 4, B.s_full[kb & 3]);
+                    for (int hh = 0; hh < 2; ++hh)
+                        bulk_g2s(dst + hh * (2 * TC_B_HALF) + th * TC_B_HALF, src + (size_t)th * TC_ACT_TILE + hh * TC_B_HALF, TC_B_HALF,
+                                 B.b_full[kb & 1]);
+                    bulk_g2s(sS + ((kb & 3) * 128 + th * TC_NTOK) * 4, src + (size_t)th * TC_ACT_TILE + TC_B_Q, TC_NTOK * 4, B.s_full[kb & 3]);
                 }
             }
         }
@@ -750,30 +483,30 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
         // a warp reaches the TMEM lanes 32 (warp index % 4) .. + 31: warps 6..9 read set 0, warps 10..13 set 1
         const int q = warp & 3, th = (warp - 6) >> 2;
         if (th < nset) {
-            float sumf[TC2_SET];
+            float sumf[TC_NTOK];
 #pragma unroll
-            for (int i = 0; i < TC2_SET; ++i) sumf[i] = 0.0f;
-            const uint32_t t_lane = tmem + ((uint32_t)(32 * q) << 16) + th * T::NP * TC2_SET;
+            for (int i = 0; i < TC_NTOK; ++i) sumf[i] = 0.0f;
+            const uint32_t t_lane = tmem + ((uint32_t)(32 * q) << 16) + th * TC_NTOK;
             const int r = 32 * q + lane;
             bool ok = true;
             for (int kb = 0; kb < nb && ok; ++kb) {
-                if (!tc2_wait(B.d_full[kb & 3], (kb >> 2) & 1, give_up, p.err) ||
-                    !tc2_wait(B.s_full[kb & 3], (kb >> 2) & 1, give_up, p.err) ||
-                    !tc2_wait(B.acc_full[th], kb & 1, give_up, p.err)) {
+                if (!tc_wait_k(5, B.d_full[kb & 3], (kb >> 2) & 1, give_up, p.err) ||
+                    !tc_wait_k(5, B.s_full[kb & 3], (kb >> 2) & 1, give_up, p.err) ||
+                    !tc_wait_k(6, B.acc_full, kb & 1, give_up, p.err)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint2 dd = lds64(sD + ((kb & 3) * 128 + r) * 8);
                 const float d = __uint_as_float(dd.x), dmin = __uint_as_float(dd.y);
-                const uint32_t yd_base = sS + ((kb & 3) * 128 + th * TC2_SET) * 4;
+                const uint32_t yd_base = sS + ((kb & 3) * 128 + th * TC_NTOK) * 4;
 #pragma unroll
-                for (int piece = 0; piece < TC2_SET / 16; ++piece) {
+                for (int piece = 0; piece < TC_NTOK / 16; ++piece) {
                     int a0[16], a1[16], a2[16], a3[16];
                     tmem_ld16(t_lane + 16 * piece, a0);
-                    tmem_ld16(t_lane + TC2_SET + 16 * piece, a1);
-                    tmem_ld16(t_lane + 2 * TC2_SET + 16 * piece, a2);
-                    if (T::NP == 4) tmem_ld16(t_lane + 3 * TC2_SET + 16 * piece, a3);
+                    tmem_ld16(t_lane + TC_N + 16 * piece, a1);
+                    tmem_ld16(t_lane + 2 * TC_N + 16 * piece, a2);
+                    if (T::NP == 4) tmem_ld16(t_lane + 3 * TC_N + 16 * piece, a3);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -791,14 +524,14 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
                     }
                 }
                 tc_fence_before();
-                mbar_arrive(B.acc_free[th]);
+                mbar_arrive(B.acc_free);
             }
             if (ok) {
                 const int row = row0 + r;
                 if (row < N) {
                     float* out = p.out + p.seg[seg].out_off;
 #pragma unroll
-                    for (int i = 0; i < TC2_SET; ++i) {
+                    for (int i = 0; i < TC_NTOK; ++i) {
                         const int slot = (tt0 + th) * TC_NTOK + i;
                         if (slot >= p.n_slots) continue;
                         const int orow = p.slot_row ? p.slot_row[slot] : slot;
@@ -813,6 +546,9 @@ __global__ void __launch_bounds__(TC2_THREADS, 1) k_gemm_tc2(GemmTcParams p) {
 done:
     tc_fence_before();
     __syncthreads();
+#ifdef DC_TC_TIMING
+    if (tid == 0) atomicAdd(&g_tc_wait[7], (unsigned long long)(clock64() - t_kernel0));
+#endif
     if (warp == 4) tmem_dealloc(tmem, NCOLS);
 }
 
@@ -877,36 +613,18 @@ int dc_launch_gemm_tc_multi(dc_ctx* ctx, const dc_weight* const* ws, const int* 
     p.err = ctx->d_err;
 #ifdef DC_TC_TIMING
     {
-        static unsigned long long* t = nullptr;
-        if (!t) {
-            cudaMalloc((void**)&t, 64);
-            cudaMemset(t, 0, 64);
-        }
-        p.timing = t;
         if (getenv("DC_TC_TIMING_DUMP")) {
-            unsigned long long h[6];
-            cudaMemcpy(h, t, 48, cudaMemcpyDeviceToHost);
-            fprintf(stderr, "gemm_tc cycles so far: expand %llu wait_b %llu vote %llu umma %llu readout %llu vote2 %llu\n", h[0], h[1], h[2], h[3], h[4], h[5]);
+            unsigned long long w2[8];
+            cudaMemcpyFromSymbol(w2, g_tc_wait, sizeof(w2));
+            fprintf(stderr, "gemm_tc wait cycles so far: a_free %llu b_full %llu a_full %llu acc_free %llu b_free %llu d/s_full %llu acc_full %llu kernel %llu\n",
+                    w2[0], w2[1], w2[2], w2[3], w2[4], w2[5], w2[6], w2[7]);
         }
     }
 #endif
-    if (ctx->gemm_tc_form == 2 && (!tile_expert || pair_tile0)) {
-        // one CTA per SM with separate warps for expansion, issue and read-out, two token tiles per CTA
-        p.pair_tile0 = pair_tile0;
-        p.pair_nset = pair_nset;
-        const dim3 grid2(pair_tile0 ? n_pairs : (p.n_tt + 1) / 2, row_tiles);
-        if (w->type == DC_TYPE_Q4_K) {
-            constexpr size_t smem = tc2_smem_bytes<DC_TYPE_Q4_K>();
-            DC_TRY(dc_kernel_setup(ctx, (const void*)k_gemm_tc2<DC_TYPE_Q4_K>, smem, "k_gemm_tc2<Q4_K>"));
-            k_gemm_tc2<DC_TYPE_Q4_K><<<grid2, TC2_THREADS, smem, ctx->stream>>>(p);
-        } else {
-            constexpr size_t smem = tc2_smem_bytes<DC_TYPE_Q6_K>();
-            DC_TRY(dc_kernel_setup(ctx, (const void*)k_gemm_tc2<DC_TYPE_Q6_K>, smem, "k_gemm_tc2<Q6_K>"));
-            k_gemm_tc2<DC_TYPE_Q6_K><<<grid2, TC2_THREADS, smem, ctx->stream>>>(p);
-        }
-        return dc_check_cuda(ctx, cudaGetLastError(), "k_gemm_tc2");
-    }
-    const dim3 grid(p.n_tt, row_tiles);
+    if (tile_expert && !pair_tile0) return dc_fail(ctx, DC_B200_INVALID_ARGUMENT, "gemm_tc: grouped matmul without its tile pairs");
+    p.pair_tile0 = pair_tile0;
+    p.pair_nset = pair_nset;
+    const dim3 grid(pair_tile0 ? n_pairs : (p.n_tt + 1) / 2, row_tiles);
     if (w->type == DC_TYPE_Q4_K) {
         constexpr size_t smem = tc_smem_bytes<DC_TYPE_Q4_K>();
         DC_TRY(dc_kernel_setup(ctx, (const void*)k_gemm_tc<DC_TYPE_Q4_K>, smem, "k_gemm_tc<Q4_K>"));

@@ -14,6 +14,7 @@
 #include <algorithm>
 
 #include "dc_common.cuh"
+#include "dc_gemm_tc.h"
 #include "dc_model.h"
 
 #define DC_TRY(expr)                       \
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(256) k_swiglu_q8k_tiled(const float* __restric
     for (long long item = (long long)blockIdx.x * 8 + warp; item < total; item += (long long)gridDim.x * 8) {
         const int b = (int)(item % nb), slot = (int)(item / nb);
         const bool live = slot < n_slots_data && (!slot_valid || slot_valid[slot] >= 0);
-        uint8_t* tile = act + ((size_t)b * n_tt + slot / 64) * (16 * 64 * 16 + 64 * 4);
+        uint8_t* tile = act + ((size_t)b * n_tt + slot / TC_NTOK) * TC_ACT_TILE;
         uint32_t w0 = 0, w1 = 0, bw = 0;
         float d = 0.0f;
         if (live) {
@@ -176,8 +177,8 @@ __global__ void __launch_bounds__(256) k_swiglu_q8k_tiled(const float* __restric
                                 __fmul_rn(silu_fast(g1.z), u1.z), __fmul_rn(silu_fast(g1.w), u1.w)};
             q8k_block_core(v, lane, w0, w1, bw, d);
         }
-        *reinterpret_cast<uint2*>(tile + (lane >> 1) * (64 * 16) + (slot % 64) * 16 + 8 * (lane & 1)) = make_uint2(w0, w1);
-        if (lane == 0) reinterpret_cast<float*>(tile + 16 * 64 * 16)[slot % 64] = d;
+        *reinterpret_cast<uint2*>(tile + tc_act_code_offset(slot % TC_NTOK, lane)) = make_uint2(w0, w1);
+        if (lane == 0) reinterpret_cast<float*>(tile + TC_B_Q)[slot % TC_NTOK] = d;
     }
 }
 
