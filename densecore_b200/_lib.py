@@ -92,6 +92,7 @@ def _signatures() -> dict:
         "dc_b200_kv_prefix_attach": (i32, [vp, i32, vp, i32, pi]),
         "dc_b200_kv_prefix_register": (i32, [vp, i32, vp, i32]),
         "dc_b200_kv_prefix_stats": (i32, [vp, vp]),
+        "dc_b200_kv_prefix_hash": (C.c_uint64, [vp, i32]),
         "dc_b200_model_prefix_stats": (i32, [vp, vp]),
         "dc_b200_sched_create": (i32, [vp, i32, i32, i32, pp]),
         "dc_b200_sched_destroy": (None, [vp]),

@@ -318,6 +318,9 @@ int dc_b200_kv_prefix_attach(dc_kv_cache* kv, int seq, const int32_t* tokens, in
 int dc_b200_kv_prefix_register(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens) {
     return kv ? dc_kv_prefix_register(kv, seq, tokens, n_tokens) : DC_B200_INVALID_ARGUMENT;
 }
+uint64_t dc_b200_kv_prefix_hash(const int32_t* tokens, int n_tokens) {
+    return tokens && n_tokens > 0 ? dc_kv_token_hash(14695981039346656037ULL, tokens, n_tokens) : 0;
+}
 int dc_b200_kv_prefix_stats(dc_kv_cache* kv, uint64_t out[4]) {
     if (!kv || !out) return DC_B200_INVALID_ARGUMENT;
     out[0] = kv->prefix_lookups;

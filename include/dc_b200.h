@@ -199,6 +199,9 @@ DC_B200_API int dc_b200_kv_block_refcount(dc_kv_cache* kv, int block);
 DC_B200_API int dc_b200_kv_prefix_attach(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens, int* cached_tokens);
 DC_B200_API int dc_b200_kv_prefix_register(dc_kv_cache* kv, int seq, const int32_t* tokens, int n_tokens);
 DC_B200_API int dc_b200_kv_prefix_stats(dc_kv_cache* kv, uint64_t out[4]);
+/* The key a prefix of n_tokens tokens is cached under (BlockManager::ComputeTokenHash without a salt,
+ * core/src/runtime/memory/kv_cache_block_manager.cpp:515-522): FNV-1a, one 64-bit step per token id.  Host only. */
+DC_B200_API uint64_t dc_b200_kv_prefix_hash(const int32_t* tokens, int n_tokens);
 /* cb_paged_attention_decode (core/src/llm/attention/paged_exec.cpp:343): writes
  * the T current tokens' K/V (f32 [T, n_kv, hd]) into the cache at positions[t]
  * of sequence seq_ids[t], then attends q [T, n_head, hd] over keys

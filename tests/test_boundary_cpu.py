@@ -54,6 +54,34 @@ def test_library_exports_the_ggml_shaped_callbacks():
     assert os.path.exists(os.path.join(ROOT, "tests", "shims", "ggml_shims_test"))
 
 
+def test_prefix_cache_key_is_the_reference_hash():
+    """The prefix cache keys a block by FNV-1a over the token ids of the whole prefix, one 64-bit step per id
+    (BlockManager::ComputeTokenHash, core/src/runtime/memory/kv_cache_block_manager.cpp:515-522, salt 0): checked
+    against a Python restatement, including the known FNV-1a offset basis for an empty continuation."""
+    from densecore_b200 import _lib
+    lib = _lib.lib()
+
+    def ref(tokens):
+        h = 14695981039346656037
+        for t in tokens:
+            h ^= int(t) & 0xFFFFFFFFFFFFFFFF
+            h = (h * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+        return h
+
+    rng = np.random.default_rng(0)
+    for n in (1, 15, 16, 17, 1024):
+        toks = rng.integers(0, 151936, size=n).astype(np.int32)
+        assert lib.dc_b200_kv_prefix_hash(toks.ctypes.data_as(ctypes.c_void_p), n) == ref(toks), n
+    one = np.array([0], dtype=np.int32)
+    assert lib.dc_b200_kv_prefix_hash(one.ctypes.data_as(ctypes.c_void_p), 1) == (14695981039346656037 * 1099511628211) % 2 ** 64
+    # a different left context changes the key of the same block contents
+    a = np.arange(32, dtype=np.int32)
+    b = a.copy()
+    b[0] = 99
+    assert lib.dc_b200_kv_prefix_hash(a.ctypes.data_as(ctypes.c_void_p), 32) != lib.dc_b200_kv_prefix_hash(b.ctypes.data_as(ctypes.c_void_p), 32)
+    assert lib.dc_b200_kv_prefix_hash(None, 0) == 0
+
+
 def test_no_cpu_fallback_without_gpu():
     """On a machine without a GPU, init fails loudly instead of computing on the CPU."""
     import torch
