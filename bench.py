@@ -68,7 +68,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+        self.gpu_index, self.proc, self.lines, self.first = gpu_index, None, [], 0
 
     def start(self):
         try:
@@ -84,6 +84,16 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_ready(self, timeout: float = 3.0):
+        """nvidia-smi takes a few hundred milliseconds to start: wait until it is sampling."""
+        t0 = time.perf_counter()
+        while self.proc and not self.lines and time.perf_counter() - t0 < timeout:
+            time.sleep(0.01)
+
+    def mark(self):
+        """Samples from here on belong to the timed region."""
+        self.first = len(self.lines)
+
     def stop(self) -> dict:
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -94,7 +104,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in self.lines[self.first:]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -537,11 +547,14 @@ def main():
     stream_counts = sorted({int(x) for x in args.streams.split(",")} | {1})
     for n_streams in stream_counts:
         sq = seqs[:n_streams]
-        toks, _ = model.decode_run(sq, first[:n_streams], args.warmup)        # warm-up: eager pass, capture, replays
         sampler = ClockSampler(local_rank) if (n_streams == 1 and rank == 0) else None
         if sampler:
             sampler.start()
+            sampler.wait_ready()
+        toks, _ = model.decode_run(sq, first[:n_streams], args.warmup)        # warm-up: eager pass, capture, replays
         barrier()
+        if sampler:
+            sampler.mark()
         if args.profiler_range and n_streams == 1:
             dc._lib.lib().dc_b200_profiler_range(1)
         t0 = time.perf_counter()
@@ -551,8 +564,6 @@ def main():
         if args.profiler_range and n_streams == 1:
             dc._lib.lib().dc_b200_profiler_range(0)
         run_launches = model.step_stats()[0]
-        if sampler:
-            clocks = sampler.stop()
         ms = max_over_ranks(ms)
         # end to end: host buffers every step
         last = toks[-1]
@@ -564,6 +575,8 @@ def main():
             last = model.decode_step(sq, last)
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
+        if sampler:
+            clocks = sampler.stop()           # samples cover the device-timed run and the end-to-end run
         results[n_streams] = dict(ms=ms, wall=wall, e2e_s=e2e_s, ctx=model.seq_len(sq[0]), last=last, run_launches=run_launches)
 
     _, weight_bytes, kv_bytes_per_tok = model.step_stats()
