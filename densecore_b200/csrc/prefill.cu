@@ -177,8 +177,7 @@ __global__ void __launch_bounds__(256) k_swiglu_q8k_tiled(const float* __restric
                                 __fmul_rn(silu_fast(g1.z), u1.z), __fmul_rn(silu_fast(g1.w), u1.w)};
             q8k_block_core(v, lane, w0, w1, bw, d);
         }
-        *reinterpret_cast<uint2*>(tile + tc_act_code_offset(slot % TC_NTOK, lane)) = make_uint2(w0, w1);
-        if (lane == 0) reinterpret_cast<float*>(tile + TC_B_Q)[slot % TC_NTOK] = d;
+        tc_act_store(tile, slot % TC_NTOK, lane, w0, w1, bw, d);
     }
 }
 
