@@ -185,7 +185,7 @@ template <>
 struct TcTraits<DC_TYPE_Q4_K> {
     // two operand planes and two sets of accumulators (the minimum term comes from the tokens' sub-block sums)
     static constexpr int NP = 2, NSET = 2, BB = DC_Q4K_BYTES, A_SIGNED = 0, TAIL_COPY = TC_ACT_TAIL;
-    static constexpr int RO_TOK = 64;         // tokens per read-out warp
+    static constexpr int RO_TOK = 32;         // tokens per read-out warp: 16 read-out warps, four per scheduler
     static constexpr int A_STAGES = 2;        // half blocks of operand planes in shared memory
 };
 template <>
