@@ -168,13 +168,20 @@ __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
 // to get here sums all runs in run order, normalises and emits (no run waits for another).
 __device__ __forceinline__ void attn_merge_tail(const AttnParams& p, int t, int kvh, int g, int tid, int warp, int lane,
                                                 int& s_last) {
-    __threadfence();
+    // release: the CTA barrier puts every thread's partial before thread 0's fence, which puts them before the
+    // ticket; acquire: the last run's thread 0 fences after its ticket, the CTA barrier passes that on
     __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(p.tickets + t * p.n_kv + kvh, 1) == p.nsplit - 1);
+    if (tid == 0) {
+        __threadfence();
+        const int last = atomicAdd(p.tickets + t * p.n_kv + kvh, 1) == p.nsplit - 1;
+        if (last) {
+            __threadfence();
+            p.tickets[t * p.n_kv + kvh] = 0;
+        }
+        s_last = last;
+    }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
-    if (tid == 0) p.tickets[t * p.n_kv + kvh] = 0;
     // ---- last run of this (token, kv head): sum the runs in run order, normalise, emit.
     // One warp per 256 outputs (two heads) = one Q8_K block of the o-projection input.
     for (int pb2 = warp; pb2 < g / 2; pb2 += 4) {

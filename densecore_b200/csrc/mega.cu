@@ -76,7 +76,8 @@ __device__ __noinline__ bool grid_wait(const MegaParams& p, unsigned epoch) {
             if (MG_BAR_SLEEP) __nanosleep(MG_BAR_SLEEP);
         }
         s_gave_up = gave_up;
-        __threadfence();
+        // (no fence here: the acquire load above orders this thread after the arrivals it observed, and the CTA
+        // barrier below passes that on to the other threads; a fence cost 0.4 us per barrier)
     }
 #ifdef DC_MEGA_SUBMARKS
     if (threadIdx.x == 0 && p.phase_ns && epoch > 7 && epoch <= 14) p.phase_ns[32 + (7 + epoch - 8) * 160 + blockIdx.x] = mg_now();
@@ -760,14 +761,21 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
         p.part_acc[idx * 128 + dim] = acc1 * sh.suffix[hq + 4];
         if (dim == 0) p.part_d[idx] = d1 * sh.suffix[hq + 4];
     }
-    __threadfence();
+    // release: the CTA barrier puts every thread's partial before thread 0's fence, which puts them before the
+    // ticket; acquire: the last run's thread 0 fences after its ticket, the CTA barrier passes that on
     __syncthreads();
     int* ticket = p.tickets + (it.t * p.n_kv + it.kvh) * p.n_hg + it.hg;
-    if (tid == 0) sh.last = (atomicAdd(ticket, 1) == p.nsplit - 1);
+    if (tid == 0) {
+        __threadfence();
+        const bool last = atomicAdd(ticket, 1) == p.nsplit - 1;
+        if (last) {
+            __threadfence();
+            *ticket = 0;
+        }
+        sh.last = last;
+    }
     __syncthreads();
     if (!sh.last) return;
-    __threadfence();
-    if (tid == 0) *ticket = 0;
 #ifdef DC_MEGA_SUBMARKS
     const unsigned long long merge_t0 = mg_now();
 #endif
