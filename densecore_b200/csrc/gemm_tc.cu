@@ -191,7 +191,7 @@ struct TcTraits<DC_TYPE_Q4_K> {
 template <>
 struct TcTraits<DC_TYPE_Q6_K> {
     static constexpr int NP = 4, NSET = 1, BB = DC_Q6K_BYTES, A_SIGNED = 1, TAIL_COPY = TC_ACT_SCALES;
-    static constexpr int RO_TOK = 64;
+    static constexpr int RO_TOK = 32;
     static constexpr int A_STAGES = 2;
 };
 
