@@ -4,8 +4,8 @@
 // (core/src/llm/matmul/batched_exec.cpp:1040-1240 serves these shapes on the CPU; per block
 // sumf += (d*yd)*float(I); sumf -= (dmin*yd)*float(M), core/src/kernels/hwy/hwy_moe_quant.cc:248-253).
 //
-// One CTA per SM owns 128 weight rows x two 64-token tiles over the whole reduction length; its warps split
-// the three jobs of a 256-value block and overlap them (see k_gemm_tc below):
+// One CTA per SM walks work items of 128 weight rows x two 64-token tiles over the whole reduction length; its
+// warps split the three jobs of a 256-value block and overlap them, across items too (see k_gemm_tc below):
 //   1. expanders turn the raw quants of the 128 rows into 8-bit operand planes in shared memory, K-major rows
 //      of 128 bytes with the 128-byte swizzle the tensor core reads at full rate (a half block is exactly one
 //      such row):
@@ -22,7 +22,8 @@
 // double-buffered and the UMMAs of a block run while the block before is read out; Q6_K's four planes fit once.
 // The token side is prepared once per activation matrix by k_quantize_q8k_tiled: the Q8_K codes of every
 // (block, 64-token tile) stored as the B operand (two halves of 64 swizzled 128-byte rows), followed by the
-// 64 block scales, so that a tile half is one contiguous bulk copy.  No multicast load anywhere.
+// 64 block scales and the tokens' sub-block sums, so that a tile half is one contiguous bulk copy.  No multicast
+// load anywhere.
 //
 // Q4_K results are bit-equal to the GEMV path and the CPU oracle.  Q6_K adds one float term per block
 // instead of the CPU small-batch kernel's eight lane partials (q6_small_batch.h:62-103): equal integers,
@@ -195,16 +196,16 @@ struct TcTraits<DC_TYPE_Q6_K> {
     static constexpr int A_STAGES = 2;
 };
 
-// ---- the kernel: the three jobs of a block (expanding operand planes, issuing UMMAs, reading
-// the accumulators out) run on different warps of one CTA per SM and overlap; a CTA owns 128 rows x two
-// 64-token tiles, so that a block's planes are expanded once for 128 tokens and every UMMA is 128 tokens wide
-// (the instruction takes about as long at N = 64 as at N = 128: measured 144 cycles each at N = 64).
-//   warps 0-3   expanders: thread r turns its row's half block into the planes of stage h (two stages)
-//   warp 4      one thread issues the UMMAs (stage h x 128 tokens -> accumulators in TMEM), commits
+// ---- the kernel: the three jobs of a block (expanding operand planes, issuing UMMAs, reading the accumulators
+// out) run on different warps of one CTA per SM and overlap.  A work item is 128 rows x two 64-token tiles, so
+// that a block's planes are expanded once for 128 tokens and every UMMA is 128 tokens wide (a stand-alone loop
+// runs the instruction in 49 cycles at N = 64 and 65 at N = 128); the CTA walks its items round robin.
+//   warps 0-3   expanders: thread r turns its row's half block into the planes of a stage (two stages)
+//   warp 4      one thread issues the UMMAs (stage x 128 tokens -> accumulators in TMEM), commits
 //               "stage free", "token codes free" and "accumulators full"
 //   warp 5      one thread loads the token tiles (codes double-buffered, interleaved so that the two tiles
-//               form one 128-row operand; block scales in a ring of four)
-//   warps 6-13  read-out: warp w owns TMEM lane quarter w % 4 and tokens 64 ((w - 6) / 4) .. + 63: adds the
+//               form one 128-row operand; block scales and sub-block sums in a ring of four)
+//   warps 6-21  read-out: warp w owns TMEM lane quarter w % 4 and tokens 32 ((w - 6) / 4) .. + 31: adds the
 //               block's float terms for its row, then frees the accumulators
 // Q4_K: two sets of accumulators (2 planes x 128 columns each) alternate by block.  Q6_K: one set (4 planes x 128
 // columns of the 512): the UMMAs of the next block wait for the read-out, the expansion does not.  Every wait is
