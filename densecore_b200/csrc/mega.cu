@@ -53,10 +53,8 @@ __device__ __noinline__ void grid_arrive(const MegaParams& p, unsigned& epoch, b
     if (trace) p.phase_ns[32 + (epoch - 8) * 160 + blockIdx.x] = mg_now();
 #endif
     if (sys_scope) ep_arrive(p);                 // this CTA's stores to other GPUs are performed first
-    if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(p.bar_counter, 1u);
-    }
+    if (threadIdx.x == 0)   // one instruction: the release covers what the CTA barrier above ordered before this thread
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.bar_counter), "r"(1u) : "memory");
 }
 // Returns true if this CTA's wait ran out: the caller then leaves the kernel (drains its copies in flight and
 // returns) instead of computing on data that other CTAs may not have written yet.  The CTAs that did arrive
@@ -326,7 +324,8 @@ __device__ __noinline__ void x_norm_phase(const MegaParams& p, MegaShared& sh, i
         const int t = pr / nb, b = pr - t * nb;
         double tot = 0.0;
         for (int i = 0; i < nb; ++i) tot += sh.red2[t * nb + i];
-        const float mean = (float)(tot / (double)H);
+        // (a power-of-two width divides exactly either way; the multiplication spares a double-precision division)
+        const float mean = (H & (H - 1)) == 0 ? (float)(tot * (1.0 / (double)H)) : (float)(tot / (double)H);
         const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
         const float ww[8] = {wv[pi][0].x, wv[pi][0].y, wv[pi][0].z, wv[pi][0].w,
                              wv[pi][1].x, wv[pi][1].y, wv[pi][1].z, wv[pi][1].w};
@@ -761,17 +760,16 @@ __device__ DC_HOT void attn_pv_phase(const MegaParams& p, const MegaLayer& L, Me
         p.part_acc[idx * 128 + dim] = acc1 * sh.suffix[hq + 4];
         if (dim == 0) p.part_d[idx] = d1 * sh.suffix[hq + 4];
     }
-    // release: the CTA barrier puts every thread's partial before thread 0's fence, which puts them before the
-    // ticket; acquire: the last run's thread 0 fences after its ticket, the CTA barrier passes that on
+    // release: the CTA barrier puts every thread's partial before thread 0's ticket, whose release half publishes
+    // them; acquire: the last run's thread 0 sees the other runs' partials through the ticket's acquire half, and the
+    // CTA barrier passes that on
     __syncthreads();
     int* ticket = p.tickets + (it.t * p.n_kv + it.kvh) * p.n_hg + it.hg;
     if (tid == 0) {
-        __threadfence();
-        const bool last = atomicAdd(ticket, 1) == p.nsplit - 1;
-        if (last) {
-            __threadfence();
-            *ticket = 0;
-        }
+        int old;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(ticket), "r"(1) : "memory");
+        const bool last = old == p.nsplit - 1;
+        if (last) *ticket = 0;
         sh.last = last;
     }
     __syncthreads();
