@@ -57,7 +57,8 @@ def build_model(ctx, cfg, all_q4k: bool):
 
 
 @pytest.mark.parametrize("name,n_prompt,all_q4k", [("moe_small", 200, True), ("dense_small", 333, True), ("moe_small", 200, False),
-                                                   ("dense_small", 333, False), ("moe_full_width", 700, False)])
+                                                   ("dense_small", 333, False), ("moe_full_width", 700, False),
+                                                   ("moe_full_width", 600, True)])
 def test_chunked_prefill_on_tensor_cores_matches_the_sixteen_token_path(ctx, name, n_prompt, all_q4k):
     cfg = dc.Config(max_seqs=2, max_ctx=1024, **CONFIGS[name])
     m = build_model(ctx, cfg, all_q4k)
@@ -66,10 +67,10 @@ def test_chunked_prefill_on_tensor_cores_matches_the_sixteen_token_path(ctx, nam
     m.set_option("prefill_attention", 0 if all_q4k else 1)
     # several chunks per prompt: 64-token chunks for the bit-identity cases, 256 for the full-width model, one
     # chunk (the default length, 2048) otherwise
-    if all_q4k:
+    if name == "moe_full_width":
+        m.set_option("prefill_chunk", 256)     # (all_q4k: lone and paired expert tiles, full and ragged, bit for bit)
+    elif all_q4k:
         m.set_option("prefill_chunk", 64)
-    elif name == "moe_full_width":
-        m.set_option("prefill_chunk", 256)
     rng = np.random.default_rng(3)
     prompt = rng.integers(0, cfg.vocab, size=n_prompt)
     res = {}
