@@ -124,6 +124,27 @@ def test_mul_mat_prompt_sized_on_tensor_cores(ctx, oracle, t, N, K):
     W.free()
 
 
+@pytest.mark.parametrize("t,N,K,M", [(Q4, 4096, 2048, 2048), (Q6, 2048, 768, 4096)])
+def test_mul_mat_tensor_cores_at_bench_sizes_against_the_row_kernels(ctx, t, N, K, M):
+    """The bench's prompt-sized shapes (every CTA of the tensor-core kernel walks several tiles): too large for
+    the CPU oracle in seconds, so the row-streaming kernels, which the oracle pins at smaller sizes, are the
+    reference here.  Q4_K bit for bit; Q6_K within the float-order tolerance of equal integer sums."""
+    rng = np.random.default_rng(1234 + N)
+    w = B.random_weight(rng, t, N, K)
+    W = ctx.upload_weight(t, w, K, N)
+    x = rng.normal(size=(M, K)).astype(np.float32)
+    x[M // 2, :] = 0.0
+    got = ctx.mul_mat(W, x)
+    ctx.set_option("gemm_tc_min_rows", 0)
+    ref = ctx.mul_mat(W, x)
+    ctx.set_option("gemm_tc_min_rows", 32)
+    if t == Q4:
+        assert np.array_equal(got, ref)
+    else:
+        assert np.abs(got - ref).max() <= 2e-6 * np.abs(ref).max()
+    W.free()
+
+
 def test_mul_mat_linearity_at_full_size(ctx, oracle):
     """Size-independent property at the lm_head size (151936 x 2048 Q6_K): scaling x by a power
     of two scales y by it exactly (Q8_K codes are unchanged, only d doubles)."""
