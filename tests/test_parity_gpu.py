@@ -93,7 +93,7 @@ def test_mul_mat_shapes(ctx, oracle, t, N, K):
 
 
 @pytest.mark.parametrize("t,N,K", [(Q4, 4096, 2048), (Q6, 2048, 768), (Q4, 1000, 512), (Q6, 1000, 2048),
-                                   (Q4, 130, 4096), (Q6, 64, 256)])
+                                   (Q4, 130, 4096), (Q6, 64, 256), (Q4, 96, 256)])
 def test_mul_mat_prompt_sized_on_tensor_cores(ctx, oracle, t, N, K):
     """M >= 32 token rows take the tcgen05 kernel (the CPU serves these shapes through cb_gemv_batched_custom,
     core/src/llm/matmul/batched_exec.cpp:1040-1240).  Its block sums are exact integers (int8 UMMA into int32
