@@ -108,10 +108,9 @@ __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
 // after the CTA's __syncthreads (grid_arrive): tell the peers
 __device__ __forceinline__ void ep_arrive(const MegaParams& p) {
     const int r = threadIdx.x;
-    if (r < p.ep_size && r != p.ep_rank) {
-        __threadfence_system();
-        red_release_sys_add(p.xcnt[r], 1u);
-    }
+    // (the release half of the reduction orders the rows stored before the CTA barrier ahead of the arrival: no
+    // separate system-scope fence)
+    if (r < p.ep_size && r != p.ep_rank) red_release_sys_add(p.xcnt[r], 1u);
 }
 // exchanges: how many have completed once this one has (all ranks count alike)
 __device__ __noinline__ bool ep_wait(const MegaParams& p, unsigned exchanges) {
