@@ -687,7 +687,7 @@ def main():
         repl = step_bytes - expert_bytes_step
         line["ep_model"] = {"replicated_bytes_per_step": repl, "expert_bytes_per_step": expert_bytes_step,
                             "speedup_ceiling": step_bytes / (repl + expert_bytes_step / world),
-                            "note": "one stream is latency-bound: every layer adds one NVLink store-fence-signal round trip"}
+                            "note": "one stream is latency-bound: every layer adds one NVLink store-signal round trip"}
     if extras:
         line["other_workloads"] = extras
     if rank == 0 and not args.no_cpu_baseline:
