@@ -168,16 +168,15 @@ __global__ void __launch_bounds__(128) k_attn_scores(const AttnParams p) {
 // to get here sums all runs in run order, normalises and emits (no run waits for another).
 __device__ __forceinline__ void attn_merge_tail(const AttnParams& p, int t, int kvh, int g, int tid, int warp, int lane,
                                                 int& s_last) {
-    // release: the CTA barrier puts every thread's partial before thread 0's fence, which puts them before the
-    // ticket; acquire: the last run's thread 0 fences after its ticket, the CTA barrier passes that on
+    // release: the CTA barrier puts every thread's partial before thread 0's ticket, whose release half publishes
+    // them; acquire: the last run's thread 0 sees the other runs' partials through the ticket's acquire half, and
+    // the CTA barrier passes that on
     __syncthreads();
     if (tid == 0) {
-        __threadfence();
-        const int last = atomicAdd(p.tickets + t * p.n_kv + kvh, 1) == p.nsplit - 1;
-        if (last) {
-            __threadfence();
-            p.tickets[t * p.n_kv + kvh] = 0;
-        }
+        int old;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p.tickets + t * p.n_kv + kvh), "r"(1) : "memory");
+        const int last = old == p.nsplit - 1;
+        if (last) p.tickets[t * p.n_kv + kvh] = 0;
         s_last = last;
     }
     __syncthreads();

@@ -229,13 +229,18 @@ __global__ void __launch_bounds__(256) k_router(const RouterParams p) {
                                                  (s_part[which * 4 + 2][t] + s_part[which * 4 + 3][t]);
         }
     }
-    __threadfence();
+    // release: the CTA barrier puts this CTA's logits before thread 0's ticket, whose release half publishes them;
+    // acquire: the last CTA's thread 0 sees the others' logits through the ticket's acquire half, and the CTA
+    // barrier passes that on
     __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(p.ticket, 1) == (int)gridDim.x - 1);
+    if (threadIdx.x == 0) {
+        int old;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p.ticket), "r"(1) : "memory");
+        s_last = old == (int)gridDim.x - 1;
+        if (s_last) *p.ticket = 0;
+    }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
-    if (threadIdx.x == 0) *p.ticket = 0;
 
     // ---- stable top-k per token, one warp per token
     for (int t = warp; t < p.T; t += 8) route_token(p, t, lane, s_prob[warp], s_ids);
